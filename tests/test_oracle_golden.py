@@ -1,0 +1,90 @@
+"""The CPU oracle against fixtures produced by executing the reference's own source
+(tests/golden/make_golden.py).  Everything here is bit-exact."""
+import pytest
+import torch
+
+import oracle
+
+QS = (2, 4, 8)
+
+
+@pytest.mark.parametrize("q", QS)
+def test_scale_pack_dequant(golden, q):
+    d = golden[f"q{q}"]
+    assert torch.equal(oracle.ref_scale_per_channel(d["x"], q), d["scale"])
+    assert torch.equal(oracle.ref_compress(d["x"], d["scale_safe"], q), d["packed"])
+    assert torch.equal(oracle.ref_decompress(d["packed"], d["scale_safe"], q), d["dequant"])
+    # pack/unpack are inverse
+    codes = oracle.ref_quant_codes(d["x"], d["scale_safe"], q)
+    assert torch.equal(oracle.ref_unpack(oracle.ref_pack(codes, q), q), codes)
+
+
+@pytest.mark.parametrize("q", QS)
+def test_zero_point_variant(golden, q):
+    d = golden[f"q{q}"]
+    s, z = oracle.ref_scale_zero_point(d["xz"], q)
+    assert torch.equal(s, d["zp_scale"]) and torch.equal(z, d["zp"])
+    assert torch.equal(oracle.ref_compress(d["xz"], s, q, z), d["zp_packed"])
+    assert torch.equal(oracle.ref_decompress(d["zp_packed"], s, q, z), d["zp_dequant"])
+
+
+@pytest.mark.parametrize("q", QS)
+def test_channel_base(golden, q):
+    d = golden[f"q{q}"]
+    idx, s = oracle.ref_statistics_channel_base(d["x"], d["cb_ratio"], q)
+    # torch.topk leaves the order of equal norms open: compare as a set, and the gathered
+    # slab column by column
+    assert sorted(idx.tolist()) == sorted(d["cb_idx"].tolist())
+    assert torch.equal(s, d["cb_scale"])
+    xo, pk = oracle.ref_compress_channel_base(d["x"], d["cb_scale"], d["cb_idx"], q)
+    assert torch.equal(xo, d["cb_outlier"]) and torch.equal(pk, d["cb_packed"])
+    xr = oracle.ref_decompress_channel_base(pk, d["cb_scale"], xo, d["cb_idx"], q)
+    assert torch.equal(xr, d["cb_restored"])
+    assert torch.equal(oracle.ref_scale_per_channel(d["xh"], q), d["xh_scale"])
+
+
+@pytest.mark.parametrize("q", QS)
+def test_fused_forward_backward(golden, q):
+    d = golden[f"q{q}"]
+    q1, q2, o = oracle.ref_fused_silu_forward(d["f_xa1"], d["f_b1"], d["f_x1"], d["f_s1"],
+                                              d["f_xa2"], d["f_b2"], d["f_x2"], d["f_s2"], q)
+    assert torch.equal(q1, d["f_q1"]) and torch.equal(q2, d["f_q2"]) and torch.equal(o, d["f_o"])
+    bo, gg, gu = oracle.ref_fused_silu_backward(d["f_xa1"], d["f_b1"], q1, d["f_s1"],
+                                                d["f_xa2"], d["f_b2"], q2, d["f_s2"], d["f_go"], q)
+    assert torch.equal(bo, d["f_bo"]) and torch.equal(gg, d["f_ggate"]) and torch.equal(gu, d["f_gup"])
+
+
+def test_softmax_prune(golden):
+    d = golden["softmax"]
+    thr = oracle.ref_softmax_threshold(d["a"], d["ratio"])
+    assert torch.equal(thr, d["thr"])
+    for t, i, v in ((d["thr"], d["idx"], d["val"]), (d["thr2"], d["idx2"], d["val2"])):
+        idx, val = oracle.ref_softmax_prune(d["a"], t)
+        assert torch.equal(idx, i.flatten()) and torch.equal(val, v)
+    idx, val = oracle.ref_softmax_prune(d["a"], d["thr"])
+    assert torch.equal(oracle.ref_softmax_restore(idx, val, d["a"].shape), d["dense"])
+
+
+def test_roundf_half_away():
+    r = torch.tensor([0.5, -0.5, 1.5, -1.5, 2.5, 0.49999997, -0.49999997, 7.5, -8.5, 0.0, 1e9, float("inf")])
+    want = torch.tensor([1.0, -1.0, 2.0, -2.0, 3.0, 0.0, -0.0, 8.0, -9.0, 0.0, 1e9, float("inf")])
+    assert torch.equal(oracle.roundf_half_away(r), want)
+
+
+def test_group_and_topk_roundtrip_properties():
+    g = torch.Generator().manual_seed(7)
+    x = torch.randn(3, 5, 256, generator=g).bfloat16()
+    for q in QS:
+        pk, s, z = oracle.group_compress(x, q)
+        xr = oracle.group_decompress(pk, s, z, q)
+        # error bounded by one step per group (plus bf16 rounding of the result)
+        err = (xr.float() - x.float()).abs().reshape(3, 5, 4, 64).amax(-1)
+        assert (err <= 1.01 * s.float() + 0.02).all()
+    logits = 3 * torch.randn(2, 2, 128, 128, generator=g)
+    logits = logits + torch.triu(torch.full((128, 128), float("-inf")), diagonal=1)
+    a = torch.softmax(logits, -1).bfloat16()
+    vals, cols, pk, s, z = oracle.topk_compress(a, 0.05, 4)
+    assert vals.shape == (2 * 2 * 128, 6) and (cols[:, 1:] > cols[:, :-1]).all()
+    ar = oracle.topk_decompress(vals, cols, pk, s, z, 4, a.shape)
+    assert torch.equal(torch.gather(ar.reshape(-1, 128), 1, cols), vals)
+    assert (ar.float() - a.float()).abs().max() < 0.05
