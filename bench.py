@@ -1,0 +1,339 @@
+#!/usr/bin/env python
+"""Benchmark of the activation-compression hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Headline workload (N = 1): the attention-map save/restore of a [4,32,512,512] bf16 causal
+softmax map, per-row top-k (ratio 0.05) + 4-bit 64-wide groups; one step = compress +
+decompress of one map.  Prints ONE JSON line (see DESIGN.md for every field).
+Under torchrun every rank works on its own shard of maps (weak scaling, no data-path
+collective); the time is the maximum over ranks.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+MAP_SHAPE = (4, 32, 512, 512)
+RATIO = 0.05
+QBIT = 4
+NBUF = 4          # distinct input/output sets rotated between steps (4 x 64 MiB in, > L2)
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return float(d["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+def make_map(seed, device, shape=MAP_SHAPE):
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    b, h, s, _ = shape
+    logits = 3 * torch.randn(b, h, s, s, generator=g)
+    logits = logits + torch.triu(torch.full((s, s), float("-inf")), diagonal=1)
+    return torch.softmax(logits, dim=-1).to(torch.bfloat16).to(device)
+
+
+def algo_bytes(shape, q_bit, ratio):
+    """Algorithmic bytes of one compress and of one decompress of a map (equal by symmetry):
+    2 B/elem dense side + q/8 packed + 3/64 group metadata + 4 k/S outlier list."""
+    s = shape[-1]
+    k = int(s * ratio)
+    numel = 1
+    for d in shape:
+        numel *= d
+    per_elem = 2.0 + q_bit / 8.0 + 3.0 / 64.0 + 4.0 * k / s
+    return numel * per_elem
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons, sampled every 200 ms while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.proc, self.lines = index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.Q,
+                                          "--format=csv,noheader,nounits", "-lms", "200"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.25)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for n, v in zip(names, f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def cpu_port_sample(target_s=12.0):
+    """The CPU restatement (oracle) of the same compress + decompress on a bounded sample:
+    maps of shape [1,8,512,512] until about `target_s` seconds have passed."""
+    import oracle
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    shape = (1, 8, 512, 512)
+    a = make_map(99, "cpu", shape)
+    nbytes = 2 * algo_bytes(shape, QBIT, RATIO)
+    oracle.topk_decompress(*oracle.topk_compress(a, RATIO, QBIT), QBIT, a.shape)   # warm-up
+    t0 = time.perf_counter()
+    reps = 0
+    while True:
+        c = oracle.topk_compress(a, RATIO, QBIT)
+        oracle.topk_decompress(*c, QBIT, a.shape)
+        reps += 1
+        el = time.perf_counter() - t0
+        if el >= target_s or reps >= 64:
+            break
+    return {"value": reps * nbytes / el / 1e9, "unit": "GB/s", "cores": cores, "kind": "port",
+            "sample": "%d x compress+decompress of a [1,8,512,512] map (%.1f s)" % (reps, el)}, el / reps, nbytes
+
+
+def run_reference(args):
+    """Reference arm: the CPU implementation of the path (the oracle port: the reference itself has
+    no CPU quantize kernel and no top-k mode) on the host cores, same metric and config."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    import oracle
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    shape = (1, 8, 512, 512)
+    a = make_map(99, "cpu", shape)
+    nbytes = 2 * algo_bytes(shape, QBIT, RATIO)
+    steps = max(1, min(args.steps, 8))
+    warm = max(1, min(args.warmup, 2))
+    for _ in range(warm):
+        oracle.topk_decompress(*oracle.topk_compress(a, RATIO, QBIT), QBIT, a.shape)
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        oracle.topk_decompress(*oracle.topk_compress(a, RATIO, QBIT), QBIT, a.shape)
+    el = time.perf_counter() - t0
+    v = steps * nbytes / el / 1e9
+    sample = "%d steps, each compress+decompress of a [1,8,512,512] map (1/16 of the workload's map)" % steps
+    print(json.dumps({
+        "impl": "reference", "metric": "activation compress+decompress GB/s", "value": v, "unit": "GB/s",
+        "n_gpus": args.gpus, "steps": steps, "warmup": warm, "ms_per_step": el / steps * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16->u8", "data": "synthetic",
+        "config": config_dict(),
+        "cpu_baseline": {"value": v, "unit": "GB/s", "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": v, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+def config_dict():
+    return {"workload": "attention-map save/restore, softmax [4,32,512,512] bf16 causal, top-k per row "
+                        "ratio 0.05 + q_bit 4 groups of 64 (BASELINE configs[1])",
+            "q_bit": QBIT, "outlier_ratio": RATIO, "rows_per_gpu": MAP_SHAPE[0] * MAP_SHAPE[1] * MAP_SHAPE[2],
+            "l2": "inputs and outputs rotated over %d distinct buffer sets (%d MiB dense) > 126 MB L2" % (
+                NBUF, NBUF * 64)}
+
+
+def time_loop(fn, steps, warmup):
+    for i in range(warmup):
+        fn(i)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(steps):
+        fn(i)
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / 1e3
+
+
+def extra_workloads(dev, hbm):
+    """Secondary lines of the same path (reported under "also"): the per-channel round trip of the
+    CPU-runnable config and a q_bit sweep at the Mistral MLP width."""
+    from hyc_lora_release_b200.operators import compress_function as cf
+    out = []
+    g = torch.Generator().manual_seed(1234)
+    for name, shape, n_out, mult, ratio, qs, nbuf in (
+            ("channel-base [4,512,4096] 0.5% outlier channels x30", (4, 512, 4096), 20, 30.0, 0.005, (4,), 12),
+            ("channel-base [1,8192,14336] 1% outlier channels x20", (1, 8192, 14336), 143, 20.0, 0.01, (2, 4, 8), 2)):
+        xs = []
+        for _ in range(nbuf):
+            x = torch.randn(*shape, generator=g)
+            ch = torch.randperm(shape[-1], generator=g)[:n_out]
+            x[:, :, ch] *= mult
+            xs.append(x.to(torch.bfloat16).to(dev))
+        for q in qs:
+            idx, s = cf.get_statistics_channel_base(xs[0], ratio, q, "per-channel")
+            k = idx.numel()
+            numel = xs[0].numel()
+            nbytes = numel * (4 + q / 4.0) + 2 * (numel // shape[-1]) * k * 2 * 2
+            keep = [None] * nbuf
+
+            def step(i):
+                j = i % nbuf
+                o, qq = cf.outlier_subtraction_fuse_compression_quantization(xs[j], s, idx, q)
+                keep[j] = cf.outlier_addition_fuse_decompression_dequantization(qq, s, o, idx, q)
+            t = time_loop(step, 6 * nbuf, nbuf)
+            gbs = 6 * nbuf * nbytes / t / 1e9
+            out.append({"workload": name, "q_bit": q, "value": gbs, "unit": "GB/s", "frac_of_hbm": gbs / hbm,
+                        "ms_per_step": t / (6 * nbuf) * 1e3})
+        del xs
+    return out
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-extras", action="store_true", help="skip the secondary workloads and the CPU sample")
+    args = ap.parse_args()
+    if args.warmup < 3:
+        args.warmup = 3
+    if args.impl == "reference":
+        return run_reference(args)
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (the kernels are sm_100a only; there is no CPU path)")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+
+    from hyc_lora_release_b200.operators import compress_function as cf
+    hbm, peak_src = peaks()
+    maps = [make_map(1000 + rank * NBUF + i, dev) for i in range(NBUF)]
+    handles = [None] * NBUF
+    dense = [None] * NBUF
+    one_way = algo_bytes(MAP_SHAPE, QBIT, RATIO)
+
+    def step(i):
+        j = i % NBUF
+        handles[j] = cf.compression_softmax_topk(maps[j], RATIO, QBIT)
+        dense[j] = handles[j].to_dense()
+
+    def barrier():
+        torch.cuda.synchronize()
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for i in range(args.warmup):
+        step(i)
+    sampler = ClockSampler(local)
+    barrier()
+    if rank == 0:
+        sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(args.steps):
+        step(i)
+    e1.record()
+    barrier()
+    secs = e0.elapsed_time(e1) / 1e3
+    clocks = sampler.stop() if rank == 0 else None
+    if dist is not None:
+        t = torch.tensor([secs], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        secs = float(t.item())
+    value = world * args.steps * 2 * one_way / secs / 1e9
+
+    # per-kernel durations of the two kernels (CUDA events on the launching stream)
+    def comp_only(i):
+        handles[i % NBUF] = cf.compression_softmax_topk(maps[i % NBUF], RATIO, QBIT)
+
+    def decomp_only(i):
+        dense[i % NBUF] = handles[i % NBUF].to_dense()
+    n_k = max(20, min(args.steps, 100))
+    t_c = time_loop(comp_only, n_k, 4) / n_k
+    t_d = time_loop(decomp_only, n_k, 4) / n_k
+    dom, t_dom = ("hyc::topk_compress_kernel<4,1>", t_c) if t_c >= t_d else ("hyc::topk_restore_kernel<4>", t_d)
+    achieved = one_way / t_dom / 1e9
+
+    # end to end: pinned host map -> device -> compress -> decompress -> host
+    host_in = [m.cpu().pin_memory() for m in maps[:2]]
+    host_out = torch.empty(MAP_SHAPE, dtype=torch.bfloat16).pin_memory()
+    dev_in = torch.empty(MAP_SHAPE, dtype=torch.bfloat16, device=dev)
+
+    def e2e_step(i):
+        dev_in.copy_(host_in[i % 2], non_blocking=True)
+        h = cf.compression_softmax_topk(dev_in, RATIO, QBIT)
+        host_out.copy_(h.to_dense(), non_blocking=True)
+    n_e = max(5, min(args.steps, 20))
+    barrier()
+    t_e = time_loop(e2e_step, n_e, 3)
+    if dist is not None:
+        t = torch.tensor([t_e], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        t_e = float(t.item())
+    dense_bytes = maps[0].numel() * 2
+    e2e = {"value": world * n_e * 2 * one_way / t_e / 1e9, "unit": "GB/s",
+           "h2d_bytes_per_step": dense_bytes, "d2h_bytes_per_step": dense_bytes, "steps": n_e,
+           "api": "compress_function.compression_softmax_topk + TopkMap.to_dense on a pinned host map"}
+
+    if rank == 0:
+        also, cpu = [], None
+        if not args.no_extras and world == 1:
+            also = extra_workloads(dev, hbm)
+            cpu, _, _ = cpu_port_sample()
+        line = {
+            "metric": "activation compress+decompress GB/s", "value": value, "unit": "GB/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": secs / args.steps * 1e3,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16->u8",
+            "data": "synthetic", "config": config_dict(), "clocks": clocks, "e2e": e2e,
+            "gpu_launches": 2 * args.steps,
+            "frac_of_hbm_peak": value / world / hbm,
+            "roofline": {"bound": "hbm", "kernel": dom, "achieved": achieved, "peak": hbm, "unit": "GB/s",
+                         "frac": achieved / hbm, "peak_source": peak_src, "traffic": None,
+                         "algorithmic_bytes_per_launch": one_way,
+                         "kernel_ms": {"compress": t_c * 1e3, "decompress": t_d * 1e3}},
+            "cpu_baseline": cpu, "also": also,
+        }
+        print(json.dumps(line))
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,75 @@
+"""ctypes binding of libhyc.so.  One entry per declaration of include/hyc.h."""
+import ctypes
+import os
+
+import torch
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "lib", "libhyc.so")
+
+if not os.path.exists(LIB_PATH):
+    raise ImportError(
+        "libhyc.so is not built (%s). Build it with `python -m hyc_lora_release_b200.build`; "
+        "there is no fallback implementation." % LIB_PATH)
+
+lib = ctypes.CDLL(LIB_PATH)
+
+_p, _i, _l, _f, _z = ctypes.c_void_p, ctypes.c_int, ctypes.c_int64, ctypes.c_float, ctypes.c_size_t
+
+SIGNATURES = {
+    "hyc_strerror": (ctypes.c_char_p, [_i]),
+    "hyc_last_cuda_error": (_i, []),
+    "hyc_version": (_i, []),
+    "hyc_colstats_scale": (_i, [_p, _i, _i, _l, _i, _p, _i, _p, _p, _p]),
+    "hyc_channel_norm_topk": (_i, [_p, _i, _i, _l, _i, _p, _p, _p]),
+    "hyc_quant_pack": (_i, [_p, _l, _i, _l, _p, _p, _p, _i, _p, _p, _i, _p]),
+    "hyc_unpack_dequant": (_i, [_p, _l, _i, _p, _p, _p, _i, _p, _p, _l, _i, _p]),
+    "hyc_group_quant_pack": (_i, [_p, _l, _i, _l, _p, _p, _p, _i, _p]),
+    "hyc_group_unpack_dequant": (_i, [_p, _l, _i, _p, _p, _p, _l, _i, _p]),
+    "hyc_softmax_prune_workspace_bytes": (_z, [_l]),
+    "hyc_softmax_prune_count": (_i, [_p, _l, _f, _p, _z, _p]),
+    "hyc_softmax_prune_fill": (_i, [_p, _l, _f, _p, _p, _p, _l, _p]),
+    "hyc_softmax_prune_restore": (_i, [_p, _p, _l, _p, _l, _p]),
+    "hyc_softmax_topk_compress": (_i, [_p, _l, _i, _i, _p, _p, _p, _p, _p, _i, _p]),
+    "hyc_softmax_topk_restore": (_i, [_p, _p, _i, _p, _p, _p, _l, _i, _p, _i, _p]),
+    "hyc_fused_lora_silu_hadamard_fwd": (_i, [_p] * 11 + [_l, _i, _i, _i, _p]),
+    "hyc_fused_lora_silu_hadamard_bwd": (_i, [_p] * 12 + [_l, _i, _i, _i, _p]),
+    "hyc_rmsnorm_fwd": (_i, [_p, _p, _f, _p, _p, _l, _i, _p]),
+    "hyc_rmsnorm_bwd": (_i, [_p, _p, _p, _p, _p, _l, _i, _p]),
+    "hyc_softmax_bwd": (_i, [_p, _p, _p, _l, _i, _p]),
+}
+
+for _name, (_res, _args) in SIGNATURES.items():
+    _fn = getattr(lib, _name)
+    _fn.restype = _res
+    _fn.argtypes = _args
+
+
+class HycError(RuntimeError):
+    pass
+
+
+def check(code, what):
+    if code != 0:
+        msg = lib.hyc_strerror(code).decode()
+        extra = ""
+        if code == -6:
+            extra = " [cudaError %d]" % lib.hyc_last_cuda_error()
+        raise HycError("%s: %s%s" % (what, msg, extra))
+
+
+def ptr(t):
+    """Device pointer of a tensor (None -> NULL)."""
+    if t is None:
+        return None
+    return ctypes.c_void_p(t.data_ptr())
+
+
+def stream_of(t):
+    return ctypes.c_void_p(torch.cuda.current_stream(t.device).cuda_stream)
+
+
+def require_cuda(*tensors):
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise RuntimeError("this operator runs only on CUDA tensors (sm_100a kernels); there is no CPU path")

@@ -1,0 +1,461 @@
+// 64-wide group quantization and the per-row top-k attention-map path.
+//
+// One warp works on 512 consecutive columns of a row at a time ("step"): lane l holds the
+// 16 consecutive columns [16 l, 16 l + 16) of the step as eight packed bf16 pairs (two
+// 128-bit loads, 32 contiguous bytes per lane).  A group of 64 columns is four adjacent
+// lanes, so group min/max needs two shuffle rounds.  In the reference byte layout the two
+// halves of a 32-column block sit in the two lanes of a pair; one shuffle per pair
+// exchanges the half-finished bytes.
+//
+// Top-k (attention map): the whole row (<= 4096 columns) stays in registers.  The k-th
+// largest magnitude is found by bisection on the 15-bit bf16 magnitude pattern; each probe
+// counts "magnitude >= candidate" with packed bf16x2 compares and one warp reduction.  The
+// selected elements are emitted in ascending column order through a warp prefix scan.
+#include "hyc_common.cuh"
+
+namespace hyc {
+
+constexpr unsigned kFull = 0xffffffffu;
+
+struct GroupParams { float s, rc, z; };
+
+// scale / zero point of one group from its min and max (all lanes of the group hold the
+// same mn, mx and compute the same result)
+template <int QBIT>
+__device__ __forceinline__ GroupParams group_params(float mn, float mx) {
+  constexpr float levels = (float)((1 << QBIT) - 1);
+  constexpr float half = (float)(1 << (QBIT - 1));
+  float d = bf16bits_to_f32(f32_to_bf16bits_rn(mx - mn));
+  float s = bf16bits_to_f32(f32_to_bf16bits_rn(__fdiv_rn(d, levels)));
+  if (s == 0.f) s = bf16bits_to_f32(f32_to_bf16bits_rn(1e-3f));
+  GroupParams p;
+  p.s = s;
+  p.rc = __frcp_rn(s);
+  float r = quotient_rn(mn, s, p.rc);
+  // roundf of an unclamped value: the magnitude may exceed the integer range of interest;
+  // anything beyond +-300 saturates the int8 zero point anyway
+  r = fminf(fmaxf(r, -300.f), 300.f);
+  float zr = (float)round_half_away_i(r);
+  p.z = fminf(fmaxf(-zr - half, -128.f), 127.f);
+  return p;
+}
+
+// min / max of the 16 values of a lane (packed pairs), then over the 4 lanes of the group
+__device__ __forceinline__ void group_minmax(const uint32_t (&xw)[8], float& mn, float& mx) {
+  __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&xw[0]);
+  __nv_bfloat162 lo = a, hi = a;
+#pragma unroll
+  for (int j = 1; j < 8; ++j) {
+    __nv_bfloat162 v = *reinterpret_cast<const __nv_bfloat162*>(&xw[j]);
+    lo = __hmin2(lo, v);
+    hi = __hmax2(hi, v);
+  }
+  mn = fminf(__bfloat162float(lo.x), __bfloat162float(lo.y));
+  mx = fmaxf(__bfloat162float(hi.x), __bfloat162float(hi.y));
+#pragma unroll
+  for (int o = 1; o <= 2; o <<= 1) {
+    mn = fminf(mn, __shfl_xor_sync(kFull, mn, o));
+    mx = fmaxf(mx, __shfl_xor_sync(kFull, mx, o));
+  }
+}
+
+// Quantize the 16 values of a lane and store them in the reference byte layout.
+// qrow points at the packed row; `lane_g` = 32*step + lane (global lane index in the row).
+template <int QBIT>
+__device__ __forceinline__ void quant_store16(const uint32_t (&xw)[8], const GroupParams& p,
+                                              uint8_t* __restrict__ qrow, int lane_g, bool valid) {
+  int c[16];
+#pragma unroll
+  for (int e = 0; e < 16; ++e) {
+    float xf = (e & 1) ? bf16hi_to_f32(xw[e >> 1]) : bf16lo_to_f32(xw[e >> 1]);
+    c[e] = quant_code_signed_zp<QBIT>(xf, p.s, p.rc, p.z);
+  }
+  uint32_t w0 = pack4_s8(c[0], c[1], c[2], c[3]), w1 = pack4_s8(c[4], c[5], c[6], c[7]);
+  uint32_t w2 = pack4_s8(c[8], c[9], c[10], c[11]), w3 = pack4_s8(c[12], c[13], c[14], c[15]);
+  const bool odd = lane_g & 1;
+  if (QBIT == 8) {
+    uint4 o = make_uint4(w0 ^ 0x80808080u, w1 ^ 0x80808080u, w2 ^ 0x80808080u, w3 ^ 0x80808080u);
+    if (valid) st_stream_v4(qrow + 16 * (int64_t)lane_g, o);
+  } else if (QBIT == 4) {
+    constexpr uint32_t M = 0x0f0f0f0fu;
+    // even lane: columns 0..15 of the block (low nibbles); odd lane: columns 16..31 (high)
+    uint32_t s0 = odd ? w0 : w2, s1 = odd ? w1 : w3;
+    uint32_t r0 = __shfl_xor_sync(kFull, s0, 1), r1 = __shfl_xor_sync(kFull, s1, 1);
+    uint2 o;
+    if (!odd) { o.x = (w0 & M) | ((r0 & M) << 4); o.y = (w1 & M) | ((r1 & M) << 4); }   // bytes 0..7
+    else      { o.x = (r0 & M) | ((w2 & M) << 4); o.y = (r1 & M) | ((w3 & M) << 4); }   // bytes 8..15
+    o.x ^= 0x88888888u; o.y ^= 0x88888888u;
+    if (valid) st_stream_v2(qrow + 8 * (int64_t)lane_g, o);
+  } else {
+    constexpr uint32_t M = 0x03030303u;
+    // byte j = c[j] | c[8+j]<<2 | c[16+j]<<4 | c[24+j]<<6 ; even lane holds c[0..15], odd c[16..31]
+    uint32_t p0, p1;
+    if (!odd) { p0 = (w0 & M) | ((w2 & M) << 2); p1 = (w1 & M) | ((w3 & M) << 2); }
+    else      { p0 = ((w0 & M) << 4) | ((w2 & M) << 6); p1 = ((w1 & M) << 4) | ((w3 & M) << 6); }
+    uint32_t send = odd ? p0 : p1;
+    uint32_t recv = __shfl_xor_sync(kFull, send, 1);
+    uint32_t o = (odd ? p1 : p0) | recv;   // even: bytes 0..3, odd: bytes 4..7
+    o ^= 0xaaaaaaaau;
+    if (valid) st_stream_u32(qrow + 4 * (int64_t)lane_g, o);
+  }
+}
+
+// Load the packed codes of the lane's 16 columns and dequantize them:
+// x_hat = bf16( (code - half - z) * s ), see unpack_dequant_kernel for why this is exact.
+template <int QBIT>
+__device__ __forceinline__ void load_dequant16(const uint8_t* __restrict__ qrow, int lane_g,
+                                               float s, float z, uint32_t (&out)[8]) {
+  constexpr uint32_t MASK = (1u << QBIT) - 1u;
+  const float off = 8388608.f + (float)(1 << (QBIT - 1)) + z;
+  uint32_t b[4];
+  int shift0 = 0, shift1 = 0;  // bit offset of the code for columns e<8 and e>=8
+  if (QBIT == 8) {
+    uint4 v = ld_stream_v4(qrow + 16 * (int64_t)lane_g);
+    b[0] = v.x; b[1] = v.y; b[2] = v.z; b[3] = v.w;
+  } else if (QBIT == 4) {
+    uint4 v = ld_stream_v4(qrow + 16 * (int64_t)(lane_g >> 1));
+    b[0] = v.x; b[1] = v.y; b[2] = v.z; b[3] = v.w;
+    shift0 = shift1 = 4 * (lane_g & 1);
+  } else {
+    uint2 v = ld_stream_v2(qrow + 8 * (int64_t)(lane_g >> 1));
+    b[0] = v.x; b[1] = v.y; b[2] = v.x; b[3] = v.y;
+    shift0 = 4 * (lane_g & 1);
+    shift1 = shift0 + 2;
+  }
+  float f[16];
+#pragma unroll
+  for (int e = 0; e < 16; ++e) {
+    uint32_t byte = b[e >> 2] >> (8 * (e & 3));
+    uint32_t code = (byte >> (e < 8 ? shift0 : shift1)) & MASK;
+    f[e] = (__uint_as_float(0x4B000000u | code) - off) * s;
+  }
+#pragma unroll
+  for (int j = 0; j < 8; ++j) out[j] = pack_bf16x2_rn(f[2 * j], f[2 * j + 1]);
+}
+
+__device__ __forceinline__ int warp_excl_scan(int v, int lane, int& total) {
+  int incl = v;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    int t = __shfl_up_sync(kFull, incl, o);
+    if (lane >= o) incl += t;
+  }
+  total = __shfl_sync(kFull, incl, 31);
+  return incl - v;
+}
+
+// ---------------------------------------------------------------- group mode (activations)
+// items = rows * steps_per_row, one warp per item.
+template <int QBIT>
+__global__ void __launch_bounds__(256)
+group_quant_kernel(const __nv_bfloat16* __restrict__ x, int64_t rows, int N, int64_t ldx,
+                   uint8_t* __restrict__ q, __nv_bfloat16* __restrict__ scale, int8_t* __restrict__ zp) {
+  const int lane = threadIdx.x & 31;
+  const int steps = (N + 511) / 512;
+  const int64_t items = rows * steps;
+  const int64_t qld = (int64_t)N * QBIT / 8, gld = N / 64;
+  for (int64_t it = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5); it < items; it += (int64_t)gridDim.x * 8) {
+    const int64_t row = it / steps;
+    const int st = (int)(it % steps);
+    const int lane_g = 32 * st + lane;
+    const int col = 16 * lane_g;
+    const bool valid = col < N;
+    uint32_t xw[8];
+    if (valid) {
+      uint4 a = ld_stream_v4(x + row * ldx + col), b = ld_stream_v4(x + row * ldx + col + 8);
+      xw[0] = a.x; xw[1] = a.y; xw[2] = a.z; xw[3] = a.w; xw[4] = b.x; xw[5] = b.y; xw[6] = b.z; xw[7] = b.w;
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) xw[j] = 0u;
+    }
+    float mn, mx;
+    group_minmax(xw, mn, mx);
+    GroupParams p = group_params<QBIT>(mn, mx);
+    quant_store16<QBIT>(xw, p, q + row * qld, lane_g, valid);
+    if (valid && (lane & 3) == 0) {
+      scale[row * gld + (col >> 6)] = __ushort_as_bfloat16(f32_to_bf16bits_rn(p.s));
+      zp[row * gld + (col >> 6)] = (int8_t)(int)p.z;
+    }
+  }
+}
+
+template <int QBIT>
+__global__ void __launch_bounds__(256)
+group_dequant_kernel(const uint8_t* __restrict__ q, int64_t rows, int N,
+                     const __nv_bfloat16* __restrict__ scale, const int8_t* __restrict__ zp,
+                     __nv_bfloat16* __restrict__ xo, int64_t ldx) {
+  const int lane = threadIdx.x & 31;
+  const int steps = (N + 511) / 512;
+  const int64_t items = rows * steps;
+  const int64_t qld = (int64_t)N * QBIT / 8, gld = N / 64;
+  for (int64_t it = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5); it < items; it += (int64_t)gridDim.x * 8) {
+    const int64_t row = it / steps;
+    const int st = (int)(it % steps);
+    const int lane_g = 32 * st + lane;
+    const int col = 16 * lane_g;
+    if (col < N) {
+      float s = __bfloat162float(scale[row * gld + (col >> 6)]);
+      float z = (float)zp[row * gld + (col >> 6)];
+      uint32_t o[8];
+      load_dequant16<QBIT>(q + row * qld, lane_g, s, z, o);
+      st_stream_v4(xo + row * ldx + col, make_uint4(o[0], o[1], o[2], o[3]));
+      st_stream_v4(xo + row * ldx + col + 8, make_uint4(o[4], o[5], o[6], o[7]));
+    }
+  }
+}
+
+// ---------------------------------------------------------------- per-row top-k (attention map)
+template <int STEPS>
+__device__ __forceinline__ int count_ge(const uint32_t (&m)[STEPS][8], uint32_t cand) {
+  const uint32_t c2 = cand | (cand << 16);
+  const __nv_bfloat162 cb = *reinterpret_cast<const __nv_bfloat162*>(&c2);
+  __nv_bfloat162 acc = __float2bfloat162_rn(0.f);
+#pragma unroll
+  for (int st = 0; st < STEPS; ++st)
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      acc = __hadd2(acc, __hge2(*reinterpret_cast<const __nv_bfloat162*>(&m[st][j]), cb));
+  int c = (int)(__bfloat162float(acc.x) + __bfloat162float(acc.y));
+  return __reduce_add_sync(kFull, c);
+}
+
+template <int QBIT, int STEPS>
+__global__ void __launch_bounds__(256)
+topk_compress_kernel(const __nv_bfloat16* __restrict__ a, int64_t rows, int S, int k,
+                     __nv_bfloat16* __restrict__ val_out, uint16_t* __restrict__ col_out,
+                     uint8_t* __restrict__ q, __nv_bfloat16* __restrict__ scale, int8_t* __restrict__ zp) {
+  const int lane = threadIdx.x & 31;
+  const int64_t qld = (int64_t)S * QBIT / 8, gld = S / 64;
+  for (int64_t row = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5); row < rows; row += (int64_t)gridDim.x * 8) {
+    const __nv_bfloat16* arow = a + row * S;
+    uint32_t xw[STEPS][8], m[STEPS][8];
+#pragma unroll
+    for (int st = 0; st < STEPS; ++st) {
+      const int col = 16 * (32 * st + lane);
+      if (col < S) {
+        uint4 u = ld_stream_v4(arow + col), v = ld_stream_v4(arow + col + 8);
+        xw[st][0] = u.x; xw[st][1] = u.y; xw[st][2] = u.z; xw[st][3] = u.w;
+        xw[st][4] = v.x; xw[st][5] = v.y; xw[st][6] = v.z; xw[st][7] = v.w;
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) xw[st][j] = 0u;
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) m[st][j] = xw[st][j] & 0x7fff7fffu;
+    }
+
+    uint32_t sel[STEPS];  // bit e set: element e of the step is an outlier
+#pragma unroll
+    for (int st = 0; st < STEPS; ++st) sel[st] = 0u;
+
+    if (k > 0) {
+      // bisection: largest T with count(m >= T) >= k
+      uint32_t T = 0u;
+      int n_ge = 32 * 16 * STEPS;
+      for (int bit = 14; bit >= 0; --bit) {
+        const uint32_t cand = T | (1u << bit);
+        const int cnt = count_ge<STEPS>(m, cand);
+        if (cnt >= k) { T = cand; n_ge = cnt; if (cnt == k) break; }
+      }
+      const uint32_t T2 = T | (T << 16);
+      int need = 0;            // how many elements equal to T are taken, lowest columns first
+      if (n_ge > k) need = k - count_ge<STEPS>(m, T + 1u);   // T + 1: next pattern, i.e. "m > T"
+      int tie_base = 0;
+#pragma unroll
+      for (int st = 0; st < STEPS; ++st) {
+        uint32_t gt = 0u, eq = 0u;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const uint32_t lo = m[st][j] & 0xffffu, hi = m[st][j] >> 16;
+          gt |= (lo > (T2 & 0xffffu) ? 1u : 0u) << (2 * j);
+          gt |= (hi > (T2 & 0xffffu) ? 1u : 0u) << (2 * j + 1);
+          eq |= (lo == (T2 & 0xffffu) ? 1u : 0u) << (2 * j);
+          eq |= (hi == (T2 & 0xffffu) ? 1u : 0u) << (2 * j + 1);
+        }
+        if (n_ge == k) {
+          sel[st] = gt | eq;
+        } else {
+          int tot;
+          int before = tie_base + warp_excl_scan(__popc(eq), lane, tot);
+          tie_base += tot;
+          // keep the ties whose rank (column order) is below `need`
+          uint32_t take = 0u;
+          int rank = before;
+#pragma unroll
+          for (int e = 0; e < 16; ++e) {
+            const uint32_t bitm = 1u << e;
+            if (eq & bitm) { if (rank < need) take |= bitm; ++rank; }
+          }
+          sel[st] = gt | take;
+        }
+      }
+      // emit in ascending column order
+      int base = 0;
+#pragma unroll
+      for (int st = 0; st < STEPS; ++st) {
+        int tot;
+        int slot = base + warp_excl_scan(__popc(sel[st]), lane, tot);
+        base += tot;
+        const int col0 = 16 * (32 * st + lane);
+#pragma unroll
+        for (int e = 0; e < 16; ++e) {
+          if (sel[st] & (1u << e)) {
+            const uint32_t w = xw[st][e >> 1];
+            const uint16_t bits = (e & 1) ? (uint16_t)(w >> 16) : (uint16_t)(w & 0xffffu);
+            if (slot < k) {
+              val_out[row * k + slot] = __ushort_as_bfloat16(bits);
+              col_out[row * k + slot] = (uint16_t)(col0 + e);
+            }
+            ++slot;
+          }
+        }
+        // the selected positions count as zero for the grouped remainder
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          uint32_t keep = 0xffffffffu;
+          if (sel[st] & (1u << (2 * j))) keep &= 0xffff0000u;
+          if (sel[st] & (1u << (2 * j + 1))) keep &= 0x0000ffffu;
+          xw[st][j] &= keep;
+        }
+      }
+    }
+
+#pragma unroll
+    for (int st = 0; st < STEPS; ++st) {
+      const int lane_g = 32 * st + lane;
+      const int col = 16 * lane_g;
+      const bool valid = col < S;
+      if (16 * 32 * st < S) {   // warp-uniform: the step holds at least one valid group
+        float mn, mx;
+        group_minmax(xw[st], mn, mx);
+        GroupParams p = group_params<QBIT>(mn, mx);
+        quant_store16<QBIT>(xw[st], p, q + row * qld, lane_g, valid);
+        if (valid && (lane & 3) == 0) {
+          scale[row * gld + (col >> 6)] = __ushort_as_bfloat16(f32_to_bf16bits_rn(p.s));
+          zp[row * gld + (col >> 6)] = (int8_t)(int)p.z;
+        }
+      }
+    }
+  }
+}
+
+template <int QBIT>
+__global__ void __launch_bounds__(256)
+topk_restore_kernel(const __nv_bfloat16* __restrict__ val, const uint16_t* __restrict__ colv, int k,
+                    const uint8_t* __restrict__ q, const __nv_bfloat16* __restrict__ scale,
+                    const int8_t* __restrict__ zp, int64_t rows, int S, __nv_bfloat16* __restrict__ ao) {
+  const int lane = threadIdx.x & 31;
+  const int steps = (S + 511) / 512;
+  const int64_t qld = (int64_t)S * QBIT / 8, gld = S / 64;
+  for (int64_t row = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5); row < rows; row += (int64_t)gridDim.x * 8) {
+    for (int st = 0; st < steps; ++st) {
+      const int lane_g = 32 * st + lane;
+      const int col = 16 * lane_g;
+      if (col < S) {
+        float s = __bfloat162float(scale[row * gld + (col >> 6)]);
+        float z = (float)zp[row * gld + (col >> 6)];
+        uint32_t o[8];
+        load_dequant16<QBIT>(q + row * qld, lane_g, s, z, o);
+        st_stream_v4(ao + row * S + col, make_uint4(o[0], o[1], o[2], o[3]));
+        st_stream_v4(ao + row * S + col + 8, make_uint4(o[4], o[5], o[6], o[7]));
+      }
+    }
+    __syncwarp();   // orders this warp's row stores before the overwrites below
+    for (int j = lane; j < k; j += 32) ao[row * S + colv[row * k + j]] = val[row * k + j];
+  }
+}
+
+static inline int warp_grid(int64_t items) {
+  int64_t blocks = (items + 7) / 8;
+  int64_t cap = (int64_t)kNumSMs * 8;
+  if (blocks > cap) blocks = cap;
+  if (blocks < 1) blocks = 1;
+  return (int)blocks;
+}
+
+}  // namespace hyc
+
+using namespace hyc;
+
+static int check_group(const void* a, const void* b, int64_t rows, int N, int64_t ldx, int q_bit) {
+  if (!a || !b) return HYC_ERR_NULL;
+  if (q_bit != 2 && q_bit != 4 && q_bit != 8) return HYC_ERR_QBIT;
+  if (rows < 0 || N <= 0 || N % 64 != 0 || ldx < N) return HYC_ERR_SHAPE;
+  if (ldx % 8 != 0) return HYC_ERR_ALIGN;
+  return HYC_OK;
+}
+
+extern "C" HYC_API int hyc_group_quant_pack(const void* x, int64_t rows, int N, int64_t ldx,
+                                    void* q_out, void* scale_out, int8_t* zp_out, int q_bit, void* stream) {
+  int rc = check_group(x, q_out, rows, N, ldx, q_bit);
+  if (rc) return rc;
+  if (!scale_out || !zp_out) return HYC_ERR_NULL;
+  if (!aligned(x, 16) || !aligned(q_out, 16)) return HYC_ERR_ALIGN;
+  if (rows == 0) return HYC_OK;
+  const int64_t items = rows * ((N + 511) / 512);
+  cudaStream_t st = (cudaStream_t)stream;
+#define GQ(QB) group_quant_kernel<QB><<<warp_grid(items), 256, 0, st>>>((const __nv_bfloat16*)x, rows, N, ldx, \
+      (uint8_t*)q_out, (__nv_bfloat16*)scale_out, zp_out)
+  if (q_bit == 2) GQ(2); else if (q_bit == 4) GQ(4); else GQ(8);
+#undef GQ
+  HYC_CHECK_LAUNCH();
+  return HYC_OK;
+}
+
+extern "C" HYC_API int hyc_group_unpack_dequant(const void* q, int64_t rows, int N,
+                                        const void* scale, const int8_t* zp,
+                                        void* x_out, int64_t ldx, int q_bit, void* stream) {
+  int rc = check_group(q, x_out, rows, N, ldx, q_bit);
+  if (rc) return rc;
+  if (!scale || !zp) return HYC_ERR_NULL;
+  if (!aligned(x_out, 16) || !aligned(q, 16)) return HYC_ERR_ALIGN;
+  if (rows == 0) return HYC_OK;
+  const int64_t items = rows * ((N + 511) / 512);
+  cudaStream_t st = (cudaStream_t)stream;
+#define GD(QB) group_dequant_kernel<QB><<<warp_grid(items), 256, 0, st>>>((const uint8_t*)q, rows, N, \
+      (const __nv_bfloat16*)scale, zp, (__nv_bfloat16*)x_out, ldx)
+  if (q_bit == 2) GD(2); else if (q_bit == 4) GD(4); else GD(8);
+#undef GD
+  HYC_CHECK_LAUNCH();
+  return HYC_OK;
+}
+
+extern "C" HYC_API int hyc_softmax_topk_compress(const void* a, int64_t rows, int S, int k,
+                                         void* val_out, uint16_t* col_out,
+                                         void* q_out, void* scale_out, int8_t* zp_out, int q_bit, void* stream) {
+  if (!a || !q_out || !scale_out || !zp_out) return HYC_ERR_NULL;
+  if (k > 0 && (!val_out || !col_out)) return HYC_ERR_NULL;
+  if (q_bit != 2 && q_bit != 4 && q_bit != 8) return HYC_ERR_QBIT;
+  if (rows < 0 || S <= 0 || S % 64 != 0 || S > 4096 || k < 0 || k > S) return HYC_ERR_SHAPE;
+  if (!aligned(a, 16) || !aligned(q_out, 16)) return HYC_ERR_ALIGN;
+  if (rows == 0) return HYC_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  const int steps = (S + 511) / 512;
+  const int grid = warp_grid(rows);
+#define TK(QB, ST) topk_compress_kernel<QB, ST><<<grid, 256, 0, st>>>((const __nv_bfloat16*)a, rows, S, k, \
+      (__nv_bfloat16*)val_out, col_out, (uint8_t*)q_out, (__nv_bfloat16*)scale_out, zp_out)
+#define TKQ(QB) do { if (steps <= 1) TK(QB, 1); else if (steps <= 2) TK(QB, 2); else if (steps <= 4) TK(QB, 4); else TK(QB, 8); } while (0)
+  if (q_bit == 2) TKQ(2); else if (q_bit == 4) TKQ(4); else TKQ(8);
+#undef TKQ
+#undef TK
+  HYC_CHECK_LAUNCH();
+  return HYC_OK;
+}
+
+extern "C" HYC_API int hyc_softmax_topk_restore(const void* val, const uint16_t* col, int k,
+                                        const void* q, const void* scale, const int8_t* zp,
+                                        int64_t rows, int S, void* a_out, int q_bit, void* stream) {
+  if (!q || !scale || !zp || !a_out) return HYC_ERR_NULL;
+  if (k > 0 && (!val || !col)) return HYC_ERR_NULL;
+  if (q_bit != 2 && q_bit != 4 && q_bit != 8) return HYC_ERR_QBIT;
+  if (rows < 0 || S <= 0 || S % 64 != 0 || S > 4096 || k < 0 || k > S) return HYC_ERR_SHAPE;
+  if (!aligned(a_out, 16) || !aligned(q, 16)) return HYC_ERR_ALIGN;
+  if (rows == 0) return HYC_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+#define TR(QB) topk_restore_kernel<QB><<<warp_grid(rows), 256, 0, st>>>((const __nv_bfloat16*)val, col, k, \
+      (const uint8_t*)q, (const __nv_bfloat16*)scale, zp, rows, S, (__nv_bfloat16*)a_out)
+  if (q_bit == 2) TR(2); else if (q_bit == 4) TR(4); else TR(8);
+#undef TR
+  HYC_CHECK_LAUNCH();
+  return HYC_OK;
+}

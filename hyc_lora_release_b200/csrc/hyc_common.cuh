@@ -1,0 +1,136 @@
+// Shared device helpers for the HyC activation-compression kernels (sm_100a).
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <stdint.h>
+#include "../../include/hyc.h"
+
+#define HYC_CHECK_LAUNCH()                                                     \
+  do {                                                                         \
+    cudaError_t e__ = cudaGetLastError();                                      \
+    if (e__ != cudaSuccess) { hyc_set_last_cuda_error((int)e__); return HYC_ERR_LAUNCH; } \
+  } while (0)
+
+#define HYC_API __attribute__((visibility("default")))
+extern "C" HYC_API void hyc_set_last_cuda_error(int e);
+
+namespace hyc {
+
+constexpr int kNumSMs = 148;
+
+__host__ __device__ inline bool aligned(const void* p, size_t a) {
+  return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0;
+}
+
+// ---- bf16 <-> f32 bit tricks -------------------------------------------------
+__device__ __forceinline__ float bf16lo_to_f32(uint32_t packed) { return __uint_as_float(packed << 16); }
+__device__ __forceinline__ float bf16hi_to_f32(uint32_t packed) { return __uint_as_float(packed & 0xffff0000u); }
+__device__ __forceinline__ float bf16bits_to_f32(uint16_t b) { return __uint_as_float(((uint32_t)b) << 16); }
+
+// round-to-nearest-even f32 pair -> packed bf16x2 (lo = a, hi = b)
+__device__ __forceinline__ uint32_t pack_bf16x2_rn(float a, float b) {
+  uint32_t r;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(b), "f"(a));
+  return r;
+}
+__device__ __forceinline__ uint16_t f32_to_bf16bits_rn(float a) {
+  return (uint16_t)(pack_bf16x2_rn(a, 0.f) & 0xffffu);
+}
+
+// ---- exact quotient ----------------------------------------------------------
+// RN(x / s) from a correctly rounded reciprocal rc = RN(1/s): one multiply and two
+// fused multiply-adds give the IEEE quotient (checked exhaustively on the host over all
+// bf16 operand pairs; results that differ sit far below 1e-20 and cannot change a code).
+// The first estimate is clamped so that a quotient that overflows stays finite; every
+// caller clamps the result to the code range afterwards.  rc == 0 yields exactly 0.
+__device__ __forceinline__ float quotient_rn(float x, float s, float rc) {
+  float q0 = fminf(fmaxf(x * rc, -300.f), 300.f);
+  float rem = fmaf(-q0, s, x);
+  return fmaf(rem, rc, q0);
+}
+
+// C roundf (halves away from zero) of a value already clamped to [-2^(q-1), 2^(q-1)-1],
+// returned as a signed integer.  RZ(r + copysign(0.5, r)) followed by truncation never
+// rounds across an integer, so 0.49999997 -> 0.
+__device__ __forceinline__ int round_half_away_i(float r) {
+  float h = __uint_as_float((__float_as_uint(r) & 0x80000000u) | 0x3f000000u);
+  return __float2int_rz(__fadd_rz(r, h));
+}
+
+template <int QBIT>
+__device__ __forceinline__ int quant_code_signed(float x, float s, float rc) {
+  constexpr float lo = -(float)(1 << (QBIT - 1));
+  constexpr float hi = (float)((1 << (QBIT - 1)) - 1);
+  float r = quotient_rn(x, s, rc);
+  r = fminf(fmaxf(r, lo), hi);
+  return round_half_away_i(r);
+}
+template <int QBIT>
+__device__ __forceinline__ int quant_code_signed_zp(float x, float s, float rc, float z) {
+  constexpr float lo = -(float)(1 << (QBIT - 1));
+  constexpr float hi = (float)((1 << (QBIT - 1)) - 1);
+  float r = quotient_rn(x, s, rc) + z;
+  r = fminf(fmaxf(r, lo), hi);
+  return round_half_away_i(r);
+}
+
+// ---- streaming 128-bit / 64-bit global access --------------------------------
+__device__ __forceinline__ uint4 ld_stream_v4(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.cs.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+  return v;
+}
+__device__ __forceinline__ uint2 ld_stream_v2(const void* p) {
+  uint2 v;
+  asm volatile("ld.global.cs.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p));
+  return v;
+}
+__device__ __forceinline__ uint32_t ld_stream_u32(const void* p) {
+  uint32_t v;
+  asm volatile("ld.global.cs.u32 %0, [%1];" : "=r"(v) : "l"(p));
+  return v;
+}
+__device__ __forceinline__ void st_stream_v4(void* p, uint4 v) {
+  asm volatile("st.global.cs.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+__device__ __forceinline__ void st_stream_v2(void* p, uint2 v) {
+  asm volatile("st.global.cs.v2.u32 [%0], {%1,%2};" ::"l"(p), "r"(v.x), "r"(v.y) : "memory");
+}
+__device__ __forceinline__ void st_stream_u32(void* p, uint32_t v) {
+  asm volatile("st.global.cs.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+// Pack eight signed codes (two's complement, low QBIT bits significant) held as the
+// bytes of two 32-bit words per slab into the reference byte layout: output byte j
+// carries slab i in bits [QBIT*i, QBIT*(i+1)).  `w[i][h]` = bytes 4h..4h+3 of slab i.
+template <int QBIT>
+__device__ __forceinline__ uint2 interleave_slabs(const uint32_t (&w)[8 / QBIT][2]) {
+  constexpr int EPP = 8 / QBIT;
+  constexpr uint32_t M = ((1u << QBIT) - 1u) * 0x01010101u;
+  constexpr uint32_t HALF = (1u << (QBIT - 1));
+  uint32_t xorv = 0;
+#pragma unroll
+  for (int i = 0; i < EPP; ++i) xorv |= (HALF << (QBIT * i));
+  xorv *= 0x01010101u;  // two's complement -> offset binary: flip the top bit of every code
+  uint2 o = make_uint2(0u, 0u);
+#pragma unroll
+  for (int i = 0; i < EPP; ++i) {
+    o.x |= (w[i][0] & M) << (QBIT * i);
+    o.y |= (w[i][1] & M) << (QBIT * i);
+  }
+  o.x ^= xorv;
+  o.y ^= xorv;
+  return o;
+}
+
+// four signed ints -> four bytes (two's complement truncation), byte k = c_k
+__device__ __forceinline__ uint32_t pack4_s8(int c0, int c1, int c2, int c3) {
+  // cvt.pack.sat.s8.s32.b32 d, a, b, c  ==  d = (c << 16) | (sat8(a) << 8) | sat8(b)
+  uint32_t hi, r;
+  asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(hi) : "r"(c3), "r"(c2), "r"(0));
+  asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(c1), "r"(c0), "r"(hi));
+  return r;
+}
+
+}  // namespace hyc

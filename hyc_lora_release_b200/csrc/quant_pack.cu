@@ -1,0 +1,295 @@
+// Per-channel quantize-and-pack and unpack-dequantize (HBM-bound streaming kernels).
+//
+// Thread t of a row produces packed bytes [8t, 8t+8) of that row.  With epp = 8/QBIT codes
+// per byte and the reference's interleaved layout, those bytes draw on epp slabs of eight
+// consecutive columns each, slab i starting at column 32*b + i*(32/epp) + 8*u where
+// (b, u) = (t / tpb, t % tpb), tpb = 4/epp.  So every thread issues epp 128-bit loads and
+// one 64-bit store (quantize) or one 64-bit load and epp 128-bit stores (dequantize), all
+// sector-aligned.  A thread keeps its columns for all the rows it visits, so the
+// per-column scale, reciprocal and zero point live in registers.
+#include "hyc_common.cuh"
+
+namespace hyc {
+
+constexpr int kThreads = 256;
+constexpr int kRowUnroll = 4;
+
+template <int QBIT>
+struct Geo {
+  static constexpr int EPP = 8 / QBIT;           // codes per byte
+  static constexpr int SLAB = 32 / EPP;          // columns between the codes of one byte
+  static constexpr int TPB = SLAB / 8;           // threads per 32-column block
+  static constexpr int COLS_PER_THREAD = 8 * EPP;
+  __device__ static __forceinline__ int slab_col(int ct, int i) {
+    return 32 * (ct / TPB) + i * SLAB + 8 * (ct % TPB);
+  }
+};
+
+// grid: (col_tiles, row_slots).  Row groups of kRowUnroll rows are dealt round-robin to slots.
+template <int QBIT, bool HAS_ZP>
+__global__ void __launch_bounds__(kThreads)
+quant_pack_kernel(const __nv_bfloat16* __restrict__ x, int64_t rows, int N, int64_t ldx,
+                  const __nv_bfloat16* __restrict__ scale, const int8_t* __restrict__ zp,
+                  const int64_t* __restrict__ oidx, int k,
+                  uint8_t* __restrict__ q, __nv_bfloat16* __restrict__ oout) {
+  using G = Geo<QBIT>;
+  constexpr int EPP = G::EPP;
+  const int ct = blockIdx.x * kThreads + threadIdx.x;
+  const int n_ct = N / G::COLS_PER_THREAD;
+  const bool active = ct < n_ct;
+  const int64_t qld = (int64_t)N / EPP;
+
+  // outlier-column mask of this block's column span (bytes, one per column)
+  extern __shared__ __align__(16) uint8_t s_mask[];
+  const int span_cols = kThreads * G::COLS_PER_THREAD;
+  const int col0 = blockIdx.x * span_cols;
+  if (k > 0) {
+    for (int i = threadIdx.x; i < span_cols / 4; i += kThreads) reinterpret_cast<uint32_t*>(s_mask)[i] = 0u;
+    __syncthreads();
+    for (int j = threadIdx.x; j < k; j += kThreads) {
+      int64_t c = oidx[j] - col0;
+      if (c >= 0 && c < span_cols) s_mask[c] = 1;
+    }
+    __syncthreads();
+  }
+
+  float s[EPP][8], rc[EPP][8], z[HAS_ZP ? EPP : 1][8];
+  if (active) {
+#pragma unroll
+    for (int i = 0; i < EPP; ++i) {
+      const int c = G::slab_col(ct, i);
+      uint4 sv = *reinterpret_cast<const uint4*>(scale + c);
+      const uint32_t sw[4] = {sv.x, sv.y, sv.z, sv.w};
+      uint2 mv = make_uint2(0u, 0u);
+      if (k > 0) mv = *reinterpret_cast<const uint2*>(s_mask + (c - col0));
+      uint2 zv = make_uint2(0u, 0u);
+      if (HAS_ZP) zv = *reinterpret_cast<const uint2*>(zp + c);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        float sf = (e & 1) ? bf16hi_to_f32(sw[e >> 1]) : bf16lo_to_f32(sw[e >> 1]);
+        s[i][e] = sf;
+        float r = __frcp_rn(sf);
+        uint32_t mb = ((e < 4 ? mv.x : mv.y) >> (8 * (e & 3))) & 0xffu;
+        rc[i][e] = mb ? 0.f : r;
+        if (HAS_ZP) {
+          int zb = (int)(int8_t)(((e < 4 ? zv.x : zv.y) >> (8 * (e & 3))) & 0xffu);
+          z[i][e] = (float)zb;
+        }
+      }
+    }
+  }
+
+  const int64_t n_groups = (rows + kRowUnroll - 1) / kRowUnroll;
+  for (int64_t g = blockIdx.y; g < n_groups; g += gridDim.y) {
+    const int64_t r0 = g * kRowUnroll;
+    if (active) {
+      uint4 v[kRowUnroll][EPP];
+#pragma unroll
+      for (int r = 0; r < kRowUnroll; ++r) {
+        const bool ok = (r0 + r) < rows;
+#pragma unroll
+        for (int i = 0; i < EPP; ++i) {
+          v[r][i] = make_uint4(0u, 0u, 0u, 0u);
+          if (ok) v[r][i] = ld_stream_v4(x + (r0 + r) * ldx + G::slab_col(ct, i));
+        }
+      }
+#pragma unroll
+      for (int r = 0; r < kRowUnroll; ++r) {
+        if ((r0 + r) >= rows) break;
+        uint32_t w[EPP][2];
+#pragma unroll
+        for (int i = 0; i < EPP; ++i) {
+          const uint32_t xw[4] = {v[r][i].x, v[r][i].y, v[r][i].z, v[r][i].w};
+          int c[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            float xf = (e & 1) ? bf16hi_to_f32(xw[e >> 1]) : bf16lo_to_f32(xw[e >> 1]);
+            c[e] = HAS_ZP ? quant_code_signed_zp<QBIT>(xf, s[i][e], rc[i][e], z[i][e])
+                          : quant_code_signed<QBIT>(xf, s[i][e], rc[i][e]);
+          }
+          w[i][0] = pack4_s8(c[0], c[1], c[2], c[3]);
+          w[i][1] = pack4_s8(c[4], c[5], c[6], c[7]);
+        }
+        st_stream_v2(q + (r0 + r) * qld + 8 * (int64_t)ct, interleave_slabs<QBIT>(w));
+      }
+    }
+    // gather the outlier columns of these rows (only the first column tile does it;
+    // the row segment was just read, so these hit in L2)
+    if (k > 0 && blockIdx.x == 0) {
+      const int cnt = kRowUnroll * k;
+      for (int t = threadIdx.x; t < cnt; t += kThreads) {
+        const int64_t row = r0 + t / k;
+        const int j = t % k;
+        if (row < rows) oout[row * k + j] = x[row * ldx + oidx[j]];
+      }
+    }
+  }
+}
+
+// With a zero point, an outlier column must still encode as "zero": rc == 0 makes the
+// quotient 0, and the zero point of that column is then added like for any other column,
+// which is what the reference does (it zeroes x, then runs the same kernel).
+
+template <int QBIT, bool HAS_ZP>
+__global__ void __launch_bounds__(kThreads)
+unpack_dequant_kernel(const uint8_t* __restrict__ q, int64_t rows, int N,
+                      const __nv_bfloat16* __restrict__ scale, const int8_t* __restrict__ zp,
+                      const int64_t* __restrict__ oidx, int k, const __nv_bfloat16* __restrict__ oin,
+                      __nv_bfloat16* __restrict__ xo, int64_t ldx) {
+  using G = Geo<QBIT>;
+  constexpr int EPP = G::EPP;
+  constexpr uint32_t MASK = (1u << QBIT) - 1u;
+  const int ct = blockIdx.x * kThreads + threadIdx.x;
+  const int n_ct = N / G::COLS_PER_THREAD;
+  const bool active = ct < n_ct;
+  const int64_t qld = (int64_t)N / EPP;
+  const int span_cols = kThreads * G::COLS_PER_THREAD;
+  const int col0 = blockIdx.x * span_cols;
+
+  // x_hat = bf16( bf16(code - half [- z]) * s ).  (code - half - z) is an integer of
+  // magnitude <= 255, exact in bf16 and in fp32; the fp32 product of two bf16 values is
+  // exact, so one rounding to bf16 reproduces the reference's bf16 multiply.
+  // 0x4B000000 | code is the float 2^23 + code; `off` folds 2^23 + half + z.
+  float s[EPP][8], off[EPP][8];
+  if (active) {
+#pragma unroll
+    for (int i = 0; i < EPP; ++i) {
+      const int c = G::slab_col(ct, i);
+      uint4 sv = *reinterpret_cast<const uint4*>(scale + c);
+      const uint32_t sw[4] = {sv.x, sv.y, sv.z, sv.w};
+      uint2 zv = make_uint2(0u, 0u);
+      if (HAS_ZP) zv = *reinterpret_cast<const uint2*>(zp + c);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        s[i][e] = (e & 1) ? bf16hi_to_f32(sw[e >> 1]) : bf16lo_to_f32(sw[e >> 1]);
+        int zb = HAS_ZP ? (int)(int8_t)(((e < 4 ? zv.x : zv.y) >> (8 * (e & 3))) & 0xffu) : 0;
+        off[i][e] = 8388608.f + (float)((1 << (QBIT - 1)) + zb);
+      }
+    }
+  }
+
+  const int64_t n_groups = (rows + kRowUnroll - 1) / kRowUnroll;
+  for (int64_t g = blockIdx.y; g < n_groups; g += gridDim.y) {
+    const int64_t r0 = g * kRowUnroll;
+    if (active) {
+      uint2 p[kRowUnroll];
+#pragma unroll
+      for (int r = 0; r < kRowUnroll; ++r) {
+        p[r] = make_uint2(0u, 0u);
+        if ((r0 + r) < rows) p[r] = ld_stream_v2(q + (r0 + r) * qld + 8 * (int64_t)ct);
+      }
+#pragma unroll
+      for (int r = 0; r < kRowUnroll; ++r) {
+        if ((r0 + r) >= rows) break;
+#pragma unroll
+        for (int i = 0; i < EPP; ++i) {
+          float f[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            uint32_t byte = ((e < 4 ? p[r].x : p[r].y) >> (8 * (e & 3)));
+            uint32_t code = (byte >> (QBIT * i)) & MASK;
+            f[e] = (__uint_as_float(0x4B000000u | code) - off[i][e]) * s[i][e];
+          }
+          uint4 o;
+          o.x = pack_bf16x2_rn(f[0], f[1]);
+          o.y = pack_bf16x2_rn(f[2], f[3]);
+          o.z = pack_bf16x2_rn(f[4], f[5]);
+          o.w = pack_bf16x2_rn(f[6], f[7]);
+          st_stream_v4(xo + (r0 + r) * ldx + G::slab_col(ct, i), o);
+        }
+      }
+    }
+    if (k > 0) {
+      // put the full-precision outlier columns back; each block patches only the columns
+      // of its own span, after its own stores to them (block-wide barrier orders the two)
+      __syncthreads();
+      const int cnt = kRowUnroll * k;
+      for (int t = threadIdx.x; t < cnt; t += kThreads) {
+        const int64_t row = r0 + t / k;
+        const int j = t % k;
+        const int64_t c = oidx[j] - col0;
+        if (row < rows && c >= 0 && c < span_cols) xo[row * ldx + oidx[j]] = oin[row * k + j];
+      }
+    }
+  }
+}
+
+static inline dim3 stream_grid(int64_t rows, int n_ct) {
+  const int col_tiles = (n_ct + kThreads - 1) / kThreads;
+  const int64_t groups = (rows + kRowUnroll - 1) / kRowUnroll;
+  // about eight resident blocks per SM in total, split over the column tiles
+  int64_t slots = (int64_t)(kNumSMs * 8 + col_tiles - 1) / col_tiles;
+  if (slots > groups) slots = groups;
+  if (slots < 1) slots = 1;
+  if (slots > 65535) slots = 65535;
+  return dim3((unsigned)col_tiles, (unsigned)slots, 1);
+}
+
+}  // namespace hyc
+
+using namespace hyc;
+
+static int check_common(const void* a, const void* b, int64_t rows, int N, int64_t ldx, int q_bit) {
+  if (!a || !b) return HYC_ERR_NULL;
+  if (q_bit != 2 && q_bit != 4 && q_bit != 8) return HYC_ERR_QBIT;
+  if (rows < 0 || N <= 0 || N % 32 != 0 || ldx < N) return HYC_ERR_SHAPE;
+  if (ldx % 8 != 0) return HYC_ERR_ALIGN;
+  return HYC_OK;
+}
+
+extern "C" HYC_API int hyc_quant_pack(const void* x, int64_t rows, int N, int64_t ldx,
+                              const void* scale, const int8_t* zp,
+                              const int64_t* outlier_idx, int k,
+                              void* q_out, void* outlier_out, int q_bit, void* stream) {
+  int rc = check_common(x, q_out, rows, N, ldx, q_bit);
+  if (rc) return rc;
+  if (!scale) return HYC_ERR_NULL;
+  if (k < 0 || k > N) return HYC_ERR_SHAPE;
+  if (k > 0 && (!outlier_idx || !outlier_out)) return HYC_ERR_NULL;
+  if (!aligned(x, 16) || !aligned(scale, 16) || !aligned(q_out, 8) || (zp && !aligned(zp, 8))) return HYC_ERR_ALIGN;
+  if (rows == 0) return HYC_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  const int cpt = 8 * (8 / q_bit);
+  dim3 grid = stream_grid(rows, N / cpt);
+  size_t smem = k > 0 ? (size_t)kThreads * cpt : 0;
+#define LAUNCH_Q(QB, ZP)                                                                          \
+  quant_pack_kernel<QB, ZP><<<grid, kThreads, smem, st>>>(                                         \
+      (const __nv_bfloat16*)x, rows, N, ldx, (const __nv_bfloat16*)scale, zp, outlier_idx, k,      \
+      (uint8_t*)q_out, (__nv_bfloat16*)outlier_out)
+  if (zp) {
+    if (q_bit == 2) LAUNCH_Q(2, true); else if (q_bit == 4) LAUNCH_Q(4, true); else LAUNCH_Q(8, true);
+  } else {
+    if (q_bit == 2) LAUNCH_Q(2, false); else if (q_bit == 4) LAUNCH_Q(4, false); else LAUNCH_Q(8, false);
+  }
+#undef LAUNCH_Q
+  HYC_CHECK_LAUNCH();
+  return HYC_OK;
+}
+
+extern "C" HYC_API int hyc_unpack_dequant(const void* q, int64_t rows, int N,
+                                  const void* scale, const int8_t* zp,
+                                  const int64_t* outlier_idx, int k, const void* outlier,
+                                  void* x_out, int64_t ldx, int q_bit, void* stream) {
+  int rc = check_common(q, x_out, rows, N, ldx, q_bit);
+  if (rc) return rc;
+  if (!scale) return HYC_ERR_NULL;
+  if (k < 0 || k > N) return HYC_ERR_SHAPE;
+  if (k > 0 && (!outlier_idx || !outlier)) return HYC_ERR_NULL;
+  if (!aligned(x_out, 16) || !aligned(scale, 16) || !aligned(q, 8) || (zp && !aligned(zp, 8))) return HYC_ERR_ALIGN;
+  if (rows == 0) return HYC_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  const int cpt = 8 * (8 / q_bit);
+  dim3 grid = stream_grid(rows, N / cpt);
+#define LAUNCH_D(QB, ZP)                                                                          \
+  unpack_dequant_kernel<QB, ZP><<<grid, kThreads, 0, st>>>(                                        \
+      (const uint8_t*)q, rows, N, (const __nv_bfloat16*)scale, zp, outlier_idx, k,                 \
+      (const __nv_bfloat16*)outlier, (__nv_bfloat16*)x_out, ldx)
+  if (zp) {
+    if (q_bit == 2) LAUNCH_D(2, true); else if (q_bit == 4) LAUNCH_D(4, true); else LAUNCH_D(8, true);
+  } else {
+    if (q_bit == 2) LAUNCH_D(2, false); else if (q_bit == 4) LAUNCH_D(4, false); else LAUNCH_D(8, false);
+  }
+#undef LAUNCH_D
+  HYC_CHECK_LAUNCH();
+  return HYC_OK;
+}

@@ -1,0 +1,158 @@
+/*
+ * libhyc -- C ABI of the B200 (sm_100a) activation-compression kernels.
+ *
+ * Every entry point replaces one launch wrapper (or one pure-PyTorch helper) of the
+ * HyC-LoRA-release operator layer; the comment above each declaration cites it
+ * (paths relative to that project's root).  Conventions:
+ *   - all pointers are DEVICE pointers unless the name says `host`;
+ *   - activations are bf16, row-major, last dimension contiguous; `rows` is the product
+ *     of the leading dimensions (batch * sequence), `ld*` a row stride in ELEMENTS;
+ *   - packed codes use the reference byte layout: inside every 32-column block, byte j
+ *     holds the codes of columns j, j+32/epp, j+2*32/epp, ... (epp = 8 / q_bit) in
+ *     ascending bit position (operators/compress_function_kernel.py:78-110);
+ *   - `stream` is a cudaStream_t passed as void*; work is stream-ordered, nothing
+ *     synchronises, nothing allocates (scratch is caller-provided and sized by the
+ *     matching *_workspace_bytes query);
+ *   - the return value is 0 or a negative HYC_ERR_* code; hyc_strerror() names it.
+ */
+#ifndef HYC_H_
+#define HYC_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum {
+  HYC_OK = 0,
+  HYC_ERR_NULL = -1,        /* a required pointer is null */
+  HYC_ERR_QBIT = -2,        /* q_bit not in {2,4,8} */
+  HYC_ERR_SHAPE = -3,       /* a dimension violates the documented divisibility / range */
+  HYC_ERR_ALIGN = -4,       /* pointer or stride not aligned for 128-bit access */
+  HYC_ERR_WORKSPACE = -5,   /* workspace missing or too small */
+  HYC_ERR_LAUNCH = -6,      /* CUDA launch failed; see hyc_last_cuda_error() */
+  HYC_ERR_CAPACITY = -7,    /* output capacity too small for the data */
+  HYC_ERR_UNSUPPORTED = -8  /* feature not available in this build */
+};
+
+const char* hyc_strerror(int code);
+int hyc_last_cuda_error(void);   /* cudaError_t of the last HYC_ERR_LAUNCH, else 0 */
+int hyc_version(void);
+
+/* ---- statistics (calibration iterations only) ------------------------------------ */
+
+/* Per-channel scale of batch sample 0: scale[n] = bf16((max_m x0[m,n] - min_m x0[m,n]) / (2^q - 1)).
+ * Replaces get_statistics_only_quant(..., 'per-channel')  (operators/compress_function.py:45-59).
+ * If outlier_idx != NULL (k entries) those columns are treated as zero and zero scales become
+ * bf16(1e-3): the scale half of get_statistics_channel_base (compress_function.py:94-104).
+ * If zp_out != NULL it also writes the int8 zero point of
+ * get_statistics_only_quant_zero_point (compress_function.py:62-77).
+ * x0: [M, N] bf16, N % 8 == 0. */
+int hyc_colstats_scale(const void* x0, int M, int N, int64_t ldx, int q_bit,
+                       const int64_t* outlier_idx, int k,
+                       void* scale_out, int8_t* zp_out, void* stream);
+
+/* Column L2 norm of sample 0 as bf16 and the k largest channels ordered by
+ * (norm descending, index ascending).  Replaces the norm/topk half of
+ * get_statistics_channel_base (compress_function.py:86-87).  N <= 32768.
+ * norm_out: [N] bf16 scratch/result; idx_out: [k] int64. */
+int hyc_channel_norm_topk(const void* x0, int M, int N, int64_t ldx, int k,
+                          void* norm_out, int64_t* idx_out, void* stream);
+
+/* ---- per-channel quantize-and-pack / unpack-dequantize ---------------------------- */
+
+/* Replaces compression_quantization (+kernel) (compress_function.py:178-210,
+ * compress_function_kernel.py:47-112), compression_quantization_with_zero_point
+ * (compress_function.py:245-275, kernel :229-301) when zp != NULL, and
+ * outlier_subtraction_fuse_compression_quantization (compress_function.py:111-143) when
+ * outlier_idx != NULL: the k outlier columns are gathered into outlier_out [rows, k] bf16 and
+ * encoded as zero; x itself is NOT modified.
+ * x [rows, N] bf16 (N % 32 == 0), scale [N] bf16, zp [N] int8 or NULL,
+ * q_out [rows, N*q_bit/8] uint8. */
+int hyc_quant_pack(const void* x, int64_t rows, int N, int64_t ldx,
+                   const void* scale, const int8_t* zp,
+                   const int64_t* outlier_idx, int k,
+                   void* q_out, void* outlier_out, int q_bit, void* stream);
+
+/* Replaces decompression_dequantization (+kernel) (compress_function.py:214-241, kernel
+ * :150-206), ..._with_zero_point (compress_function.py:278-306, kernel :324-388) when
+ * zp != NULL, and outlier_addition_fuse_decompression_dequantization
+ * (compress_function.py:147-174) when outlier_idx != NULL (x[:, idx[j]] = outlier[:, j]).
+ * x_out [rows, N] bf16 with row stride ldx. */
+int hyc_unpack_dequant(const void* q, int64_t rows, int N,
+                       const void* scale, const int8_t* zp,
+                       const int64_t* outlier_idx, int k, const void* outlier,
+                       void* x_out, int64_t ldx, int q_bit, void* stream);
+
+/* ---- 64-wide group mode (no counterpart in the reference: scale and zero point are
+ *      taken from each group of 64 values of a row; same arithmetic as
+ *      compress_function.py:62-77 / compress_function_kernel.py:279-299, 376-387) ------ */
+int hyc_group_quant_pack(const void* x, int64_t rows, int N, int64_t ldx,
+                         void* q_out, void* scale_out, int8_t* zp_out, int q_bit, void* stream);
+int hyc_group_unpack_dequant(const void* q, int64_t rows, int N,
+                             const void* scale, const int8_t* zp,
+                             void* x_out, int64_t ldx, int q_bit, void* stream);
+
+/* ---- attention map: threshold prune (the reference's behaviour) --------------------- */
+
+/* compression_softmax (compress_function.py:309-313): keep a[i] > bf16(threshold) and
+ * a[i] != 0, as the COO list of the flattened map.  Two phases because the caller owns the
+ * output: phase 1 counts per tile and leaves exclusive offsets plus the total in `workspace`
+ * (copy the int64 at workspace[0] to the host to size idx/val); phase 2 writes them.
+ * workspace bytes: hyc_softmax_prune_workspace_bytes(numel). */
+size_t hyc_softmax_prune_workspace_bytes(int64_t numel);
+int hyc_softmax_prune_count(const void* a, int64_t numel, float threshold,
+                            void* workspace, size_t workspace_bytes, void* stream);
+int hyc_softmax_prune_fill(const void* a, int64_t numel, float threshold,
+                           const void* workspace, int64_t* idx_out, void* val_out,
+                           int64_t capacity, void* stream);
+/* to_dense (compress_function.py:316-317): zero-fill and scatter. */
+int hyc_softmax_prune_restore(const int64_t* idx, const void* val, int64_t nnz,
+                              void* a_out, int64_t numel, void* stream);
+
+/* ---- attention map: per-row top-k + grouped remainder (no counterpart in the reference;
+ *      the reference prunes by one global threshold, compress_function.py:30-32, 309-313) -- */
+/* a [rows, S] bf16 (S % 64 == 0, S <= 4096, k <= S): the k largest magnitudes of every row
+ * (equal magnitudes: lower column first) go to val_out [rows,k] bf16 / col_out [rows,k] uint16 in
+ * ascending column order; the row with those positions zeroed is group-quantized. */
+int hyc_softmax_topk_compress(const void* a, int64_t rows, int S, int k,
+                              void* val_out, uint16_t* col_out,
+                              void* q_out, void* scale_out, int8_t* zp_out, int q_bit, void* stream);
+int hyc_softmax_topk_restore(const void* val, const uint16_t* col, int k,
+                             const void* q, const void* scale, const int8_t* zp,
+                             int64_t rows, int S, void* a_out, int q_bit, void* stream);
+
+/* ---- fused LoRA-SiLU-Hadamard elementwise kernels ------------------------------------- */
+
+/* triton_fuse_silu_forward (operators/triton_fuse_lora_silu_hadamard_forward_kernels.py:28-181).
+ * xa* [rows, R] bf16 (R == 16), bt* [N, R] bf16 (the LoRA-B weight as stored, i.e. b^T),
+ * x* [rows, N] bf16 (the frozen-weight products), s* [N] bf16.  N % 32 == 0.
+ * Writes q1, q2 [rows, N*q_bit/8] and o [rows, N] bf16. */
+int hyc_fused_lora_silu_hadamard_fwd(const void* xa1, const void* bt1, const void* x1, const void* s1,
+                                     const void* xa2, const void* bt2, const void* x2, const void* s2,
+                                     void* q1, void* q2, void* o,
+                                     int64_t rows, int N, int R, int q_bit, void* stream);
+/* triton_fuse_silu_backward (operators/triton_fuse_lora_silu_hadamard_backward_kernels.py:28-178).
+ * Writes o, grad_gate, grad_up [rows, N] bf16. */
+int hyc_fused_lora_silu_hadamard_bwd(const void* xa1, const void* bt1, const void* q1, const void* s1,
+                                     const void* xa2, const void* bt2, const void* q2, const void* s2,
+                                     const void* grad_o, void* o, void* grad_gate, void* grad_up,
+                                     int64_t rows, int N, int R, int q_bit, void* stream);
+
+/* ---- producers / consumers of the saved tensors ----------------------------------------- */
+
+/* rmsnorm_forward / rmsnorm_backward (operators/rmsnorm_kernels.py:10-54, 58-113, wrappers
+ * :116-185).  rstd [rows] fp32.  The backward keeps the reference's LayerNorm-style mean term. */
+int hyc_rmsnorm_fwd(const void* x, const void* w, float eps, void* y, float* rstd,
+                    int64_t rows, int N, void* stream);
+int hyc_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd, void* dx,
+                    int64_t rows, int N, void* stream);
+/* softmax_backward (operators/softmax_kernels.py:7-56): o = (g - sum(y*g)) * y per row. */
+int hyc_softmax_bwd(const void* y, const void* g, void* o, int64_t rows, int S, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* HYC_H_ */

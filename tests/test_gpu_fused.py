@@ -1,0 +1,118 @@
+"""Fused LoRA-SiLU-Hadamard forward/backward, RMSNorm and softmax backward against the golden
+fixtures and the CPU oracle.  Packed codes are bit-exact; bf16 outputs are compared within the
+tolerance of the path: max |err| <= 1e-2 * max|ref| and cosine > 0.999 (sigmoid and the rank-16
+dot are evaluated in a different order on the device, so a bf16 ulp may differ)."""
+import pytest
+import torch
+
+import oracle
+
+pytestmark = pytest.mark.gpu
+QS = (2, 4, 8)
+DEV = "cuda"
+
+
+def close(a, b, rel=1e-2, cos=0.999):
+    a, b = a.float().cpu().flatten(), b.float().cpu().flatten()
+    scale = b.abs().max().clamp(min=1e-30)
+    c = torch.nn.functional.cosine_similarity(a, b, dim=0) if b.abs().sum() > 0 else torch.tensor(1.0)
+    return bool((a - b).abs().max() <= rel * scale) and bool(c > cos)
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from hyc_lora_release_b200.operators import (
+        rmsnorm_kernels, softmax_kernels,
+        triton_fuse_lora_silu_hadamard_backward_kernels as bk,
+        triton_fuse_lora_silu_hadamard_forward_kernels as fk)
+    return fk.triton_fuse_silu_forward, bk.triton_fuse_silu_backward, rmsnorm_kernels, softmax_kernels
+
+
+@pytest.mark.parametrize("q", QS)
+def test_golden_fused(ops, golden, q):
+    fwd, bwd, _, _ = ops
+    d = {k: (v.to(DEV) if torch.is_tensor(v) else v) for k, v in golden[f"q{q}"].items()}
+    q1, q2, o = fwd(d["f_xa1"], d["f_b1"], d["f_x1"], d["f_s1"], d["f_xa2"], d["f_b2"], d["f_x2"], d["f_s2"], q)
+    assert torch.equal(q1, d["f_q1"]) and torch.equal(q2, d["f_q2"])
+    assert close(o, d["f_o"])
+    assert (o != d["f_o"]).float().mean() < 0.02          # almost every element identical
+    bo, gg, gu = bwd(d["f_xa1"], d["f_b1"], q1, d["f_s1"], d["f_xa2"], d["f_b2"], q2, d["f_s2"], d["f_go"], q)
+    assert close(bo, d["f_bo"]) and close(gg, d["f_ggate"]) and close(gu, d["f_gup"])
+    # the backward recomputes the forward output from the saved codes
+    assert (bo != d["f_bo"]).float().mean() < 0.02
+
+
+@pytest.mark.parametrize("q", QS)
+@pytest.mark.parametrize("shape", [(1, 16, 32), (2, 50, 96), (1, 37, 11008), (2, 128, 1024)])
+def test_oracle_fused(ops, q, shape):
+    fwd, bwd, _, _ = ops
+    B, M, N = shape
+    g = torch.Generator().manual_seed(B * M + N + q)
+    R = 16
+    xa1, xa2 = torch.randn(B, M, R, generator=g).bfloat16(), torch.randn(B, M, R, generator=g).bfloat16()
+    # LoRA-B as the layers pass it: the transposed view of an [N, R] weight
+    w1, w2 = (torch.randn(N, R, generator=g) * 0.05).bfloat16(), (torch.randn(N, R, generator=g) * 0.05).bfloat16()
+    b1, b2 = w1.T, w2.T
+    x1, x2 = torch.randn(B, M, N, generator=g).bfloat16(), torch.randn(B, M, N, generator=g).bfloat16()
+    s1, s2 = oracle.ref_scale_per_channel(x1, q), oracle.ref_scale_per_channel(x2, q)
+    s1 = torch.where(s1 == 0, torch.tensor(1e-3, dtype=torch.bfloat16), s1)
+    s2 = torch.where(s2 == 0, torch.tensor(1e-3, dtype=torch.bfloat16), s2)
+    go = torch.randn(B, M, N, generator=g).bfloat16()
+    oq1, oq2, oo = oracle.ref_fused_silu_forward(xa1, b1, x1, s1, xa2, b2, x2, s2, q)
+    t = lambda *a: [v.to(DEV) for v in a]
+    q1, q2, o = fwd(*t(xa1, b1, x1, s1, xa2, b2, x2, s2), q)
+    assert torch.equal(q1.cpu(), oq1) and torch.equal(q2.cpu(), oq2) and close(o, oo)
+    # contiguous [R, N] LoRA-B (what the reference's wrapper makes) gives the same result
+    q1c, q2c, oc = fwd(*t(xa1, b1.contiguous(), x1, s1, xa2, b2.contiguous(), x2, s2), q)
+    assert torch.equal(q1c, q1) and torch.equal(oc, o)
+    ob, ogg, ogu = oracle.ref_fused_silu_backward(xa1, b1, oq1, s1, xa2, b2, oq2, s2, go, q)
+    bo, gg, gu = bwd(*t(xa1, b1, oq1, s1, xa2, b2, oq2, s2, go), q)
+    assert close(bo, ob) and close(gg, ogg) and close(gu, ogu)
+
+
+def test_fused_linearity_at_full_width(ops):
+    """Size-independent properties at the Mistral width: grad_up is linear in grad_o, and a zero
+    LoRA-B makes o = silu(dequant(q1)) * dequant(q2)."""
+    fwd, bwd, _, _ = ops
+    from hyc_lora_release_b200.operators import compress_function as cf
+    g = torch.Generator().manual_seed(4)
+    B, M, N, R, q = 1, 512, 14336, 16, 4
+    xa = torch.randn(B, M, R, generator=g).bfloat16().to(DEV)
+    bz = torch.zeros(R, N, dtype=torch.bfloat16, device=DEV)
+    x1 = torch.randn(B, M, N, generator=g).bfloat16().to(DEV)
+    x2 = torch.randn(B, M, N, generator=g).bfloat16().to(DEV)
+    s1, s2 = cf.get_statistics_only_quant(x1, q, "per-channel"), cf.get_statistics_only_quant(x2, q, "per-channel")
+    q1, q2, o = fwd(xa, bz, x1, s1, xa, bz, x2, s2, q)
+    assert torch.equal(q1, cf.compression_quantization(x1, s1, q)) and torch.equal(q2, cf.compression_quantization(x2, s2, q))
+    go = torch.randn(B, M, N, generator=g).bfloat16().to(DEV)
+    bo, gg, gu = bwd(xa, bz, q1, s1, xa, bz, q2, s2, go, q)
+    d1, d2 = cf.decompression_dequantization(q1, s1, q), cf.decompression_dequantization(q2, s2, q)
+    sig = torch.sigmoid(d1.float()).bfloat16()
+    want = ((d1 * sig) * d2)
+    assert close(bo, want)
+    _, _, gu2 = bwd(xa, bz, q1, s1, xa, bz, q2, s2, go * 2, q)
+    assert torch.equal(gu2, gu * 2)
+
+
+@pytest.mark.parametrize("shape", [(3, 64), (2, 7, 4096), (1, 33, 11008), (5, 16384)])
+def test_rmsnorm(ops, shape):
+    _, _, rn, _ = ops
+    g = torch.Generator().manual_seed(sum(shape))
+    x = torch.randn(*shape, generator=g).bfloat16()
+    w = (1 + 0.1 * torch.randn(shape[-1], generator=g)).bfloat16()
+    y, mean, rstd, bs, nw = rn.rmsnorm_forward(x.to(DEV), w.to(DEV), 1e-5)
+    oy, orstd = oracle.ref_rmsnorm_forward(x, w, 1e-5)
+    assert torch.allclose(rstd.cpu(), orstd, rtol=1e-5, atol=0) and close(y, oy, rel=4e-3)
+    dy = torch.randn(*shape, generator=g).bfloat16()
+    dx, none = rn.rmsnorm_backward(dy.to(DEV), x.to(DEV), w.to(DEV), mean, rstd, True, 1e-5, nw, bs)
+    assert none is None and close(dx, oracle.ref_rmsnorm_backward(dy, x, w, orstd), rel=4e-3)
+
+
+@pytest.mark.parametrize("shape", [(1, 2, 8, 8), (2, 3, 100, 104), (1, 4, 512, 512), (1, 1, 16, 4096)])
+def test_softmax_backward(ops, shape):
+    _, _, _, sm = ops
+    g = torch.Generator().manual_seed(sum(shape))
+    y = torch.softmax(3 * torch.randn(*shape, generator=g), -1).bfloat16()
+    gy = torch.randn(*shape, generator=g).bfloat16()
+    o = sm.softmax_backward(y.to(DEV), gy.to(DEV))
+    assert close(o, oracle.ref_softmax_backward(y, gy), rel=4e-3)

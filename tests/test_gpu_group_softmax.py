@@ -1,0 +1,127 @@
+"""Group mode, attention-map threshold prune and per-row top-k against the CPU oracle."""
+import pytest
+import torch
+
+import oracle
+
+pytestmark = pytest.mark.gpu
+QS = (2, 4, 8)
+DEV = "cuda"
+
+
+@pytest.fixture(scope="module")
+def cf():
+    from hyc_lora_release_b200.operators import compress_function
+    return compress_function
+
+
+def _softmax_map(b, h, s, seed, causal=True):
+    g = torch.Generator().manual_seed(seed)
+    logits = 3 * torch.randn(b, h, s, s, generator=g)
+    if causal:
+        logits = logits + torch.triu(torch.full((s, s), float("-inf")), diagonal=1)
+    return torch.softmax(logits, dim=-1).to(torch.bfloat16)
+
+
+@pytest.mark.parametrize("q", QS)
+@pytest.mark.parametrize("shape", [(1, 64), (5, 192), (7, 512), (3, 1088), (2, 4096), (9, 11008)])
+def test_group_mode(cf, q, shape):
+    rows, N = shape
+    g = torch.Generator().manual_seed(rows * N + q)
+    x = torch.randn(rows, N, generator=g) * torch.rand(rows, 1, generator=g) * 4 + torch.randn(rows, 1, generator=g)
+    x[0, :64] = 0.375              # a constant group (zero range)
+    x[-1, -64:] = 200.0 + torch.rand(64, generator=g)   # zero point saturates
+    x = x.to(torch.bfloat16)
+    pk, s, z = cf.compression_group(x.to(DEV), q)
+    opk, os_, oz = oracle.group_compress(x, q)
+    assert torch.equal(s.cpu(), os_) and torch.equal(z.cpu(), oz) and torch.equal(pk.cpu(), opk)
+    assert torch.equal(cf.decompression_group(pk, s, z, q).cpu(), oracle.group_decompress(opk, os_, oz, q))
+
+
+def test_softmax_prune_golden(cf, golden):
+    d = golden["softmax"]
+    a = d["a"].to(DEV)
+    thr = cf.get_statistics_softmax(a, d["ratio"])
+    assert torch.equal(thr.cpu(), d["thr"])
+    for t, i, v in ((d["thr"], d["idx"], d["val"]), (d["thr2"], d["idx2"], d["val2"])):
+        sp = cf.compression_softmax(a, t.to(DEV))
+        assert sp.is_sparse and torch.equal(sp.indices().cpu(), i) and torch.equal(sp.values().cpu(), v)
+    sp = cf.compression_softmax(a, d["thr"])
+    assert torch.equal(sp.to_dense().reshape(a.shape).cpu(), d["dense"])              # what the layers call
+    assert torch.equal(cf.decompression_softmax(sp).reshape(a.shape).cpu(), d["dense"])  # our restore kernel
+    h, thr2 = cf.compression_pack_softmax_base(a, d["ratio"], 0, 5, None)
+    assert torch.equal(thr2.cpu(), d["thr"]) and torch.equal(h.indices().cpu(), d["idx"])
+
+
+@pytest.mark.parametrize("shape", [(1, 1, 8, 8), (2, 3, 100, 100), (1, 2, 512, 512), (1, 1, 1000, 1000)])
+def test_softmax_prune_oracle(cf, shape):
+    a = _softmax_map(*shape[:3], seed=sum(shape))
+    thr = oracle.ref_softmax_threshold(a, 0.05)
+    sp = cf.compression_softmax(a.to(DEV), thr)
+    idx, val = oracle.ref_softmax_prune(a, thr)
+    assert torch.equal(sp.indices().reshape(-1).cpu(), idx) and torch.equal(sp.values().cpu(), val)
+    assert torch.equal(cf.decompression_softmax(sp).reshape(a.shape).cpu(), oracle.ref_softmax_restore(idx, val, a.shape))
+    # nothing kept / everything kept
+    none = cf.compression_softmax(a.to(DEV), 2.0)
+    assert none.values().numel() == 0 and torch.equal(cf.decompression_softmax(none).cpu(), torch.zeros(a.numel(), dtype=torch.bfloat16))
+    allk = cf.compression_softmax(a.to(DEV), -1.0)
+    assert allk.values().numel() == int((a != 0).sum())
+
+
+@pytest.mark.parametrize("q", QS)
+@pytest.mark.parametrize("shape", [(1, 1, 64, 64), (2, 2, 128, 128), (1, 2, 512, 512), (1, 1, 320, 320), (1, 1, 64, 2048)])
+def test_topk_mode(cf, q, shape):
+    b, h, r, s = shape
+    if r == s:
+        a = _softmax_map(b, h, s, seed=s + q)
+    else:
+        g = torch.Generator().manual_seed(s + q)
+        a = torch.softmax(3 * torch.randn(b, h, r, s, generator=g), -1).to(torch.bfloat16)
+    m = cf.compression_softmax_topk(a.to(DEV), 0.05, q)
+    vals, cols, pk, sc, zp = oracle.topk_compress(a, 0.05, q)
+    assert torch.equal(m.col.cpu().to(torch.int64) & 0xFFFF, cols)
+    assert torch.equal(m.val.cpu(), vals)
+    assert torch.equal(m.scale.cpu(), sc) and torch.equal(m.zp.cpu(), zp) and torch.equal(m.q.cpu(), pk)
+    assert torch.equal(m.to_dense().cpu(), oracle.topk_decompress(vals, cols, pk, sc, zp, q, a.shape))
+
+
+def test_topk_ties_and_signs(cf):
+    """Many equal magnitudes (ties go to the lower column), negative values, all-zero rows."""
+    g = torch.Generator().manual_seed(77)
+    S = 256
+    x = (torch.randint(-3, 4, (40, S), generator=g).float() * 0.25)
+    x[0] = 0.0
+    x[1] = 1.0
+    x[2, ::2] = -2.0
+    x = x.to(torch.bfloat16)
+    for ratio in (0.05, 0.25, 0.0, 1.0):
+        m = cf.compression_softmax_topk(x.to(DEV), ratio, 4)
+        vals, cols, pk, sc, zp = oracle.topk_compress(x, ratio, 4)
+        assert torch.equal(m.col.cpu().to(torch.int64) & 0xFFFF, cols) and torch.equal(m.val.cpu(), vals)
+        assert torch.equal(m.q.cpu(), pk) and torch.equal(m.scale.cpu(), sc) and torch.equal(m.zp.cpu(), zp)
+        assert torch.equal(m.to_dense().cpu(), oracle.topk_decompress(vals, cols, pk, sc, zp, 4, x.shape))
+
+
+def test_topk_config1_full_size_properties(cf):
+    """[4,32,512,512] causal softmax map, ratio 0.05, q_bit 4: checked through size-independent
+    properties plus the oracle on a slice."""
+    a = _softmax_map(4, 32, 512, seed=1).to(DEV)
+    m = cf.compression_softmax_topk(a, 0.05, 4)
+    k = 25
+    assert m.val.shape == (4 * 32 * 512, k)
+    cols = m.col.to(torch.int64) & 0xFFFF
+    assert (cols[:, 1:] > cols[:, :-1]).all()                      # strictly ascending columns
+    a2 = a.reshape(-1, 512)
+    assert torch.equal(torch.gather(a2, 1, cols), m.val)            # values are the map's own entries
+    kth = torch.topk(a2.float(), k, dim=-1).values[:, -1:]
+    assert (m.val.float() >= kth).all()                             # nothing below the k-th largest
+    d = m.to_dense()
+    assert torch.equal(torch.gather(d.reshape(-1, 512), 1, cols), m.val)   # outliers restored exactly
+    assert (d.float() - a.float()).abs().max() <= 0.04
+    # restore -> compress again gives the same outlier set (idempotence of the selection)
+    m2 = cf.compression_softmax_topk(d, 0.05, 4)
+    assert torch.equal(m2.val, m.val)
+    sl = slice(0, 2048)
+    vals, oc, pk, sc, zp = oracle.topk_compress(a2[sl].cpu(), 0.05, 4)
+    assert torch.equal(cols[sl].cpu(), oc) and torch.equal(m.q[sl].cpu(), pk) and torch.equal(m.scale[sl].cpu(), sc)
+    assert m.nbytes() < 0.45 * a.numel() * 2
