@@ -216,6 +216,36 @@ def extra_workloads(dev, hbm):
     return out
 
 
+def run_profile(args):
+    """Minimal launch sequence of one workload (few launches, inputs > L2, < 2 GB on the device)."""
+    from hyc_lora_release_b200.operators import compress_function as cf
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    if args.profile == "attn_topk":
+        maps = [make_map(1000 + i, dev) for i in range(NBUF)]
+        nbytes = 2 * algo_bytes(MAP_SHAPE, QBIT, RATIO)
+
+        def step(i):
+            cf.compression_softmax_topk(maps[i % NBUF], RATIO, QBIT).to_dense()
+    else:
+        q = int(args.profile[-1])
+        g = torch.Generator().manual_seed(1234)
+        xs = []
+        for _ in range(2):
+            x = torch.randn(1, 8192, 14336, generator=g)
+            x[:, :, torch.randperm(14336, generator=g)[:143]] *= 20.0
+            xs.append(x.to(torch.bfloat16).to(dev))
+        idx, s = cf.get_statistics_channel_base(xs[0], 0.01, q, "per-channel")
+        nbytes = xs[0].numel() * (4 + q / 4.0)
+
+        def step(i):
+            o, qq = cf.outlier_subtraction_fuse_compression_quantization(xs[i % 2], s, idx, q)
+            cf.outlier_addition_fuse_decompression_dequantization(qq, s, o, idx, q)
+    t = time_loop(step, args.steps, args.warmup)
+    print(json.dumps({"profile": args.profile, "steps": args.steps, "ms_per_step": t / args.steps * 1e3,
+                      "GBps": args.steps * nbytes / t / 1e9}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -223,11 +253,15 @@ def main():
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-extras", action="store_true", help="skip the secondary workloads and the CPU sample")
+    ap.add_argument("--profile", default=None, choices=["attn_topk", "channel_q4", "channel_q2", "channel_q8"],
+                    help="run only W+K steps of one workload and print timing (for a profiler capture)")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3
     if args.impl == "reference":
         return run_reference(args)
+    if args.profile:
+        return run_profile(args)
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

@@ -17,26 +17,29 @@ namespace hyc {
 
 constexpr unsigned kFull = 0xffffffffu;
 
-struct GroupParams { float s, rc, z; };
+struct GroupParams { float s, rc, zc, z; };   // zc = z + 2^(q-1)
 
-// scale / zero point of one group from its min and max (all lanes of the group hold the
-// same mn, mx and compute the same result)
+// Group-mode arithmetic (fp32, one rounding per operation; the fused-multiply-add is
+// deliberately not used so that a plain fp32 statement on any machine reproduces it):
+//   d = bf16(mx - mn);  s = bf16(d * (1/levels)), 1e-3 when zero;  rc = 1/s
+//   z = clamp(rint(clamp(-mn*rc, +-300)) - half, -128, 127)
+//   code = rint(clamp(x*rc + (z + half), 0, levels))           rint = half to even
+// rint of a value in [0, 2^22) is "add 2^23 in round-to-nearest": the integer lands in
+// the low mantissa bits, so no float->int conversion is issued per element.
 template <int QBIT>
 __device__ __forceinline__ GroupParams group_params(float mn, float mx) {
-  constexpr float levels = (float)((1 << QBIT) - 1);
+  constexpr float inv_levels = 1.0f / (float)((1 << QBIT) - 1);
   constexpr float half = (float)(1 << (QBIT - 1));
-  float d = bf16bits_to_f32(f32_to_bf16bits_rn(mx - mn));
-  float s = bf16bits_to_f32(f32_to_bf16bits_rn(__fdiv_rn(d, levels)));
+  float d = bf16bits_to_f32(f32_to_bf16bits_rn(__fsub_rn(mx, mn)));
+  float s = bf16bits_to_f32(f32_to_bf16bits_rn(__fmul_rn(d, inv_levels)));
   if (s == 0.f) s = bf16bits_to_f32(f32_to_bf16bits_rn(1e-3f));
   GroupParams p;
   p.s = s;
   p.rc = __frcp_rn(s);
-  float r = quotient_rn(mn, s, p.rc);
-  // roundf of an unclamped value: the magnitude may exceed the integer range of interest;
-  // anything beyond +-300 saturates the int8 zero point anyway
-  r = fminf(fmaxf(r, -300.f), 300.f);
-  float zr = (float)round_half_away_i(r);
-  p.z = fminf(fmaxf(-zr - half, -128.f), 127.f);
+  float t = fminf(fmaxf(__fmul_rn(-mn, p.rc), -300.f), 300.f);
+  float zr = __fadd_rn(__fadd_rn(t, 12582912.f), -12582912.f);   // rint, |t| <= 300
+  p.z = fminf(fmaxf(zr - half, -128.f), 127.f);
+  p.zc = p.z + half;
   return p;
 }
 
@@ -59,43 +62,53 @@ __device__ __forceinline__ void group_minmax(const uint32_t (&xw)[8], float& mn,
   }
 }
 
+// unsigned code of one value, left in the low byte of a float's bit pattern (2^23 + code)
+template <int QBIT>
+__device__ __forceinline__ uint32_t group_code_bits(float x, const GroupParams& p) {
+  constexpr float levels = (float)((1 << QBIT) - 1);
+  float u = __fadd_rn(__fmul_rn(x, p.rc), p.zc);
+  u = fminf(fmaxf(u, 0.f), levels);
+  return __float_as_uint(__fadd_rn(u, 8388608.f));
+}
+
 // Quantize the 16 values of a lane and store them in the reference byte layout.
 // qrow points at the packed row; `lane_g` = 32*step + lane (global lane index in the row).
 template <int QBIT>
 __device__ __forceinline__ void quant_store16(const uint32_t (&xw)[8], const GroupParams& p,
                                               uint8_t* __restrict__ qrow, int lane_g, bool valid) {
-  int c[16];
+  uint32_t w[4];   // w[i] = codes 4i..4i+3, one per byte
 #pragma unroll
-  for (int e = 0; e < 16; ++e) {
-    float xf = (e & 1) ? bf16hi_to_f32(xw[e >> 1]) : bf16lo_to_f32(xw[e >> 1]);
-    c[e] = quant_code_signed_zp<QBIT>(xf, p.s, p.rc, p.z);
+  for (int i = 0; i < 4; ++i) {
+    uint32_t b[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int idx = 4 * i + e;
+      float xf = (idx & 1) ? bf16hi_to_f32(xw[idx >> 1]) : bf16lo_to_f32(xw[idx >> 1]);
+      b[e] = group_code_bits<QBIT>(xf, p);
+    }
+    // low bytes of b0..b3 -> one word
+    w[i] = __byte_perm(__byte_perm(b[0], b[1], 0x0040), __byte_perm(b[2], b[3], 0x0040), 0x5410);
   }
-  uint32_t w0 = pack4_s8(c[0], c[1], c[2], c[3]), w1 = pack4_s8(c[4], c[5], c[6], c[7]);
-  uint32_t w2 = pack4_s8(c[8], c[9], c[10], c[11]), w3 = pack4_s8(c[12], c[13], c[14], c[15]);
+  const uint32_t w0 = w[0], w1 = w[1], w2 = w[2], w3 = w[3];
   const bool odd = lane_g & 1;
   if (QBIT == 8) {
-    uint4 o = make_uint4(w0 ^ 0x80808080u, w1 ^ 0x80808080u, w2 ^ 0x80808080u, w3 ^ 0x80808080u);
-    if (valid) st_stream_v4(qrow + 16 * (int64_t)lane_g, o);
+    if (valid) st_stream_v4(qrow + 16 * (int64_t)lane_g, make_uint4(w0, w1, w2, w3));
   } else if (QBIT == 4) {
-    constexpr uint32_t M = 0x0f0f0f0fu;
     // even lane: columns 0..15 of the block (low nibbles); odd lane: columns 16..31 (high)
     uint32_t s0 = odd ? w0 : w2, s1 = odd ? w1 : w3;
     uint32_t r0 = __shfl_xor_sync(kFull, s0, 1), r1 = __shfl_xor_sync(kFull, s1, 1);
     uint2 o;
-    if (!odd) { o.x = (w0 & M) | ((r0 & M) << 4); o.y = (w1 & M) | ((r1 & M) << 4); }   // bytes 0..7
-    else      { o.x = (r0 & M) | ((w2 & M) << 4); o.y = (r1 & M) | ((w3 & M) << 4); }   // bytes 8..15
-    o.x ^= 0x88888888u; o.y ^= 0x88888888u;
+    if (!odd) { o.x = w0 | (r0 << 4); o.y = w1 | (r1 << 4); }   // bytes 0..7
+    else      { o.x = r0 | (w2 << 4); o.y = r1 | (w3 << 4); }   // bytes 8..15
     if (valid) st_stream_v2(qrow + 8 * (int64_t)lane_g, o);
   } else {
-    constexpr uint32_t M = 0x03030303u;
     // byte j = c[j] | c[8+j]<<2 | c[16+j]<<4 | c[24+j]<<6 ; even lane holds c[0..15], odd c[16..31]
     uint32_t p0, p1;
-    if (!odd) { p0 = (w0 & M) | ((w2 & M) << 2); p1 = (w1 & M) | ((w3 & M) << 2); }
-    else      { p0 = ((w0 & M) << 4) | ((w2 & M) << 6); p1 = ((w1 & M) << 4) | ((w3 & M) << 6); }
+    if (!odd) { p0 = w0 | (w2 << 2); p1 = w1 | (w3 << 2); }
+    else      { p0 = (w0 << 4) | (w2 << 6); p1 = (w1 << 4) | (w3 << 6); }
     uint32_t send = odd ? p0 : p1;
     uint32_t recv = __shfl_xor_sync(kFull, send, 1);
     uint32_t o = (odd ? p1 : p0) | recv;   // even: bytes 0..3, odd: bytes 4..7
-    o ^= 0xaaaaaaaau;
     if (valid) st_stream_u32(qrow + 4 * (int64_t)lane_g, o);
   }
 }
@@ -205,16 +218,17 @@ group_dequant_kernel(const uint8_t* __restrict__ q, int64_t rows, int N,
 }
 
 // ---------------------------------------------------------------- per-row top-k (attention map)
-template <int STEPS>
-__device__ __forceinline__ int count_ge(const uint32_t (&m)[STEPS][8], uint32_t cand) {
-  const uint32_t c2 = cand | (cand << 16);
-  const __nv_bfloat162 cb = *reinterpret_cast<const __nv_bfloat162*>(&c2);
+__device__ __forceinline__ __nv_bfloat162 as_bf162(uint32_t v) { return *reinterpret_cast<__nv_bfloat162*>(&v); }
+__device__ __forceinline__ uint32_t as_u32(__nv_bfloat162 v) { return *reinterpret_cast<uint32_t*>(&v); }
+
+// number of keys >= cand over the whole warp; keys are 15-bit magnitude patterns, which
+// order like the positive bf16 values they spell, so packed bf16x2 compares count them
+template <int NREG>
+__device__ __forceinline__ int count_ge(const uint32_t (&m)[NREG], uint32_t cand) {
+  const __nv_bfloat162 cb = as_bf162(cand | (cand << 16));
   __nv_bfloat162 acc = __float2bfloat162_rn(0.f);
 #pragma unroll
-  for (int st = 0; st < STEPS; ++st)
-#pragma unroll
-    for (int j = 0; j < 8; ++j)
-      acc = __hadd2(acc, __hge2(*reinterpret_cast<const __nv_bfloat162*>(&m[st][j]), cb));
+  for (int j = 0; j < NREG; ++j) acc = __hadd2(acc, __hge2(as_bf162(m[j]), cb));
   int c = (int)(__bfloat162float(acc.x) + __bfloat162float(acc.y));
   return __reduce_add_sync(kFull, c);
 }
@@ -228,7 +242,8 @@ topk_compress_kernel(const __nv_bfloat16* __restrict__ a, int64_t rows, int S, i
   const int64_t qld = (int64_t)S * QBIT / 8, gld = S / 64;
   for (int64_t row = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5); row < rows; row += (int64_t)gridDim.x * 8) {
     const __nv_bfloat16* arow = a + row * S;
-    uint32_t xw[STEPS][8], m[STEPS][8];
+    uint32_t xw[STEPS][8];
+    uint32_t m[STEPS * 8];
 #pragma unroll
     for (int st = 0; st < STEPS; ++st) {
       const int col = 16 * (32 * st + lane);
@@ -241,82 +256,118 @@ topk_compress_kernel(const __nv_bfloat16* __restrict__ a, int64_t rows, int S, i
         for (int j = 0; j < 8; ++j) xw[st][j] = 0u;
       }
 #pragma unroll
-      for (int j = 0; j < 8; ++j) m[st][j] = xw[st][j] & 0x7fff7fffu;
+      for (int j = 0; j < 8; ++j) m[st * 8 + j] = xw[st][j] & 0x7fff7fffu;
     }
 
-    uint32_t sel[STEPS];  // bit e set: element e of the step is an outlier
-#pragma unroll
-    for (int st = 0; st < STEPS; ++st) sel[st] = 0u;
-
     if (k > 0) {
-      // bisection: largest T with count(m >= T) >= k
-      uint32_t T = 0u;
-      int n_ge = 32 * 16 * STEPS;
-      for (int bit = 14; bit >= 0; --bit) {
-        const uint32_t cand = T | (1u << bit);
-        const int cnt = count_ge<STEPS>(m, cand);
-        if (cnt >= k) { T = cand; n_ge = cnt; if (cnt == k) break; }
-      }
-      const uint32_t T2 = T | (T << 16);
-      int need = 0;            // how many elements equal to T are taken, lowest columns first
-      if (n_ge > k) need = k - count_ge<STEPS>(m, T + 1u);   // T + 1: next pattern, i.e. "m > T"
-      int tie_base = 0;
+      // ---- a lower bound from few candidates: the two largest keys of each of the lane's
+      // 2*STEPS eight-element streams (the low and the high halves of the packed registers).
+      // They are distinct elements of the row, so the k-th largest of them is <= the k-th
+      // largest of the row, and usually equal to it.
+      uint32_t cand[2 * STEPS];
+      uint32_t lane_max = 0u;
 #pragma unroll
       for (int st = 0; st < STEPS; ++st) {
-        uint32_t gt = 0u, eq = 0u;
+        __nv_bfloat162 m1 = as_bf162(m[st * 8]), m2 = __float2bfloat162_rn(0.f);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const uint32_t lo = m[st][j] & 0xffffu, hi = m[st][j] >> 16;
-          gt |= (lo > (T2 & 0xffffu) ? 1u : 0u) << (2 * j);
-          gt |= (hi > (T2 & 0xffffu) ? 1u : 0u) << (2 * j + 1);
-          eq |= (lo == (T2 & 0xffffu) ? 1u : 0u) << (2 * j);
-          eq |= (hi == (T2 & 0xffffu) ? 1u : 0u) << (2 * j + 1);
+        for (int j = 1; j < 8; ++j) {
+          const __nv_bfloat162 v = as_bf162(m[st * 8 + j]);
+          m2 = __hmax2(m2, __hmin2(m1, v));
+          m1 = __hmax2(m1, v);
         }
-        if (n_ge == k) {
-          sel[st] = gt | eq;
-        } else {
-          int tot;
-          int before = tie_base + warp_excl_scan(__popc(eq), lane, tot);
-          tie_base += tot;
-          // keep the ties whose rank (column order) is below `need`
-          uint32_t take = 0u;
-          int rank = before;
-#pragma unroll
-          for (int e = 0; e < 16; ++e) {
-            const uint32_t bitm = 1u << e;
-            if (eq & bitm) { if (rank < need) take |= bitm; ++rank; }
-          }
-          sel[st] = gt | take;
+        cand[2 * st] = as_u32(m1);
+        cand[2 * st + 1] = as_u32(m2);
+        const uint32_t c1 = as_u32(m1);
+        lane_max = max(lane_max, max(c1 & 0xffffu, c1 >> 16));
+      }
+      const uint32_t U = __reduce_max_sync(kFull, lane_max);     // largest key of the row
+      uint32_t L = 0u;
+      if (k <= 128 * STEPS) {
+        // bitwise bisection over the candidates: largest L with count_cand(>= L) >= k
+        for (int bit = 14; bit >= 0; --bit) {
+          const uint32_t c = L | (1u << bit);
+          if (c > U) continue;
+          const int cnt = count_ge<2 * STEPS>(cand, c);
+          if (cnt >= k) { L = c; if (cnt == k) break; }
         }
       }
-      // emit in ascending column order
+      // ---- exact threshold on the full row: largest T in [L, U] with count(>= T) >= k
+      uint32_t T = L;
+      int n_ge = count_ge<8 * STEPS>(m, L);
+      if (n_ge > k) {
+        uint32_t lo = L, hi = U + 1u;          // count(>= lo) >= k, count(>= hi) < k
+        while (hi - lo > 1u) {
+          const uint32_t mid = (lo + hi) >> 1;
+          const int cnt = count_ge<8 * STEPS>(m, mid);
+          if (cnt >= k) { lo = mid; n_ge = cnt; if (cnt == k) break; } else { hi = mid; }
+        }
+        T = lo;
+      }
+      // ---- selection masks (0xffff per selected half)
+      const __nv_bfloat162 Tb = as_bf162(T | (T << 16));
+      uint32_t sel[STEPS][8];
+      if (n_ge == k) {
+#pragma unroll
+        for (int st = 0; st < STEPS; ++st)
+#pragma unroll
+          for (int j = 0; j < 8; ++j) sel[st][j] = __hge2_mask(as_bf162(m[st * 8 + j]), Tb);
+      } else {
+        // more than k keys are >= T: all keys > T, and the ties in ascending column order
+        int need = k - count_ge<8 * STEPS>(m, T + 1u);
+        int tie_base = 0;
+#pragma unroll
+        for (int st = 0; st < STEPS; ++st) {
+          uint32_t eq[8];
+          int neq = 0;
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            eq[j] = __heq2_mask(as_bf162(m[st * 8 + j]), Tb);
+            neq += __popc(eq[j]) >> 4;
+          }
+          int tot;
+          int rank = tie_base + warp_excl_scan(neq, lane, tot);
+          tie_base += tot;
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            uint32_t take = 0u;
+            if (eq[j] & 0xffffu) { if (rank < need) take |= 0xffffu; ++rank; }
+            if (eq[j] >> 16) { if (rank < need) take |= 0xffff0000u; ++rank; }
+            sel[st][j] = __hgt2_mask(as_bf162(m[st * 8 + j]), Tb) | take;
+          }
+        }
+      }
+      // ---- emit in ascending column order, then zero the selected positions
       int base = 0;
 #pragma unroll
       for (int st = 0; st < STEPS; ++st) {
-        int tot;
-        int slot = base + warp_excl_scan(__popc(sel[st]), lane, tot);
-        base += tot;
-        const int col0 = 16 * (32 * st + lane);
-#pragma unroll
-        for (int e = 0; e < 16; ++e) {
-          if (sel[st] & (1u << e)) {
-            const uint32_t w = xw[st][e >> 1];
-            const uint16_t bits = (e & 1) ? (uint16_t)(w >> 16) : (uint16_t)(w & 0xffffu);
-            if (slot < k) {
-              val_out[row * k + slot] = __ushort_as_bfloat16(bits);
-              col_out[row * k + slot] = (uint16_t)(col0 + e);
-            }
-            ++slot;
-          }
-        }
-        // the selected positions count as zero for the grouped remainder
+        int nsel = 0;
+        uint32_t bits = 0u;       // bit e: element e of this step is selected
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
-          uint32_t keep = 0xffffffffu;
-          if (sel[st] & (1u << (2 * j))) keep &= 0xffff0000u;
-          if (sel[st] & (1u << (2 * j + 1))) keep &= 0x0000ffffu;
-          xw[st][j] &= keep;
+          bits |= (sel[st][j] & 1u) << (2 * j);
+          bits |= (sel[st][j] >> 31) << (2 * j + 1);
         }
+        nsel = __popc(bits);
+        int tot;
+        int slot = base + warp_excl_scan(nsel, lane, tot);
+        base += tot;
+        const int col0 = 16 * (32 * st + lane);
+        while (bits) {
+          const int e = __ffs(bits) - 1;
+          bits &= bits - 1u;
+          // element e of the step: register e/2, half e%2 (dynamic register choice via selects)
+          uint32_t w = xw[st][0];
+#pragma unroll
+          for (int j = 1; j < 8; ++j) w = ((e >> 1) == j) ? xw[st][j] : w;
+          const uint16_t vb = (e & 1) ? (uint16_t)(w >> 16) : (uint16_t)(w & 0xffffu);
+          if (slot < k) {
+            val_out[row * k + slot] = __ushort_as_bfloat16(vb);
+            col_out[row * k + slot] = (uint16_t)(col0 + e);
+          }
+          ++slot;
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) xw[st][j] &= ~sel[st][j];
       }
     }
 
@@ -348,6 +399,15 @@ topk_restore_kernel(const __nv_bfloat16* __restrict__ val, const uint16_t* __res
   const int steps = (S + 511) / 512;
   const int64_t qld = (int64_t)S * QBIT / 8, gld = S / 64;
   for (int64_t row = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5); row < rows; row += (int64_t)gridDim.x * 8) {
+    // the outlier list of the row is fetched first so that its latency overlaps the de-quantization
+    constexpr int PRE = 4;
+    uint16_t pc[PRE], pv[PRE];
+#pragma unroll
+    for (int i = 0; i < PRE; ++i) {
+      const int j = lane + 32 * i;
+      pc[i] = 0; pv[i] = 0;
+      if (j < k) { pc[i] = colv[row * k + j]; pv[i] = __bfloat16_as_ushort(val[row * k + j]); }
+    }
     for (int st = 0; st < steps; ++st) {
       const int lane_g = 32 * st + lane;
       const int col = 16 * lane_g;
@@ -361,7 +421,12 @@ topk_restore_kernel(const __nv_bfloat16* __restrict__ val, const uint16_t* __res
       }
     }
     __syncwarp();   // orders this warp's row stores before the overwrites below
-    for (int j = lane; j < k; j += 32) ao[row * S + colv[row * k + j]] = val[row * k + j];
+#pragma unroll
+    for (int i = 0; i < PRE; ++i) {
+      const int j = lane + 32 * i;
+      if (j < k) ao[row * S + pc[i]] = __ushort_as_bfloat16(pv[i]);
+    }
+    for (int j = lane + 32 * PRE; j < k; j += 32) ao[row * S + colv[row * k + j]] = val[row * k + j];
   }
 }
 

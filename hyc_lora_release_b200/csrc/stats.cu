@@ -53,7 +53,8 @@ colstats_kernel(const __nv_bfloat16* __restrict__ x0, int M, int N, int64_t ldx,
         // zero point from the unguarded scale: -round_half_even(bf16(min / scale)) - 2^(q-1), as int8
         float zq = bf16_round(__fdiv_rn(b, sc));
         float zz = bf16_round(-rintf(zq) - (float)(1 << (q_bit - 1)));
-        zz = fminf(fmaxf(zz, -128.f), 127.f);
+        // the reference casts the bf16 value to int8, which wraps when a column's minimum is positive
+        zz = fminf(fmaxf(zz, -2.0e9f), 2.0e9f);
         zp_out[col] = (int8_t)(int)zz;
       }
       if (oidx != nullptr && sc == 0.f) sc = bf16_round(0.f + 1e-3f);

@@ -165,6 +165,8 @@ def _quant(x, s, q_bit, z=None, channel=None):
         idx = channel.to(device=x.device, dtype=torch.int64).contiguous()
         k = idx.numel()
         xo = torch.empty((B, M, k), dtype=BF16, device=x.device)
+    if rows == 0:
+        return q, xo
     check(lib.hyc_quant_pack(ptr(xr), rows, N, ld, ptr(s), ptr(zt), ptr(idx) if k else None, k, ptr(q),
                              ptr(xo) if k else None, q_bit, stream_of(x)), "hyc_quant_pack")
     return q, xo
@@ -181,6 +183,8 @@ def _dequant(q, s, q_bit, z=None, channel=None, x_outlier=None):
     if z is not None:
         zt = z.reshape(-1).to(torch.int8).contiguous()
     x = torch.empty((B, M, N), dtype=BF16, device=q.device)
+    if B * M == 0:
+        return x
     k, idx, xo = 0, None, None
     if channel is not None:
         idx = channel.to(device=q.device, dtype=torch.int64).contiguous()

@@ -1,29 +1,33 @@
 """GROUP-mode quantizer oracle (test infrastructure; see package docstring).
 
-GROUP mode has no counterpart in the reference: the reference computes one
-scale per hidden column from batch sample 0 (compress_function.py:45-59).
-This mode applies the same min/max scale + zero-point arithmetic
-(compress_function.py:62-77; compress_function_kernel.py:279-299, 376-387) to
-every 64-wide group along the last dimension, with the statistics taken from
-the group itself.  This file is the specification; **parity unpinned**.
+GROUP mode has no counterpart in the reference: the reference computes one scale per
+hidden column from batch sample 0 (compress_function.py:45-59).  This mode takes scale
+and zero point from every 64-wide group of a row, in the spirit of the reference's
+zero-point variant (compress_function.py:62-77; compress_function_kernel.py:279-299,
+376-387) but with arithmetic chosen so that a GPU can do it in one pass at memory speed:
+a reciprocal multiply instead of a divide and round-half-to-even (``torch.round``)
+instead of ``roundf``.  This file is the specification; **parity unpinned**.
 
-Definition, per group g of 64 consecutive values of one row (bf16 in):
-  mn, mx   = min, max of the group
-  s        = bf16( f32( bf16(mx - mn) ) / (2^q - 1) );   s = bf16(1e-3) if s == 0
-  z        = clamp( -roundf( f32(mn) / f32(s) ) - 2^(q-1), -128, 127 )   (int8)
-  code     = clamp( roundf( f32(x) / f32(s) + z ), -2^(q-1), 2^(q-1)-1 ) + 2^(q-1)
-  x_hat    = bf16( bf16( bf16(code - 2^(q-1)) - z ) * s )
-with fp32 IEEE division, roundf = halves away from zero, and the reference's
-interleaved 32-column byte layout for the codes.
+Definition, per group of 64 consecutive values of one row (bf16 in, all arithmetic fp32
+with one rounding per operation unless a bf16 rounding is written out):
+  mn, mx  = min, max of the group
+  d       = bf16(mx - mn)
+  s       = bf16(d * (1 / levels)),  levels = 2^q - 1;   s = bf16(1e-3) if s == 0
+  rc      = 1 / s
+  z       = clamp( rint(clamp(-mn * rc, -300, 300)) - 2^(q-1), -128, 127 )      (int8)
+  code    = rint( clamp( x * rc + (z + 2^(q-1)), 0, levels ) )                   (unsigned)
+  x_hat   = bf16( (code - 2^(q-1) - z) * s )
+rint = round half to even.  The codes use the reference's interleaved 32-column bytes.
 """
 import torch
-from .quant import roundf_half_away, ref_pack, ref_unpack
+from .quant import ref_pack, ref_unpack
 
 __all__ = ["GROUP", "group_stats", "group_quant_codes", "group_compress",
            "group_decompress"]
 
 GROUP = 64
 BF16 = torch.bfloat16
+F32 = torch.float32
 
 
 def group_stats(x: torch.Tensor, q_bit: int):
@@ -31,21 +35,25 @@ def group_stats(x: torch.Tensor, q_bit: int):
     *lead, n = x.shape
     assert n % GROUP == 0
     xg = x.to(BF16).reshape(*lead, n // GROUP, GROUP)
-    mx = xg.max(dim=-1).values
-    mn = xg.min(dim=-1).values
-    s = ((mx - mn).to(BF16).float() / float(2 ** q_bit - 1)).to(BF16)
+    mx = xg.max(dim=-1).values.float()
+    mn = xg.min(dim=-1).values.float()
+    inv_levels = torch.tensor(1.0, dtype=F32) / float(2 ** q_bit - 1)
+    d = (mx - mn).to(BF16).float()
+    s = (d * inv_levels).to(BF16)
     s = torch.where(s == 0, torch.tensor(1e-3, dtype=BF16), s)
+    rc = 1.0 / s.float()
     half = 2 ** (q_bit - 1)
-    z = (-roundf_half_away(mn.float() / s.float()) - half).clamp(-128, 127)
+    z = (torch.round((-mn * rc).clamp(-300, 300)) - half).clamp(-128, 127)
     return s, z.to(torch.int8)
 
 
 def group_quant_codes(x, s, z, q_bit: int) -> torch.Tensor:
     *lead, n = x.shape
     xg = x.to(BF16).float().reshape(*lead, n // GROUP, GROUP)
-    r = xg / s.float().unsqueeze(-1) + z.float().unsqueeze(-1)
+    rc = (1.0 / s.float()).unsqueeze(-1)
     half = 2 ** (q_bit - 1)
-    c = roundf_half_away(r).clamp(-half, half - 1) + half
+    u = xg * rc + (z.float() + half).unsqueeze(-1)
+    c = torch.round(torch.nan_to_num(u, nan=0.0).clamp(0, 2 ** q_bit - 1))
     return c.to(torch.uint8).reshape(*lead, n)
 
 
@@ -59,6 +67,5 @@ def group_decompress(packed, s, z, q_bit: int) -> torch.Tensor:
     codes = ref_unpack(packed, q_bit)
     *lead, n = codes.shape
     half = 2 ** (q_bit - 1)
-    v = (codes.float().to(BF16) - half).to(BF16).reshape(*lead, n // GROUP, GROUP)
-    v = (v - z.to(BF16).unsqueeze(-1)).to(BF16)
-    return (v * s.to(BF16).unsqueeze(-1)).to(BF16).reshape(*lead, n)
+    v = (codes.float() - half).reshape(*lead, n // GROUP, GROUP) - z.float().unsqueeze(-1)
+    return (v * s.float().unsqueeze(-1)).to(BF16).reshape(*lead, n)
