@@ -17,29 +17,29 @@ namespace hyc {
 
 constexpr unsigned kFull = 0xffffffffu;
 
-struct GroupParams { float s, rc, zc, z; };   // zc = z + 2^(q-1)
+struct GroupParams { float s, rcl, zcl, z; };
 
-// Group-mode arithmetic (fp32, one rounding per operation; the fused-multiply-add is
-// deliberately not used so that a plain fp32 statement on any machine reproduces it):
-//   d = bf16(mx - mn);  s = bf16(d * (1/levels)), 1e-3 when zero;  rc = 1/s
+// Group-mode arithmetic (fp32, one rounding per operation):
+//   d = bf16(mx - mn);  il = 1/levels;  s = bf16(d * il), 1e-3 when zero;  rc = 1/s
 //   z = clamp(rint(clamp(-mn*rc, +-300)) - half, -128, 127)
-//   code = rint(clamp(x*rc + (z + half), 0, levels))           rint = half to even
-// rint of a value in [0, 2^22) is "add 2^23 in round-to-nearest": the integer lands in
-// the low mantissa bits, so no float->int conversion is issued per element.
+//   u = sat01(fma(x, rc*il, (z + half)*il));   code = rint(u * levels)     rint = half to even
+// Per element that is one saturating fma and one fma with 2^23 as addend (the integer
+// lands in the low mantissa bits): both run on the FMA pipe, no min/max, no conversion.
 template <int QBIT>
 __device__ __forceinline__ GroupParams group_params(float mn, float mx) {
-  constexpr float inv_levels = 1.0f / (float)((1 << QBIT) - 1);
+  constexpr float il = 1.0f / (float)((1 << QBIT) - 1);
   constexpr float half = (float)(1 << (QBIT - 1));
   float d = bf16bits_to_f32(f32_to_bf16bits_rn(__fsub_rn(mx, mn)));
-  float s = bf16bits_to_f32(f32_to_bf16bits_rn(__fmul_rn(d, inv_levels)));
+  float s = bf16bits_to_f32(f32_to_bf16bits_rn(__fmul_rn(d, il)));
   if (s == 0.f) s = bf16bits_to_f32(f32_to_bf16bits_rn(1e-3f));
   GroupParams p;
   p.s = s;
-  p.rc = __frcp_rn(s);
-  float t = fminf(fmaxf(__fmul_rn(-mn, p.rc), -300.f), 300.f);
+  const float rc = __frcp_rn(s);
+  float t = fminf(fmaxf(__fmul_rn(-mn, rc), -300.f), 300.f);
   float zr = __fadd_rn(__fadd_rn(t, 12582912.f), -12582912.f);   // rint, |t| <= 300
   p.z = fminf(fmaxf(zr - half, -128.f), 127.f);
-  p.zc = p.z + half;
+  p.rcl = __fmul_rn(rc, il);
+  p.zcl = __fmul_rn(p.z + half, il);
   return p;
 }
 
@@ -66,9 +66,10 @@ __device__ __forceinline__ void group_minmax(const uint32_t (&xw)[8], float& mn,
 template <int QBIT>
 __device__ __forceinline__ uint32_t group_code_bits(float x, const GroupParams& p) {
   constexpr float levels = (float)((1 << QBIT) - 1);
-  float u = __fadd_rn(__fmul_rn(x, p.rc), p.zc);
-  u = fminf(fmaxf(u, 0.f), levels);
-  return __float_as_uint(__fadd_rn(u, 8388608.f));
+  float u, r;
+  asm("fma.rn.sat.f32 %0, %1, %2, %3;" : "=f"(u) : "f"(x), "f"(p.rcl), "f"(p.zcl));
+  asm("fma.rn.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(u), "f"(levels), "f"(8388608.f));
+  return __float_as_uint(r);
 }
 
 // Quantize the 16 values of a lane and store them in the reference byte layout.
@@ -294,14 +295,20 @@ topk_compress_kernel(const __nv_bfloat16* __restrict__ a, int64_t rows, int S, i
       // ---- exact threshold on the full row: largest T in [L, U] with count(>= T) >= k
       uint32_t T = L;
       int n_ge = count_ge<8 * STEPS>(m, L);
+      // more than k keys >= L: either equal keys at L (then T = L and the tie rule decides), or a
+      // stream held more than two of the k largest (rare; bisect on the whole row above L)
       if (n_ge > k) {
-        uint32_t lo = L, hi = U + 1u;          // count(>= lo) >= k, count(>= hi) < k
-        while (hi - lo > 1u) {
-          const uint32_t mid = (lo + hi) >> 1;
-          const int cnt = count_ge<8 * STEPS>(m, mid);
-          if (cnt >= k) { lo = mid; n_ge = cnt; if (cnt == k) break; } else { hi = mid; }
+        const int n_gt = count_ge<8 * STEPS>(m, L + 1u);
+        if (n_gt >= k) {
+          uint32_t lo = L + 1u, hi = U + 1u;   // count(>= lo) >= k, count(>= hi) < k
+          n_ge = n_gt;
+          while (n_ge != k && hi - lo > 1u) {
+            const uint32_t mid = (lo + hi) >> 1;
+            const int cnt = count_ge<8 * STEPS>(m, mid);
+            if (cnt >= k) { lo = mid; n_ge = cnt; } else { hi = mid; }
+          }
+          T = lo;
         }
-        T = lo;
       }
       // ---- selection masks (0xffff per selected half)
       const __nv_bfloat162 Tb = as_bf162(T | (T << 16));
@@ -340,14 +347,13 @@ topk_compress_kernel(const __nv_bfloat16* __restrict__ a, int64_t rows, int S, i
       int base = 0;
 #pragma unroll
       for (int st = 0; st < STEPS; ++st) {
-        int nsel = 0;
-        uint32_t bits = 0u;       // bit e: element e of this step is selected
+        // bit e: element e of this step is selected.  A mask register is 0xffff per selected
+        // half, so bit 2j of its low half and bit 2j+1 of its high half are picked out.
+        uint32_t acc = 0u;
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          bits |= (sel[st][j] & 1u) << (2 * j);
-          bits |= (sel[st][j] >> 31) << (2 * j + 1);
-        }
-        nsel = __popc(bits);
+        for (int j = 0; j < 8; ++j) acc |= sel[st][j] & ((1u << (2 * j)) | (1u << (17 + 2 * j)));
+        uint32_t bits = (acc | (acc >> 16)) & 0xffffu;
+        const int nsel = __popc(bits);
         int tot;
         int slot = base + warp_excl_scan(nsel, lane, tot);
         base += tot;

@@ -41,10 +41,10 @@ __device__ __forceinline__ uint16_t f32_to_bf16bits_rn(float a) {
 // RN(x / s) from a correctly rounded reciprocal rc = RN(1/s): one multiply and two
 // fused multiply-adds give the IEEE quotient (checked exhaustively on the host over all
 // bf16 operand pairs; results that differ sit far below 1e-20 and cannot change a code).
-// The first estimate is clamped so that a quotient that overflows stays finite; every
-// caller clamps the result to the code range afterwards.  rc == 0 yields exactly 0.
+// Domain: |x / s| must stay below the fp32 range (an overflowing first estimate would turn
+// into a NaN); every caller clamps the result to the code range.  rc == 0 yields exactly 0.
 __device__ __forceinline__ float quotient_rn(float x, float s, float rc) {
-  float q0 = fminf(fmaxf(x * rc, -300.f), 300.f);
+  float q0 = x * rc;
   float rem = fmaf(-q0, s, x);
   return fmaf(rem, rc, q0);
 }

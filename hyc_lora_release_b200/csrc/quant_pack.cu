@@ -12,7 +12,7 @@
 namespace hyc {
 
 constexpr int kThreads = 256;
-constexpr int kRowUnroll = 4;
+constexpr int kRowUnroll = 2;
 
 template <int QBIT>
 struct Geo {
@@ -27,7 +27,7 @@ struct Geo {
 
 // grid: (col_tiles, row_slots).  Row groups of kRowUnroll rows are dealt round-robin to slots.
 template <int QBIT, bool HAS_ZP>
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(kThreads, (QBIT == 2 || (QBIT == 4 && HAS_ZP)) ? 2 : 4)
 quant_pack_kernel(const __nv_bfloat16* __restrict__ x, int64_t rows, int N, int64_t ldx,
                   const __nv_bfloat16* __restrict__ scale, const int8_t* __restrict__ zp,
                   const int64_t* __restrict__ oidx, int k,
