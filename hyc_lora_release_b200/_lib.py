@@ -9,7 +9,7 @@ LIB_PATH = os.path.join(_HERE, "lib", "libhyc.so")
 
 if not os.path.exists(LIB_PATH):
     raise ImportError(
-        "libhyc.so is not built (%s). Build it with `python -m hyc_lora_release_b200.build`; "
+        "libhyc.so is not built (%s). Build it with `python hyc_lora_release_b200/build.py`; "
         "there is no fallback implementation." % LIB_PATH)
 
 lib = ctypes.CDLL(LIB_PATH)
@@ -37,6 +37,11 @@ SIGNATURES = {
     "hyc_rmsnorm_fwd": (_i, [_p, _p, _f, _p, _p, _l, _i, _p]),
     "hyc_rmsnorm_bwd": (_i, [_p, _p, _p, _p, _p, _l, _i, _p]),
     "hyc_softmax_bwd": (_i, [_p, _p, _p, _l, _i, _p]),
+    "hyc_gemm_bf16_tcgen05": (_i, [_p, _p, _i, _i, _i, _i, _p, _p, _i, _p, _p, _l, _l, _p, _p, _l, _l, _p, _p, _p, _p]),
+    "hyc_mlp_gateup_fwd_tcgen05": (_i, [_p, _p, _p, _i, _i, _i, _p, _p, _l, _l, _p, _p, _l, _l,
+                                        _p, _p, _p, _p, _p, _p, _p, _i, _p, _p]),
+    "hyc_mlp_graddown_bwd_tcgen05": (_i, [_p, _p, _i, _i, _i, _p, _p, _l, _l, _p, _p, _l, _l, _p, _p, _l, _l,
+                                          _p, _p, _p, _p, _p, _p, _p, _i, _p, _p]),
 }
 
 for _name, (_res, _args) in SIGNATURES.items():

@@ -1,6 +1,6 @@
 """Build lib/libhyc.so (sm_100a) from csrc/*.cu with nvcc.
 
-    python -m hyc_lora_release_b200.build [--force]
+    python hyc_lora_release_b200/build.py [--force] [-v]
 
 Objects go to csrc/build/, the shared library to lib/.  Both are kept out of version
 control; the library is what the Python layer loads through ctypes.

@@ -1,0 +1,702 @@
+// tcgen05 / TMEM GEMMs of the LoRA MLP with the activation-compression work in the epilogue.
+//
+// One persistent kernel, three epilogues:
+//   STORE    : D = A * B (+ rank-16 LoRA terms, + residual), bf16 out.  Down projection, grad_x.
+//   GATEUP   : [gate_main | up_main] tile = x * [Wg ; Wu]^T, then per element: quantize-and-pack
+//              both main branches, add the LoRA terms, SiLU, Hadamard product (forward).
+//   GRADDOWN : grad_down tile = g * Wd (+ LoRA), then per element: unpack-dequantize the saved
+//              gate/up codes, recompute the forward, emit hadamard, grad_gate, grad_up (backward).
+//
+// Structure of a CTA (320 threads, one CTA per SM, tiles dealt round-robin):
+//   warp 0      : TMA producer; 128x64 A tile and 128x64 B tile per stage (128-byte swizzle),
+//                 5 stages, mbarrier full/empty pairs.
+//   warp 1      : allocates 256 TMEM columns (two 128x128 fp32 accumulators), issues
+//                 tcgen05.mma (M128 N128 K16, bf16 -> fp32) from one lane, commits to mbarriers.
+//   warps 2..9  : epilogue.  Warp w reads TMEM lanes 32*(w%4).. (tcgen05.ld 32x32b.x32) for half of
+//                 the tile's columns, so the epilogue of tile i overlaps the MMAs of tile i+1.
+// The B operand is either K-major ([N,K] row-major, the forward weights) or MN-major ([K,N]
+// row-major: the same weights read for the backward products, no transposed copy).
+// Every wait is bounded: when a limit is hit the kernel records a code in *status and drains.
+// No cluster launch and no multicast: each CTA fetches its own tiles.
+#include "hyc_common.cuh"
+#include <cuda.h>
+
+namespace hyc {
+namespace tc {
+
+constexpr int BM = 128, BN = 128, BK = 64;
+constexpr int STAGES = 5;
+constexpr int STAGE_A_BYTES = BM * BK * 2;
+constexpr int STAGE_B_BYTES = BN * BK * 2;
+constexpr int STAGE_BYTES = STAGE_A_BYTES + STAGE_B_BYTES;
+constexpr int EPI_WARPS = 8;
+constexpr int THREADS = 64 + 32 * EPI_WARPS;
+constexpr int TMEM_COLS = 256;
+constexpr int EPI_SMEM_BYTES = 3 * 128 * 16 * 4 + 4 * 128 * 4;   // three fp32 LoRA tiles + four float vectors
+constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + EPI_SMEM_BYTES + 256;
+constexpr uint32_t SPIN_LIMIT = 1u << 22;
+
+enum { EPI_STORE = 0, EPI_GATEUP = 1, EPI_GRADDOWN = 2 };
+enum { ST_OK = 0, ST_TIMEOUT_PRODUCER = 1, ST_TIMEOUT_MMA = 2, ST_TIMEOUT_EPILOGUE = 3 };
+
+struct LoraTerm {
+  const __nv_bfloat16* xa;    // [M, 16] row-major, or null
+  const __nv_bfloat16* bt;    // element (col, r) at bt[col * ld_col + r * ld_r]
+  int64_t ld_col, ld_r;
+};
+
+struct Params {
+  int M, N, K1, K2;           // K2 > 0: a second (A2, B2) pair is accumulated into the same tile
+  int epi, q_bit;
+  LoraTerm l0, l1, l2;        // STORE: l0/l1 added; GATEUP: l0 gate, l1 up; GRADDOWN: l0 grad LoRA, l1 gate, l2 up
+  const __nv_bfloat16* residual;   // STORE, [M, N] or null
+  __nv_bfloat16* out0;        // STORE: D ; GATEUP: o ; GRADDOWN: o (hadamard)
+  __nv_bfloat16* out1;        // GRADDOWN: grad_gate
+  __nv_bfloat16* out2;        // GRADDOWN: grad_up
+  __nv_bfloat16* dbg1;        // GATEUP: optional bf16 copy of gate_main
+  __nv_bfloat16* dbg2;        // GATEUP: optional bf16 copy of up_main
+  uint8_t* q1;                // GATEUP: out ; GRADDOWN: in
+  uint8_t* q2;
+  const __nv_bfloat16* s1;    // per-channel scales [N]
+  const __nv_bfloat16* s2;
+  int* status;
+};
+
+// ------------------------------------------------------------------ PTX wrappers
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+  return ok != 0;
+}
+// bounded wait; false = gave up (either the limit was hit here or another role raised abort)
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  for (uint32_t i = 0; i < SPIN_LIMIT; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((i & 63u) == 63u && *abort_flag) return false;
+  }
+  return false;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&v)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+        "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+        "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
+        "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+      : "r"(taddr) : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// shared-memory matrix descriptor, 128-byte swizzle, descriptor version 1
+__device__ __forceinline__ uint64_t make_desc(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr & 0x3ffffu) >> 4);
+  d |= (uint64_t)(lbo_bytes >> 4) << 16;
+  d |= (uint64_t)(sbo_bytes >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+
+__device__ __forceinline__ void epi_bar_sync() { asm volatile("bar.sync 1, %0;" ::"n"(32 * EPI_WARPS) : "memory"); }
+
+__device__ __forceinline__ float bfr(float v) { return bf16bits_to_f32(f32_to_bf16bits_rn(v)); }
+
+// dot of the thread's LoRA-A row (16 floats) with the fp32 LoRA-B row of a column in shared memory
+__device__ __forceinline__ float lora_dot(const float (&xa)[16], const float* __restrict__ brow) {
+  const float4 b0 = *reinterpret_cast<const float4*>(brow), b1 = *reinterpret_cast<const float4*>(brow + 4);
+  const float4 b2 = *reinterpret_cast<const float4*>(brow + 8), b3 = *reinterpret_cast<const float4*>(brow + 12);
+  float a = xa[0] * b0.x;
+  a = fmaf(xa[1], b0.y, a); a = fmaf(xa[2], b0.z, a); a = fmaf(xa[3], b0.w, a);
+  a = fmaf(xa[4], b1.x, a); a = fmaf(xa[5], b1.y, a); a = fmaf(xa[6], b1.z, a); a = fmaf(xa[7], b1.w, a);
+  a = fmaf(xa[8], b2.x, a); a = fmaf(xa[9], b2.y, a); a = fmaf(xa[10], b2.z, a); a = fmaf(xa[11], b2.w, a);
+  a = fmaf(xa[12], b3.x, a); a = fmaf(xa[13], b3.y, a); a = fmaf(xa[14], b3.z, a); a = fmaf(xa[15], b3.w, a);
+  return a;
+}
+
+__device__ __forceinline__ void load_xa_row(const __nv_bfloat16* xa, int64_t row, bool valid, float (&out)[16]) {
+  uint4 u = make_uint4(0u, 0u, 0u, 0u), v = u;
+  if (valid && xa != nullptr) {
+    u = *reinterpret_cast<const uint4*>(xa + row * 16);
+    v = *reinterpret_cast<const uint4*>(xa + row * 16 + 8);
+  }
+  const uint32_t w[8] = {u.x, u.y, u.z, u.w, v.x, v.y, v.z, v.w};
+#pragma unroll
+  for (int j = 0; j < 8; ++j) { out[2 * j] = bf16lo_to_f32(w[j]); out[2 * j + 1] = bf16hi_to_f32(w[j]); }
+}
+
+// cooperative staging of a LoRA-B tile (ncols x 16) as fp32 into shared memory
+__device__ __forceinline__ void stage_lora_tile(const LoraTerm& t, int n0, int ncols, float* dst, int et) {
+  if (t.bt == nullptr) return;
+  for (int i = et; i < ncols * 16; i += 32 * EPI_WARPS) {
+    const int c = i >> 4, r = i & 15;
+    dst[i] = __bfloat162float(t.bt[(int64_t)(n0 + c) * t.ld_col + (int64_t)r * t.ld_r]);
+  }
+}
+
+struct SiluTerms { float y1, sig, y1s, y2, o; };
+__device__ __forceinline__ SiluTerms silu_terms(float x1, float l1, float x2, float l2) {
+  SiluTerms r;
+  r.y1 = bfr(x1 + bfr(l1));
+  r.sig = bfr(1.f / (1.f + __expf(-r.y1)));
+  r.y1s = bfr(r.y1 * r.sig);
+  r.y2 = bfr(x2 + bfr(l2));
+  r.o = bfr(r.y1s * r.y2);
+  return r;
+}
+
+// The reference byte layout of a 32-column block: byte j carries, at bit QBIT*i, the code of
+// column j + i*SLAB (SLAB = 32/EPP columns, EPP = 8/QBIT).  A block is SLAB bytes = NW words.
+template <int QBIT> struct BlockGeo {
+  static constexpr int EPP = 8 / QBIT, SLAB = 32 / EPP, NW = SLAB / 4;
+  static constexpr uint32_t CM = (1u << QBIT) - 1u;
+};
+
+template <int QBIT>
+__device__ __forceinline__ void put_code(uint32_t (&words)[BlockGeo<QBIT>::NW], int c, uint32_t code) {
+  using G = BlockGeo<QBIT>;
+  const int j = c % G::SLAB, i = c / G::SLAB;
+  words[j >> 2] |= code << (8 * (j & 3) + QBIT * i);
+}
+template <int QBIT>
+__device__ __forceinline__ uint32_t get_code(const uint32_t (&words)[BlockGeo<QBIT>::NW], int c) {
+  using G = BlockGeo<QBIT>;
+  const int j = c % G::SLAB, i = c / G::SLAB;
+  return (words[j >> 2] >> (8 * (j & 3) + QBIT * i)) & G::CM;
+}
+template <int QBIT>
+__device__ __forceinline__ void store_block_words(uint8_t* dst, const uint32_t (&w)[BlockGeo<QBIT>::NW]) {
+  if constexpr (QBIT == 8) {
+    *reinterpret_cast<uint4*>(dst) = make_uint4(w[0], w[1], w[2], w[3]);
+    *reinterpret_cast<uint4*>(dst + 16) = make_uint4(w[4], w[5], w[6], w[7]);
+  } else if constexpr (QBIT == 4) {
+    *reinterpret_cast<uint4*>(dst) = make_uint4(w[0], w[1], w[2], w[3]);
+  } else {
+    *reinterpret_cast<uint2*>(dst) = make_uint2(w[0], w[1]);
+  }
+}
+template <int QBIT>
+__device__ __forceinline__ void load_block_words(const uint8_t* src, bool valid, uint32_t (&w)[BlockGeo<QBIT>::NW]) {
+#pragma unroll
+  for (int i = 0; i < BlockGeo<QBIT>::NW; ++i) w[i] = 0u;
+  if (!valid) return;
+  if constexpr (QBIT == 8) {
+    const uint4 a = *reinterpret_cast<const uint4*>(src), b = *reinterpret_cast<const uint4*>(src + 16);
+    w[0] = a.x; w[1] = a.y; w[2] = a.z; w[3] = a.w; w[4] = b.x; w[5] = b.y; w[6] = b.z; w[7] = b.w;
+  } else if constexpr (QBIT == 4) {
+    const uint4 a = *reinterpret_cast<const uint4*>(src);
+    w[0] = a.x; w[1] = a.y; w[2] = a.z; w[3] = a.w;
+  } else {
+    const uint2 a = *reinterpret_cast<const uint2*>(src);
+    w[0] = a.x; w[1] = a.y;
+  }
+}
+
+__device__ __forceinline__ void store8_bf16(__nv_bfloat16* dst, const float (&v)[8]) {
+  uint4 o;
+  o.x = pack_bf16x2_rn(v[0], v[1]); o.y = pack_bf16x2_rn(v[2], v[3]);
+  o.z = pack_bf16x2_rn(v[4], v[5]); o.w = pack_bf16x2_rn(v[6], v[7]);
+  *reinterpret_cast<uint4*>(dst) = o;
+}
+
+// ------------------------------------------------------------------ epilogues (one 32-column chunk per call)
+// cb = column offset of the chunk inside the tile, ncol0 = first output column of the tile.
+template <int QBIT>
+__device__ __forceinline__ void epi_gateup_block(const Params& p, int64_t row, bool valid, int ncol0, int cb,
+                                                 const uint32_t (&g)[32], const uint32_t (&u)[32],
+                                                 const float (&xa1)[16], const float (&xa2)[16],
+                                                 const float* sB1, const float* sB2, const float* sS1, const float* sR1,
+                                                 const float* sS2, const float* sR2) {
+  using G = BlockGeo<QBIT>;
+  const int64_t n = (int64_t)ncol0 + cb;
+  uint32_t w1[G::NW], w2[G::NW];
+#pragma unroll
+  for (int i = 0; i < G::NW; ++i) { w1[i] = 0u; w2[i] = 0u; }
+#pragma unroll
+  for (int c8 = 0; c8 < 4; ++c8) {
+    float o[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const int c = 8 * c8 + e, tc = cb + c;
+      // the frozen-weight products are bf16 tensors in the reference before anything else touches them
+      const float x1 = bfr(__uint_as_float(g[c])), x2 = bfr(__uint_as_float(u[c]));
+      put_code<QBIT>(w1, c, (uint32_t)(quant_code_signed<QBIT>(x1, sS1[tc], sR1[tc]) + (1 << (QBIT - 1))));
+      put_code<QBIT>(w2, c, (uint32_t)(quant_code_signed<QBIT>(x2, sS2[tc], sR2[tc]) + (1 << (QBIT - 1))));
+      o[e] = silu_terms(x1, lora_dot(xa1, sB1 + tc * 16), x2, lora_dot(xa2, sB2 + tc * 16)).o;
+    }
+    if (valid) store8_bf16(p.out0 + row * p.N + n + 8 * c8, o);
+  }
+  if (valid) {
+    store_block_words<QBIT>(p.q1 + (row * p.N + n) * QBIT / 8, w1);
+    store_block_words<QBIT>(p.q2 + (row * p.N + n) * QBIT / 8, w2);
+    if (p.dbg1 != nullptr) {
+#pragma unroll
+      for (int c8 = 0; c8 < 4; ++c8) {
+        float a[8], b[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) { a[e] = __uint_as_float(g[8 * c8 + e]); b[e] = __uint_as_float(u[8 * c8 + e]); }
+        store8_bf16(p.dbg1 + row * p.N + n + 8 * c8, a);
+        store8_bf16(p.dbg2 + row * p.N + n + 8 * c8, b);
+      }
+    }
+  }
+}
+
+template <int QBIT>
+__device__ __forceinline__ void epi_graddown_block(const Params& p, int64_t row, bool valid, int ncol0, int cb,
+                                                   const uint32_t (&acc)[32], const float (&xg)[16],
+                                                   const float (&xa1)[16], const float (&xa2)[16],
+                                                   const float* sBd, const float* sB1, const float* sB2,
+                                                   const float* sS1, const float* sS2) {
+  using G = BlockGeo<QBIT>;
+  constexpr float HALF = (float)(1 << (QBIT - 1));
+  const int64_t n = (int64_t)ncol0 + cb;
+  uint32_t w1[G::NW], w2[G::NW];
+  load_block_words<QBIT>(p.q1 + (row * p.N + n) * QBIT / 8, valid, w1);
+  load_block_words<QBIT>(p.q2 + (row * p.N + n) * QBIT / 8, valid, w2);
+#pragma unroll
+  for (int c8 = 0; c8 < 4; ++c8) {
+    float o[8], gg[8], gu[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const int c = 8 * c8 + e, tc = cb + c;
+      float gd = bfr(__uint_as_float(acc[c]));
+      if (p.l0.bt != nullptr) gd = bfr(gd + bfr(lora_dot(xg, sBd + tc * 16)));
+      const float x1 = bfr(((float)get_code<QBIT>(w1, c) - HALF) * sS1[tc]);
+      const float x2 = bfr(((float)get_code<QBIT>(w2, c) - HALF) * sS2[tc]);
+      const SiluTerms t = silu_terms(x1, lora_dot(xa1, sB1 + tc * 16), x2, lora_dot(xa2, sB2 + tc * 16));
+      o[e] = t.o;
+      const float gh1 = bfr(gd * t.y2);
+      gu[e] = bfr(gd * t.y1s);
+      const float inner = bfr(1.f + bfr(t.y1 * bfr(1.f - t.sig)));
+      gg[e] = bfr(gh1 * bfr(t.sig * inner));
+    }
+    if (valid) {
+      store8_bf16(p.out0 + row * p.N + n + 8 * c8, o);
+      store8_bf16(p.out1 + row * p.N + n + 8 * c8, gg);
+      store8_bf16(p.out2 + row * p.N + n + 8 * c8, gu);
+    }
+  }
+}
+
+__device__ __forceinline__ void epi_store_block(const Params& p, int64_t row, bool valid, int ncol0, int cb,
+                                                const uint32_t (&acc)[32], const float (&xa0)[16], const float (&xa1)[16],
+                                                const float* sB0, const float* sB1) {
+  const int64_t n = (int64_t)ncol0 + cb;
+#pragma unroll
+  for (int c8 = 0; c8 < 4; ++c8) {
+    float o[8], r[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) r[e] = 0.f;
+    const bool has_res = p.residual != nullptr && valid;
+    if (has_res) {
+      const uint4 q = *reinterpret_cast<const uint4*>(p.residual + row * p.N + n + 8 * c8);
+      r[0] = bf16lo_to_f32(q.x); r[1] = bf16hi_to_f32(q.x); r[2] = bf16lo_to_f32(q.y); r[3] = bf16hi_to_f32(q.y);
+      r[4] = bf16lo_to_f32(q.z); r[5] = bf16hi_to_f32(q.z); r[6] = bf16lo_to_f32(q.w); r[7] = bf16hi_to_f32(q.w);
+    }
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const int c = 8 * c8 + e, tc = cb + c;
+      float v = bfr(__uint_as_float(acc[c]));
+      if (p.l0.bt != nullptr) v = bfr(v + bfr(lora_dot(xa0, sB0 + tc * 16)));
+      if (p.l1.bt != nullptr) v = bfr(v + bfr(lora_dot(xa1, sB1 + tc * 16)));
+      if (has_res) v = bfr(v + r[e]);
+      o[e] = v;
+    }
+    if (valid) store8_bf16(p.out0 + row * p.N + n + 8 * c8, o);
+  }
+}
+
+// ------------------------------------------------------------------ the kernel
+template <int EPI, int QBIT, bool B_MN>
+__global__ void __launch_bounds__(THREADS, 1)
+mlp_gemm_kernel(const __grid_constant__ CUtensorMap mapA1, const __grid_constant__ CUtensorMap mapB1,
+                const __grid_constant__ CUtensorMap mapA2, const __grid_constant__ CUtensorMap mapB2,
+                const Params p) {
+  extern __shared__ uint8_t smem_raw[];
+  // 1024-byte alignment for the 128-byte swizzle atoms
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint8_t* stage_base = smem;
+  float* epi_f = reinterpret_cast<float*>(smem + STAGES * STAGE_BYTES);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES + EPI_SMEM_BYTES);
+  uint64_t* full = bars;                       // [STAGES]
+  uint64_t* empty = bars + STAGES;             // [STAGES]
+  uint64_t* tmem_full = bars + 2 * STAGES;     // [2]
+  uint64_t* tmem_empty = bars + 2 * STAGES + 2;  // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tiles_m = (p.M + BM - 1) / BM;
+  constexpr int TILE_N = (EPI == EPI_GATEUP) ? 64 : BN;     // output columns per tile
+  const int tiles_n = p.N / TILE_N;
+  const int num_tiles = tiles_m * tiles_n;
+  const int kb1 = p.K1 / BK, kb_total = (p.K1 + p.K2) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+    for (int b = 0; b < 2; ++b) { mbar_init(&tmem_full[b], 1); mbar_init(&tmem_empty[b], EPI_WARPS); }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * TILE_N;
+        for (int kb = 0; kb < kb_total; ++kb) {
+          if (!mbar_wait(&empty[stage], phase ^ 1u, abort_flag)) {
+            if (!*abort_flag) { *abort_flag = 1; atomicExch(p.status, ST_TIMEOUT_PRODUCER); }
+            ok = false;
+            break;
+          }
+          const bool seg2 = kb >= kb1;
+          const CUtensorMap* ma = seg2 ? &mapA2 : &mapA1;
+          const CUtensorMap* mb = seg2 ? &mapB2 : &mapB1;
+          const int k0 = (seg2 ? kb - kb1 : kb) * BK;
+          const uint32_t sa = smem_u32(stage_base + stage * STAGE_BYTES);
+          const uint32_t sb = sa + STAGE_A_BYTES;
+          mbar_expect_tx(&full[stage], STAGE_BYTES);
+          tma_load_2d(sa, ma, &full[stage], k0, m0);
+          if (EPI == EPI_GATEUP) {
+            // 64 rows of Wg then 64 rows of Wu: one K-major 128-row B tile
+            tma_load_2d(sb, &mapB1, &full[stage], k0, n0);
+            tma_load_2d(sb + 64 * BK * 2, &mapB2, &full[stage], k0, n0);
+          } else if (B_MN) {
+            // [K, N] row-major: two boxes of 64 k-rows x 64 columns
+            tma_load_2d(sb, mb, &full[stage], n0, k0);
+            tma_load_2d(sb + 64 * 128, mb, &full[stage], n0 + 64, k0);
+          } else {
+            tma_load_2d(sb, mb, &full[stage], k0, n0);
+            tma_load_2d(sb + 64 * BK * 2, mb, &full[stage], k0, n0 + 64);
+          }
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      // instruction descriptor: fp32 accumulate, bf16 x bf16, M = 128, N = 128, B major as given
+      const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((B_MN ? 1u : 0u) << 16) |
+                             ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+      int stage = 0;
+      uint32_t phase = 0;
+      int it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++it) {
+        const int buf = it & 1;
+        const uint32_t bphase = (uint32_t)(it >> 1) & 1u;
+        if (!mbar_wait(&tmem_empty[buf], bphase ^ 1u, abort_flag)) {
+          if (!*abort_flag) { *abort_flag = 1; atomicExch(p.status, ST_TIMEOUT_MMA); }
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + (uint32_t)(buf * BN);
+        for (int kb = 0; kb < kb_total; ++kb) {
+          if (!mbar_wait(&full[stage], phase, abort_flag)) {
+            if (!*abort_flag) { *abort_flag = 1; atomicExch(p.status, ST_TIMEOUT_MMA); }
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(stage_base + stage * STAGE_BYTES);
+          const uint32_t sb = sa + STAGE_A_BYTES;
+          const uint64_t adesc = make_desc(sa, 16, 1024);
+          const uint64_t bdesc = B_MN ? make_desc(sb, 64 * 128, 1024) : make_desc(sb, 16, 1024);
+#pragma unroll
+          for (int kk = 0; kk < BK / 16; ++kk) {
+            // K-major: 16 elements = 32 bytes further along the swizzled row; MN-major: 16 k-rows of 128 bytes
+            const uint64_t a = adesc + (uint64_t)(kk * 2);
+            const uint64_t b = bdesc + (uint64_t)(B_MN ? kk * 128 : kk * 2);
+            tc_mma(d_tmem, a, b, idesc, (kb > 0 || kk > 0) ? 1u : 0u);
+          }
+          tc_commit(&empty[stage]);
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+        if (ok) tc_commit(&tmem_full[buf]);
+      }
+    }
+  } else {
+    // ------------------------------------------------ epilogue warps
+    const int et = threadIdx.x - 64;
+    const int quad = warp & 3;
+    const int chalf = (warp - 2) >> 2;
+    float* sB0 = epi_f;                  // [128][16]
+    float* sB1 = epi_f + 128 * 16;
+    float* sB2 = epi_f + 2 * 128 * 16;
+    float* sV = epi_f + 3 * 128 * 16;    // four float vectors of 128
+    int it = 0;
+    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++it) {
+      const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * TILE_N;
+      const int buf = it & 1;
+      const uint32_t bphase = (uint32_t)(it >> 1) & 1u;
+      const int64_t row = (int64_t)m0 + quad * 32 + lane;
+      const bool valid = row < p.M;
+
+      // stage the per-tile LoRA-B rows and scales (previous tile's readers are done: barrier at the end)
+      if (EPI == EPI_STORE) {
+        stage_lora_tile(p.l0, n0, BN, sB0, et);
+        stage_lora_tile(p.l1, n0, BN, sB1, et);
+      } else if (EPI == EPI_GATEUP) {
+        stage_lora_tile(p.l0, n0, 64, sB0, et);
+        stage_lora_tile(p.l1, n0, 64, sB1, et);
+        if (et < 64) {
+          const float a = __bfloat162float(p.s1[n0 + et]), b = __bfloat162float(p.s2[n0 + et]);
+          sV[et] = a; sV[128 + et] = __frcp_rn(a); sV[256 + et] = b; sV[384 + et] = __frcp_rn(b);
+        }
+      } else {
+        stage_lora_tile(p.l0, n0, BN, sB0, et);
+        stage_lora_tile(p.l1, n0, BN, sB1, et);
+        stage_lora_tile(p.l2, n0, BN, sB2, et);
+        if (et < 128) { sV[et] = __bfloat162float(p.s1[n0 + et]); sV[128 + et] = __bfloat162float(p.s2[n0 + et]); }
+      }
+      float xa0[16], xa1[16], xa2[16];
+      load_xa_row(p.l0.xa, row, valid, xa0);
+      load_xa_row(p.l1.xa, row, valid, xa1);
+      if (EPI == EPI_GRADDOWN) load_xa_row(p.l2.xa, row, valid, xa2);
+      epi_bar_sync();
+
+      if (!mbar_wait(&tmem_full[buf], bphase, abort_flag)) {
+        if (!*abort_flag) { *abort_flag = 1; atomicExch(p.status, ST_TIMEOUT_EPILOGUE); }
+        break;
+      }
+      tc_fence_after();
+      const uint32_t t_lane = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(buf * BN);
+      if (EPI == EPI_GATEUP) {
+        uint32_t g[32], u[32];
+        tc_ld32(t_lane + (uint32_t)(32 * chalf), g);
+        tc_ld32(t_lane + (uint32_t)(64 + 32 * chalf), u);
+        epi_gateup_block<QBIT>(p, row, valid, n0, 32 * chalf, g, u, xa0, xa1, sB0, sB1, sV, sV + 128, sV + 256, sV + 384);
+      } else {
+#pragma unroll 1
+        for (int ch = 0; ch < 2; ++ch) {
+          uint32_t acc[32];
+          const int cb = 64 * chalf + 32 * ch;
+          tc_ld32(t_lane + (uint32_t)cb, acc);
+          if (EPI == EPI_STORE) epi_store_block(p, row, valid, n0, cb, acc, xa0, xa1, sB0, sB1);
+          else epi_graddown_block<QBIT>(p, row, valid, n0, cb, acc, xa0, xa1, xa2, sB0, sB1, sB2, sV, sV + 128);
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tmem_empty[buf]);
+      epi_bar_sync();    // everyone is done with the staged tile before the next one overwrites it
+    }
+  }
+
+  // ------------------------------------------------ teardown
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+  }
+}
+
+// ------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) != cudaSuccess ||
+        qres != cudaDriverEntryPointSuccess)
+      return nullptr;
+    fn = reinterpret_cast<EncodeTiledFn>(sym);
+  }
+  return fn;
+}
+
+// row-major bf16 matrix [rows, cols] (cols contiguous), box = 64 columns x box_rows rows, 128-byte swizzle
+static bool make_map(CUtensorMap* m, const void* ptr, int64_t rows, int64_t cols, int box_rows) {
+  EncodeTiledFn enc = get_encode();
+  if (!enc) return false;
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
+  cuuint32_t box[2] = {64u, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1u, 1u};
+  return enc(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int EPI, int QBIT, bool B_MN>
+static int launch(const CUtensorMap& a1, const CUtensorMap& b1, const CUtensorMap& a2, const CUtensorMap& b2,
+                  const Params& p, cudaStream_t st) {
+  auto kern = mlp_gemm_kernel<EPI, QBIT, B_MN>;
+  static bool attr = false;
+  if (!attr) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess) {
+      hyc_set_last_cuda_error((int)cudaGetLastError());
+      return HYC_ERR_LAUNCH;
+    }
+    attr = true;
+  }
+  constexpr int TILE_N = (EPI == EPI_GATEUP) ? 64 : BN;
+  const int tiles = ((p.M + BM - 1) / BM) * (p.N / TILE_N);
+  const int grid = tiles < kNumSMs ? tiles : kNumSMs;
+  kern<<<grid, THREADS, SMEM_BYTES, st>>>(a1, b1, a2, b2, p);
+  HYC_CHECK_LAUNCH();
+  return HYC_OK;
+}
+
+}  // namespace tc
+}  // namespace hyc
+
+using namespace hyc;
+using namespace hyc::tc;
+
+static LoraTerm make_term(const void* xa, const void* bt, int64_t ld_col, int64_t ld_r) {
+  LoraTerm t;
+  t.xa = (const __nv_bfloat16*)xa;
+  t.bt = (const __nv_bfloat16*)bt;
+  t.ld_col = ld_col;
+  t.ld_r = ld_r;
+  return t;
+}
+
+extern "C" HYC_API int hyc_gemm_bf16_tcgen05(
+    const void* A, const void* B, int M, int N, int K, int b_is_kn,
+    const void* A2, const void* B2, int K2,
+    const void* xa0, const void* bt0, int64_t bt0_ld_col, int64_t bt0_ld_r,
+    const void* xa1, const void* bt1, int64_t bt1_ld_col, int64_t bt1_ld_r,
+    const void* residual, void* D, int* status, void* stream) {
+  if (!A || !B || !D || !status) return HYC_ERR_NULL;
+  if ((K2 > 0) != (A2 != nullptr && B2 != nullptr)) return HYC_ERR_NULL;
+  if (M <= 0 || N <= 0 || K <= 0 || N % BN != 0 || K % BK != 0 || K2 < 0 || K2 % BK != 0) return HYC_ERR_SHAPE;
+  if (!aligned(A, 16) || !aligned(B, 16) || !aligned(D, 16) || (residual && !aligned(residual, 16)) ||
+      (xa0 && !aligned(xa0, 16)) || (xa1 && !aligned(xa1, 16))) return HYC_ERR_ALIGN;
+  if ((bt0 != nullptr) != (xa0 != nullptr) || (bt1 != nullptr) != (xa1 != nullptr)) return HYC_ERR_NULL;
+  CUtensorMap a1, b1, a2, b2;
+  bool ok = make_map(&a1, A, M, K, BM);
+  ok = ok && (b_is_kn ? make_map(&b1, B, K, N, 64) : make_map(&b1, B, N, K, 64));
+  if (K2 > 0) {
+    ok = ok && make_map(&a2, A2, M, K2, BM);
+    ok = ok && (b_is_kn ? make_map(&b2, B2, K2, N, 64) : make_map(&b2, B2, N, K2, 64));
+  } else {
+    a2 = a1; b2 = b1;
+  }
+  if (!ok) return HYC_ERR_UNSUPPORTED;
+  Params p = {};
+  p.M = M; p.N = N; p.K1 = K; p.K2 = K2; p.epi = EPI_STORE; p.q_bit = 0;
+  p.l0 = make_term(xa0, bt0, bt0_ld_col, bt0_ld_r);
+  p.l1 = make_term(xa1, bt1, bt1_ld_col, bt1_ld_r);
+  p.l2 = make_term(nullptr, nullptr, 0, 0);
+  p.residual = (const __nv_bfloat16*)residual;
+  p.out0 = (__nv_bfloat16*)D;
+  p.status = status;
+  cudaStream_t st = (cudaStream_t)stream;
+  return b_is_kn ? launch<EPI_STORE, 4, true>(a1, b1, a2, b2, p, st) : launch<EPI_STORE, 4, false>(a1, b1, a2, b2, p, st);
+}
+
+extern "C" HYC_API int hyc_mlp_gateup_fwd_tcgen05(
+    const void* x, const void* wg, const void* wu, int T, int H, int I,
+    const void* xa1, const void* b1t, int64_t b1_ld_col, int64_t b1_ld_r,
+    const void* xa2, const void* b2t, int64_t b2_ld_col, int64_t b2_ld_r,
+    const void* s1, const void* s2, void* q1, void* q2, void* o, void* main1_or_null, void* main2_or_null,
+    int q_bit, int* status, void* stream) {
+  if (!x || !wg || !wu || !xa1 || !b1t || !xa2 || !b2t || !s1 || !s2 || !q1 || !q2 || !o || !status) return HYC_ERR_NULL;
+  if (q_bit != 2 && q_bit != 4 && q_bit != 8) return HYC_ERR_QBIT;
+  if (T <= 0 || H <= 0 || I <= 0 || I % 64 != 0 || H % BK != 0) return HYC_ERR_SHAPE;
+  const void* al[] = {x, wg, wu, xa1, xa2, q1, q2, o};
+  for (const void* q : al) if (!aligned(q, 16)) return HYC_ERR_ALIGN;
+  CUtensorMap a1, bg, bu;
+  if (!make_map(&a1, x, T, H, BM) || !make_map(&bg, wg, I, H, 64) || !make_map(&bu, wu, I, H, 64)) return HYC_ERR_UNSUPPORTED;
+  Params p = {};
+  p.M = T; p.N = I; p.K1 = H; p.K2 = 0; p.epi = EPI_GATEUP; p.q_bit = q_bit;
+  p.l0 = make_term(xa1, b1t, b1_ld_col, b1_ld_r);
+  p.l1 = make_term(xa2, b2t, b2_ld_col, b2_ld_r);
+  p.l2 = make_term(nullptr, nullptr, 0, 0);
+  p.out0 = (__nv_bfloat16*)o;
+  p.dbg1 = (__nv_bfloat16*)main1_or_null; p.dbg2 = (__nv_bfloat16*)main2_or_null;
+  p.q1 = (uint8_t*)q1; p.q2 = (uint8_t*)q2;
+  p.s1 = (const __nv_bfloat16*)s1; p.s2 = (const __nv_bfloat16*)s2;
+  p.status = status;
+  cudaStream_t st = (cudaStream_t)stream;
+  // the A2 slot is unused; mapB2 carries the up-projection weight
+  if (q_bit == 2) return launch<EPI_GATEUP, 2, false>(a1, bg, a1, bu, p, st);
+  if (q_bit == 4) return launch<EPI_GATEUP, 4, false>(a1, bg, a1, bu, p, st);
+  return launch<EPI_GATEUP, 8, false>(a1, bg, a1, bu, p, st);
+}
+
+extern "C" HYC_API int hyc_mlp_graddown_bwd_tcgen05(
+    const void* g, const void* wd, int T, int H, int I,
+    const void* gdm, const void* adt, int64_t ad_ld_col, int64_t ad_ld_r,
+    const void* xa1, const void* b1t, int64_t b1_ld_col, int64_t b1_ld_r,
+    const void* xa2, const void* b2t, int64_t b2_ld_col, int64_t b2_ld_r,
+    const void* q1, const void* s1, const void* q2, const void* s2,
+    void* o, void* grad_gate, void* grad_up, int q_bit, int* status, void* stream) {
+  if (!g || !wd || !xa1 || !b1t || !xa2 || !b2t || !q1 || !s1 || !q2 || !s2 || !o || !grad_gate || !grad_up || !status)
+    return HYC_ERR_NULL;
+  if ((gdm != nullptr) != (adt != nullptr)) return HYC_ERR_NULL;
+  if (q_bit != 2 && q_bit != 4 && q_bit != 8) return HYC_ERR_QBIT;
+  if (T <= 0 || H <= 0 || I <= 0 || I % BN != 0 || H % BK != 0) return HYC_ERR_SHAPE;
+  const void* al[] = {g, wd, xa1, xa2, q1, q2, o, grad_gate, grad_up};
+  for (const void* q : al) if (!aligned(q, 16)) return HYC_ERR_ALIGN;
+  if (gdm && !aligned(gdm, 16)) return HYC_ERR_ALIGN;
+  CUtensorMap a1, b1;
+  // wd is [H, I] row-major: the K = H rows are the reduction dimension, so B is MN-major
+  if (!make_map(&a1, g, T, H, BM) || !make_map(&b1, wd, H, I, 64)) return HYC_ERR_UNSUPPORTED;
+  Params p = {};
+  p.M = T; p.N = I; p.K1 = H; p.K2 = 0; p.epi = EPI_GRADDOWN; p.q_bit = q_bit;
+  p.l0 = make_term(gdm, adt, ad_ld_col, ad_ld_r);
+  p.l1 = make_term(xa1, b1t, b1_ld_col, b1_ld_r);
+  p.l2 = make_term(xa2, b2t, b2_ld_col, b2_ld_r);
+  p.out0 = (__nv_bfloat16*)o; p.out1 = (__nv_bfloat16*)grad_gate; p.out2 = (__nv_bfloat16*)grad_up;
+  p.q1 = (uint8_t*)const_cast<void*>(q1); p.q2 = (uint8_t*)const_cast<void*>(q2);
+  p.s1 = (const __nv_bfloat16*)s1; p.s2 = (const __nv_bfloat16*)s2;
+  p.status = status;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (q_bit == 2) return launch<EPI_GRADDOWN, 2, true>(a1, b1, a1, b1, p, st);
+  if (q_bit == 4) return launch<EPI_GRADDOWN, 4, true>(a1, b1, a1, b1, p, st);
+  return launch<EPI_GRADDOWN, 8, true>(a1, b1, a1, b1, p, st);
+}

@@ -1,0 +1,197 @@
+"""MLP half of the HyC-LoRA fused decoder layer on the tcgen05 kernels.
+
+Mirrors the MLP part of ``FusedLlamaLayerIntraInterFullFuseFunc.forward/backward``
+(models/llama/fused_llama_layer_intra_inter_full_fuse.py:203-252 and :359-396; the Mistral
+twin is identical for this part) with plain bf16 frozen weights:
+
+  forward : RMSNorm -> save x (outlier channels + per-channel codes) -> gate/up GEMMs with the
+            quantizer, LoRA add, SiLU and Hadamard in the GEMM epilogue -> save x_norm codes ->
+            down GEMM with LoRA add and residual in the epilogue;
+  backward: grad_down GEMM with the de-quantize / recompute / SiLU-Hadamard backward in the
+            epilogue -> LoRA gradients -> grad_x GEMM (gate and up accumulated in one tile) ->
+            RMSNorm backward on the restored x.
+
+Only packed codes, scales, the outlier slab, the rank-16 LoRA activations and rstd are kept
+between the two passes.  Weights use the nn.Linear layout ([out, in]); the LoRA factors are
+``lora_A.weight`` [r, in] and ``lora_B.weight`` [out, r].
+"""
+import ctypes
+from dataclasses import dataclass, field
+from typing import Optional
+
+import torch
+
+from ._lib import HycError, check, lib, ptr, require_cuda, stream_of
+from .operators import compress_function as cf
+from .operators.rmsnorm_kernels import rmsnorm_backward, rmsnorm_forward
+
+BF16 = torch.bfloat16
+_KERNEL_STATUS = {1: "TMA producer wait timed out", 2: "MMA issuer wait timed out", 3: "epilogue wait timed out"}
+
+
+def _status_tensor(device):
+    return torch.zeros(1, dtype=torch.int32, device=device)
+
+
+def check_status(status, what):
+    """Raise if a bounded wait inside a tcgen05 kernel gave up (synchronises)."""
+    v = int(status.item())
+    if v != 0:
+        raise HycError("%s: %s" % (what, _KERNEL_STATUS.get(v, "status %d" % v)))
+
+
+def _lora(xa, bt, ld_col, ld_r):
+    if xa is None:
+        return [None, None, 0, 0]
+    return [ptr(xa), ptr(bt), ld_col, ld_r]
+
+
+def gemm(a, b, *, b_is_kn=False, a2=None, b2=None, lora0=None, lora1=None, residual=None, status=None):
+    """D = a @ op(b) (+ a2 @ op(b2)) (+ LoRA terms) (+ residual) on the tcgen05 kernel.
+
+    a [M,K] bf16; b [N,K] (b_is_kn=False) or [K,N] (b_is_kn=True), both row-major.
+    lora = (xa [M,16], bt, ld_col, ld_r): adds xa @ Bt^T with Bt(col, r) = bt[col*ld_col + r*ld_r]."""
+    require_cuda(a, b)
+    M, K = a.shape
+    N = b.shape[1] if b_is_kn else b.shape[0]
+    K2 = 0 if a2 is None else a2.shape[1]
+    d = torch.empty((M, N), dtype=BF16, device=a.device)
+    st = status if status is not None else _status_tensor(a.device)
+    l0 = _lora(*lora0) if lora0 else [None, None, 0, 0]
+    l1 = _lora(*lora1) if lora1 else [None, None, 0, 0]
+    check(lib.hyc_gemm_bf16_tcgen05(ptr(a), ptr(b), M, N, K, 1 if b_is_kn else 0, ptr(a2), ptr(b2), K2,
+                                    *l0, *l1, ptr(residual), ptr(d), ptr(st), stream_of(a)), "hyc_gemm_bf16_tcgen05")
+    return d
+
+
+@dataclass
+class MLPWeights:
+    """Frozen bf16 weights ([out, in]) and LoRA factors of one MLP."""
+    norm_w: torch.Tensor   # [H]
+    wg: torch.Tensor       # [I, H]
+    wu: torch.Tensor       # [I, H]
+    wd: torch.Tensor       # [H, I]
+    ag: torch.Tensor       # gate lora_A.weight [r, H]
+    bg: torch.Tensor       # gate lora_B.weight [I, r]
+    au: torch.Tensor
+    bu: torch.Tensor
+    ad: torch.Tensor       # down lora_A.weight [r, I]
+    bd: torch.Tensor       # down lora_B.weight [H, r]
+
+
+@dataclass
+class MLPState:
+    """Calibration state of the MLP part of a layer (the reference keeps the same entries in
+    ``static_value``, fused_llama_layer_intra_inter_full_fuse.py:557-570)."""
+    iteration: int = 0
+    iteration_threshold: int = 5
+    q_bit: int = 4
+    layernorm_outlier_ratio: float = 0.005
+    static_value: dict = field(default_factory=lambda: {
+        'x_medium': {'outlier_channel_index': None, 'scale': None},
+        'x_norm_2': {'scale': None}, 'gate': {'scale': None}, 'up': {'scale': None}})
+
+
+def mlp_forward(x_medium, w: MLPWeights, state: MLPState, eps=1e-5, status=None):
+    """-> (x_out [B,M,H], saved tuple).  Advances the calibration state like the layer does."""
+    require_cuda(x_medium)
+    B, M, H = x_medium.shape
+    T, I, q = B * M, w.wg.shape[0], state.q_bit
+    st = status if status is not None else _status_tensor(x_medium.device)
+    calib = state.iteration < state.iteration_threshold
+    sv = state.static_value
+
+    x_norm, _, rstd, _, _ = rmsnorm_forward(x_medium, w.norm_w, eps)
+    xm_o, xm_q, xm_idx, xm_scale = cf.compression_pack_channel_base(
+        x_medium, state.layernorm_outlier_ratio, q, 'per-channel', state.iteration, state.iteration_threshold,
+        sv['x_medium'])
+    xn2 = x_norm.reshape(T, H)
+    gate_xa = xn2 @ w.ag.t()
+    up_xa = xn2 @ w.au.t()
+    dev = x_medium.device
+    epp = 8 // q
+    q1 = torch.empty((B, M, I // epp), dtype=torch.uint8, device=dev)
+    q2 = torch.empty((B, M, I // epp), dtype=torch.uint8, device=dev)
+    had = torch.empty((B, M, I), dtype=BF16, device=dev)
+
+    def gateup(s1, s2, m1=None, m2=None):
+        check(lib.hyc_mlp_gateup_fwd_tcgen05(
+            ptr(xn2), ptr(w.wg), ptr(w.wu), T, H, I,
+            ptr(gate_xa), ptr(w.bg), 16, 1, ptr(up_xa), ptr(w.bu), 16, 1,
+            ptr(s1), ptr(s2), ptr(q1), ptr(q2), ptr(had), ptr(m1), ptr(m2), q, ptr(st), stream_of(x_medium)),
+            "hyc_mlp_gateup_fwd_tcgen05")
+
+    if calib:
+        # calibration iterations: the scales depend on the finished main branches, so the GEMM runs
+        # twice (first pass only materialises gate_main / up_main); steady state is single-pass
+        ones = torch.ones(I, dtype=BF16, device=dev)
+        m1 = torch.empty((B, M, I), dtype=BF16, device=dev)
+        m2 = torch.empty((B, M, I), dtype=BF16, device=dev)
+        gateup(ones, ones, m1, m2)
+        gate_scale = cf.get_statistics_only_quant(m1, q, 'per-channel')
+        up_scale = cf.get_statistics_only_quant(m2, q, 'per-channel')
+        del m1, m2
+    else:
+        gate_scale, up_scale = sv['gate']['scale'], sv['up']['scale']
+    gs = gate_scale.to(BF16).reshape(-1).contiguous()
+    us = up_scale.to(BF16).reshape(-1).contiguous()
+    gateup(gs, us)
+
+    xn_q, xn_scale = cf.compression_pack_quant_base(x_norm, q, 'per-channel', state.iteration,
+                                                    state.iteration_threshold, sv['x_norm_2'])
+    had2 = had.reshape(T, I)
+    down_xa = had2 @ w.ad.t()
+    x_out = gemm(had2, w.wd, lora0=(down_xa, w.bd, 16, 1), residual=x_medium.reshape(T, H).contiguous(), status=st)
+
+    if calib:
+        it = state.iteration
+        sv['x_medium'] = cf.update_dict(sv['x_medium'], {'outlier_channel_index': xm_idx, 'scale': xm_scale}, it)
+        sv['x_norm_2'] = cf.update_dict(sv['x_norm_2'], {'scale': xn_scale}, it)
+        sv['gate'] = cf.update_dict(sv['gate'], {'scale': gate_scale}, it)
+        sv['up'] = cf.update_dict(sv['up'], {'scale': up_scale}, it)
+    state.iteration += 1
+
+    saved = dict(rstd=rstd, xm_o=xm_o, xm_q=xm_q, xm_scale=xm_scale, xm_idx=xm_idx, xn_q=xn_q, xn_scale=xn_scale,
+                 gate_q=q1, gate_scale=gs, up_q=q2, up_scale=us, gate_xa=gate_xa, up_xa=up_xa, down_xa=down_xa,
+                 q_bit=q, shape=(B, M, H))
+    return x_out.reshape(B, M, H), saved
+
+
+def mlp_backward(grad_out, saved, w: MLPWeights, status=None):
+    """-> dict(grad_x, grad_ag, grad_bg, grad_au, grad_bu, grad_ad, grad_bd); LoRA gradients in the
+    layout of the weights they belong to ([r, in] / [out, r])."""
+    B, M, H = saved['shape']
+    T, I, q = B * M, w.wg.shape[0], saved['q_bit']
+    dev = grad_out.device
+    st = status if status is not None else _status_tensor(dev)
+    g = grad_out.to(BF16).reshape(T, H).contiguous()
+    down_xa, gate_xa, up_xa = saved['down_xa'], saved['gate_xa'], saved['up_xa']
+
+    grad_bd = g.t() @ down_xa                      # [H, r]
+    gdm = g @ w.bd                                 # [T, r]
+    had = torch.empty((T, I), dtype=BF16, device=dev)
+    gg = torch.empty((T, I), dtype=BF16, device=dev)
+    gu = torch.empty((T, I), dtype=BF16, device=dev)
+    check(lib.hyc_mlp_graddown_bwd_tcgen05(
+        ptr(g), ptr(w.wd), T, H, I, ptr(gdm), ptr(w.ad), 1, I,
+        ptr(gate_xa), ptr(w.bg), 16, 1, ptr(up_xa), ptr(w.bu), 16, 1,
+        ptr(saved['gate_q']), ptr(saved['gate_scale']), ptr(saved['up_q']), ptr(saved['up_scale']),
+        ptr(had), ptr(gg), ptr(gu), q, ptr(st), stream_of(grad_out)), "hyc_mlp_graddown_bwd_tcgen05")
+    grad_ad = gdm.t() @ had                        # [r, I]
+
+    x_norm = cf.decompression_dequantization(saved['xn_q'], saved['xn_scale'], q).reshape(T, H)
+    gm_gate = gg @ w.bg                            # [T, r]
+    gm_up = gu @ w.bu
+    grad_ag = gm_gate.t() @ x_norm                 # [r, H]
+    grad_au = gm_up.t() @ x_norm
+    grad_bg = gg.t() @ gate_xa                     # [I, r]
+    grad_bu = gu.t() @ up_xa
+    # grad wrt x_norm: gate and up products accumulate in one tensor-memory tile
+    grad_xn = gemm(gg, w.wg, b_is_kn=True, a2=gu, b2=w.wu,
+                   lora0=(gm_gate, w.ag, 1, H), lora1=(gm_up, w.au, 1, H), status=st)
+    x_medium = cf.outlier_addition_fuse_decompression_dequantization(
+        saved['xm_q'], saved['xm_scale'], saved['xm_o'], saved['xm_idx'], q)
+    grad_norm, _ = rmsnorm_backward(grad_xn.reshape(B, M, H), x_medium, w.norm_w, None, saved['rstd'], True, 1e-5, 0, 0)
+    grad_x = grad_norm + g.reshape(B, M, H)
+    return dict(grad_x=grad_x, grad_ag=grad_ag, grad_bg=grad_bg, grad_au=grad_au, grad_bu=grad_bu,
+                grad_ad=grad_ad, grad_bd=grad_bd, hadamard=had, g_gate=gg, g_up=gu)

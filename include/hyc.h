@@ -152,6 +152,49 @@ int hyc_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* r
 /* softmax_backward (operators/softmax_kernels.py:7-56): o = (g - sum(y*g)) * y per row. */
 int hyc_softmax_bwd(const void* y, const void* g, void* o, int64_t rows, int S, void* stream);
 
+/* ---- tcgen05 / TMEM GEMMs of the LoRA MLP (activation compression in the epilogue) ------------
+ * bf16 operands, fp32 accumulation in tensor memory, operands staged by TMA.  `status` is a
+ * caller-provided device int, zero before the call; a non-zero value afterwards means a bounded
+ * wait inside the kernel gave up (1 producer, 2 MMA issuer, 3 epilogue) and the output is invalid.
+ * LoRA operands: xa* is the [rows, 16] activation of the LoRA-A projection; bt* addresses the LoRA-B
+ * factor as element (column, r) at bt[column * ld_col + r * ld_r], so both the [out, r] weight and
+ * its [r, out] transpose can be passed without a copy. */
+
+/* D[M,N] = A[M,K] * B (+ A2[M,K2] * B2) (+ xa0 * bt0^T) (+ xa1 * bt1^T) (+ residual), each partial
+ * rounded to bf16 like the reference's tensor-by-tensor code.  b_is_kn = 0: B is [N,K] row-major (an
+ * nn.Linear weight, forward use); 1: B is [K,N] row-major (the same weight used for a backward
+ * product, read in place).  N % 128 == 0, K % 64 == 0.
+ * Replaces the matmuls of lora_forward / lora_backward (models/utils/compute_utils.py:18-36) and the
+ * hand-inlined copies (models/llama/fused_llama_layer_intra_inter_full_fuse.py:247, 359-364, 379-384). */
+int hyc_gemm_bf16_tcgen05(const void* A, const void* B, int M, int N, int K, int b_is_kn,
+                          const void* A2, const void* B2, int K2,
+                          const void* xa0, const void* bt0, int64_t bt0_ld_col, int64_t bt0_ld_r,
+                          const void* xa1, const void* bt1, int64_t bt1_ld_col, int64_t bt1_ld_r,
+                          const void* residual, void* D, int* status, void* stream);
+
+/* gate/up projections and triton_fuse_silu_forward in one kernel
+ * (fused_llama_layer_intra_inter_full_fuse.py:218-235 + triton_fuse_lora_silu_hadamard_forward_kernels.py):
+ * gate_main = x * wg^T and up_main = x * wu^T stay in tensor memory; the epilogue rounds them to bf16,
+ * quantizes and packs them (q1, q2), adds the LoRA terms, applies SiLU and the Hadamard product (o).
+ * x [T,H], wg/wu [I,H], s1/s2 [I] bf16, q1/q2 [T, I*q_bit/8], o [T,I].  I % 64 == 0, H % 64 == 0.
+ * main1/main2 (optional, [T,I] bf16) receive the bf16 main branches for inspection. */
+int hyc_mlp_gateup_fwd_tcgen05(const void* x, const void* wg, const void* wu, int T, int H, int I,
+                               const void* xa1, const void* b1t, int64_t b1_ld_col, int64_t b1_ld_r,
+                               const void* xa2, const void* b2t, int64_t b2_ld_col, int64_t b2_ld_r,
+                               const void* s1, const void* s2, void* q1, void* q2, void* o,
+                               void* main1_or_null, void* main2_or_null, int q_bit, int* status, void* stream);
+
+/* grad_down = g * wd (+ gdm * ad^T) and triton_fuse_silu_backward in one kernel
+ * (fused_llama_layer_intra_inter_full_fuse.py:359-369 + triton_fuse_lora_silu_hadamard_backward_kernels.py):
+ * the epilogue unpacks and de-quantizes the saved gate/up codes, recomputes the forward and writes
+ * o (hadamard), grad_gate, grad_up [T,I].  g [T,H], wd [H,I] (the down weight as stored).  I % 128 == 0. */
+int hyc_mlp_graddown_bwd_tcgen05(const void* g, const void* wd, int T, int H, int I,
+                                 const void* gdm, const void* adt, int64_t ad_ld_col, int64_t ad_ld_r,
+                                 const void* xa1, const void* b1t, int64_t b1_ld_col, int64_t b1_ld_r,
+                                 const void* xa2, const void* b2t, int64_t b2_ld_col, int64_t b2_ld_r,
+                                 const void* q1, const void* s1, const void* q2, const void* s2,
+                                 void* o, void* grad_gate, void* grad_up, int q_bit, int* status, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
