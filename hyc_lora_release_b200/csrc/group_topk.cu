@@ -16,6 +16,7 @@
 namespace hyc {
 
 constexpr unsigned kFull = 0xffffffffu;
+constexpr int kStageEntries = 256;   // outlier-list entries a warp stages in shared memory
 
 struct GroupParams { float s, rcl, zcl, z; };
 
@@ -241,6 +242,8 @@ topk_compress_kernel(const __nv_bfloat16* __restrict__ a, int64_t rows, int S, i
                      uint8_t* __restrict__ q, __nv_bfloat16* __restrict__ scale, int8_t* __restrict__ zp) {
   const int lane = threadIdx.x & 31;
   const int64_t qld = (int64_t)S * QBIT / 8, gld = S / 64;
+  __shared__ __align__(16) uint32_t s_x[8][32][8];          // the lane's 16 values, per warp
+  __shared__ uint32_t s_out[8][kStageEntries];              // staged (column, value) words, per warp
   for (int64_t row = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5); row < rows; row += (int64_t)gridDim.x * 8) {
     const __nv_bfloat16* arow = a + row * S;
     uint32_t xw[STEPS][8];
@@ -343,7 +346,15 @@ topk_compress_kernel(const __nv_bfloat16* __restrict__ a, int64_t rows, int S, i
           }
         }
       }
-      // ---- emit in ascending column order, then zero the selected positions
+      // ---- emit in ascending column order, then zero the selected positions.
+      // The lane's registers are parked in shared memory so that the few selected elements can be
+      // picked by index; (column << 16 | value bits) words are gathered per warp and written out
+      // as one coalesced pass.  Lists longer than the staging area go straight to global memory.
+      const bool staged = k <= kStageEntries;
+      uint32_t* sx = s_x[threadIdx.x >> 5][lane];
+      uint32_t* so = s_out[threadIdx.x >> 5];
+      __nv_bfloat16* vrow = val_out + row * k;
+      uint16_t* crow = col_out + row * k;
       int base = 0;
 #pragma unroll
       for (int st = 0; st < STEPS; ++st) {
@@ -353,27 +364,34 @@ topk_compress_kernel(const __nv_bfloat16* __restrict__ a, int64_t rows, int S, i
 #pragma unroll
         for (int j = 0; j < 8; ++j) acc |= sel[st][j] & ((1u << (2 * j)) | (1u << (17 + 2 * j)));
         uint32_t bits = (acc | (acc >> 16)) & 0xffffu;
-        const int nsel = __popc(bits);
         int tot;
-        int slot = base + warp_excl_scan(nsel, lane, tot);
+        int slot = base + warp_excl_scan(__popc(bits), lane, tot);
         base += tot;
-        const int col0 = 16 * (32 * st + lane);
+        *reinterpret_cast<uint4*>(sx) = make_uint4(xw[st][0], xw[st][1], xw[st][2], xw[st][3]);
+        *reinterpret_cast<uint4*>(sx + 4) = make_uint4(xw[st][4], xw[st][5], xw[st][6], xw[st][7]);
+        const uint32_t col0 = (uint32_t)(16 * (32 * st + lane));
         while (bits) {
           const int e = __ffs(bits) - 1;
           bits &= bits - 1u;
-          // element e of the step: register e/2, half e%2 (dynamic register choice via selects)
-          uint32_t w = xw[st][0];
-#pragma unroll
-          for (int j = 1; j < 8; ++j) w = ((e >> 1) == j) ? xw[st][j] : w;
-          const uint16_t vb = (e & 1) ? (uint16_t)(w >> 16) : (uint16_t)(w & 0xffffu);
+          const uint32_t v = reinterpret_cast<const uint16_t*>(sx)[e];
           if (slot < k) {
-            val_out[row * k + slot] = __ushort_as_bfloat16(vb);
-            col_out[row * k + slot] = (uint16_t)(col0 + e);
+            if (staged) so[slot] = ((col0 + e) << 16) | v;
+            else { vrow[slot] = __ushort_as_bfloat16((uint16_t)v); crow[slot] = (uint16_t)(col0 + e); }
           }
           ++slot;
         }
+        __syncwarp();
 #pragma unroll
         for (int j = 0; j < 8; ++j) xw[st][j] &= ~sel[st][j];
+      }
+      if (staged) {
+        __syncwarp();
+        for (int j = lane; j < k; j += 32) {
+          const uint32_t w = so[j];
+          vrow[j] = __ushort_as_bfloat16((uint16_t)(w & 0xffffu));
+          crow[j] = (uint16_t)(w >> 16);
+        }
+        __syncwarp();
       }
     }
 

@@ -8,10 +8,11 @@
 //              gate/up codes, recompute the forward, emit hadamard, grad_gate, grad_up (backward).
 //
 // Structure of a CTA (320 threads, one CTA per SM, tiles dealt round-robin):
-//   warp 0      : TMA producer; 128x64 A tile and 128x64 B tile per stage (128-byte swizzle),
-//                 5 stages, mbarrier full/empty pairs.
-//   warp 1      : allocates 256 TMEM columns (two 128x128 fp32 accumulators), issues
-//                 tcgen05.mma (M128 N128 K16, bf16 -> fp32) from one lane, commits to mbarriers.
+//   warp 0      : TMA producer; 128x64 A tile and 256x64 B tile per stage (128-byte swizzle),
+//                 4 stages of 48 KB, mbarrier full/empty pairs.
+//   warp 1      : allocates all 512 TMEM columns (two 128x256 fp32 accumulators), issues
+//                 tcgen05.mma (M128 N256 K16, bf16 -> fp32) from one lane, commits to mbarriers.
+//                 N = 256 keeps the shared-memory read rate of the MMA below the SM's limit.
 //   warps 2..9  : epilogue.  Warp w reads TMEM lanes 32*(w%4).. (tcgen05.ld 32x32b.x32) for half of
 //                 the tile's columns, so the epilogue of tile i overlaps the MMAs of tile i+1.
 // The B operand is either K-major ([N,K] row-major, the forward weights) or MN-major ([K,N]
@@ -24,15 +25,15 @@
 namespace hyc {
 namespace tc {
 
-constexpr int BM = 128, BN = 128, BK = 64;
-constexpr int STAGES = 5;
+constexpr int BM = 128, BN = 256, BK = 64;
+constexpr int STAGES = 4;
 constexpr int STAGE_A_BYTES = BM * BK * 2;
 constexpr int STAGE_B_BYTES = BN * BK * 2;
 constexpr int STAGE_BYTES = STAGE_A_BYTES + STAGE_B_BYTES;
 constexpr int EPI_WARPS = 8;
 constexpr int THREADS = 64 + 32 * EPI_WARPS;
-constexpr int TMEM_COLS = 256;
-constexpr int EPI_SMEM_BYTES = 3 * 128 * 16 * 4 + 4 * 128 * 4;   // three fp32 LoRA tiles + four float vectors
+constexpr int TMEM_COLS = 512;
+constexpr int EPI_SMEM_BYTES = 3 * BN * 16 * 2 + 4 * BN * 4;   // three bf16 LoRA-B tiles + four float vectors
 constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + EPI_SMEM_BYTES + 256;
 constexpr uint32_t SPIN_LIMIT = 1u << 22;
 
@@ -134,15 +135,18 @@ __device__ __forceinline__ void epi_bar_sync() { asm volatile("bar.sync 1, %0;" 
 
 __device__ __forceinline__ float bfr(float v) { return bf16bits_to_f32(f32_to_bf16bits_rn(v)); }
 
-// dot of the thread's LoRA-A row (16 floats) with the fp32 LoRA-B row of a column in shared memory
-__device__ __forceinline__ float lora_dot(const float (&xa)[16], const float* __restrict__ brow) {
-  const float4 b0 = *reinterpret_cast<const float4*>(brow), b1 = *reinterpret_cast<const float4*>(brow + 4);
-  const float4 b2 = *reinterpret_cast<const float4*>(brow + 8), b3 = *reinterpret_cast<const float4*>(brow + 12);
-  float a = xa[0] * b0.x;
-  a = fmaf(xa[1], b0.y, a); a = fmaf(xa[2], b0.z, a); a = fmaf(xa[3], b0.w, a);
-  a = fmaf(xa[4], b1.x, a); a = fmaf(xa[5], b1.y, a); a = fmaf(xa[6], b1.z, a); a = fmaf(xa[7], b1.w, a);
-  a = fmaf(xa[8], b2.x, a); a = fmaf(xa[9], b2.y, a); a = fmaf(xa[10], b2.z, a); a = fmaf(xa[11], b2.w, a);
-  a = fmaf(xa[12], b3.x, a); a = fmaf(xa[13], b3.y, a); a = fmaf(xa[14], b3.z, a); a = fmaf(xa[15], b3.w, a);
+// dot of the thread's LoRA-A row (16 floats) with the bf16 LoRA-B row of a column in shared memory
+// (all lanes read the same 32 bytes: a broadcast)
+__device__ __forceinline__ float lora_dot(const float (&xa)[16], const __nv_bfloat16* __restrict__ brow) {
+  const uint4 u = *reinterpret_cast<const uint4*>(brow), v = *reinterpret_cast<const uint4*>(brow + 8);
+  const uint32_t w[8] = {u.x, u.y, u.z, u.w, v.x, v.y, v.z, v.w};
+  float a = xa[0] * bf16lo_to_f32(w[0]);
+  a = fmaf(xa[1], bf16hi_to_f32(w[0]), a);
+#pragma unroll
+  for (int j = 1; j < 8; ++j) {
+    a = fmaf(xa[2 * j], bf16lo_to_f32(w[j]), a);
+    a = fmaf(xa[2 * j + 1], bf16hi_to_f32(w[j]), a);
+  }
   return a;
 }
 
@@ -157,12 +161,12 @@ __device__ __forceinline__ void load_xa_row(const __nv_bfloat16* xa, int64_t row
   for (int j = 0; j < 8; ++j) { out[2 * j] = bf16lo_to_f32(w[j]); out[2 * j + 1] = bf16hi_to_f32(w[j]); }
 }
 
-// cooperative staging of a LoRA-B tile (ncols x 16) as fp32 into shared memory
-__device__ __forceinline__ void stage_lora_tile(const LoraTerm& t, int n0, int ncols, float* dst, int et) {
+// cooperative staging of a LoRA-B tile (ncols x 16, bf16) into shared memory
+__device__ __forceinline__ void stage_lora_tile(const LoraTerm& t, int n0, int ncols, __nv_bfloat16* dst, int et) {
   if (t.bt == nullptr) return;
   for (int i = et; i < ncols * 16; i += 32 * EPI_WARPS) {
     const int c = i >> 4, r = i & 15;
-    dst[i] = __bfloat162float(t.bt[(int64_t)(n0 + c) * t.ld_col + (int64_t)r * t.ld_r]);
+    dst[i] = t.bt[(int64_t)(n0 + c) * t.ld_col + (int64_t)r * t.ld_r];
   }
 }
 
@@ -237,7 +241,7 @@ template <int QBIT>
 __device__ __forceinline__ void epi_gateup_block(const Params& p, int64_t row, bool valid, int ncol0, int cb,
                                                  const uint32_t (&g)[32], const uint32_t (&u)[32],
                                                  const float (&xa1)[16], const float (&xa2)[16],
-                                                 const float* sB1, const float* sB2, const float* sS1, const float* sR1,
+                                                 const __nv_bfloat16* sB1, const __nv_bfloat16* sB2, const float* sS1, const float* sR1,
                                                  const float* sS2, const float* sR2) {
   using G = BlockGeo<QBIT>;
   const int64_t n = (int64_t)ncol0 + cb;
@@ -278,7 +282,7 @@ template <int QBIT>
 __device__ __forceinline__ void epi_graddown_block(const Params& p, int64_t row, bool valid, int ncol0, int cb,
                                                    const uint32_t (&acc)[32], const float (&xg)[16],
                                                    const float (&xa1)[16], const float (&xa2)[16],
-                                                   const float* sBd, const float* sB1, const float* sB2,
+                                                   const __nv_bfloat16* sBd, const __nv_bfloat16* sB1, const __nv_bfloat16* sB2,
                                                    const float* sS1, const float* sS2) {
   using G = BlockGeo<QBIT>;
   constexpr float HALF = (float)(1 << (QBIT - 1));
@@ -313,7 +317,7 @@ __device__ __forceinline__ void epi_graddown_block(const Params& p, int64_t row,
 
 __device__ __forceinline__ void epi_store_block(const Params& p, int64_t row, bool valid, int ncol0, int cb,
                                                 const uint32_t (&acc)[32], const float (&xa0)[16], const float (&xa1)[16],
-                                                const float* sB0, const float* sB1) {
+                                                const __nv_bfloat16* sB0, const __nv_bfloat16* sB1) {
   const int64_t n = (int64_t)ncol0 + cb;
 #pragma unroll
   for (int c8 = 0; c8 < 4; ++c8) {
@@ -349,7 +353,7 @@ mlp_gemm_kernel(const __grid_constant__ CUtensorMap mapA1, const __grid_constant
   // 1024-byte alignment for the 128-byte swizzle atoms
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint8_t* stage_base = smem;
-  float* epi_f = reinterpret_cast<float*>(smem + STAGES * STAGE_BYTES);
+  __nv_bfloat16* epi_b = reinterpret_cast<__nv_bfloat16*>(smem + STAGES * STAGE_BYTES);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES + EPI_SMEM_BYTES);
   uint64_t* full = bars;                       // [STAGES]
   uint64_t* empty = bars + STAGES;             // [STAGES]
@@ -360,7 +364,7 @@ mlp_gemm_kernel(const __grid_constant__ CUtensorMap mapA1, const __grid_constant
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tiles_m = (p.M + BM - 1) / BM;
-  constexpr int TILE_N = (EPI == EPI_GATEUP) ? 64 : BN;     // output columns per tile
+  constexpr int TILE_N = (EPI == EPI_GATEUP) ? BN / 2 : BN;     // output columns per tile
   const int tiles_n = p.N / TILE_N;
   const int num_tiles = tiles_m * tiles_n;
   const int kb1 = p.K1 / BK, kb_total = (p.K1 + p.K2) / BK;
@@ -403,16 +407,18 @@ mlp_gemm_kernel(const __grid_constant__ CUtensorMap mapA1, const __grid_constant
           mbar_expect_tx(&full[stage], STAGE_BYTES);
           tma_load_2d(sa, ma, &full[stage], k0, m0);
           if (EPI == EPI_GATEUP) {
-            // 64 rows of Wg then 64 rows of Wu: one K-major 128-row B tile
+            // 128 rows of Wg then 128 rows of Wu: one K-major 256-row B tile (boxes of 64 rows)
             tma_load_2d(sb, &mapB1, &full[stage], k0, n0);
-            tma_load_2d(sb + 64 * BK * 2, &mapB2, &full[stage], k0, n0);
+            tma_load_2d(sb + 8192, &mapB1, &full[stage], k0, n0 + 64);
+            tma_load_2d(sb + 16384, &mapB2, &full[stage], k0, n0);
+            tma_load_2d(sb + 24576, &mapB2, &full[stage], k0, n0 + 64);
           } else if (B_MN) {
-            // [K, N] row-major: two boxes of 64 k-rows x 64 columns
-            tma_load_2d(sb, mb, &full[stage], n0, k0);
-            tma_load_2d(sb + 64 * 128, mb, &full[stage], n0 + 64, k0);
+            // [K, N] row-major: four boxes of 64 k-rows x 64 columns (8 KB each)
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j) tma_load_2d(sb + j * 8192, mb, &full[stage], n0 + 64 * j, k0);
           } else {
-            tma_load_2d(sb, mb, &full[stage], k0, n0);
-            tma_load_2d(sb + 64 * BK * 2, mb, &full[stage], k0, n0 + 64);
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j) tma_load_2d(sb + j * 8192, mb, &full[stage], k0, n0 + 64 * j);
           }
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
@@ -421,7 +427,7 @@ mlp_gemm_kernel(const __grid_constant__ CUtensorMap mapA1, const __grid_constant
   } else if (warp == 1) {
     // ------------------------------------------------ MMA issuer
     if (lane == 0) {
-      // instruction descriptor: fp32 accumulate, bf16 x bf16, M = 128, N = 128, B major as given
+      // instruction descriptor: fp32 accumulate, bf16 x bf16, M = 128, N = 256, B major as given
       const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((B_MN ? 1u : 0u) << 16) |
                              ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
       int stage = 0;
@@ -466,10 +472,10 @@ mlp_gemm_kernel(const __grid_constant__ CUtensorMap mapA1, const __grid_constant
     const int et = threadIdx.x - 64;
     const int quad = warp & 3;
     const int chalf = (warp - 2) >> 2;
-    float* sB0 = epi_f;                  // [128][16]
-    float* sB1 = epi_f + 128 * 16;
-    float* sB2 = epi_f + 2 * 128 * 16;
-    float* sV = epi_f + 3 * 128 * 16;    // four float vectors of 128
+    __nv_bfloat16* sB0 = epi_b;                  // [BN][16]
+    __nv_bfloat16* sB1 = epi_b + BN * 16;
+    __nv_bfloat16* sB2 = epi_b + 2 * BN * 16;
+    float* sV = reinterpret_cast<float*>(epi_b + 3 * BN * 16);    // four float vectors of BN
     int it = 0;
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++it) {
       const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * TILE_N;
@@ -483,17 +489,17 @@ mlp_gemm_kernel(const __grid_constant__ CUtensorMap mapA1, const __grid_constant
         stage_lora_tile(p.l0, n0, BN, sB0, et);
         stage_lora_tile(p.l1, n0, BN, sB1, et);
       } else if (EPI == EPI_GATEUP) {
-        stage_lora_tile(p.l0, n0, 64, sB0, et);
-        stage_lora_tile(p.l1, n0, 64, sB1, et);
-        if (et < 64) {
+        stage_lora_tile(p.l0, n0, TILE_N, sB0, et);
+        stage_lora_tile(p.l1, n0, TILE_N, sB1, et);
+        if (et < TILE_N) {
           const float a = __bfloat162float(p.s1[n0 + et]), b = __bfloat162float(p.s2[n0 + et]);
-          sV[et] = a; sV[128 + et] = __frcp_rn(a); sV[256 + et] = b; sV[384 + et] = __frcp_rn(b);
+          sV[et] = a; sV[BN + et] = __frcp_rn(a); sV[2 * BN + et] = b; sV[3 * BN + et] = __frcp_rn(b);
         }
       } else {
         stage_lora_tile(p.l0, n0, BN, sB0, et);
         stage_lora_tile(p.l1, n0, BN, sB1, et);
         stage_lora_tile(p.l2, n0, BN, sB2, et);
-        if (et < 128) { sV[et] = __bfloat162float(p.s1[n0 + et]); sV[128 + et] = __bfloat162float(p.s2[n0 + et]); }
+        sV[et] = __bfloat162float(p.s1[n0 + et]); sV[BN + et] = __bfloat162float(p.s2[n0 + et]);
       }
       float xa0[16], xa1[16], xa2[16];
       load_xa_row(p.l0.xa, row, valid, xa0);
@@ -508,18 +514,23 @@ mlp_gemm_kernel(const __grid_constant__ CUtensorMap mapA1, const __grid_constant
       tc_fence_after();
       const uint32_t t_lane = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(buf * BN);
       if (EPI == EPI_GATEUP) {
-        uint32_t g[32], u[32];
-        tc_ld32(t_lane + (uint32_t)(32 * chalf), g);
-        tc_ld32(t_lane + (uint32_t)(64 + 32 * chalf), u);
-        epi_gateup_block<QBIT>(p, row, valid, n0, 32 * chalf, g, u, xa0, xa1, sB0, sB1, sV, sV + 128, sV + 256, sV + 384);
-      } else {
+        // gate columns [0, 128) and up columns [128, 256) of the accumulator; this warp takes 64 of each
 #pragma unroll 1
         for (int ch = 0; ch < 2; ++ch) {
-          uint32_t acc[32];
+          uint32_t g[32], u[32];
           const int cb = 64 * chalf + 32 * ch;
+          tc_ld32(t_lane + (uint32_t)cb, g);
+          tc_ld32(t_lane + (uint32_t)(TILE_N + cb), u);
+          epi_gateup_block<QBIT>(p, row, valid, n0, cb, g, u, xa0, xa1, sB0, sB1, sV, sV + BN, sV + 2 * BN, sV + 3 * BN);
+        }
+      } else {
+#pragma unroll 1
+        for (int ch = 0; ch < 4; ++ch) {
+          uint32_t acc[32];
+          const int cb = 128 * chalf + 32 * ch;
           tc_ld32(t_lane + (uint32_t)cb, acc);
           if (EPI == EPI_STORE) epi_store_block(p, row, valid, n0, cb, acc, xa0, xa1, sB0, sB1);
-          else epi_graddown_block<QBIT>(p, row, valid, n0, cb, acc, xa0, xa1, xa2, sB0, sB1, sB2, sV, sV + 128);
+          else epi_graddown_block<QBIT>(p, row, valid, n0, cb, acc, xa0, xa1, xa2, sB0, sB1, sB2, sV, sV + BN);
         }
       }
       tc_fence_before();
@@ -581,7 +592,7 @@ static int launch(const CUtensorMap& a1, const CUtensorMap& b1, const CUtensorMa
     }
     attr = true;
   }
-  constexpr int TILE_N = (EPI == EPI_GATEUP) ? 64 : BN;
+  constexpr int TILE_N = (EPI == EPI_GATEUP) ? BN / 2 : BN;
   const int tiles = ((p.M + BM - 1) / BM) * (p.N / TILE_N);
   const int grid = tiles < kNumSMs ? tiles : kNumSMs;
   kern<<<grid, THREADS, SMEM_BYTES, st>>>(a1, b1, a2, b2, p);
@@ -646,7 +657,7 @@ extern "C" HYC_API int hyc_mlp_gateup_fwd_tcgen05(
     int q_bit, int* status, void* stream) {
   if (!x || !wg || !wu || !xa1 || !b1t || !xa2 || !b2t || !s1 || !s2 || !q1 || !q2 || !o || !status) return HYC_ERR_NULL;
   if (q_bit != 2 && q_bit != 4 && q_bit != 8) return HYC_ERR_QBIT;
-  if (T <= 0 || H <= 0 || I <= 0 || I % 64 != 0 || H % BK != 0) return HYC_ERR_SHAPE;
+  if (T <= 0 || H <= 0 || I <= 0 || I % (BN / 2) != 0 || H % BK != 0) return HYC_ERR_SHAPE;
   const void* al[] = {x, wg, wu, xa1, xa2, q1, q2, o};
   for (const void* q : al) if (!aligned(q, 16)) return HYC_ERR_ALIGN;
   CUtensorMap a1, bg, bu;

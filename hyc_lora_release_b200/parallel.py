@@ -1,0 +1,68 @@
+"""Token-shard data parallelism for the compression path.
+
+Every operator on the path is independent per token row (or per attention-map row), so the
+multi-GPU layout is: contiguous token shards per rank, frozen and LoRA weights replicated, and
+ONE exchange per step: a sum all-reduce of the flattened LoRA gradients (then a division by the
+world size).  During calibration the statistics are made identical on all ranks: scales and
+thresholds are averaged, rank 0's outlier channel index is broadcast.  The reference has no
+distributed code at all; this is the minimal scheme its data-parallel use would need.
+"""
+from typing import Dict, Iterable, List, Tuple
+
+import torch
+import torch.distributed as dist
+
+
+def shard_bounds(total: int, rank: int, world: int) -> Tuple[int, int]:
+    """Contiguous [begin, end) of `total` tokens for `rank`; the first total % world ranks get one more."""
+    if world <= 0 or not (0 <= rank < world):
+        raise ValueError("bad rank/world")
+    base, rem = divmod(total, world)
+    begin = rank * base + min(rank, rem)
+    return begin, begin + base + (1 if rank < rem else 0)
+
+
+def flatten_grads(grads: Iterable[torch.Tensor], dtype=torch.float32) -> Tuple[torch.Tensor, List[Tuple[torch.Size, int]]]:
+    grads = list(grads)
+    meta = [(g.shape, g.numel()) for g in grads]
+    flat = torch.cat([g.reshape(-1).to(dtype) for g in grads]) if grads else torch.empty(0, dtype=dtype)
+    return flat, meta
+
+
+def unflatten_grads(flat: torch.Tensor, meta, like: Iterable[torch.Tensor]) -> List[torch.Tensor]:
+    out, off = [], 0
+    for (shape, n), ref in zip(meta, like):
+        out.append(flat[off:off + n].reshape(shape).to(ref.dtype))
+        off += n
+    return out
+
+
+def allreduce_lora_grads(grads: Dict[str, torch.Tensor], group=None, average=True) -> Dict[str, torch.Tensor]:
+    """One all-reduce over a single flattened fp32 buffer holding every LoRA gradient."""
+    if not dist.is_initialized() or dist.get_world_size(group) == 1:
+        return grads
+    names = sorted(grads)
+    flat, meta = flatten_grads([grads[n] for n in names])
+    dist.all_reduce(flat, op=dist.ReduceOp.SUM, group=group)
+    if average:
+        flat /= dist.get_world_size(group)
+    return dict(zip(names, unflatten_grads(flat, meta, [grads[n] for n in names])))
+
+
+def sync_calibration(static_value: dict, group=None) -> dict:
+    """Make calibration statistics identical on all ranks: floating-point entries are averaged,
+    the outlier channel index of rank 0 wins."""
+    if not dist.is_initialized() or dist.get_world_size(group) == 1:
+        return static_value
+    world = dist.get_world_size(group)
+    for entry in static_value.values():
+        for name, t in entry.items():
+            if t is None:
+                continue
+            if name == 'outlier_channel_index':
+                dist.broadcast(t, src=0, group=group)
+            else:
+                buf = t.float()
+                dist.all_reduce(buf, op=dist.ReduceOp.SUM, group=group)
+                entry[name] = (buf / world).to(t.dtype)
+    return static_value

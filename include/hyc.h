@@ -163,7 +163,7 @@ int hyc_softmax_bwd(const void* y, const void* g, void* o, int64_t rows, int S, 
 /* D[M,N] = A[M,K] * B (+ A2[M,K2] * B2) (+ xa0 * bt0^T) (+ xa1 * bt1^T) (+ residual), each partial
  * rounded to bf16 like the reference's tensor-by-tensor code.  b_is_kn = 0: B is [N,K] row-major (an
  * nn.Linear weight, forward use); 1: B is [K,N] row-major (the same weight used for a backward
- * product, read in place).  N % 128 == 0, K % 64 == 0.
+ * product, read in place).  N % 256 == 0, K % 64 == 0.
  * Replaces the matmuls of lora_forward / lora_backward (models/utils/compute_utils.py:18-36) and the
  * hand-inlined copies (models/llama/fused_llama_layer_intra_inter_full_fuse.py:247, 359-364, 379-384). */
 int hyc_gemm_bf16_tcgen05(const void* A, const void* B, int M, int N, int K, int b_is_kn,
@@ -176,7 +176,7 @@ int hyc_gemm_bf16_tcgen05(const void* A, const void* B, int M, int N, int K, int
  * (fused_llama_layer_intra_inter_full_fuse.py:218-235 + triton_fuse_lora_silu_hadamard_forward_kernels.py):
  * gate_main = x * wg^T and up_main = x * wu^T stay in tensor memory; the epilogue rounds them to bf16,
  * quantizes and packs them (q1, q2), adds the LoRA terms, applies SiLU and the Hadamard product (o).
- * x [T,H], wg/wu [I,H], s1/s2 [I] bf16, q1/q2 [T, I*q_bit/8], o [T,I].  I % 64 == 0, H % 64 == 0.
+ * x [T,H], wg/wu [I,H], s1/s2 [I] bf16, q1/q2 [T, I*q_bit/8], o [T,I].  I % 128 == 0, H % 64 == 0.
  * main1/main2 (optional, [T,I] bf16) receive the bf16 main branches for inspection. */
 int hyc_mlp_gateup_fwd_tcgen05(const void* x, const void* wg, const void* wu, int T, int H, int I,
                                const void* xa1, const void* b1t, int64_t b1_ld_col, int64_t b1_ld_r,
@@ -187,7 +187,7 @@ int hyc_mlp_gateup_fwd_tcgen05(const void* x, const void* wg, const void* wu, in
 /* grad_down = g * wd (+ gdm * ad^T) and triton_fuse_silu_backward in one kernel
  * (fused_llama_layer_intra_inter_full_fuse.py:359-369 + triton_fuse_lora_silu_hadamard_backward_kernels.py):
  * the epilogue unpacks and de-quantizes the saved gate/up codes, recomputes the forward and writes
- * o (hadamard), grad_gate, grad_up [T,I].  g [T,H], wd [H,I] (the down weight as stored).  I % 128 == 0. */
+ * o (hadamard), grad_gate, grad_up [T,I].  g [T,H], wd [H,I] (the down weight as stored).  I % 256 == 0. */
 int hyc_mlp_graddown_bwd_tcgen05(const void* g, const void* wd, int T, int H, int I,
                                  const void* gdm, const void* adt, int64_t ad_ld_col, int64_t ad_ld_r,
                                  const void* xa1, const void* b1t, int64_t b1_ld_col, int64_t b1_ld_r,
