@@ -194,3 +194,67 @@ extern "C" HYC_API int hyc_softmax_prune_restore(const int64_t* idx, const void*
   }
   return HYC_OK;
 }
+
+// ---------------------------------------------------------------------------------------------
+// Variant for callers that must not allocate device memory when they call: a training loop whose
+// HBM is handed out up front by a fixed memory plan, or a host framework that forbids allocation
+// inside an operator callback, has no buffer to offer as the count/fill workspace.  Here the tile
+// offsets live in a file-scope device array instead, so the whole compaction is ONE call that
+// allocates nothing.
+//
+//   * The array holds kStaticMaxTiles + 1 int64 (512 KiB + 8 B) and stays resident on every GPU
+//     that loads the library until the process exits.  Maps of more than kStaticMaxTiles * 4096
+//     elements (268,435,456) are refused with HYC_ERR_CAPACITY.
+//   * The first call on a device looks the array's device address up (cudaGetSymbolAddress, with
+//     that device current) and remembers it; make that first call outside of any stream capture.
+//   * All calls on a device share the array.  Every entry a call reads is written by that same
+//     call first (the count kernel writes each tile's slot, the scan writes the total), so nothing
+//     has to be cleared between calls; but two calls that overlap on the GPU (different streams)
+//     would race on it.  Serialise them.
+constexpr int64_t kStaticMaxTiles = 65536;
+static __device__ __align__(256) int64_t g_prune_offsets[1 + kStaticMaxTiles];
+
+static int64_t* static_offsets_for_current_device(int* err) {
+  static int64_t* cached[64] = {nullptr};
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= 64) { *err = (int)(e != cudaSuccess ? e : cudaErrorInvalidDevice); return nullptr; }
+  if (cached[dev] == nullptr) {
+    // g_prune_offsets is a host-side handle here, not a device address: ask the runtime for the address
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_prune_offsets);
+    if (e != cudaSuccess || p == nullptr) { *err = (int)e; return nullptr; }
+    cached[dev] = reinterpret_cast<int64_t*>(p);
+  }
+  return cached[dev];
+}
+
+extern "C" HYC_API int hyc_softmax_prune_static(const void* a, int64_t numel, float threshold,
+                                                int64_t* idx_out, void* val_out, int64_t capacity,
+                                                int64_t* nnz_out, void* stream) {
+  if (!a || !nnz_out) return HYC_ERR_NULL;
+  if (capacity > 0 && (!idx_out || !val_out)) return HYC_ERR_NULL;
+  if (numel <= 0 || capacity < 0) return HYC_ERR_SHAPE;
+  if (!aligned(a, 16) || !aligned(nnz_out, 8)) return HYC_ERR_ALIGN;
+  const int64_t nt = n_tiles_of(numel);
+  if (nt > kStaticMaxTiles) return HYC_ERR_CAPACITY;   // map too large for the built-in scratch
+  int err = 0;
+  int64_t* ws = static_offsets_for_current_device(&err);
+  if (!ws) { hyc_set_last_cuda_error(err); return HYC_ERR_LAUNCH; }
+  cudaStream_t st = (cudaStream_t)stream;
+  const float thr = thr_bf16(threshold);
+  prune_count_kernel<<<tile_grid(nt), kTileThreads, 0, st>>>((const __nv_bfloat16*)a, numel, thr, nt, ws);
+  HYC_CHECK_LAUNCH();
+  prune_scan_kernel<<<1, 1024, 0, st>>>(ws, nt);
+  HYC_CHECK_LAUNCH();
+  if (capacity > 0) {
+    prune_fill_kernel<<<tile_grid(nt), kTileThreads, 0, st>>>((const __nv_bfloat16*)a, numel, thr, nt, ws, idx_out,
+                                                              (__nv_bfloat16*)val_out, capacity);
+    HYC_CHECK_LAUNCH();
+  }
+  if (cudaMemcpyAsync(nnz_out, ws, sizeof(int64_t), cudaMemcpyDeviceToDevice, st) != cudaSuccess) {
+    hyc_set_last_cuda_error((int)cudaGetLastError());
+    return HYC_ERR_LAUNCH;
+  }
+  return HYC_OK;
+}

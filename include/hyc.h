@@ -112,6 +112,18 @@ int hyc_softmax_prune_fill(const void* a, int64_t numel, float threshold,
 int hyc_softmax_prune_restore(const int64_t* idx, const void* val, int64_t nnz,
                               void* a_out, int64_t numel, void* stream);
 
+/* No counterpart in the reference.  The same threshold prune for callers that must not allocate
+ * device memory at call time (a fixed up-front memory plan, or a host that forbids allocation inside
+ * operator callbacks) and so have no workspace to pass: the tile offsets live in a 512 KiB array built
+ * into the library (resident on every GPU that loads it), count + scan + fill run in this one call,
+ * and nothing is allocated.  nnz_out (device int64) receives the number of kept entries; entries
+ * beyond `capacity` are dropped, so compare the two.  Limit: numel <= 268,435,456 (else
+ * HYC_ERR_CAPACITY).  The first call on each device resolves the array's address and should be made
+ * outside of stream capture.  Calls share the array: do not let two of them overlap on one GPU. */
+int hyc_softmax_prune_static(const void* a, int64_t numel, float threshold,
+                             int64_t* idx_out, void* val_out, int64_t capacity,
+                             int64_t* nnz_out, void* stream);
+
 /* ---- attention map: per-row top-k + grouped remainder (no counterpart in the reference;
  *      the reference prunes by one global threshold, compress_function.py:30-32, 309-313) -- */
 /* a [rows, S] bf16 (S % 64 == 0, S <= 4096, k <= S): the k largest magnitudes of every row
