@@ -71,8 +71,8 @@ fused_silu_kernel(const __nv_bfloat16* __restrict__ xa1, const __nv_bfloat16* __
     s1[nt][0] = bf16lo_to_f32(sa); s1[nt][1] = bf16hi_to_f32(sa);
     s2[nt][0] = bf16lo_to_f32(sb); s2[nt][1] = bf16hi_to_f32(sb);
     if (!BACKWARD) {
-      r1[nt][0] = __frcp_rn(s1[nt][0]); r1[nt][1] = __frcp_rn(s1[nt][1]);
-      r2[nt][0] = __frcp_rn(s2[nt][0]); r2[nt][1] = __frcp_rn(s2[nt][1]);
+      r1[nt][0] = fastq_scale<QBIT>(__frcp_rn(s1[nt][0])); r1[nt][1] = fastq_scale<QBIT>(__frcp_rn(s1[nt][1]));
+      r2[nt][0] = fastq_scale<QBIT>(__frcp_rn(s2[nt][0])); r2[nt][1] = fastq_scale<QBIT>(__frcp_rn(s2[nt][1]));
     }
   }
 
@@ -125,8 +125,8 @@ fused_silu_kernel(const __nv_bfloat16* __restrict__ xa1, const __nv_bfloat16* __
             const int nt = i * NPS + jj;
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
-              uint32_t c1 = ((uint32_t)quant_code_signed<QBIT>(m1[h][nt][e], s1[nt][e], r1[nt][e]) + (uint32_t)(1 << (QBIT - 1))) & CM;
-              uint32_t c2 = ((uint32_t)quant_code_signed<QBIT>(m2[h][nt][e], s2[nt][e], r2[nt][e]) + (uint32_t)(1 << (QBIT - 1))) & CM;
+              uint32_t c1 = fastq_code_bits<QBIT>(m1[h][nt][e], r1[nt][e]) & CM;
+              uint32_t c2 = fastq_code_bits<QBIT>(m2[h][nt][e], r2[nt][e]) & CM;
               p1 |= c1 << (QBIT * i + 8 * e);
               p2 |= c2 << (QBIT * i + 8 * e);
             }

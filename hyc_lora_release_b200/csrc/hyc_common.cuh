@@ -74,6 +74,46 @@ __device__ __forceinline__ int quant_code_signed_zp(float x, float s, float rc, 
   return round_half_away_i(r);
 }
 
+// ---- fast exact per-channel quantizer (no zero point) ---------------------------
+// code = clamp(roundf(RN(x / s)), -2^(q-1), 2^(q-1)-1) + 2^(q-1) without a division, a clamp pair
+// or a float->int conversion.  Why it is exact: x and s are bf16 (8-bit significands), so a
+// quotient that is not exactly a half-integer stays at least 1/510 away from every half-integer,
+// while an exact half-integer quotient is reproduced by x * RN(1/s) to within 2^-23 relative.
+// Multiplying by (1 + delta) pushes ties away from zero (C roundf) by more than that error and
+// moves every other value by far less than 1/510; round-to-nearest then gives the reference code.
+// Checked exhaustively on the host over all bf16 scale significands and all bf16 inputs.
+//   q = 2, 4 : u = min(sat(fma(x, rcs, 0.5)), (2^q-1)/2^q),  rcs = RN(1/s) * (1 + 2^-16) / 2^q,
+//              code = low mantissa bits of fma(u, 2^q, 2^23)
+//   q = 8    : t = clamp(x * rc, -128, 127),  code = low byte of fma(t, 1 + 2^-18, 1.5 * 2^23) ^ 0x80
+// A column with rcs == 0 (outlier column) encodes as zero.
+template <int QBIT>
+__device__ __forceinline__ float fastq_scale(float rc) {
+  if (QBIT == 8) return rc;
+  return rc * ((1.0f + 1.0f / 65536.0f) / (float)(1 << QBIT));
+}
+// offset-binary code in the low byte of the returned word (upper bits are not zero)
+template <int QBIT>
+__device__ __forceinline__ uint32_t fastq_code_bits(float x, float rcs) {
+  if (QBIT == 8) {
+    const float t = fminf(fmaxf(x * rcs, -128.f), 127.f);
+    return __float_as_uint(fmaf(t, 1.0f + 1.0f / 262144.0f, 12582912.f)) ^ 0x80u;
+  } else {
+    constexpr float P = (float)(1 << QBIT);
+    float u;
+    asm("fma.rn.sat.f32 %0, %1, %2, %3;" : "=f"(u) : "f"(x), "f"(rcs), "f"(0.5f));
+    u = fminf(u, (P - 1.0f) / P);
+    return __float_as_uint(fmaf(u, P, 8388608.f));
+  }
+}
+// low bytes of four words -> one word (byte k = low byte of bk)
+__device__ __forceinline__ uint32_t gather_low_bytes(uint32_t b0, uint32_t b1, uint32_t b2, uint32_t b3) {
+  return __byte_perm(__byte_perm(b0, b1, 0x0040), __byte_perm(b2, b3, 0x0040), 0x5410);
+}
+// byte k (0..3) of w as the float 2^23 + byte
+__device__ __forceinline__ float byte_to_magic_float(uint32_t w, int k) {
+  return __uint_as_float(__byte_perm(w, 0x4B000000u, 0x7540u + (uint32_t)k));
+}
+
 // ---- streaming 128-bit / 64-bit global access --------------------------------
 __device__ __forceinline__ uint4 ld_stream_v4(const void* p) {
   uint4 v;

@@ -256,8 +256,8 @@ __device__ __forceinline__ void epi_gateup_block(const Params& p, int64_t row, b
       const int c = 8 * c8 + e, tc = cb + c;
       // the frozen-weight products are bf16 tensors in the reference before anything else touches them
       const float x1 = bfr(__uint_as_float(g[c])), x2 = bfr(__uint_as_float(u[c]));
-      put_code<QBIT>(w1, c, (uint32_t)(quant_code_signed<QBIT>(x1, sS1[tc], sR1[tc]) + (1 << (QBIT - 1))));
-      put_code<QBIT>(w2, c, (uint32_t)(quant_code_signed<QBIT>(x2, sS2[tc], sR2[tc]) + (1 << (QBIT - 1))));
+      put_code<QBIT>(w1, c, fastq_code_bits<QBIT>(x1, sR1[tc]) & G::CM);
+      put_code<QBIT>(w2, c, fastq_code_bits<QBIT>(x2, sR2[tc]) & G::CM);
       o[e] = silu_terms(x1, lora_dot(xa1, sB1 + tc * 16), x2, lora_dot(xa2, sB2 + tc * 16)).o;
     }
     if (valid) store8_bf16(p.out0 + row * p.N + n + 8 * c8, o);
@@ -493,7 +493,8 @@ mlp_gemm_kernel(const __grid_constant__ CUtensorMap mapA1, const __grid_constant
         stage_lora_tile(p.l1, n0, TILE_N, sB1, et);
         if (et < TILE_N) {
           const float a = __bfloat162float(p.s1[n0 + et]), b = __bfloat162float(p.s2[n0 + et]);
-          sV[et] = a; sV[BN + et] = __frcp_rn(a); sV[2 * BN + et] = b; sV[3 * BN + et] = __frcp_rn(b);
+          sV[et] = a; sV[BN + et] = fastq_scale<QBIT>(__frcp_rn(a));
+          sV[2 * BN + et] = b; sV[3 * BN + et] = fastq_scale<QBIT>(__frcp_rn(b));
         }
       } else {
         stage_lora_tile(p.l0, n0, BN, sB0, et);

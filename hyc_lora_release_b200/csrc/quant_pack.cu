@@ -11,8 +11,14 @@
 
 namespace hyc {
 
+#ifndef HYC_ROW_UNROLL
+#define HYC_ROW_UNROLL 2
+#endif
+#ifndef HYC_Q_MINBLOCKS
+#define HYC_Q_MINBLOCKS 4
+#endif
 constexpr int kThreads = 256;
-constexpr int kRowUnroll = 2;
+constexpr int kRowUnroll = HYC_ROW_UNROLL;
 
 template <int QBIT>
 struct Geo {
@@ -25,9 +31,33 @@ struct Geo {
   }
 };
 
+constexpr int kMaxOwn = 2;   // outlier columns a thread handles itself; more -> block-wide fallback
+
+// Outlier columns.  The block builds a map "column of my span -> position j in the outlier list"
+// in shared memory; each thread then knows which of its own columns are outliers (rarely any).
+// Such a thread moves the full-precision value itself, right next to its streaming loads/stores,
+// so the gather (quantize) and the scatter (de-quantize) cost nothing for the other 99 % of threads.
+struct OwnOutliers {
+  int n;                 // number of outlier columns owned (may exceed kMaxOwn: see overflow flag)
+  int col[kMaxOwn];      // absolute column
+  int j[kMaxOwn];        // position in the outlier list
+};
+
+__device__ __forceinline__ void build_outlier_map(int16_t* s_map, int* s_overflow, int span_cols, int col0,
+                                                  const int64_t* __restrict__ oidx, int k) {
+  for (int i = threadIdx.x; i < span_cols / 2; i += blockDim.x) reinterpret_cast<uint32_t*>(s_map)[i] = 0xffffffffu;
+  if (threadIdx.x == 0) *s_overflow = 0;
+  __syncthreads();
+  for (int j = threadIdx.x; j < k; j += blockDim.x) {
+    const int64_t c = oidx[j] - col0;
+    if (c >= 0 && c < span_cols) s_map[c] = (int16_t)j;
+  }
+  __syncthreads();
+}
+
 // grid: (col_tiles, row_slots).  Row groups of kRowUnroll rows are dealt round-robin to slots.
 template <int QBIT, bool HAS_ZP>
-__global__ void __launch_bounds__(kThreads, (QBIT == 2 || (QBIT == 4 && HAS_ZP)) ? 2 : 4)
+__global__ void __launch_bounds__(kThreads, (QBIT == 2 || (QBIT == 4 && HAS_ZP)) ? 2 : HYC_Q_MINBLOCKS)
 quant_pack_kernel(const __nv_bfloat16* __restrict__ x, int64_t rows, int N, int64_t ldx,
                   const __nv_bfloat16* __restrict__ scale, const int8_t* __restrict__ zp,
                   const int64_t* __restrict__ oidx, int k,
@@ -39,45 +69,55 @@ quant_pack_kernel(const __nv_bfloat16* __restrict__ x, int64_t rows, int N, int6
   const bool active = ct < n_ct;
   const int64_t qld = (int64_t)N / EPP;
 
-  // outlier-column mask of this block's column span (bytes, one per column)
-  extern __shared__ __align__(16) uint8_t s_mask[];
+  extern __shared__ __align__(16) uint8_t s_dyn[];
+  int16_t* s_map = reinterpret_cast<int16_t*>(s_dyn);
   const int span_cols = kThreads * G::COLS_PER_THREAD;
   const int col0 = blockIdx.x * span_cols;
-  if (k > 0) {
-    for (int i = threadIdx.x; i < span_cols / 4; i += kThreads) reinterpret_cast<uint32_t*>(s_mask)[i] = 0u;
-    __syncthreads();
-    for (int j = threadIdx.x; j < k; j += kThreads) {
-      int64_t c = oidx[j] - col0;
-      if (c >= 0 && c < span_cols) s_mask[c] = 1;
-    }
-    __syncthreads();
-  }
+  int* s_overflow = reinterpret_cast<int*>(s_dyn + 2 * span_cols);
+  if (k > 0) build_outlier_map(s_map, s_overflow, span_cols, col0, oidx, k);
 
-  float s[EPP][8], rc[EPP][8], z[HAS_ZP ? EPP : 1][8];
+  // without a zero point only one constant per column is needed (see fastq_code_bits); the
+  // zero-point variant keeps the exact quotient (scale, reciprocal, zero point per column)
+  float s[HAS_ZP ? EPP : 1][8], rc[EPP][8], z[HAS_ZP ? EPP : 1][8];
+  OwnOutliers own;
+  own.n = 0;
+#pragma unroll
+  for (int i = 0; i < kMaxOwn; ++i) { own.col[i] = 0; own.j[i] = 0; }
   if (active) {
 #pragma unroll
     for (int i = 0; i < EPP; ++i) {
       const int c = G::slab_col(ct, i);
       uint4 sv = *reinterpret_cast<const uint4*>(scale + c);
       const uint32_t sw[4] = {sv.x, sv.y, sv.z, sv.w};
-      uint2 mv = make_uint2(0u, 0u);
-      if (k > 0) mv = *reinterpret_cast<const uint2*>(s_mask + (c - col0));
+      uint4 mv = make_uint4(0xffffffffu, 0xffffffffu, 0xffffffffu, 0xffffffffu);
+      if (k > 0) mv = *reinterpret_cast<const uint4*>(s_map + (c - col0));
+      const uint32_t mw[4] = {mv.x, mv.y, mv.z, mv.w};
       uint2 zv = make_uint2(0u, 0u);
       if (HAS_ZP) zv = *reinterpret_cast<const uint2*>(zp + c);
 #pragma unroll
       for (int e = 0; e < 8; ++e) {
         float sf = (e & 1) ? bf16hi_to_f32(sw[e >> 1]) : bf16lo_to_f32(sw[e >> 1]);
-        s[i][e] = sf;
-        float r = __frcp_rn(sf);
-        uint32_t mb = ((e < 4 ? mv.x : mv.y) >> (8 * (e & 3))) & 0xffu;
-        rc[i][e] = mb ? 0.f : r;
+        if (HAS_ZP) s[i][e] = sf;
+        float r = HAS_ZP ? __frcp_rn(sf) : fastq_scale<QBIT>(__frcp_rn(sf));
+        const int jv = (int)(int16_t)((mw[e >> 1] >> (16 * (e & 1))) & 0xffffu);
+        if (jv >= 0) {
+          r = 0.f;     // the column encodes as zero, as if it had been cleared beforehand
+#pragma unroll
+          for (int t = 0; t < kMaxOwn; ++t)
+            if (own.n == t) { own.col[t] = c + e; own.j[t] = jv; }
+          ++own.n;
+        }
+        rc[i][e] = r;
         if (HAS_ZP) {
           int zb = (int)(int8_t)(((e < 4 ? zv.x : zv.y) >> (8 * (e & 3))) & 0xffu);
           z[i][e] = (float)zb;
         }
       }
     }
+    if (own.n > kMaxOwn) atomicOr(s_overflow, 1);
   }
+  bool overflow = false;
+  if (k > 0) { __syncthreads(); overflow = *s_overflow != 0; }
 
   const int64_t n_groups = (rows + kRowUnroll - 1) / kRowUnroll;
   for (int64_t g = blockIdx.y; g < n_groups; g += gridDim.y) {
@@ -93,34 +133,66 @@ quant_pack_kernel(const __nv_bfloat16* __restrict__ x, int64_t rows, int N, int6
           if (ok) v[r][i] = ld_stream_v4(x + (r0 + r) * ldx + G::slab_col(ct, i));
         }
       }
+      // the owner of an outlier column fetches its full-precision value alongside the vector loads
+      // (same cache lines, so the latency is shared)
+      __nv_bfloat16 ov[kRowUnroll][kMaxOwn];
+      if (own.n > 0 && !overflow) {
+#pragma unroll
+        for (int r = 0; r < kRowUnroll; ++r)
+#pragma unroll
+          for (int t = 0; t < kMaxOwn; ++t)
+            if (t < own.n && (r0 + r) < rows) ov[r][t] = x[(r0 + r) * ldx + own.col[t]];
+      }
 #pragma unroll
       for (int r = 0; r < kRowUnroll; ++r) {
         if ((r0 + r) >= rows) break;
-        uint32_t w[EPP][2];
+        uint2 packed;
+        if (HAS_ZP) {
+          uint32_t w[EPP][2];
 #pragma unroll
-        for (int i = 0; i < EPP; ++i) {
-          const uint32_t xw[4] = {v[r][i].x, v[r][i].y, v[r][i].z, v[r][i].w};
-          int c[8];
+          for (int i = 0; i < EPP; ++i) {
+            const uint32_t xw[4] = {v[r][i].x, v[r][i].y, v[r][i].z, v[r][i].w};
+            int c[8];
 #pragma unroll
-          for (int e = 0; e < 8; ++e) {
-            float xf = (e & 1) ? bf16hi_to_f32(xw[e >> 1]) : bf16lo_to_f32(xw[e >> 1]);
-            c[e] = HAS_ZP ? quant_code_signed_zp<QBIT>(xf, s[i][e], rc[i][e], z[i][e])
-                          : quant_code_signed<QBIT>(xf, s[i][e], rc[i][e]);
+            for (int e = 0; e < 8; ++e) {
+              float xf = (e & 1) ? bf16hi_to_f32(xw[e >> 1]) : bf16lo_to_f32(xw[e >> 1]);
+              c[e] = quant_code_signed_zp<QBIT>(xf, s[i][e], rc[i][e], z[i][e]);
+            }
+            w[i][0] = pack4_s8(c[0], c[1], c[2], c[3]);
+            w[i][1] = pack4_s8(c[4], c[5], c[6], c[7]);
           }
-          w[i][0] = pack4_s8(c[0], c[1], c[2], c[3]);
-          w[i][1] = pack4_s8(c[4], c[5], c[6], c[7]);
+          packed = interleave_slabs<QBIT>(w);
+        } else {
+          packed = make_uint2(0u, 0u);
+#pragma unroll
+          for (int i = 0; i < EPP; ++i) {
+            const uint32_t xw[4] = {v[r][i].x, v[r][i].y, v[r][i].z, v[r][i].w};
+            uint32_t b[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+              float xf = (e & 1) ? bf16hi_to_f32(xw[e >> 1]) : bf16lo_to_f32(xw[e >> 1]);
+              b[e] = fastq_code_bits<QBIT>(xf, rc[i][e]);
+            }
+            // codes are already offset-binary and below 2^QBIT: slab i goes to bit QBIT*i of each byte
+            packed.x |= gather_low_bytes(b[0], b[1], b[2], b[3]) << (QBIT * i);
+            packed.y |= gather_low_bytes(b[4], b[5], b[6], b[7]) << (QBIT * i);
+          }
         }
-        st_stream_v2(q + (r0 + r) * qld + 8 * (int64_t)ct, interleave_slabs<QBIT>(w));
+        st_stream_v2(q + (r0 + r) * qld + 8 * (int64_t)ct, packed);
+        if (own.n > 0 && !overflow) {
+#pragma unroll
+          for (int t = 0; t < kMaxOwn; ++t)
+            if (t < own.n) oout[(r0 + r) * k + own.j[t]] = ov[r][t];
+        }
       }
     }
-    // gather the outlier columns of these rows (only the first column tile does it;
-    // the row segment was just read, so these hit in L2)
-    if (k > 0 && blockIdx.x == 0) {
-      const int cnt = kRowUnroll * k;
-      for (int t = threadIdx.x; t < cnt; t += kThreads) {
+    if (overflow) {
+      // rare: some thread owns more than kMaxOwn outlier columns; the block gathers its span together
+      for (int t = threadIdx.x; t < kRowUnroll * k; t += kThreads) {
         const int64_t row = r0 + t / k;
         const int j = t % k;
-        if (row < rows) oout[row * k + j] = x[row * ldx + oidx[j]];
+        const int64_t c = oidx[j] - col0;
+        if (row < rows && c >= 0 && c < span_cols) oout[row * k + j] = x[row * ldx + oidx[j]];
       }
     }
   }
@@ -146,11 +218,20 @@ unpack_dequant_kernel(const uint8_t* __restrict__ q, int64_t rows, int N,
   const int span_cols = kThreads * G::COLS_PER_THREAD;
   const int col0 = blockIdx.x * span_cols;
 
+  extern __shared__ __align__(16) uint8_t s_dyn[];
+  int16_t* s_map = reinterpret_cast<int16_t*>(s_dyn);
+  int* s_overflow = reinterpret_cast<int*>(s_dyn + 2 * span_cols);
+  if (k > 0) build_outlier_map(s_map, s_overflow, span_cols, col0, oidx, k);
+
   // x_hat = bf16( bf16(code - half [- z]) * s ).  (code - half - z) is an integer of
   // magnitude <= 255, exact in bf16 and in fp32; the fp32 product of two bf16 values is
   // exact, so one rounding to bf16 reproduces the reference's bf16 multiply.
   // 0x4B000000 | code is the float 2^23 + code; `off` folds 2^23 + half + z.
   float s[EPP][8], off[EPP][8];
+  OwnOutliers own;
+  own.n = 0;
+#pragma unroll
+  for (int i = 0; i < kMaxOwn; ++i) { own.col[i] = 0; own.j[i] = 0; }
   if (active) {
 #pragma unroll
     for (int i = 0; i < EPP; ++i) {
@@ -159,14 +240,27 @@ unpack_dequant_kernel(const uint8_t* __restrict__ q, int64_t rows, int N,
       const uint32_t sw[4] = {sv.x, sv.y, sv.z, sv.w};
       uint2 zv = make_uint2(0u, 0u);
       if (HAS_ZP) zv = *reinterpret_cast<const uint2*>(zp + c);
+      uint4 mv = make_uint4(0xffffffffu, 0xffffffffu, 0xffffffffu, 0xffffffffu);
+      if (k > 0) mv = *reinterpret_cast<const uint4*>(s_map + (c - col0));
+      const uint32_t mw[4] = {mv.x, mv.y, mv.z, mv.w};
 #pragma unroll
       for (int e = 0; e < 8; ++e) {
         s[i][e] = (e & 1) ? bf16hi_to_f32(sw[e >> 1]) : bf16lo_to_f32(sw[e >> 1]);
         int zb = HAS_ZP ? (int)(int8_t)(((e < 4 ? zv.x : zv.y) >> (8 * (e & 3))) & 0xffu) : 0;
         off[i][e] = 8388608.f + (float)((1 << (QBIT - 1)) + zb);
+        const int jv = (int)(int16_t)((mw[e >> 1] >> (16 * (e & 1))) & 0xffffu);
+        if (jv >= 0) {
+#pragma unroll
+          for (int t = 0; t < kMaxOwn; ++t)
+            if (own.n == t) { own.col[t] = c + e; own.j[t] = jv; }
+          ++own.n;
+        }
       }
     }
+    if (own.n > kMaxOwn) atomicOr(s_overflow, 1);
   }
+  bool overflow = false;
+  if (k > 0) { __syncthreads(); overflow = *s_overflow != 0; }
 
   const int64_t n_groups = (rows + kRowUnroll - 1) / kRowUnroll;
   for (int64_t g = blockIdx.y; g < n_groups; g += gridDim.y) {
@@ -178,18 +272,26 @@ unpack_dequant_kernel(const uint8_t* __restrict__ q, int64_t rows, int N,
         p[r] = make_uint2(0u, 0u);
         if ((r0 + r) < rows) p[r] = ld_stream_v2(q + (r0 + r) * qld + 8 * (int64_t)ct);
       }
+      __nv_bfloat16 ov[kRowUnroll][kMaxOwn];
+      if (own.n > 0 && !overflow) {
+#pragma unroll
+        for (int r = 0; r < kRowUnroll; ++r)
+#pragma unroll
+          for (int t = 0; t < kMaxOwn; ++t)
+            if (t < own.n && (r0 + r) < rows) ov[r][t] = oin[(r0 + r) * k + own.j[t]];
+      }
 #pragma unroll
       for (int r = 0; r < kRowUnroll; ++r) {
         if ((r0 + r) >= rows) break;
 #pragma unroll
         for (int i = 0; i < EPP; ++i) {
+          // the codes of slab i, one per byte, then each byte straight into the float 2^23 + code
+          constexpr uint32_t BM = MASK * 0x01010101u;
+          const uint32_t f0 = (p[r].x >> (QBIT * i)) & BM, f1 = (p[r].y >> (QBIT * i)) & BM;
           float f[8];
 #pragma unroll
-          for (int e = 0; e < 8; ++e) {
-            uint32_t byte = ((e < 4 ? p[r].x : p[r].y) >> (8 * (e & 3)));
-            uint32_t code = (byte >> (QBIT * i)) & MASK;
-            f[e] = (__uint_as_float(0x4B000000u | code) - off[i][e]) * s[i][e];
-          }
+          for (int e = 0; e < 8; ++e)
+            f[e] = (byte_to_magic_float(e < 4 ? f0 : f1, e & 3) - off[i][e]) * s[i][e];
           uint4 o;
           o.x = pack_bf16x2_rn(f[0], f[1]);
           o.y = pack_bf16x2_rn(f[2], f[3]);
@@ -197,14 +299,17 @@ unpack_dequant_kernel(const uint8_t* __restrict__ q, int64_t rows, int N,
           o.w = pack_bf16x2_rn(f[6], f[7]);
           st_stream_v4(xo + (r0 + r) * ldx + G::slab_col(ct, i), o);
         }
+        // the owner of an outlier column puts the saved value back, after its own store to that spot
+        if (own.n > 0 && !overflow) {
+#pragma unroll
+          for (int t = 0; t < kMaxOwn; ++t)
+            if (t < own.n) xo[(r0 + r) * ldx + own.col[t]] = ov[r][t];
+        }
       }
     }
-    if (k > 0) {
-      // put the full-precision outlier columns back; each block patches only the columns
-      // of its own span, after its own stores to them (block-wide barrier orders the two)
-      __syncthreads();
-      const int cnt = kRowUnroll * k;
-      for (int t = threadIdx.x; t < cnt; t += kThreads) {
+    if (overflow) {
+      __syncthreads();   // the block's stores to these rows come first
+      for (int t = threadIdx.x; t < kRowUnroll * k; t += kThreads) {
         const int64_t row = r0 + t / k;
         const int j = t % k;
         const int64_t c = oidx[j] - col0;
@@ -214,11 +319,15 @@ unpack_dequant_kernel(const uint8_t* __restrict__ q, int64_t rows, int N,
   }
 }
 
-static inline dim3 stream_grid(int64_t rows, int n_ct) {
+// One resident wave: blocks_per_sm * 148 blocks in total, split over the column tiles, so that the
+// per-block set-up (reciprocals, outlier map) is paid once per SM slot and not once per wave.
+template <typename Kernel>
+static inline dim3 stream_grid(Kernel kern, size_t smem, int64_t rows, int n_ct) {
   const int col_tiles = (n_ct + kThreads - 1) / kThreads;
   const int64_t groups = (rows + kRowUnroll - 1) / kRowUnroll;
-  // about eight resident blocks per SM in total, split over the column tiles
-  int64_t slots = (int64_t)(kNumSMs * 8 + col_tiles - 1) / col_tiles;
+  int per_sm = 0;
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, kThreads, smem) != cudaSuccess || per_sm < 1) per_sm = 2;
+  int64_t slots = ((int64_t)kNumSMs * per_sm) / col_tiles;
   if (slots > groups) slots = groups;
   if (slots < 1) slots = 1;
   if (slots > 65535) slots = 65535;
@@ -244,16 +353,15 @@ extern "C" HYC_API int hyc_quant_pack(const void* x, int64_t rows, int N, int64_
   int rc = check_common(x, q_out, rows, N, ldx, q_bit);
   if (rc) return rc;
   if (!scale) return HYC_ERR_NULL;
-  if (k < 0 || k > N) return HYC_ERR_SHAPE;
+  if (k < 0 || k > N || k > 32767) return HYC_ERR_SHAPE;
   if (k > 0 && (!outlier_idx || !outlier_out)) return HYC_ERR_NULL;
   if (!aligned(x, 16) || !aligned(scale, 16) || !aligned(q_out, 8) || (zp && !aligned(zp, 8))) return HYC_ERR_ALIGN;
   if (rows == 0) return HYC_OK;
   cudaStream_t st = (cudaStream_t)stream;
   const int cpt = 8 * (8 / q_bit);
-  dim3 grid = stream_grid(rows, N / cpt);
-  size_t smem = k > 0 ? (size_t)kThreads * cpt : 0;
+  size_t smem = k > 0 ? (size_t)kThreads * cpt * 2 + 16 : 0;   // int16 column map + overflow flag
 #define LAUNCH_Q(QB, ZP)                                                                          \
-  quant_pack_kernel<QB, ZP><<<grid, kThreads, smem, st>>>(                                         \
+  quant_pack_kernel<QB, ZP><<<stream_grid(quant_pack_kernel<QB, ZP>, smem, rows, N / cpt), kThreads, smem, st>>>( \
       (const __nv_bfloat16*)x, rows, N, ldx, (const __nv_bfloat16*)scale, zp, outlier_idx, k,      \
       (uint8_t*)q_out, (__nv_bfloat16*)outlier_out)
   if (zp) {
@@ -273,15 +381,15 @@ extern "C" HYC_API int hyc_unpack_dequant(const void* q, int64_t rows, int N,
   int rc = check_common(q, x_out, rows, N, ldx, q_bit);
   if (rc) return rc;
   if (!scale) return HYC_ERR_NULL;
-  if (k < 0 || k > N) return HYC_ERR_SHAPE;
+  if (k < 0 || k > N || k > 32767) return HYC_ERR_SHAPE;
   if (k > 0 && (!outlier_idx || !outlier)) return HYC_ERR_NULL;
   if (!aligned(x_out, 16) || !aligned(scale, 16) || !aligned(q, 8) || (zp && !aligned(zp, 8))) return HYC_ERR_ALIGN;
   if (rows == 0) return HYC_OK;
   cudaStream_t st = (cudaStream_t)stream;
   const int cpt = 8 * (8 / q_bit);
-  dim3 grid = stream_grid(rows, N / cpt);
+  size_t smem = k > 0 ? (size_t)kThreads * cpt * 2 + 16 : 0;
 #define LAUNCH_D(QB, ZP)                                                                          \
-  unpack_dequant_kernel<QB, ZP><<<grid, kThreads, 0, st>>>(                                        \
+  unpack_dequant_kernel<QB, ZP><<<stream_grid(unpack_dequant_kernel<QB, ZP>, smem, rows, N / cpt), kThreads, smem, st>>>(                                        \
       (const uint8_t*)q, rows, N, (const __nv_bfloat16*)scale, zp, outlier_idx, k,                 \
       (const __nv_bfloat16*)outlier, (__nv_bfloat16*)x_out, ldx)
   if (zp) {
