@@ -116,36 +116,49 @@ __device__ __forceinline__ void quant_store16(const uint32_t (&xw)[8], const Gro
 }
 
 // Load the packed codes of the lane's 16 columns and dequantize them:
-// x_hat = bf16( (code - half - z) * s ), see unpack_dequant_kernel for why this is exact.
+// x_hat = bf16( (code - half - z) * s ).  (code - half - z) is an exact small integer.
+//   q = 2, 4 : packed bf16x2: 0x4300 | code is the bf16 128 + code; subtract 128 + half, subtract z
+//              (both exact), multiply by the scale (one rounding, like the reference's bf16 multiply).
+//   q = 8    : through fp32 (codes reach 255): 0x4B000000 | code is 2^23 + code.
 template <int QBIT>
 __device__ __forceinline__ void load_dequant16(const uint8_t* __restrict__ qrow, int lane_g,
                                                float s, float z, uint32_t (&out)[8]) {
   constexpr uint32_t MASK = (1u << QBIT) - 1u;
-  const float off = 8388608.f + (float)(1 << (QBIT - 1)) + z;
-  uint32_t b[4];
-  int shift0 = 0, shift1 = 0;  // bit offset of the code for columns e<8 and e>=8
   if (QBIT == 8) {
-    uint4 v = ld_stream_v4(qrow + 16 * (int64_t)lane_g);
-    b[0] = v.x; b[1] = v.y; b[2] = v.z; b[3] = v.w;
-  } else if (QBIT == 4) {
-    uint4 v = ld_stream_v4(qrow + 16 * (int64_t)(lane_g >> 1));
-    b[0] = v.x; b[1] = v.y; b[2] = v.z; b[3] = v.w;
-    shift0 = shift1 = 4 * (lane_g & 1);
+    const float off = 8388608.f + (float)(1 << (QBIT - 1)) + z;
+    const uint4 v = ld_stream_v4(qrow + 16 * (int64_t)lane_g);
+    const uint32_t b[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float f0 = (byte_to_magic_float(b[j >> 1], (2 * j) & 3) - off) * s;
+      const float f1 = (byte_to_magic_float(b[j >> 1], ((2 * j) & 3) + 1) - off) * s;
+      out[j] = pack_bf16x2_rn(f0, f1);
+    }
   } else {
-    uint2 v = ld_stream_v2(qrow + 8 * (int64_t)(lane_g >> 1));
-    b[0] = v.x; b[1] = v.y; b[2] = v.x; b[3] = v.y;
-    shift0 = 4 * (lane_g & 1);
-    shift1 = shift0 + 2;
-  }
-  float f[16];
+    constexpr uint32_t BM = MASK * 0x01010101u;
+    constexpr uint32_t C1 = 0x4300u | (uint32_t)(1 << (QBIT - 1));      // bf16 bits of 128 + half
+    const uint32_t c1 = C1 | (C1 << 16);
+    const uint32_t zb = f32_to_bf16bits_rn(z), z2 = zb | (zb << 16);
+    const uint32_t sb = f32_to_bf16bits_rn(s), s2 = sb | (sb << 16);
+    uint32_t w[4];    // codes of columns 4i..4i+3, one per byte
+    if (QBIT == 4) {
+      const uint4 v = ld_stream_v4(qrow + 16 * (int64_t)(lane_g >> 1));
+      const int sh = 4 * (lane_g & 1);          // even lane: low nibbles, odd lane: high nibbles
+      w[0] = (v.x >> sh) & BM; w[1] = (v.y >> sh) & BM; w[2] = (v.z >> sh) & BM; w[3] = (v.w >> sh) & BM;
+    } else {
+      const uint2 v = ld_stream_v2(qrow + 8 * (int64_t)(lane_g >> 1));
+      const int sh = 4 * (lane_g & 1);          // columns 0..7: field sh, columns 8..15: field sh + 2
+      w[0] = (v.x >> sh) & BM; w[1] = (v.y >> sh) & BM; w[2] = (v.x >> (sh + 2)) & BM; w[3] = (v.y >> (sh + 2)) & BM;
+    }
 #pragma unroll
-  for (int e = 0; e < 16; ++e) {
-    uint32_t byte = b[e >> 2] >> (8 * (e & 3));
-    uint32_t code = (byte >> (e < 8 ? shift0 : shift1)) & MASK;
-    f[e] = (__uint_as_float(0x4B000000u | code) - off) * s;
+    for (int j = 0; j < 8; ++j) {
+      const uint32_t pr = __byte_perm(w[j >> 1], 0x43434343u, (j & 1) ? 0x4342u : 0x4140u);
+      __nv_bfloat162 t = __hsub2(*reinterpret_cast<const __nv_bfloat162*>(&pr), *reinterpret_cast<const __nv_bfloat162*>(&c1));
+      t = __hsub2(t, *reinterpret_cast<const __nv_bfloat162*>(&z2));
+      t = __hmul2(t, *reinterpret_cast<const __nv_bfloat162*>(&s2));
+      out[j] = *reinterpret_cast<const uint32_t*>(&t);
+    }
   }
-#pragma unroll
-  for (int j = 0; j < 8; ++j) out[j] = pack_bf16x2_rn(f[2 * j], f[2 * j + 1]);
 }
 
 __device__ __forceinline__ int warp_excl_scan(int v, int lane, int& total) {
@@ -177,8 +190,7 @@ group_quant_kernel(const __nv_bfloat16* __restrict__ x, int64_t rows, int N, int
     const bool valid = col < N;
     uint32_t xw[8];
     if (valid) {
-      uint4 a = ld_stream_v4(x + row * ldx + col), b = ld_stream_v4(x + row * ldx + col + 8);
-      xw[0] = a.x; xw[1] = a.y; xw[2] = a.z; xw[3] = a.w; xw[4] = b.x; xw[5] = b.y; xw[6] = b.z; xw[7] = b.w;
+      ld_stream_v8(x + row * ldx + col, xw);
     } else {
 #pragma unroll
       for (int j = 0; j < 8; ++j) xw[j] = 0u;
@@ -213,8 +225,7 @@ group_dequant_kernel(const uint8_t* __restrict__ q, int64_t rows, int N,
       float z = (float)zp[row * gld + (col >> 6)];
       uint32_t o[8];
       load_dequant16<QBIT>(q + row * qld, lane_g, s, z, o);
-      st_stream_v4(xo + row * ldx + col, make_uint4(o[0], o[1], o[2], o[3]));
-      st_stream_v4(xo + row * ldx + col + 8, make_uint4(o[4], o[5], o[6], o[7]));
+      st_stream_v8(xo + row * ldx + col, o);
     }
   }
 }
@@ -252,9 +263,7 @@ topk_compress_kernel(const __nv_bfloat16* __restrict__ a, int64_t rows, int S, i
     for (int st = 0; st < STEPS; ++st) {
       const int col = 16 * (32 * st + lane);
       if (col < S) {
-        uint4 u = ld_stream_v4(arow + col), v = ld_stream_v4(arow + col + 8);
-        xw[st][0] = u.x; xw[st][1] = u.y; xw[st][2] = u.z; xw[st][3] = u.w;
-        xw[st][4] = v.x; xw[st][5] = v.y; xw[st][6] = v.z; xw[st][7] = v.w;
+        ld_stream_v8(arow + col, xw[st]);
       } else {
 #pragma unroll
         for (int j = 0; j < 8; ++j) xw[st][j] = 0u;
@@ -440,8 +449,7 @@ topk_restore_kernel(const __nv_bfloat16* __restrict__ val, const uint16_t* __res
         float z = (float)zp[row * gld + (col >> 6)];
         uint32_t o[8];
         load_dequant16<QBIT>(q + row * qld, lane_g, s, z, o);
-        st_stream_v4(ao + row * S + col, make_uint4(o[0], o[1], o[2], o[3]));
-        st_stream_v4(ao + row * S + col + 8, make_uint4(o[4], o[5], o[6], o[7]));
+        st_stream_v8(ao + row * S + col, o);
       }
     }
     __syncwarp();   // orders this warp's row stores before the overwrites below
@@ -470,7 +478,7 @@ static int check_group(const void* a, const void* b, int64_t rows, int N, int64_
   if (!a || !b) return HYC_ERR_NULL;
   if (q_bit != 2 && q_bit != 4 && q_bit != 8) return HYC_ERR_QBIT;
   if (rows < 0 || N <= 0 || N % 64 != 0 || ldx < N) return HYC_ERR_SHAPE;
-  if (ldx % 8 != 0) return HYC_ERR_ALIGN;
+  if (ldx % 16 != 0) return HYC_ERR_ALIGN;   // 256-bit row accesses
   return HYC_OK;
 }
 
@@ -479,7 +487,7 @@ extern "C" HYC_API int hyc_group_quant_pack(const void* x, int64_t rows, int N, 
   int rc = check_group(x, q_out, rows, N, ldx, q_bit);
   if (rc) return rc;
   if (!scale_out || !zp_out) return HYC_ERR_NULL;
-  if (!aligned(x, 16) || !aligned(q_out, 16)) return HYC_ERR_ALIGN;
+  if (!aligned(x, 32) || !aligned(q_out, 16)) return HYC_ERR_ALIGN;
   if (rows == 0) return HYC_OK;
   const int64_t items = rows * ((N + 511) / 512);
   cudaStream_t st = (cudaStream_t)stream;
@@ -497,7 +505,7 @@ extern "C" HYC_API int hyc_group_unpack_dequant(const void* q, int64_t rows, int
   int rc = check_group(q, x_out, rows, N, ldx, q_bit);
   if (rc) return rc;
   if (!scale || !zp) return HYC_ERR_NULL;
-  if (!aligned(x_out, 16) || !aligned(q, 16)) return HYC_ERR_ALIGN;
+  if (!aligned(x_out, 32) || !aligned(q, 16)) return HYC_ERR_ALIGN;
   if (rows == 0) return HYC_OK;
   const int64_t items = rows * ((N + 511) / 512);
   cudaStream_t st = (cudaStream_t)stream;
@@ -516,7 +524,7 @@ extern "C" HYC_API int hyc_softmax_topk_compress(const void* a, int64_t rows, in
   if (k > 0 && (!val_out || !col_out)) return HYC_ERR_NULL;
   if (q_bit != 2 && q_bit != 4 && q_bit != 8) return HYC_ERR_QBIT;
   if (rows < 0 || S <= 0 || S % 64 != 0 || S > 4096 || k < 0 || k > S) return HYC_ERR_SHAPE;
-  if (!aligned(a, 16) || !aligned(q_out, 16)) return HYC_ERR_ALIGN;
+  if (!aligned(a, 32) || !aligned(q_out, 16)) return HYC_ERR_ALIGN;
   if (rows == 0) return HYC_OK;
   cudaStream_t st = (cudaStream_t)stream;
   const int steps = (S + 511) / 512;
@@ -538,7 +546,7 @@ extern "C" HYC_API int hyc_softmax_topk_restore(const void* val, const uint16_t*
   if (k > 0 && (!val || !col)) return HYC_ERR_NULL;
   if (q_bit != 2 && q_bit != 4 && q_bit != 8) return HYC_ERR_QBIT;
   if (rows < 0 || S <= 0 || S % 64 != 0 || S > 4096 || k < 0 || k > S) return HYC_ERR_SHAPE;
-  if (!aligned(a_out, 16) || !aligned(q, 16)) return HYC_ERR_ALIGN;
+  if (!aligned(a_out, 32) || !aligned(q, 16)) return HYC_ERR_ALIGN;
   if (rows == 0) return HYC_OK;
   cudaStream_t st = (cudaStream_t)stream;
 #define TR(QB) topk_restore_kernel<QB><<<warp_grid(rows), 256, 0, st>>>((const __nv_bfloat16*)val, col, k, \

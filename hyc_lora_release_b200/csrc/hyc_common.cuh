@@ -131,6 +131,15 @@ __device__ __forceinline__ uint32_t ld_stream_u32(const void* p) {
   asm volatile("ld.global.cs.u32 %0, [%1];" : "=r"(v) : "l"(p));
   return v;
 }
+// 256-bit accesses (sm_100): p must be 32-byte aligned
+__device__ __forceinline__ void ld_stream_v8(const void* p, uint32_t (&v)[8]) {
+  asm volatile("ld.global.cs.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+               : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]) : "l"(p));
+}
+__device__ __forceinline__ void st_stream_v8(void* p, const uint32_t (&v)[8]) {
+  asm volatile("st.global.cs.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(p), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]),
+               "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]) : "memory");
+}
 __device__ __forceinline__ void st_stream_v4(void* p, uint4 v) {
   asm volatile("st.global.cs.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
 }

@@ -47,7 +47,7 @@ struct LoraTerm {
 };
 
 struct Params {
-  int M, N, K1, K2;           // K2 > 0: a second (A2, B2) pair is accumulated into the same tile
+  int M, N, K1, K2, K3;       // K2, K3 > 0: further (A, B) pairs accumulated into the same tile
   int epi, q_bit;
   LoraTerm l0, l1, l2;        // STORE: l0/l1 added; GATEUP: l0 gate, l1 up; GRADDOWN: l0 grad LoRA, l1 gate, l2 up
   const __nv_bfloat16* residual;   // STORE, [M, N] or null
@@ -133,7 +133,9 @@ __device__ __forceinline__ uint64_t make_desc(uint32_t smem_addr, uint32_t lbo_b
 
 __device__ __forceinline__ void epi_bar_sync() { asm volatile("bar.sync 1, %0;" ::"n"(32 * EPI_WARPS) : "memory"); }
 
-__device__ __forceinline__ float bfr(float v) { return bf16bits_to_f32(f32_to_bf16bits_rn(v)); }
+// round to bf16 and back: the value goes into the high half of the packed conversion, where its
+// bits already are the float
+__device__ __forceinline__ float bfr(float v) { return __uint_as_float(pack_bf16x2_rn(0.f, v) & 0xffff0000u); }
 
 // dot of the thread's LoRA-A row (16 floats) with the bf16 LoRA-B row of a column in shared memory
 // (all lanes read the same 32 bytes: a broadcast)
@@ -174,7 +176,7 @@ struct SiluTerms { float y1, sig, y1s, y2, o; };
 __device__ __forceinline__ SiluTerms silu_terms(float x1, float l1, float x2, float l2) {
   SiluTerms r;
   r.y1 = bfr(x1 + bfr(l1));
-  r.sig = bfr(1.f / (1.f + __expf(-r.y1)));
+  r.sig = bfr(__fdividef(1.f, 1.f + __expf(-r.y1)));
   r.y1s = bfr(r.y1 * r.sig);
   r.y2 = bfr(x2 + bfr(l2));
   r.o = bfr(r.y1s * r.y2);
@@ -280,9 +282,9 @@ __device__ __forceinline__ void epi_gateup_block(const Params& p, int64_t row, b
 
 template <int QBIT>
 __device__ __forceinline__ void epi_graddown_block(const Params& p, int64_t row, bool valid, int ncol0, int cb,
-                                                   const uint32_t (&acc)[32], const float (&xg)[16],
+                                                   const uint32_t (&acc)[32],
                                                    const float (&xa1)[16], const float (&xa2)[16],
-                                                   const __nv_bfloat16* sBd, const __nv_bfloat16* sB1, const __nv_bfloat16* sB2,
+                                                   const __nv_bfloat16* sB1, const __nv_bfloat16* sB2,
                                                    const float* sS1, const float* sS2) {
   using G = BlockGeo<QBIT>;
   constexpr float HALF = (float)(1 << (QBIT - 1));
@@ -296,8 +298,7 @@ __device__ __forceinline__ void epi_graddown_block(const Params& p, int64_t row,
 #pragma unroll
     for (int e = 0; e < 8; ++e) {
       const int c = 8 * c8 + e, tc = cb + c;
-      float gd = bfr(__uint_as_float(acc[c]));
-      if (p.l0.bt != nullptr) gd = bfr(gd + bfr(lora_dot(xg, sBd + tc * 16)));
+      const float gd = bfr(__uint_as_float(acc[c]));   // the LoRA part of grad_down arrived as an extra K block
       const float x1 = bfr(((float)get_code<QBIT>(w1, c) - HALF) * sS1[tc]);
       const float x2 = bfr(((float)get_code<QBIT>(w2, c) - HALF) * sS2[tc]);
       const SiluTerms t = silu_terms(x1, lora_dot(xa1, sB1 + tc * 16), x2, lora_dot(xa2, sB2 + tc * 16));
@@ -348,6 +349,7 @@ template <int EPI, int QBIT, bool B_MN>
 __global__ void __launch_bounds__(THREADS, 1)
 mlp_gemm_kernel(const __grid_constant__ CUtensorMap mapA1, const __grid_constant__ CUtensorMap mapB1,
                 const __grid_constant__ CUtensorMap mapA2, const __grid_constant__ CUtensorMap mapB2,
+                const __grid_constant__ CUtensorMap mapA3, const __grid_constant__ CUtensorMap mapB3,
                 const Params p) {
   extern __shared__ uint8_t smem_raw[];
   // 1024-byte alignment for the 128-byte swizzle atoms
@@ -367,7 +369,7 @@ mlp_gemm_kernel(const __grid_constant__ CUtensorMap mapA1, const __grid_constant
   constexpr int TILE_N = (EPI == EPI_GATEUP) ? BN / 2 : BN;     // output columns per tile
   const int tiles_n = p.N / TILE_N;
   const int num_tiles = tiles_m * tiles_n;
-  const int kb1 = p.K1 / BK, kb_total = (p.K1 + p.K2) / BK;
+  const int kb1 = p.K1 / BK, kb2 = (p.K1 + p.K2) / BK, kb_total = (p.K1 + p.K2 + p.K3) / BK;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
@@ -398,10 +400,10 @@ mlp_gemm_kernel(const __grid_constant__ CUtensorMap mapA1, const __grid_constant
             ok = false;
             break;
           }
-          const bool seg2 = kb >= kb1;
-          const CUtensorMap* ma = seg2 ? &mapA2 : &mapA1;
-          const CUtensorMap* mb = seg2 ? &mapB2 : &mapB1;
-          const int k0 = (seg2 ? kb - kb1 : kb) * BK;
+          const int seg = kb < kb1 ? 0 : (kb < kb2 ? 1 : 2);
+          const CUtensorMap* ma = seg == 0 ? &mapA1 : (seg == 1 ? &mapA2 : &mapA3);
+          const CUtensorMap* mb = seg == 0 ? &mapB1 : (seg == 1 ? &mapB2 : &mapB3);
+          const int k0 = (seg == 0 ? kb : (seg == 1 ? kb - kb1 : kb - kb2)) * BK;
           const uint32_t sa = smem_u32(stage_base + stage * STAGE_BYTES);
           const uint32_t sb = sa + STAGE_A_BYTES;
           mbar_expect_tx(&full[stage], STAGE_BYTES);
@@ -497,13 +499,12 @@ mlp_gemm_kernel(const __grid_constant__ CUtensorMap mapA1, const __grid_constant
           sV[2 * BN + et] = b; sV[3 * BN + et] = fastq_scale<QBIT>(__frcp_rn(b));
         }
       } else {
-        stage_lora_tile(p.l0, n0, BN, sB0, et);
         stage_lora_tile(p.l1, n0, BN, sB1, et);
         stage_lora_tile(p.l2, n0, BN, sB2, et);
         sV[et] = __bfloat162float(p.s1[n0 + et]); sV[BN + et] = __bfloat162float(p.s2[n0 + et]);
       }
       float xa0[16], xa1[16], xa2[16];
-      load_xa_row(p.l0.xa, row, valid, xa0);
+      if (EPI != EPI_GRADDOWN) load_xa_row(p.l0.xa, row, valid, xa0);
       load_xa_row(p.l1.xa, row, valid, xa1);
       if (EPI == EPI_GRADDOWN) load_xa_row(p.l2.xa, row, valid, xa2);
       epi_bar_sync();
@@ -531,7 +532,7 @@ mlp_gemm_kernel(const __grid_constant__ CUtensorMap mapA1, const __grid_constant
           const int cb = 128 * chalf + 32 * ch;
           tc_ld32(t_lane + (uint32_t)cb, acc);
           if (EPI == EPI_STORE) epi_store_block(p, row, valid, n0, cb, acc, xa0, xa1, sB0, sB1);
-          else epi_graddown_block<QBIT>(p, row, valid, n0, cb, acc, xa0, xa1, xa2, sB0, sB1, sB2, sV, sV + BN);
+          else epi_graddown_block<QBIT>(p, row, valid, n0, cb, acc, xa1, xa2, sB1, sB2, sV, sV + BN);
         }
       }
       tc_fence_before();
@@ -583,7 +584,7 @@ static bool make_map(CUtensorMap* m, const void* ptr, int64_t rows, int64_t cols
 
 template <int EPI, int QBIT, bool B_MN>
 static int launch(const CUtensorMap& a1, const CUtensorMap& b1, const CUtensorMap& a2, const CUtensorMap& b2,
-                  const Params& p, cudaStream_t st) {
+                  const CUtensorMap& a3, const CUtensorMap& b3, const Params& p, cudaStream_t st) {
   auto kern = mlp_gemm_kernel<EPI, QBIT, B_MN>;
   static bool attr = false;
   if (!attr) {
@@ -596,7 +597,7 @@ static int launch(const CUtensorMap& a1, const CUtensorMap& b1, const CUtensorMa
   constexpr int TILE_N = (EPI == EPI_GATEUP) ? BN / 2 : BN;
   const int tiles = ((p.M + BM - 1) / BM) * (p.N / TILE_N);
   const int grid = tiles < kNumSMs ? tiles : kNumSMs;
-  kern<<<grid, THREADS, SMEM_BYTES, st>>>(a1, b1, a2, b2, p);
+  kern<<<grid, THREADS, SMEM_BYTES, st>>>(a1, b1, a2, b2, a3, b3, p);
   HYC_CHECK_LAUNCH();
   return HYC_OK;
 }
@@ -618,28 +619,35 @@ static LoraTerm make_term(const void* xa, const void* bt, int64_t ld_col, int64_
 
 extern "C" HYC_API int hyc_gemm_bf16_tcgen05(
     const void* A, const void* B, int M, int N, int K, int b_is_kn,
-    const void* A2, const void* B2, int K2,
+    const void* A2, const void* B2, int K2, const void* A3, const void* B3, int K3,
     const void* xa0, const void* bt0, int64_t bt0_ld_col, int64_t bt0_ld_r,
     const void* xa1, const void* bt1, int64_t bt1_ld_col, int64_t bt1_ld_r,
     const void* residual, void* D, int* status, void* stream) {
   if (!A || !B || !D || !status) return HYC_ERR_NULL;
   if ((K2 > 0) != (A2 != nullptr && B2 != nullptr)) return HYC_ERR_NULL;
-  if (M <= 0 || N <= 0 || K <= 0 || N % BN != 0 || K % BK != 0 || K2 < 0 || K2 % BK != 0) return HYC_ERR_SHAPE;
+  if ((K3 > 0) != (A3 != nullptr && B3 != nullptr)) return HYC_ERR_NULL;
+  if (M <= 0 || N <= 0 || K <= 0 || N % BN != 0 || K % BK != 0 || K2 < 0 || K2 % BK != 0 || K3 < 0 || K3 % BK != 0)
+    return HYC_ERR_SHAPE;
   if (!aligned(A, 16) || !aligned(B, 16) || !aligned(D, 16) || (residual && !aligned(residual, 16)) ||
-      (xa0 && !aligned(xa0, 16)) || (xa1 && !aligned(xa1, 16))) return HYC_ERR_ALIGN;
+      (xa0 && !aligned(xa0, 16)) || (xa1 && !aligned(xa1, 16)) || (A2 && (!aligned(A2, 16) || !aligned(B2, 16))) ||
+      (A3 && (!aligned(A3, 16) || !aligned(B3, 16)))) return HYC_ERR_ALIGN;
   if ((bt0 != nullptr) != (xa0 != nullptr) || (bt1 != nullptr) != (xa1 != nullptr)) return HYC_ERR_NULL;
-  CUtensorMap a1, b1, a2, b2;
+  CUtensorMap a1, b1, a2, b2, a3, b3;
   bool ok = make_map(&a1, A, M, K, BM);
   ok = ok && (b_is_kn ? make_map(&b1, B, K, N, 64) : make_map(&b1, B, N, K, 64));
+  a2 = a1; b2 = b1;
   if (K2 > 0) {
     ok = ok && make_map(&a2, A2, M, K2, BM);
     ok = ok && (b_is_kn ? make_map(&b2, B2, K2, N, 64) : make_map(&b2, B2, N, K2, 64));
-  } else {
-    a2 = a1; b2 = b1;
+  }
+  a3 = a1; b3 = b1;
+  if (K3 > 0) {
+    ok = ok && make_map(&a3, A3, M, K3, BM);
+    ok = ok && (b_is_kn ? make_map(&b3, B3, K3, N, 64) : make_map(&b3, B3, N, K3, 64));
   }
   if (!ok) return HYC_ERR_UNSUPPORTED;
   Params p = {};
-  p.M = M; p.N = N; p.K1 = K; p.K2 = K2; p.epi = EPI_STORE; p.q_bit = 0;
+  p.M = M; p.N = N; p.K1 = K; p.K2 = K2; p.K3 = K3; p.epi = EPI_STORE; p.q_bit = 0;
   p.l0 = make_term(xa0, bt0, bt0_ld_col, bt0_ld_r);
   p.l1 = make_term(xa1, bt1, bt1_ld_col, bt1_ld_r);
   p.l2 = make_term(nullptr, nullptr, 0, 0);
@@ -647,7 +655,8 @@ extern "C" HYC_API int hyc_gemm_bf16_tcgen05(
   p.out0 = (__nv_bfloat16*)D;
   p.status = status;
   cudaStream_t st = (cudaStream_t)stream;
-  return b_is_kn ? launch<EPI_STORE, 4, true>(a1, b1, a2, b2, p, st) : launch<EPI_STORE, 4, false>(a1, b1, a2, b2, p, st);
+  return b_is_kn ? launch<EPI_STORE, 4, true>(a1, b1, a2, b2, a3, b3, p, st)
+                 : launch<EPI_STORE, 4, false>(a1, b1, a2, b2, a3, b3, p, st);
 }
 
 extern "C" HYC_API int hyc_mlp_gateup_fwd_tcgen05(
@@ -664,7 +673,7 @@ extern "C" HYC_API int hyc_mlp_gateup_fwd_tcgen05(
   CUtensorMap a1, bg, bu;
   if (!make_map(&a1, x, T, H, BM) || !make_map(&bg, wg, I, H, 64) || !make_map(&bu, wu, I, H, 64)) return HYC_ERR_UNSUPPORTED;
   Params p = {};
-  p.M = T; p.N = I; p.K1 = H; p.K2 = 0; p.epi = EPI_GATEUP; p.q_bit = q_bit;
+  p.M = T; p.N = I; p.K1 = H; p.K2 = 0; p.K3 = 0; p.epi = EPI_GATEUP; p.q_bit = q_bit;
   p.l0 = make_term(xa1, b1t, b1_ld_col, b1_ld_r);
   p.l1 = make_term(xa2, b2t, b2_ld_col, b2_ld_r);
   p.l2 = make_term(nullptr, nullptr, 0, 0);
@@ -675,32 +684,34 @@ extern "C" HYC_API int hyc_mlp_gateup_fwd_tcgen05(
   p.status = status;
   cudaStream_t st = (cudaStream_t)stream;
   // the A2 slot is unused; mapB2 carries the up-projection weight
-  if (q_bit == 2) return launch<EPI_GATEUP, 2, false>(a1, bg, a1, bu, p, st);
-  if (q_bit == 4) return launch<EPI_GATEUP, 4, false>(a1, bg, a1, bu, p, st);
-  return launch<EPI_GATEUP, 8, false>(a1, bg, a1, bu, p, st);
+  if (q_bit == 2) return launch<EPI_GATEUP, 2, false>(a1, bg, a1, bu, a1, bg, p, st);
+  if (q_bit == 4) return launch<EPI_GATEUP, 4, false>(a1, bg, a1, bu, a1, bg, p, st);
+  return launch<EPI_GATEUP, 8, false>(a1, bg, a1, bu, a1, bg, p, st);
 }
 
 extern "C" HYC_API int hyc_mlp_graddown_bwd_tcgen05(
     const void* g, const void* wd, int T, int H, int I,
-    const void* gdm, const void* adt, int64_t ad_ld_col, int64_t ad_ld_r,
+    const void* a_lora, const void* b_lora, int k_lora,
     const void* xa1, const void* b1t, int64_t b1_ld_col, int64_t b1_ld_r,
     const void* xa2, const void* b2t, int64_t b2_ld_col, int64_t b2_ld_r,
     const void* q1, const void* s1, const void* q2, const void* s2,
     void* o, void* grad_gate, void* grad_up, int q_bit, int* status, void* stream) {
   if (!g || !wd || !xa1 || !b1t || !xa2 || !b2t || !q1 || !s1 || !q2 || !s2 || !o || !grad_gate || !grad_up || !status)
     return HYC_ERR_NULL;
-  if ((gdm != nullptr) != (adt != nullptr)) return HYC_ERR_NULL;
+  if ((k_lora > 0) != (a_lora != nullptr && b_lora != nullptr)) return HYC_ERR_NULL;
   if (q_bit != 2 && q_bit != 4 && q_bit != 8) return HYC_ERR_QBIT;
-  if (T <= 0 || H <= 0 || I <= 0 || I % BN != 0 || H % BK != 0) return HYC_ERR_SHAPE;
+  if (T <= 0 || H <= 0 || I <= 0 || I % BN != 0 || H % BK != 0 || k_lora < 0 || k_lora % BK != 0) return HYC_ERR_SHAPE;
   const void* al[] = {g, wd, xa1, xa2, q1, q2, o, grad_gate, grad_up};
   for (const void* q : al) if (!aligned(q, 16)) return HYC_ERR_ALIGN;
-  if (gdm && !aligned(gdm, 16)) return HYC_ERR_ALIGN;
-  CUtensorMap a1, b1;
+  if (a_lora && (!aligned(a_lora, 16) || !aligned(b_lora, 16))) return HYC_ERR_ALIGN;
+  CUtensorMap a1, b1, a2, b2;
   // wd is [H, I] row-major: the K = H rows are the reduction dimension, so B is MN-major
   if (!make_map(&a1, g, T, H, BM) || !make_map(&b1, wd, H, I, 64)) return HYC_ERR_UNSUPPORTED;
+  a2 = a1; b2 = b1;
+  if (k_lora > 0 && (!make_map(&a2, a_lora, T, k_lora, BM) || !make_map(&b2, b_lora, k_lora, I, 64))) return HYC_ERR_UNSUPPORTED;
   Params p = {};
-  p.M = T; p.N = I; p.K1 = H; p.K2 = 0; p.epi = EPI_GRADDOWN; p.q_bit = q_bit;
-  p.l0 = make_term(gdm, adt, ad_ld_col, ad_ld_r);
+  p.M = T; p.N = I; p.K1 = H; p.K2 = k_lora; p.K3 = 0; p.epi = EPI_GRADDOWN; p.q_bit = q_bit;
+  p.l0 = make_term(nullptr, nullptr, 0, 0);
   p.l1 = make_term(xa1, b1t, b1_ld_col, b1_ld_r);
   p.l2 = make_term(xa2, b2t, b2_ld_col, b2_ld_r);
   p.out0 = (__nv_bfloat16*)o; p.out1 = (__nv_bfloat16*)grad_gate; p.out2 = (__nv_bfloat16*)grad_up;
@@ -708,7 +719,7 @@ extern "C" HYC_API int hyc_mlp_graddown_bwd_tcgen05(
   p.s1 = (const __nv_bfloat16*)s1; p.s2 = (const __nv_bfloat16*)s2;
   p.status = status;
   cudaStream_t st = (cudaStream_t)stream;
-  if (q_bit == 2) return launch<EPI_GRADDOWN, 2, true>(a1, b1, a1, b1, p, st);
-  if (q_bit == 4) return launch<EPI_GRADDOWN, 4, true>(a1, b1, a1, b1, p, st);
-  return launch<EPI_GRADDOWN, 8, true>(a1, b1, a1, b1, p, st);
+  if (q_bit == 2) return launch<EPI_GRADDOWN, 2, true>(a1, b1, a2, b2, a1, b1, p, st);
+  if (q_bit == 4) return launch<EPI_GRADDOWN, 4, true>(a1, b1, a2, b2, a1, b1, p, st);
+  return launch<EPI_GRADDOWN, 8, true>(a1, b1, a2, b2, a1, b1, p, st);
 }

@@ -223,11 +223,16 @@ unpack_dequant_kernel(const uint8_t* __restrict__ q, int64_t rows, int N,
   int* s_overflow = reinterpret_cast<int*>(s_dyn + 2 * span_cols);
   if (k > 0) build_outlier_map(s_map, s_overflow, span_cols, col0, oidx, k);
 
-  // x_hat = bf16( bf16(code - half [- z]) * s ).  (code - half - z) is an integer of
-  // magnitude <= 255, exact in bf16 and in fp32; the fp32 product of two bf16 values is
-  // exact, so one rounding to bf16 reproduces the reference's bf16 multiply.
-  // 0x4B000000 | code is the float 2^23 + code; `off` folds 2^23 + half + z.
-  float s[EPP][8], off[EPP][8];
+  // x_hat = bf16( bf16(code - half [- z]) * s ).  (code - half - z) is an integer of magnitude
+  // <= 255, exact in bf16; the product of two bf16 values rounded once to bf16 is the reference's
+  // bf16 multiply.
+  //   q = 2, 4 : packed bf16x2 arithmetic on two columns at a time.  0x4300 | code is the bf16
+  //              128 + code; one byte-permute builds the pair, one packed subtract removes
+  //              128 + half (+ z), one packed multiply applies the scale pair as loaded.
+  //   q = 8    : codes reach 255, so the integer goes through fp32: 0x4B000000 | code is 2^23 + code.
+  constexpr bool PACKED = QBIT < 8;
+  uint32_t s2[EPP][4], off2[(PACKED && HAS_ZP) ? EPP : 1][4];
+  float s[PACKED ? 1 : EPP][8], off[PACKED ? 1 : EPP][8];
   OwnOutliers own;
   own.n = 0;
 #pragma unroll
@@ -244,10 +249,19 @@ unpack_dequant_kernel(const uint8_t* __restrict__ q, int64_t rows, int N,
       if (k > 0) mv = *reinterpret_cast<const uint4*>(s_map + (c - col0));
       const uint32_t mw[4] = {mv.x, mv.y, mv.z, mv.w};
 #pragma unroll
+      for (int j = 0; j < 4; ++j) s2[i][j] = sw[j];
+#pragma unroll
       for (int e = 0; e < 8; ++e) {
-        s[i][e] = (e & 1) ? bf16hi_to_f32(sw[e >> 1]) : bf16lo_to_f32(sw[e >> 1]);
         int zb = HAS_ZP ? (int)(int8_t)(((e < 4 ? zv.x : zv.y) >> (8 * (e & 3))) & 0xffu) : 0;
-        off[i][e] = 8388608.f + (float)((1 << (QBIT - 1)) + zb);
+        if (PACKED) {
+          if (HAS_ZP) {
+            const uint32_t ob = f32_to_bf16bits_rn((float)zb);   // |z| <= 128: exact in bf16
+            if (e & 1) off2[i][e >> 1] |= ob << 16; else off2[i][e >> 1] = ob;
+          }
+        } else {
+          s[i][e] = (e & 1) ? bf16hi_to_f32(sw[e >> 1]) : bf16lo_to_f32(sw[e >> 1]);
+          off[i][e] = 8388608.f + (float)((1 << (QBIT - 1)) + zb);
+        }
         const int jv = (int)(int16_t)((mw[e >> 1] >> (16 * (e & 1))) & 0xffffu);
         if (jv >= 0) {
 #pragma unroll
@@ -288,15 +302,33 @@ unpack_dequant_kernel(const uint8_t* __restrict__ q, int64_t rows, int N,
           // the codes of slab i, one per byte, then each byte straight into the float 2^23 + code
           constexpr uint32_t BM = MASK * 0x01010101u;
           const uint32_t f0 = (p[r].x >> (QBIT * i)) & BM, f1 = (p[r].y >> (QBIT * i)) & BM;
-          float f[8];
-#pragma unroll
-          for (int e = 0; e < 8; ++e)
-            f[e] = (byte_to_magic_float(e < 4 ? f0 : f1, e & 3) - off[i][e]) * s[i][e];
           uint4 o;
-          o.x = pack_bf16x2_rn(f[0], f[1]);
-          o.y = pack_bf16x2_rn(f[2], f[3]);
-          o.z = pack_bf16x2_rn(f[4], f[5]);
-          o.w = pack_bf16x2_rn(f[6], f[7]);
+          if (PACKED) {
+            constexpr uint32_t C1 = 0x4300u + (uint32_t)((1 << (QBIT - 1)) << 0);   // bf16 bits of 128 + half (half < 128)
+            uint32_t ow[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              // bytes 2j, 2j+1 of the slab -> the bf16 pair (128 + code, 128 + code)
+              const uint32_t pr = __byte_perm(j < 2 ? f0 : f1, 0x43434343u, 0x4040u | (uint32_t)((2 * j) & 3) | ((uint32_t)(((2 * j) & 3) + 1) << 8));
+              const uint32_t sub = C1 | (C1 << 16);
+              __nv_bfloat162 v = __hsub2(*reinterpret_cast<const __nv_bfloat162*>(&pr),
+                                         *reinterpret_cast<const __nv_bfloat162*>(&sub));
+              // code - half in [-8, 7] minus z in [-128, 127]: still an exact bf16 integer
+              if (HAS_ZP) v = __hsub2(v, *reinterpret_cast<const __nv_bfloat162*>(&off2[i][j]));
+              const __nv_bfloat162 m = __hmul2(v, *reinterpret_cast<const __nv_bfloat162*>(&s2[i][j]));
+              ow[j] = *reinterpret_cast<const uint32_t*>(&m);
+            }
+            o = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+          } else {
+            float f[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e)
+              f[e] = (byte_to_magic_float(e < 4 ? f0 : f1, e & 3) - off[i][e]) * s[i][e];
+            o.x = pack_bf16x2_rn(f[0], f[1]);
+            o.y = pack_bf16x2_rn(f[2], f[3]);
+            o.z = pack_bf16x2_rn(f[4], f[5]);
+            o.w = pack_bf16x2_rn(f[6], f[7]);
+          }
           st_stream_v4(xo + (r0 + r) * ldx + G::slab_col(ct, i), o);
         }
         // the owner of an outlier column puts the saved value back, after its own store to that spot

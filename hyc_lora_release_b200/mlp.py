@@ -46,8 +46,9 @@ def _lora(xa, bt, ld_col, ld_r):
     return [ptr(xa), ptr(bt), ld_col, ld_r]
 
 
-def gemm(a, b, *, b_is_kn=False, a2=None, b2=None, lora0=None, lora1=None, residual=None, status=None):
-    """D = a @ op(b) (+ a2 @ op(b2)) (+ LoRA terms) (+ residual) on the tcgen05 kernel.
+def gemm(a, b, *, b_is_kn=False, a2=None, b2=None, a3=None, b3=None, lora0=None, lora1=None, residual=None,
+         status=None):
+    """D = a @ op(b) (+ a2 @ op(b2)) (+ a3 @ op(b3)) (+ LoRA terms) (+ residual) on the tcgen05 kernel.
 
     a [M,K] bf16; b [N,K] (b_is_kn=False) or [K,N] (b_is_kn=True), both row-major.
     lora = (xa [M,16], bt, ld_col, ld_r): adds xa @ Bt^T with Bt(col, r) = bt[col*ld_col + r*ld_r]."""
@@ -55,12 +56,14 @@ def gemm(a, b, *, b_is_kn=False, a2=None, b2=None, lora0=None, lora1=None, resid
     M, K = a.shape
     N = b.shape[1] if b_is_kn else b.shape[0]
     K2 = 0 if a2 is None else a2.shape[1]
+    K3 = 0 if a3 is None else a3.shape[1]
     d = torch.empty((M, N), dtype=BF16, device=a.device)
     st = status if status is not None else _status_tensor(a.device)
     l0 = _lora(*lora0) if lora0 else [None, None, 0, 0]
     l1 = _lora(*lora1) if lora1 else [None, None, 0, 0]
     check(lib.hyc_gemm_bf16_tcgen05(ptr(a), ptr(b), M, N, K, 1 if b_is_kn else 0, ptr(a2), ptr(b2), K2,
-                                    *l0, *l1, ptr(residual), ptr(d), ptr(st), stream_of(a)), "hyc_gemm_bf16_tcgen05")
+                                    ptr(a3), ptr(b3), K3, *l0, *l1, ptr(residual), ptr(d), ptr(st), stream_of(a)),
+          "hyc_gemm_bf16_tcgen05")
     return d
 
 
@@ -77,6 +80,25 @@ class MLPWeights:
     bu: torch.Tensor
     ad: torch.Tensor       # down lora_A.weight [r, I]
     bd: torch.Tensor       # down lora_B.weight [H, r]
+
+    def padded(self):
+        """LoRA factors zero-padded to a K of 64 so that a rank-16 product can ride along a GEMM as one more
+        K block (built once per optimizer step; a few hundred KB):
+          ad_rows  [64, I]  rows 0..15 = Ad            (second operand of grad_down's LoRA part, [K, N])
+          ad_cols  [I, 64]  columns 0..15 = Ad^T       (projects hadamard to the padded down LoRA activation)
+          bd_cols  [H, 64]  columns 0..15 = Bd         (second operand of the down projection's LoRA part, [N, K])
+          agu_rows [64, H]  rows 0..15 = Ag, 16..31 = Au (second operand of grad_x's LoRA part, [K, N])"""
+        key = tuple(t._version for t in (self.ag, self.au, self.ad, self.bd))
+        if getattr(self, "_pad_key", None) != key:
+            r, I = self.ad.shape
+            H = self.bd.shape[0]
+            dev, dt = self.ad.device, self.ad.dtype
+            ad_rows = torch.zeros(64, I, dtype=dt, device=dev); ad_rows[:r] = self.ad
+            bd_cols = torch.zeros(H, 64, dtype=dt, device=dev); bd_cols[:, :r] = self.bd
+            agu_rows = torch.zeros(64, H, dtype=dt, device=dev); agu_rows[:r] = self.ag; agu_rows[r:2 * r] = self.au
+            self._pad = dict(ad_rows=ad_rows, ad_cols=ad_rows.t().contiguous(), bd_cols=bd_cols, agu_rows=agu_rows)
+            self._pad_key = key
+        return self._pad
 
 
 @dataclass
@@ -140,8 +162,11 @@ def mlp_forward(x_medium, w: MLPWeights, state: MLPState, eps=1e-5, status=None)
     xn_q, xn_scale = cf.compression_pack_quant_base(x_norm, q, 'per-channel', state.iteration,
                                                     state.iteration_threshold, sv['x_norm_2'])
     had2 = had.reshape(T, I)
-    down_xa = had2 @ w.ad.t()
-    x_out = gemm(had2, w.wd, lora0=(down_xa, w.bd, 16, 1), residual=x_medium.reshape(T, H).contiguous(), status=st)
+    pad = w.padded()
+    down_xa64 = had2 @ pad["ad_cols"]              # [T, 64]: the LoRA-A activation of the down projection, zero-padded
+    down_xa = down_xa64[:, :16]
+    # down = hadamard @ Wd^T + down_xa @ Bd^T (one more K block) + residual
+    x_out = gemm(had2, w.wd, a2=down_xa64, b2=pad["bd_cols"], residual=x_medium.reshape(T, H).contiguous(), status=st)
 
     if calib:
         it = state.iteration
@@ -167,28 +192,31 @@ def mlp_backward(grad_out, saved, w: MLPWeights, status=None):
     g = grad_out.to(BF16).reshape(T, H).contiguous()
     down_xa, gate_xa, up_xa = saved['down_xa'], saved['gate_xa'], saved['up_xa']
 
+    pad = w.padded()
     grad_bd = g.t() @ down_xa                      # [H, r]
-    gdm = g @ w.bd                                 # [T, r]
+    gdm64 = g @ pad["bd_cols"]                     # [T, 64], first 16 columns = g @ Bd
+    gdm = gdm64[:, :16]
     had = torch.empty((T, I), dtype=BF16, device=dev)
     gg = torch.empty((T, I), dtype=BF16, device=dev)
     gu = torch.empty((T, I), dtype=BF16, device=dev)
     check(lib.hyc_mlp_graddown_bwd_tcgen05(
-        ptr(g), ptr(w.wd), T, H, I, ptr(gdm), ptr(w.ad), 1, I,
+        ptr(g), ptr(w.wd), T, H, I, ptr(gdm64), ptr(pad["ad_rows"]), 64,
         ptr(gate_xa), ptr(w.bg), 16, 1, ptr(up_xa), ptr(w.bu), 16, 1,
         ptr(saved['gate_q']), ptr(saved['gate_scale']), ptr(saved['up_q']), ptr(saved['up_scale']),
         ptr(had), ptr(gg), ptr(gu), q, ptr(st), stream_of(grad_out)), "hyc_mlp_graddown_bwd_tcgen05")
     grad_ad = gdm.t() @ had                        # [r, I]
 
     x_norm = cf.decompression_dequantization(saved['xn_q'], saved['xn_scale'], q).reshape(T, H)
-    gm_gate = gg @ w.bg                            # [T, r]
-    gm_up = gu @ w.bu
+    gm64 = torch.zeros((T, 64), dtype=BF16, device=dev)
+    gm64[:, :16] = gg @ w.bg                       # [T, r] each, side by side in a zero-padded K block
+    gm64[:, 16:32] = gu @ w.bu
+    gm_gate, gm_up = gm64[:, :16], gm64[:, 16:32]
     grad_ag = gm_gate.t() @ x_norm                 # [r, H]
     grad_au = gm_up.t() @ x_norm
     grad_bg = gg.t() @ gate_xa                     # [I, r]
     grad_bu = gu.t() @ up_xa
     # grad wrt x_norm: gate and up products accumulate in one tensor-memory tile
-    grad_xn = gemm(gg, w.wg, b_is_kn=True, a2=gu, b2=w.wu,
-                   lora0=(gm_gate, w.ag, 1, H), lora1=(gm_up, w.au, 1, H), status=st)
+    grad_xn = gemm(gg, w.wg, b_is_kn=True, a2=gu, b2=w.wu, a3=gm64, b3=pad["agu_rows"], status=st)
     x_medium = cf.outlier_addition_fuse_decompression_dequantization(
         saved['xm_q'], saved['xm_scale'], saved['xm_o'], saved['xm_idx'], q)
     grad_norm, _ = rmsnorm_backward(grad_xn.reshape(B, M, H), x_medium, w.norm_w, None, saved['rstd'], True, 1e-5, 0, 0)

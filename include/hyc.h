@@ -172,14 +172,17 @@ int hyc_softmax_bwd(const void* y, const void* g, void* o, int64_t rows, int S, 
  * factor as element (column, r) at bt[column * ld_col + r * ld_r], so both the [out, r] weight and
  * its [r, out] transpose can be passed without a copy. */
 
-/* D[M,N] = A[M,K] * B (+ A2[M,K2] * B2) (+ xa0 * bt0^T) (+ xa1 * bt1^T) (+ residual), each partial
- * rounded to bf16 like the reference's tensor-by-tensor code.  b_is_kn = 0: B is [N,K] row-major (an
- * nn.Linear weight, forward use); 1: B is [K,N] row-major (the same weight used for a backward
- * product, read in place).  N % 256 == 0, K % 64 == 0.
+/* D[M,N] = A[M,K] * B (+ A2[M,K2] * B2) (+ A3[M,K3] * B3) (+ xa0 * bt0^T) (+ xa1 * bt1^T) (+ residual).
+ * Up to three (A, B) pairs accumulate in the same tensor-memory tile; K2, K3 may be 0.  A rank-16 LoRA
+ * product can be passed either as an extra pair whose K is padded with zeros to 64 (it then costs one more
+ * MMA block and nothing in the epilogue) or as xa/bt, evaluated per element in the epilogue and rounded to
+ * bf16 separately like the reference's tensor-by-tensor code.
+ * b_is_kn = 0: every B is [N,K] row-major (an nn.Linear weight, forward use); 1: every B is [K,N] row-major
+ * (the same weight used for a backward product, read in place).  N % 256 == 0, K, K2, K3 % 64 == 0.
  * Replaces the matmuls of lora_forward / lora_backward (models/utils/compute_utils.py:18-36) and the
  * hand-inlined copies (models/llama/fused_llama_layer_intra_inter_full_fuse.py:247, 359-364, 379-384). */
 int hyc_gemm_bf16_tcgen05(const void* A, const void* B, int M, int N, int K, int b_is_kn,
-                          const void* A2, const void* B2, int K2,
+                          const void* A2, const void* B2, int K2, const void* A3, const void* B3, int K3,
                           const void* xa0, const void* bt0, int64_t bt0_ld_col, int64_t bt0_ld_r,
                           const void* xa1, const void* bt1, int64_t bt1_ld_col, int64_t bt1_ld_r,
                           const void* residual, void* D, int* status, void* stream);
@@ -196,12 +199,15 @@ int hyc_mlp_gateup_fwd_tcgen05(const void* x, const void* wg, const void* wu, in
                                const void* s1, const void* s2, void* q1, void* q2, void* o,
                                void* main1_or_null, void* main2_or_null, int q_bit, int* status, void* stream);
 
-/* grad_down = g * wd (+ gdm * ad^T) and triton_fuse_silu_backward in one kernel
+/* grad_down = g * wd (+ a_lora * b_lora) and triton_fuse_silu_backward in one kernel
  * (fused_llama_layer_intra_inter_full_fuse.py:359-369 + triton_fuse_lora_silu_hadamard_backward_kernels.py):
  * the epilogue unpacks and de-quantizes the saved gate/up codes, recomputes the forward and writes
- * o (hadamard), grad_gate, grad_up [T,I].  g [T,H], wd [H,I] (the down weight as stored).  I % 256 == 0. */
+ * o (hadamard), grad_gate, grad_up [T,I].  g [T,H], wd [H,I] (the down weight as stored).  I % 256 == 0.
+ * The LoRA part of grad_down, (g * Bd^T) * Ad, is passed as a zero-padded extra K block:
+ * a_lora [T, k_lora] (the rank-16 product g * Bd^T in its first columns), b_lora [k_lora, I] (Ad in its
+ * first rows), k_lora a multiple of 64 or 0. */
 int hyc_mlp_graddown_bwd_tcgen05(const void* g, const void* wd, int T, int H, int I,
-                                 const void* gdm, const void* adt, int64_t ad_ld_col, int64_t ad_ld_r,
+                                 const void* a_lora, const void* b_lora, int k_lora,
                                  const void* xa1, const void* b1t, int64_t b1_ld_col, int64_t b1_ld_r,
                                  const void* xa2, const void* b2t, int64_t b2_ld_col, int64_t b2_ld_r,
                                  const void* q1, const void* s1, const void* q2, const void* s2,

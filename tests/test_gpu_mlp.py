@@ -61,6 +61,12 @@ def test_gemm_two_segments_lora_residual(mlp):
     mlp.check_status(st, "gemm")
     ref = a.float() @ b.float() + a2.float() @ b2.float() + xa0.float() @ w0.float() + xa1.float() @ w1.float().t() + res.float()
     assert close(d, ref, rel=6e-3)
+    # the same LoRA products as a third, zero-padded K segment instead of epilogue terms
+    a3 = torch.zeros(M, 64, dtype=BF16); a3[:, :R] = xa0; a3[:, R:2 * R] = xa1
+    b3 = torch.zeros(64, N, dtype=BF16); b3[:R] = w0; b3[R:2 * R] = w1.t()
+    d3 = mlp.gemm(a_, b_, b_is_kn=True, a2=a2_, b2=b2_, a3=a3.to(DEV), b3=b3.to(DEV), residual=res_, status=st)
+    mlp.check_status(st, "gemm")
+    assert close(d3, ref, rel=6e-3)
 
 
 def _mlp_problem(g, B, M, H, I, R=16):
@@ -106,13 +112,15 @@ def test_gateup_and_graddown_epilogues(mlp, q):
     gout = _randn(g, T, H)
     gdm, ad = _randn(g, T, R), _randn(g, R, I, scale=0.05)
     had = torch.empty(T, I, dtype=BF16, device=DEV); gg = torch.empty_like(had); gu = torch.empty_like(had)
-    goutd, gdmd, add = map(d, (gout, gdm, ad))
-    check(lib.hyc_mlp_graddown_bwd_tcgen05(ptr(goutd), ptr(wdd), T, H, I, ptr(gdmd), ptr(add), 1, I,
+    gdm64 = torch.zeros(T, 64, dtype=BF16); gdm64[:, :R] = gdm      # the LoRA part rides along as a padded K block
+    ad64 = torch.zeros(64, I, dtype=BF16); ad64[:R] = ad
+    goutd, gdmd, add = map(d, (gout, gdm64, ad64))
+    check(lib.hyc_mlp_graddown_bwd_tcgen05(ptr(goutd), ptr(wdd), T, H, I, ptr(gdmd), ptr(add), 64,
                                            ptr(xa1d), ptr(bgd), 16, 1, ptr(xa2d), ptr(bud), 16, 1,
                                            ptr(q1), ptr(s1d), ptr(q2), ptr(s2d), ptr(had), ptr(gg), ptr(gu), q,
                                            ptr(st), stream_of(xd)), "graddown")
     mlp.check_status(st, "graddown")
-    grad_down = ((gout.float() @ wd.float()).to(BF16) + (gdm.float() @ ad.float()).to(BF16)).to(BF16)
+    grad_down = (gout.float() @ wd.float() + gdm.float() @ ad.float()).to(BF16)
     ob, ogg, ogu = oracle.ref_fused_silu_backward(xa1[None], bg.t(), q1.cpu()[None], s1[None], xa2[None], bu.t(),
                                                   q2.cpu()[None], s2[None], grad_down[None], q)
     assert close(had, ob[0]) and close(gg, ogg[0]) and close(gu, ogu[0])
