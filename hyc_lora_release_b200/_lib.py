@@ -38,6 +38,8 @@ SIGNATURES = {
     "hyc_rmsnorm_fwd": (_i, [_p, _p, _f, _p, _p, _l, _i, _p]),
     "hyc_rmsnorm_bwd": (_i, [_p, _p, _p, _p, _p, _l, _i, _p]),
     "hyc_softmax_bwd": (_i, [_p, _p, _p, _l, _i, _p]),
+    "hyc_lora_grad_a_workspace_bytes": (_z, [_i, _i, _i]),
+    "hyc_lora_grad_a_dequant": (_i, [_p, _p, _p, _l, _i, _i, _i, _i, _p, _p, _z, _p]),
     "hyc_gemm_bf16_tcgen05": (_i, [_p, _p, _i, _i, _i, _i, _p, _p, _i, _p, _p, _i,
                                    _p, _p, _l, _l, _p, _p, _l, _l, _p, _p, _p, _p]),
     "hyc_mlp_gateup_fwd_tcgen05": (_i, [_p, _p, _p, _i, _i, _i, _p, _p, _l, _l, _p, _p, _l, _l,

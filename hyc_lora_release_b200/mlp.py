@@ -67,6 +67,20 @@ def gemm(a, b, *, b_is_kn=False, a2=None, b2=None, a3=None, b3=None, lora0=None,
     return d
 
 
+def lora_grad_a(q, scale, gm, r2, q_bit):
+    """out [r2, H] = gm[:, :r2]^T @ dequant(q, scale), the packed activation de-quantized inside the kernel.
+    q [T, H*q_bit/8] uint8, scale [H] bf16, gm [T, >= r2] bf16 (row stride a multiple of 8)."""
+    require_cuda(q, scale, gm)
+    T = q.shape[0]
+    H = scale.numel()
+    out = torch.empty((r2, H), dtype=BF16, device=q.device)
+    nbytes = lib.hyc_lora_grad_a_workspace_bytes(T, H, r2)
+    ws = torch.empty(nbytes // 4, dtype=torch.float32, device=q.device)
+    check(lib.hyc_lora_grad_a_dequant(ptr(q), ptr(scale), ptr(gm), gm.stride(0), r2, T, H, q_bit, ptr(out), ptr(ws),
+                                      nbytes, stream_of(q)), "hyc_lora_grad_a_dequant")
+    return out
+
+
 @dataclass
 class MLPWeights:
     """Frozen bf16 weights ([out, in]) and LoRA factors of one MLP."""
@@ -206,13 +220,13 @@ def mlp_backward(grad_out, saved, w: MLPWeights, status=None):
         ptr(had), ptr(gg), ptr(gu), q, ptr(st), stream_of(grad_out)), "hyc_mlp_graddown_bwd_tcgen05")
     grad_ad = gdm.t() @ had                        # [r, I]
 
-    x_norm = cf.decompression_dequantization(saved['xn_q'], saved['xn_scale'], q).reshape(T, H)
     gm64 = torch.zeros((T, 64), dtype=BF16, device=dev)
     gm64[:, :16] = gg @ w.bg                       # [T, r] each, side by side in a zero-padded K block
     gm64[:, 16:32] = gu @ w.bu
     gm_gate, gm_up = gm64[:, :16], gm64[:, 16:32]
-    grad_ag = gm_gate.t() @ x_norm                 # [r, H]
-    grad_au = gm_up.t() @ x_norm
+    # LoRA-A gradients of gate and up in one pass over the packed x_norm (de-quantized in shared memory)
+    ga = lora_grad_a(saved['xn_q'].reshape(T, -1), saved['xn_scale'].to(BF16).reshape(-1).contiguous(), gm64, 32, q)
+    grad_ag, grad_au = ga[:16], ga[16:32]          # [r, H] each
     grad_bg = gg.t() @ gate_xa                     # [I, r]
     grad_bu = gu.t() @ up_xa
     # grad wrt x_norm: gate and up products accumulate in one tensor-memory tile

@@ -213,6 +213,19 @@ int hyc_mlp_graddown_bwd_tcgen05(const void* g, const void* wd, int T, int H, in
                                  const void* q1, const void* s1, const void* q2, const void* s2,
                                  void* o, void* grad_gate, void* grad_up, int q_bit, int* status, void* stream);
 
+/* LoRA-A gradient with the de-quantizer inside the contraction:
+ *   out[r, h] = sum_t gm[t, r] * x_hat[t, h],   x_hat = decompression_dequantization(q, scale)
+ * Replaces `decompression_dequantization` followed by `x.mT @ grad_medium` of lora_backward
+ * (models/utils/compute_utils.py:30-32; call sites fused_llama_layer_intra_inter_full_fuse.py:375-383): the
+ * packed codes are unpacked into shared-memory tiles and fed to the tensor cores; x_hat is never written to
+ * HBM.  q [T, H*q_bit/8], scale [H] bf16, gm [T, ldg] bf16 of which the first R2 columns are used (R2 a
+ * multiple of 16, <= 64: several LoRA adapters that share the input can be stacked), out [R2, H] bf16.
+ * H % 128 == 0.  workspace: hyc_lora_grad_a_workspace_bytes(T, H, R2) bytes of fp32 partial sums. */
+size_t hyc_lora_grad_a_workspace_bytes(int T, int H, int R2);
+int hyc_lora_grad_a_dequant(const void* q, const void* scale, const void* gm, int64_t ldg, int R2,
+                            int T, int H, int q_bit, void* out, void* workspace, size_t workspace_bytes,
+                            void* stream);
+
 #ifdef __cplusplus
 }
 #endif

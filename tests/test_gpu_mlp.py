@@ -69,6 +69,24 @@ def test_gemm_two_segments_lora_residual(mlp):
     assert close(d3, ref, rel=6e-3)
 
 
+@pytest.mark.parametrize("q", (2, 4, 8))
+@pytest.mark.parametrize("T,H,R2,ldg", [(64, 128, 16, 16), (300, 512, 32, 64), (1024, 4096, 32, 64), (257, 256, 64, 72)])
+def test_lora_grad_a_with_dequant_inside(mlp, q, T, H, R2, ldg):
+    """out = gm^T @ dequant(codes): against the oracle's de-quantizer followed by an fp32 product."""
+    g = torch.Generator().manual_seed(T + H + q)
+    x = _randn(g, 1, T, H)
+    s = oracle.ref_scale_per_channel(x, q)
+    s = torch.where(s == 0, torch.tensor(1e-3, dtype=BF16), s)
+    codes = oracle.ref_compress(x, s, q)[0]
+    xhat = oracle.ref_decompress(codes[None], s, q)[0]
+    gm = torch.zeros(T, ldg, dtype=BF16)
+    gm[:, :R2] = _randn(g, T, R2)
+    gm[:, R2:] = 7.0                      # columns beyond R2 must be ignored
+    out = mlp.lora_grad_a(codes.to(DEV), s.reshape(-1).to(DEV), gm.to(DEV), R2, q)
+    ref = gm[:, :R2].float().t() @ xhat.float()
+    assert out.shape == (R2, H) and close(out, ref, rel=4e-3)
+
+
 def _mlp_problem(g, B, M, H, I, R=16):
     x = _randn(g, B, M, H)
     x[:, :, torch.randperm(H, generator=g)[: max(1, H // 200)]] *= 20
