@@ -37,6 +37,15 @@ def peaks():
     return 6650.0, "fallback"
 
 
+def tensor_peaks():
+    """(burst, sustained) dense bf16 TFLOP/s and where they come from."""
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return float(d["bf16_tflops"]), float(d.get("bf16_tflops_sustained", d["bf16_tflops"])), "measured"
+    return 1590.0, 1400.0, "fallback"
+
+
 def make_map(seed, device, shape=MAP_SHAPE):
     g = torch.Generator(device="cpu").manual_seed(seed)
     b, h, s, _ = shape
@@ -183,35 +192,49 @@ def time_loop(fn, steps, warmup):
 
 
 def extra_workloads(dev, hbm):
-    """Secondary lines of the same path (reported under "also"): the per-channel round trip of the
-    CPU-runnable config and a q_bit sweep at the Mistral MLP width."""
+    """Secondary lines of the same path (reported under "also"): the per-channel round trip
+    (outlier channels + q-bit codes) of the CPU-runnable config and a q_bit sweep at the Mistral MLP
+    width.  Outputs are pre-allocated and each pass over the buffer sets is replayed from a CUDA graph,
+    so the small config measures the kernels and not the Python call overhead."""
     from hyc_lora_release_b200.operators import compress_function as cf
     out = []
     g = torch.Generator().manual_seed(1234)
     for name, shape, n_out, mult, ratio, qs, nbuf in (
-            ("channel-base [4,512,4096] 0.5% outlier channels x30", (4, 512, 4096), 20, 30.0, 0.005, (4,), 12),
-            ("channel-base [1,8192,14336] 1% outlier channels x20", (1, 8192, 14336), 143, 20.0, 0.01, (2, 4, 8), 2)):
+            ("channel-base round trip [4,512,4096] bf16, 0.5% outlier channels x30 (BASELINE configs[0])",
+             (4, 512, 4096), 20, 30.0, 0.005, (4,), 12),
+            ("channel-base round trip [1,8192,14336] bf16, 1% outlier channels x20 (BASELINE configs[3], per GPU)",
+             (1, 8192, 14336), 143, 20.0, 0.01, (2, 4, 8), 2)):
         xs = []
         for _ in range(nbuf):
             x = torch.randn(*shape, generator=g)
             ch = torch.randperm(shape[-1], generator=g)[:n_out]
             x[:, :, ch] *= mult
             xs.append(x.to(torch.bfloat16).to(dev))
+        B, M, N = shape
         for q in qs:
             idx, s = cf.get_statistics_channel_base(xs[0], ratio, q, "per-channel")
             k = idx.numel()
             numel = xs[0].numel()
-            nbytes = numel * (4 + q / 4.0) + 2 * (numel // shape[-1]) * k * 2 * 2
-            keep = [None] * nbuf
+            nbytes = numel * (4 + q / 4.0) + 2 * (B * M) * k * 2
+            qb = [torch.empty((B, M, N * q // 8), dtype=torch.uint8, device=dev) for _ in range(nbuf)]
+            ob = [torch.empty((B, M, k), dtype=torch.bfloat16, device=dev) for _ in range(nbuf)]
+            xb = [torch.empty(shape, dtype=torch.bfloat16, device=dev) for _ in range(nbuf)]
 
-            def step(i):
-                j = i % nbuf
-                o, qq = cf.outlier_subtraction_fuse_compression_quantization(xs[j], s, idx, q)
-                keep[j] = cf.outlier_addition_fuse_decompression_dequantization(qq, s, o, idx, q)
-            t = time_loop(step, 6 * nbuf, nbuf)
-            gbs = 6 * nbuf * nbytes / t / 1e9
+            def one_pass():
+                for j in range(nbuf):
+                    cf.outlier_subtraction_fuse_compression_quantization(xs[j], s, idx, q, out=(qb[j], ob[j]))
+                    cf.outlier_addition_fuse_decompression_dequantization(qb[j], s, ob[j], idx, q, out=xb[j])
+            one_pass()
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                one_pass()
+            reps = max(3, 48 // nbuf)
+            t = time_loop(lambda i: graph.replay(), reps, 3)
+            gbs = reps * nbuf * nbytes / t / 1e9
             out.append({"workload": name, "q_bit": q, "value": gbs, "unit": "GB/s", "frac_of_hbm": gbs / hbm,
-                        "ms_per_step": t / (6 * nbuf) * 1e3})
+                        "ms_per_step": t / (reps * nbuf) * 1e3, "launch": "CUDA graph replay of %d compress+decompress pairs" % nbuf})
+            del graph, qb, ob, xb
         del xs
     return out
 
@@ -221,6 +244,11 @@ def run_profile(args):
     from hyc_lora_release_b200.operators import compress_function as cf
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(dev)
+    if args.profile == "mlp":
+        line = mlp_workload(dev, None, steps=args.steps, warmup=args.warmup)
+        print(json.dumps({"profile": "mlp", "steps": args.steps, "ms_per_step": line["ms_per_step"],
+                          "tokens_per_s": line["value"], "tflops": line["roofline"]["achieved"]}))
+        return
     if args.profile == "attn_topk":
         maps = [make_map(1000 + i, dev) for i in range(NBUF)]
         nbytes = 2 * algo_bytes(MAP_SHAPE, QBIT, RATIO)
@@ -246,6 +274,55 @@ def run_profile(args):
                       "GBps": args.steps * nbytes / t / 1e9}))
 
 
+def mlp_workload(dev, dist=None, steps=20, warmup=4):
+    """Fused LoRA-SiLU-Hadamard MLP forward + backward at Llama-2-7B shapes (BASELINE configs[2]):
+    x [4,512,4096] per GPU, frozen W ~ N(0, .02), LoRA rank 16, saved activations 4-bit with 0.5 % outlier
+    channels; calibration (5 iterations) happens before the timed region.  With several ranks every rank
+    runs its own token shard and the LoRA gradients are all-reduced inside the timed step."""
+    from hyc_lora_release_b200 import mlp, parallel
+    g = torch.Generator().manual_seed(4321)
+    B, M, H, I, R = 4, 512, 4096, 11008, 16
+    T = B * M
+    rn = lambda *sh, sc=1.0: (torch.randn(*sh, generator=g) * sc).to(torch.bfloat16).to(dev)
+    x = torch.randn(B, M, H, generator=g)
+    x[:, :, torch.randperm(H, generator=g)[:20]] *= 30
+    x = x.to(torch.bfloat16).to(dev)
+    ku = lambda out, inp: ((torch.rand(out, inp, generator=g) * 2 - 1) * (1.0 / inp) ** 0.5).to(torch.bfloat16).to(dev)
+    W = mlp.MLPWeights(norm_w=torch.ones(H, dtype=torch.bfloat16, device=dev),
+                       wg=rn(I, H, sc=.02), wu=rn(I, H, sc=.02), wd=rn(H, I, sc=.02),
+                       ag=ku(R, H), bg=rn(I, R, sc=.02), au=ku(R, H), bu=rn(I, R, sc=.02), ad=ku(R, I), bd=rn(H, R, sc=.02))
+    state = mlp.MLPState(q_bit=4, layernorm_outlier_ratio=0.005)
+    st = torch.zeros(1, dtype=torch.int32, device=dev)
+    gout = rn(B, M, H)
+
+    def step(i):
+        out, saved = mlp.mlp_forward(x, W, state, status=st)
+        grads = mlp.mlp_backward(gout, saved, W, status=st)
+        lora = {k: v for k, v in grads.items() if k in ("grad_ag", "grad_bg", "grad_au", "grad_bu", "grad_ad", "grad_bd")}
+        parallel.allreduce_lora_grads(lora)
+    for i in range(6):          # calibration iterations
+        step(i)
+    mlp.check_status(st, "mlp")
+    t = time_loop(step, steps, warmup)
+    mlp.check_status(st, "mlp")
+    world = 1
+    if dist is not None:
+        world = dist.get_world_size()
+        tt = torch.tensor([t], device=dev)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        t = float(tt.item())
+    flop_per_token = 12 * H * I + R * (18 * H + 22 * I)
+    burst, sustained, src = tensor_peaks()
+    tf = T * flop_per_token * steps / t / 1e12
+    return {"workload": "fused LoRA-SiLU-Hadamard MLP fwd+bwd, Llama-2-7B shapes, x [4,512,4096] per GPU, q_bit 4 (BASELINE configs[2])",
+            "metric": "tokens/s", "value": world * T * steps / t, "unit": "tokens/s", "ms_per_step": t / steps * 1e3,
+            "tokens_per_gpu": T, "flop_per_token": flop_per_token,
+            "roofline": {"bound": "tensor", "achieved": tf, "peak": sustained, "unit": "TFLOP/s", "frac": tf / sustained,
+                         "peak_source": src + " (sustained; burst %.0f -> frac %.3f)" % (burst, tf / burst)},
+            "gpu_launches_per_step": 4, "note": "4 tcgen05 GEMM launches + streaming kernels per step; "
+            "LoRA-gradient all-reduce inside the step when n_gpus > 1"}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -253,7 +330,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-extras", action="store_true", help="skip the secondary workloads and the CPU sample")
-    ap.add_argument("--profile", default=None, choices=["attn_topk", "channel_q4", "channel_q2", "channel_q8"],
+    ap.add_argument("--profile", default=None, choices=["attn_topk", "channel_q4", "channel_q2", "channel_q8", "mlp"],
                     help="run only W+K steps of one workload and print timing (for a profiler capture)")
     args = ap.parse_args()
     if args.warmup < 3:
@@ -346,11 +423,17 @@ def main():
            "h2d_bytes_per_step": dense_bytes, "d2h_bytes_per_step": dense_bytes, "steps": n_e,
            "api": "compress_function.compression_softmax_topk + TopkMap.to_dense on a pinned host map"}
 
+    mlp_line = None
+    if not args.no_extras:
+        barrier()
+        mlp_line = mlp_workload(dev, dist)      # every rank takes part (all-reduce inside)
     if rank == 0:
         also, cpu = [], None
         if not args.no_extras and world == 1:
             also = extra_workloads(dev, hbm)
             cpu, _, _ = cpu_port_sample()
+        if mlp_line is not None:
+            also.append(mlp_line)
         line = {
             "metric": "activation compress+decompress GB/s", "value": value, "unit": "GB/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": secs / args.steps * 1e3,

@@ -146,7 +146,7 @@ def get_statistics_channel_base(x: torch.Tensor, outlier_ratio: float, q_bit: in
 
 # ******************** compress / decompress interface ********************
 
-def _quant(x, s, q_bit, z=None, channel=None):
+def _quant(x, s, q_bit, z=None, channel=None, out=None):
     require_cuda(x, s)
     _check_q(q_bit)
     x = _as_hidden(x)
@@ -159,12 +159,16 @@ def _quant(x, s, q_bit, z=None, channel=None):
     if z is not None:
         zt = z.reshape(-1).to(torch.int8).contiguous()
     epp = 8 // q_bit
-    q = torch.empty((B, M, N // epp), dtype=torch.uint8, device=x.device)
     k, idx, xo = 0, None, None
     if channel is not None:
         idx = channel.to(device=x.device, dtype=torch.int64).contiguous()
         k = idx.numel()
-        xo = torch.empty((B, M, k), dtype=BF16, device=x.device)
+    if out is not None:      # caller-provided (q, x_outlier) buffers, e.g. reused across steps
+        q, xo = out
+    else:
+        q = torch.empty((B, M, N // epp), dtype=torch.uint8, device=x.device)
+        if channel is not None:
+            xo = torch.empty((B, M, k), dtype=BF16, device=x.device)
     if rows == 0:
         return q, xo
     check(lib.hyc_quant_pack(ptr(xr), rows, N, ld, ptr(s), ptr(zt), ptr(idx) if k else None, k, ptr(q),
@@ -172,7 +176,7 @@ def _quant(x, s, q_bit, z=None, channel=None):
     return q, xo
 
 
-def _dequant(q, s, q_bit, z=None, channel=None, x_outlier=None):
+def _dequant(q, s, q_bit, z=None, channel=None, x_outlier=None, out=None):
     require_cuda(q, s)
     _check_q(q_bit)
     B, M, _ = q.shape
@@ -182,7 +186,7 @@ def _dequant(q, s, q_bit, z=None, channel=None, x_outlier=None):
     zt = None
     if z is not None:
         zt = z.reshape(-1).to(torch.int8).contiguous()
-    x = torch.empty((B, M, N), dtype=BF16, device=q.device)
+    x = out if out is not None else torch.empty((B, M, N), dtype=BF16, device=q.device)
     if B * M == 0:
         return x
     k, idx, xo = 0, None, None
@@ -195,17 +199,18 @@ def _dequant(q, s, q_bit, z=None, channel=None, x_outlier=None):
     return x
 
 
-def outlier_subtraction_fuse_compression_quantization(x, s, channel, quantize_bit=8, dtype=torch.bfloat16):
+def outlier_subtraction_fuse_compression_quantization(x, s, channel, quantize_bit=8, dtype=torch.bfloat16, out=None):
     """compress_function.py:111-143 -> (x_outlier [B,M,k] bf16, q uint8).  One kernel: the
-    outlier columns are gathered and encoded as zero; ``x`` is left untouched."""
-    q, xo = _quant(x, s, quantize_bit, channel=channel)
+    outlier columns are gathered and encoded as zero; ``x`` is left untouched.
+    ``out=(q, x_outlier)`` (not in the reference) writes into existing buffers."""
+    q, xo = _quant(x, s, quantize_bit, channel=channel, out=out)
     return xo, q
 
 
 def outlier_addition_fuse_decompression_dequantization(q, s, x_outlier, channel, quantize_bit=8, is_head=False,
-                                                       num_heads=1, dtype=torch.bfloat16):
-    """compress_function.py:147-174."""
-    x = _dequant(q, s, quantize_bit, channel=channel, x_outlier=x_outlier)
+                                                       num_heads=1, dtype=torch.bfloat16, out=None):
+    """compress_function.py:147-174.  ``out`` (not in the reference): an existing [B,M,N] bf16 buffer."""
+    x = _dequant(q, s, quantize_bit, channel=channel, x_outlier=x_outlier, out=out)
     return hidden_to_head_shape(x, num_heads=num_heads) if is_head else x
 
 
