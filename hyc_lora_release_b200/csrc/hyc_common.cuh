@@ -82,14 +82,15 @@ __device__ __forceinline__ int quant_code_signed_zp(float x, float s, float rc, 
 // Multiplying by (1 + delta) pushes ties away from zero (C roundf) by more than that error and
 // moves every other value by far less than 1/510; round-to-nearest then gives the reference code.
 // Checked exhaustively on the host over all bf16 scale significands and all bf16 inputs.
-//   q = 2, 4 : u = min(sat(fma(x, rcs, 0.5)), (2^q-1)/2^q),  rcs = RN(1/s) * (1 + 2^-16) / 2^q,
-//              code = low mantissa bits of fma(u, 2^q, 2^23)
+//   q = 2, 4 : u = sat(fma(x, rcs, 2^(q-1)/L)),  rcs = RN(1/s) * (1 + 2^-16) / L,  L = 2^q - 1,
+//              code = low mantissa bits of fma(u, L, 2^23).  Saturation at 0 and 1 IS the clamp to
+//              [-2^(q-1), 2^(q-1)-1]; the inexact constants cost < 1e-6 code units, far inside the margin.
 //   q = 8    : t = clamp(x * rc, -128, 127),  code = low byte of fma(t, 1 + 2^-18, 1.5 * 2^23) ^ 0x80
 // A column with rcs == 0 (outlier column) encodes as zero.
 template <int QBIT>
 __device__ __forceinline__ float fastq_scale(float rc) {
   if (QBIT == 8) return rc;
-  return rc * ((1.0f + 1.0f / 65536.0f) / (float)(1 << QBIT));
+  return rc * ((1.0f + 1.0f / 65536.0f) / (float)((1 << QBIT) - 1));
 }
 // offset-binary code in the low byte of the returned word (upper bits are not zero)
 template <int QBIT>
@@ -98,11 +99,11 @@ __device__ __forceinline__ uint32_t fastq_code_bits(float x, float rcs) {
     const float t = fminf(fmaxf(x * rcs, -128.f), 127.f);
     return __float_as_uint(fmaf(t, 1.0f + 1.0f / 262144.0f, 12582912.f)) ^ 0x80u;
   } else {
-    constexpr float P = (float)(1 << QBIT);
+    constexpr float L = (float)((1 << QBIT) - 1);
+    constexpr float C2 = (float)(1 << (QBIT - 1)) / L;
     float u;
-    asm("fma.rn.sat.f32 %0, %1, %2, %3;" : "=f"(u) : "f"(x), "f"(rcs), "f"(0.5f));
-    u = fminf(u, (P - 1.0f) / P);
-    return __float_as_uint(fmaf(u, P, 8388608.f));
+    asm("fma.rn.sat.f32 %0, %1, %2, %3;" : "=f"(u) : "f"(x), "f"(rcs), "f"(C2));
+    return __float_as_uint(fmaf(u, L, 8388608.f));
   }
 }
 // low bytes of four words -> one word (byte k = low byte of bk)

@@ -17,8 +17,12 @@ namespace hyc {
 #ifndef HYC_Q_MINBLOCKS
 #define HYC_Q_MINBLOCKS 4
 #endif
-constexpr int kThreads = 256;
+constexpr int kThreads = 256;          // upper bound; the launch picks the width that wastes fewest lanes
 constexpr int kRowUnroll = HYC_ROW_UNROLL;
+#ifndef HYC_DEQ_UNROLL
+#define HYC_DEQ_UNROLL 8
+#endif
+constexpr int kDeqUnroll = HYC_DEQ_UNROLL;          // the de-quantizer loads only 8 bytes per row: keep more rows in flight
 
 template <int QBIT>
 struct Geo {
@@ -64,14 +68,14 @@ quant_pack_kernel(const __nv_bfloat16* __restrict__ x, int64_t rows, int N, int6
                   uint8_t* __restrict__ q, __nv_bfloat16* __restrict__ oout) {
   using G = Geo<QBIT>;
   constexpr int EPP = G::EPP;
-  const int ct = blockIdx.x * kThreads + threadIdx.x;
+  const int ct = blockIdx.x * blockDim.x + threadIdx.x;
   const int n_ct = N / G::COLS_PER_THREAD;
   const bool active = ct < n_ct;
   const int64_t qld = (int64_t)N / EPP;
 
   extern __shared__ __align__(16) uint8_t s_dyn[];
   int16_t* s_map = reinterpret_cast<int16_t*>(s_dyn);
-  const int span_cols = kThreads * G::COLS_PER_THREAD;
+  const int span_cols = blockDim.x * G::COLS_PER_THREAD;
   const int col0 = blockIdx.x * span_cols;
   int* s_overflow = reinterpret_cast<int*>(s_dyn + 2 * span_cols);
   if (k > 0) build_outlier_map(s_map, s_overflow, span_cols, col0, oidx, k);
@@ -188,7 +192,7 @@ quant_pack_kernel(const __nv_bfloat16* __restrict__ x, int64_t rows, int N, int6
     }
     if (overflow) {
       // rare: some thread owns more than kMaxOwn outlier columns; the block gathers its span together
-      for (int t = threadIdx.x; t < kRowUnroll * k; t += kThreads) {
+      for (int t = threadIdx.x; t < kRowUnroll * k; t += blockDim.x) {
         const int64_t row = r0 + t / k;
         const int j = t % k;
         const int64_t c = oidx[j] - col0;
@@ -211,11 +215,11 @@ unpack_dequant_kernel(const uint8_t* __restrict__ q, int64_t rows, int N,
   using G = Geo<QBIT>;
   constexpr int EPP = G::EPP;
   constexpr uint32_t MASK = (1u << QBIT) - 1u;
-  const int ct = blockIdx.x * kThreads + threadIdx.x;
+  const int ct = blockIdx.x * blockDim.x + threadIdx.x;
   const int n_ct = N / G::COLS_PER_THREAD;
   const bool active = ct < n_ct;
   const int64_t qld = (int64_t)N / EPP;
-  const int span_cols = kThreads * G::COLS_PER_THREAD;
+  const int span_cols = blockDim.x * G::COLS_PER_THREAD;
   const int col0 = blockIdx.x * span_cols;
 
   extern __shared__ __align__(16) uint8_t s_dyn[];
@@ -276,27 +280,28 @@ unpack_dequant_kernel(const uint8_t* __restrict__ q, int64_t rows, int N,
   bool overflow = false;
   if (k > 0) { __syncthreads(); overflow = *s_overflow != 0; }
 
-  const int64_t n_groups = (rows + kRowUnroll - 1) / kRowUnroll;
+  const int64_t n_groups = (rows + kDeqUnroll - 1) / kDeqUnroll;
   for (int64_t g = blockIdx.y; g < n_groups; g += gridDim.y) {
-    const int64_t r0 = g * kRowUnroll;
+    const int64_t r0 = g * kDeqUnroll;
     if (active) {
-      uint2 p[kRowUnroll];
+      uint2 p[kDeqUnroll];
 #pragma unroll
-      for (int r = 0; r < kRowUnroll; ++r) {
+      for (int r = 0; r < kDeqUnroll; ++r) {
         p[r] = make_uint2(0u, 0u);
         if ((r0 + r) < rows) p[r] = ld_stream_v2(q + (r0 + r) * qld + 8 * (int64_t)ct);
       }
-      __nv_bfloat16 ov[kRowUnroll][kMaxOwn];
+      __nv_bfloat16 ov[kDeqUnroll][kMaxOwn];
       if (own.n > 0 && !overflow) {
 #pragma unroll
-        for (int r = 0; r < kRowUnroll; ++r)
+        for (int r = 0; r < kDeqUnroll; ++r)
 #pragma unroll
           for (int t = 0; t < kMaxOwn; ++t)
             if (t < own.n && (r0 + r) < rows) ov[r][t] = oin[(r0 + r) * k + own.j[t]];
       }
 #pragma unroll
-      for (int r = 0; r < kRowUnroll; ++r) {
+      for (int r = 0; r < kDeqUnroll; ++r) {
         if ((r0 + r) >= rows) break;
+        uint4 prev = make_uint4(0u, 0u, 0u, 0u);
 #pragma unroll
         for (int i = 0; i < EPP; ++i) {
           // the codes of slab i, one per byte, then each byte straight into the float 2^23 + code
@@ -329,7 +334,17 @@ unpack_dequant_kernel(const uint8_t* __restrict__ q, int64_t rows, int N,
             o.z = pack_bf16x2_rn(f[4], f[5]);
             o.w = pack_bf16x2_rn(f[6], f[7]);
           }
-          st_stream_v4(xo + (r0 + r) * ldx + G::slab_col(ct, i), o);
+          if (EPP == 4) {
+            // 2-bit codes: a thread owns the whole 32-column block, so two slabs make one 32-byte store
+            if (i & 1) {
+              const uint32_t w8[8] = {prev.x, prev.y, prev.z, prev.w, o.x, o.y, o.z, o.w};
+              st_stream_v8(xo + (r0 + r) * ldx + G::slab_col(ct, i - 1), w8);
+            } else {
+              prev = o;
+            }
+          } else {
+            st_stream_v4(xo + (r0 + r) * ldx + G::slab_col(ct, i), o);
+          }
         }
         // the owner of an outlier column puts the saved value back, after its own store to that spot
         if (own.n > 0 && !overflow) {
@@ -341,7 +356,7 @@ unpack_dequant_kernel(const uint8_t* __restrict__ q, int64_t rows, int N,
     }
     if (overflow) {
       __syncthreads();   // the block's stores to these rows come first
-      for (int t = threadIdx.x; t < kRowUnroll * k; t += kThreads) {
+      for (int t = threadIdx.x; t < kDeqUnroll * k; t += blockDim.x) {
         const int64_t row = r0 + t / k;
         const int j = t % k;
         const int64_t c = oidx[j] - col0;
@@ -353,12 +368,23 @@ unpack_dequant_kernel(const uint8_t* __restrict__ q, int64_t rows, int N,
 
 // One resident wave: blocks_per_sm * 148 blocks in total, split over the column tiles, so that the
 // per-block set-up (reciprocals, outlier map) is paid once per SM slot and not once per wave.
+// block width in {256, 224, ..., 128} that leaves the fewest idle lanes in the last column tile
+static inline int pick_threads(int n_ct) {
+  int best = 256, best_waste = 1 << 30;
+  for (int t = 256; t >= 128; t -= 32) {
+    const int tiles = (n_ct + t - 1) / t;
+    const int waste = tiles * t - n_ct;
+    if (waste < best_waste) { best_waste = waste; best = t; }
+  }
+  return best;
+}
+
 template <typename Kernel>
-static inline dim3 stream_grid(Kernel kern, size_t smem, int64_t rows, int n_ct) {
-  const int col_tiles = (n_ct + kThreads - 1) / kThreads;
-  const int64_t groups = (rows + kRowUnroll - 1) / kRowUnroll;
+static inline dim3 stream_grid(Kernel kern, int threads, size_t smem, int64_t rows, int n_ct, int unroll) {
+  const int col_tiles = (n_ct + threads - 1) / threads;
+  const int64_t groups = (rows + unroll - 1) / unroll;
   int per_sm = 0;
-  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, kThreads, smem) != cudaSuccess || per_sm < 1) per_sm = 2;
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, threads, smem) != cudaSuccess || per_sm < 1) per_sm = 2;
   int64_t slots = ((int64_t)kNumSMs * per_sm) / col_tiles;
   if (slots > groups) slots = groups;
   if (slots < 1) slots = 1;
@@ -391,9 +417,10 @@ extern "C" HYC_API int hyc_quant_pack(const void* x, int64_t rows, int N, int64_
   if (rows == 0) return HYC_OK;
   cudaStream_t st = (cudaStream_t)stream;
   const int cpt = 8 * (8 / q_bit);
-  size_t smem = k > 0 ? (size_t)kThreads * cpt * 2 + 16 : 0;   // int16 column map + overflow flag
+  const int threads = pick_threads(N / cpt);
+  size_t smem = k > 0 ? (size_t)threads * cpt * 2 + 16 : 0;   // int16 column map + overflow flag
 #define LAUNCH_Q(QB, ZP)                                                                          \
-  quant_pack_kernel<QB, ZP><<<stream_grid(quant_pack_kernel<QB, ZP>, smem, rows, N / cpt), kThreads, smem, st>>>( \
+  quant_pack_kernel<QB, ZP><<<stream_grid(quant_pack_kernel<QB, ZP>, threads, smem, rows, N / cpt, kRowUnroll), threads, smem, st>>>( \
       (const __nv_bfloat16*)x, rows, N, ldx, (const __nv_bfloat16*)scale, zp, outlier_idx, k,      \
       (uint8_t*)q_out, (__nv_bfloat16*)outlier_out)
   if (zp) {
@@ -415,13 +442,15 @@ extern "C" HYC_API int hyc_unpack_dequant(const void* q, int64_t rows, int N,
   if (!scale) return HYC_ERR_NULL;
   if (k < 0 || k > N || k > 32767) return HYC_ERR_SHAPE;
   if (k > 0 && (!outlier_idx || !outlier)) return HYC_ERR_NULL;
-  if (!aligned(x_out, 16) || !aligned(scale, 16) || !aligned(q, 8) || (zp && !aligned(zp, 8))) return HYC_ERR_ALIGN;
+  if (!aligned(x_out, q_bit == 2 ? 32 : 16) || !aligned(scale, 16) || !aligned(q, 8) || (zp && !aligned(zp, 8))) return HYC_ERR_ALIGN;
+  if (q_bit == 2 && ldx % 16 != 0) return HYC_ERR_ALIGN;
   if (rows == 0) return HYC_OK;
   cudaStream_t st = (cudaStream_t)stream;
   const int cpt = 8 * (8 / q_bit);
-  size_t smem = k > 0 ? (size_t)kThreads * cpt * 2 + 16 : 0;
+  const int threads = pick_threads(N / cpt);
+  size_t smem = k > 0 ? (size_t)threads * cpt * 2 + 16 : 0;
 #define LAUNCH_D(QB, ZP)                                                                          \
-  unpack_dequant_kernel<QB, ZP><<<stream_grid(unpack_dequant_kernel<QB, ZP>, smem, rows, N / cpt), kThreads, smem, st>>>(                                        \
+  unpack_dequant_kernel<QB, ZP><<<stream_grid(unpack_dequant_kernel<QB, ZP>, threads, smem, rows, N / cpt, kDeqUnroll), threads, smem, st>>>(                                        \
       (const uint8_t*)q, rows, N, (const __nv_bfloat16*)scale, zp, outlier_idx, k,                 \
       (const __nv_bfloat16*)outlier, (__nv_bfloat16*)x_out, ldx)
   if (zp) {
