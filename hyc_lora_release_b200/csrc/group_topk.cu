@@ -11,67 +11,12 @@
 // largest magnitude is found by bisection on the 15-bit bf16 magnitude pattern; each probe
 // counts "magnitude >= candidate" with packed bf16x2 compares and one warp reduction.  The
 // selected elements are emitted in ascending column order through a warp prefix scan.
-#include "hyc_common.cuh"
+#include "group_math.cuh"
+#include "topk_lane.cuh"
 
 namespace hyc {
 
-constexpr unsigned kFull = 0xffffffffu;
 constexpr int kStageEntries = 256;   // outlier-list entries a warp stages in shared memory
-
-struct GroupParams { float s, rcl, zcl, z; };
-
-// Group-mode arithmetic (fp32, one rounding per operation):
-//   d = bf16(mx - mn);  il = 1/levels;  s = bf16(d * il), 1e-3 when zero;  rc = 1/s
-//   z = clamp(rint(clamp(-mn*rc, +-300)) - half, -128, 127)
-//   u = sat01(fma(x, rc*il, (z + half)*il));   code = rint(u * levels)     rint = half to even
-// Per element that is one saturating fma and one fma with 2^23 as addend (the integer
-// lands in the low mantissa bits): both run on the FMA pipe, no min/max, no conversion.
-template <int QBIT>
-__device__ __forceinline__ GroupParams group_params(float mn, float mx) {
-  constexpr float il = 1.0f / (float)((1 << QBIT) - 1);
-  constexpr float half = (float)(1 << (QBIT - 1));
-  float d = bf16bits_to_f32(f32_to_bf16bits_rn(__fsub_rn(mx, mn)));
-  float s = bf16bits_to_f32(f32_to_bf16bits_rn(__fmul_rn(d, il)));
-  if (s == 0.f) s = bf16bits_to_f32(f32_to_bf16bits_rn(1e-3f));
-  GroupParams p;
-  p.s = s;
-  const float rc = __frcp_rn(s);
-  float t = fminf(fmaxf(__fmul_rn(-mn, rc), -300.f), 300.f);
-  float zr = __fadd_rn(__fadd_rn(t, 12582912.f), -12582912.f);   // rint, |t| <= 300
-  p.z = fminf(fmaxf(zr - half, -128.f), 127.f);
-  p.rcl = __fmul_rn(rc, il);
-  p.zcl = __fmul_rn(p.z + half, il);
-  return p;
-}
-
-// min / max of the 16 values of a lane (packed pairs), then over the 4 lanes of the group
-__device__ __forceinline__ void group_minmax(const uint32_t (&xw)[8], float& mn, float& mx) {
-  __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&xw[0]);
-  __nv_bfloat162 lo = a, hi = a;
-#pragma unroll
-  for (int j = 1; j < 8; ++j) {
-    __nv_bfloat162 v = *reinterpret_cast<const __nv_bfloat162*>(&xw[j]);
-    lo = __hmin2(lo, v);
-    hi = __hmax2(hi, v);
-  }
-  mn = fminf(__bfloat162float(lo.x), __bfloat162float(lo.y));
-  mx = fmaxf(__bfloat162float(hi.x), __bfloat162float(hi.y));
-#pragma unroll
-  for (int o = 1; o <= 2; o <<= 1) {
-    mn = fminf(mn, __shfl_xor_sync(kFull, mn, o));
-    mx = fmaxf(mx, __shfl_xor_sync(kFull, mx, o));
-  }
-}
-
-// unsigned code of one value, left in the low byte of a float's bit pattern (2^23 + code)
-template <int QBIT>
-__device__ __forceinline__ uint32_t group_code_bits(float x, const GroupParams& p) {
-  constexpr float levels = (float)((1 << QBIT) - 1);
-  float u, r;
-  asm("fma.rn.sat.f32 %0, %1, %2, %3;" : "=f"(u) : "f"(x), "f"(p.rcl), "f"(p.zcl));
-  asm("fma.rn.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(u), "f"(levels), "f"(8388608.f));
-  return __float_as_uint(r);
-}
 
 // Quantize the 16 values of a lane and store them in the reference byte layout.
 // qrow points at the packed row; `lane_g` = 32*step + lane (global lane index in the row).
@@ -527,6 +472,12 @@ extern "C" HYC_API int hyc_softmax_topk_compress(const void* a, int64_t rows, in
   if (!aligned(a, 32) || !aligned(q_out, 16)) return HYC_ERR_ALIGN;
   if (rows == 0) return HYC_OK;
   cudaStream_t st = (cudaStream_t)stream;
+  if (topk_lane_ok(S, k) && aligned(q_out, 32)) {
+    const int rc = topk_lane_compress(a, rows, S, k, val_out, col_out, q_out, scale_out, zp_out, q_bit, st);
+    if (rc) return rc;
+    HYC_CHECK_LAUNCH();
+    return HYC_OK;
+  }
   const int steps = (S + 511) / 512;
   const int grid = warp_grid(rows);
 #define TK(QB, ST) topk_compress_kernel<QB, ST><<<grid, 256, 0, st>>>((const __nv_bfloat16*)a, rows, S, k, \
@@ -549,6 +500,12 @@ extern "C" HYC_API int hyc_softmax_topk_restore(const void* val, const uint16_t*
   if (!aligned(a_out, 32) || !aligned(q, 16)) return HYC_ERR_ALIGN;
   if (rows == 0) return HYC_OK;
   cudaStream_t st = (cudaStream_t)stream;
+  if (topk_lane_ok(S, k) && aligned(q, 32)) {
+    const int rc = topk_lane_restore(val, col, k, q, scale, zp, rows, S, a_out, q_bit, st);
+    if (rc) return rc;
+    HYC_CHECK_LAUNCH();
+    return HYC_OK;
+  }
 #define TR(QB) topk_restore_kernel<QB><<<warp_grid(rows), 256, 0, st>>>((const __nv_bfloat16*)val, col, k, \
       (const uint8_t*)q, (const __nv_bfloat16*)scale, zp, rows, S, (__nv_bfloat16*)a_out)
   if (q_bit == 2) TR(2); else if (q_bit == 4) TR(4); else TR(8);

@@ -1,0 +1,22 @@
+// Per-row top-k kernels in the "one lane = one group of 64 columns" layout (rows of 64 * 2^n columns).
+#pragma once
+#include "group_math.cuh"
+
+namespace hyc {
+
+constexpr int kLaneStageEntries = 256;   // (column, value) words a warp stages in shared memory
+
+// rows of 64, 128, ..., 2048 columns whose outlier lists (all rows of a warp) fit the staging area
+inline bool topk_lane_ok(int S, int k) {
+  if (S < 64 || S > 2048 || (S & (S - 1)) != 0) return false;
+  const int rows_per_warp = 32 / (S / 64);
+  return (int64_t)rows_per_warp * k <= kLaneStageEntries;
+}
+
+// both return 0 or a negative HYC_ERR_* (arguments already validated by the caller)
+int topk_lane_compress(const void* a, int64_t rows, int S, int k, void* val_out, uint16_t* col_out,
+                       void* q_out, void* scale_out, int8_t* zp_out, int q_bit, cudaStream_t st);
+int topk_lane_restore(const void* val, const uint16_t* col, int k, const void* q, const void* scale,
+                      const int8_t* zp, int64_t rows, int S, void* a_out, int q_bit, cudaStream_t st);
+
+}  // namespace hyc

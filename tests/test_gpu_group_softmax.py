@@ -69,7 +69,8 @@ def test_softmax_prune_oracle(cf, shape):
 
 
 @pytest.mark.parametrize("q", QS)
-@pytest.mark.parametrize("shape", [(1, 1, 64, 64), (2, 2, 128, 128), (1, 2, 512, 512), (1, 1, 320, 320), (1, 1, 64, 2048)])
+@pytest.mark.parametrize("shape", [(1, 1, 64, 64), (2, 2, 128, 128), (1, 2, 512, 512), (1, 1, 320, 320), (1, 1, 64, 2048),
+                                   (1, 1, 13, 128), (1, 1, 5, 1024), (1, 3, 256, 256), (1, 1, 3, 4096)])
 def test_topk_mode(cf, q, shape):
     b, h, r, s = shape
     if r == s:
@@ -100,6 +101,25 @@ def test_topk_ties_and_signs(cf):
         assert torch.equal(m.col.cpu().to(torch.int64) & 0xFFFF, cols) and torch.equal(m.val.cpu(), vals)
         assert torch.equal(m.q.cpu(), pk) and torch.equal(m.scale.cpu(), sc) and torch.equal(m.zp.cpu(), zp)
         assert torch.equal(m.to_dense().cpu(), oracle.topk_decompress(vals, cols, pk, sc, zp, 4, x.shape))
+
+
+@pytest.mark.parametrize("S,rows", [(64, 37), (512, 7), (2048, 3)])
+def test_topk_ties_lane_layout(cf, S, rows):
+    """Few distinct magnitudes in rows of 64 * 2^n columns (one lane per group of 64): partial ties at the
+    threshold inside a lane, across lanes, rows with fewer non-zeros than k, and a ragged last warp."""
+    g = torch.Generator().manual_seed(S + rows)
+    x = (torch.randint(-2, 3, (rows, S), generator=g).float() * 0.5)
+    x[0] = 0.0
+    x[1, : S // 2] = 0.0
+    x[2] = -1.0
+    x = x.to(torch.bfloat16)
+    for ratio in (0.02, 0.05, 0.11):
+        for q in (2, 4, 8):
+            m = cf.compression_softmax_topk(x.to(DEV), ratio, q)
+            vals, cols, pk, sc, zp = oracle.topk_compress(x, ratio, q)
+            assert torch.equal(m.col.cpu().to(torch.int64) & 0xFFFF, cols) and torch.equal(m.val.cpu(), vals)
+            assert torch.equal(m.q.cpu(), pk) and torch.equal(m.scale.cpu(), sc) and torch.equal(m.zp.cpu(), zp)
+            assert torch.equal(m.to_dense().cpu(), oracle.topk_decompress(vals, cols, pk, sc, zp, q, x.shape))
 
 
 def test_topk_config1_full_size_properties(cf):
