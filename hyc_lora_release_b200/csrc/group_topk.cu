@@ -13,6 +13,7 @@
 // selected elements are emitted in ascending column order through a warp prefix scan.
 #include "group_math.cuh"
 #include "topk_lane.cuh"
+#include "lane_group.cuh"
 
 namespace hyc {
 
@@ -172,6 +173,58 @@ group_dequant_kernel(const uint8_t* __restrict__ q, int64_t rows, int N,
       load_dequant16<QBIT>(q + row * qld, lane_g, s, z, o);
       st_stream_v8(xo + row * ldx + col, o);
     }
+  }
+}
+
+// ---------------------------------------------------------------- group mode, contiguous rows
+// With ldx == N the tensor is a flat list of groups; one lane per group, 32 consecutive groups (4 KB)
+// per warp and round, moved through shared memory so that every global access is a full 1 KB run.
+template <int QBIT>
+__global__ void __launch_bounds__(256, HYC_LANE_MINB)
+group_flat_quant_kernel(const __nv_bfloat16* __restrict__ x, int64_t n_groups, uint8_t* __restrict__ q,
+                        __nv_bfloat16* __restrict__ scale, int8_t* __restrict__ zp) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  __shared__ __align__(16) uint32_t s_x[8][32 * 32];
+  const int64_t items = (n_groups + 31) / 32;
+  for (int64_t item = (int64_t)blockIdx.x * nwarps + warp; item < items; item += (int64_t)gridDim.x * nwarps) {
+    const int64_t g0 = item * 32, left = n_groups - g0;
+    const int nv = (int)(left < 32 ? left : 32);
+    lane_run_to_shared(x + g0 * 64, nv * 4, s_x[warp], lane);
+    __syncwarp();
+    uint32_t xw[32];
+    lane_slot_load(s_x[warp] + lane * 32, lane, xw);
+    float mn, mx;
+    lane_minmax(xw, mn, mx);
+    const GroupParams p = group_params<QBIT>(mn, mx);
+    if (lane < nv) {
+      lane_quant_store<QBIT>(xw, p, q + (g0 + lane) * (64 * QBIT / 8));
+      scale[g0 + lane] = __ushort_as_bfloat16(f32_to_bf16bits_rn(p.s));
+      zp[g0 + lane] = (int8_t)(int)p.z;
+    }
+    __syncwarp();
+  }
+}
+
+template <int QBIT>
+__global__ void __launch_bounds__(256, HYC_LANE_MINB)
+group_flat_dequant_kernel(const uint8_t* __restrict__ q, int64_t n_groups, const __nv_bfloat16* __restrict__ scale,
+                          const int8_t* __restrict__ zp, __nv_bfloat16* __restrict__ xo) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  __shared__ __align__(16) uint32_t s_x[8][32 * 32];
+  const int64_t items = (n_groups + 31) / 32;
+  for (int64_t item = (int64_t)blockIdx.x * nwarps + warp; item < items; item += (int64_t)gridDim.x * nwarps) {
+    const int64_t g0 = item * 32, left = n_groups - g0;
+    const int nv = (int)(left < 32 ? left : 32);
+    if (lane < nv) {
+      const float s = __bfloat162float(scale[g0 + lane]);
+      const float z = (float)zp[g0 + lane];
+      uint32_t o[32];
+      lane_load_dequant<QBIT>(q + (g0 + lane) * (64 * QBIT / 8), s, z, o);
+      lane_slot_store(s_x[warp] + lane * 32, lane, o);
+    }
+    __syncwarp();
+    lane_shared_to_run(s_x[warp], xo + g0 * 64, nv * 4, lane);
+    __syncwarp();
   }
 }
 
@@ -434,8 +487,18 @@ extern "C" HYC_API int hyc_group_quant_pack(const void* x, int64_t rows, int N, 
   if (!scale_out || !zp_out) return HYC_ERR_NULL;
   if (!aligned(x, 32) || !aligned(q_out, 16)) return HYC_ERR_ALIGN;
   if (rows == 0) return HYC_OK;
-  const int64_t items = rows * ((N + 511) / 512);
   cudaStream_t st = (cudaStream_t)stream;
+  if (ldx == N && aligned(q_out, 32)) {
+    const int64_t n_groups = rows * (N / 64);
+    int grid, threads;
+#define GFQ(QB) do { auto kern = group_flat_quant_kernel<QB>; lane_launch_shape(kern, n_groups, 32, grid, threads); \
+      kern<<<grid, threads, 0, st>>>((const __nv_bfloat16*)x, n_groups, (uint8_t*)q_out, (__nv_bfloat16*)scale_out, zp_out); } while (0)
+    if (q_bit == 2) GFQ(2); else if (q_bit == 4) GFQ(4); else GFQ(8);
+#undef GFQ
+    HYC_CHECK_LAUNCH();
+    return HYC_OK;
+  }
+  const int64_t items = rows * ((N + 511) / 512);
 #define GQ(QB) group_quant_kernel<QB><<<warp_grid(items), 256, 0, st>>>((const __nv_bfloat16*)x, rows, N, ldx, \
       (uint8_t*)q_out, (__nv_bfloat16*)scale_out, zp_out)
   if (q_bit == 2) GQ(2); else if (q_bit == 4) GQ(4); else GQ(8);
@@ -452,8 +515,18 @@ extern "C" HYC_API int hyc_group_unpack_dequant(const void* q, int64_t rows, int
   if (!scale || !zp) return HYC_ERR_NULL;
   if (!aligned(x_out, 32) || !aligned(q, 16)) return HYC_ERR_ALIGN;
   if (rows == 0) return HYC_OK;
-  const int64_t items = rows * ((N + 511) / 512);
   cudaStream_t st = (cudaStream_t)stream;
+  if (ldx == N && aligned(q, 32)) {
+    const int64_t n_groups = rows * (N / 64);
+    int grid, threads;
+#define GFD(QB) do { auto kern = group_flat_dequant_kernel<QB>; lane_launch_shape(kern, n_groups, 32, grid, threads); \
+      kern<<<grid, threads, 0, st>>>((const uint8_t*)q, n_groups, (const __nv_bfloat16*)scale, zp, (__nv_bfloat16*)x_out); } while (0)
+    if (q_bit == 2) GFD(2); else if (q_bit == 4) GFD(4); else GFD(8);
+#undef GFD
+    HYC_CHECK_LAUNCH();
+    return HYC_OK;
+  }
+  const int64_t items = rows * ((N + 511) / 512);
 #define GD(QB) group_dequant_kernel<QB><<<warp_grid(items), 256, 0, st>>>((const uint8_t*)q, rows, N, \
       (const __nv_bfloat16*)scale, zp, (__nv_bfloat16*)x_out, ldx)
   if (q_bit == 2) GD(2); else if (q_bit == 4) GD(4); else GD(8);

@@ -35,22 +35,79 @@ struct Geo {
   }
 };
 
-constexpr int kMaxOwn = 2;   // outlier columns a thread handles itself; more -> block-wide fallback
+constexpr int kMaxOwn = 2;        // outlier columns a lane serves from registers
+constexpr int kWarpList = 32 * kMaxOwn;   // outlier columns of a warp's span that are dealt out to its lanes
 
-// Outlier columns.  The block builds a map "column of my span -> position j in the outlier list"
-// in shared memory; each thread then knows which of its own columns are outliers (rarely any).
-// Such a thread moves the full-precision value itself, right next to its streaming loads/stores,
-// so the gather (quantize) and the scatter (de-quantize) cost nothing for the other 99 % of threads.
-struct OwnOutliers {
-  int n;                 // number of outlier columns owned (may exceed kMaxOwn: see overflow flag)
+// Outlier columns.  The block builds a map "column of my span -> position j in the outlier list" in
+// shared memory.  The outlier columns inside a warp's span (512 columns for 4-bit codes) are then DEALT
+// OUT to the lanes of that warp, one or two each, whoever owns the column: however the columns cluster,
+// no lane has more than two scalar copies per row, and it issues them right next to its streaming
+// loads, so their latency is hidden.  (Letting the owner of a column copy it makes the one thread that
+// owns several outliers the slowest of the kernel, and every block waits for the slowest warp.)
+// Columns beyond the first two per lane of a warp's span (outlier ratios above 12 % for 4-bit codes) stay
+// with their owner, which looks them up in the map again for every row: slow, rare, correct.
+struct LaneOutliers {
+  int n;                 // entries served by this lane (0..kMaxOwn)
   int col[kMaxOwn];      // absolute column
   int j[kMaxOwn];        // position in the outlier list
+  uint32_t extra;        // columns owned by this thread that were not dealt out: bit (8 * slab + element)
+  bool warp_has;         // the warp's span holds at least one outlier column (warp-uniform)
 };
 
-__device__ __forceinline__ void build_outlier_map(int16_t* s_map, int* s_overflow, int span_cols, int col0,
+__device__ __forceinline__ int warp_excl_scan_i(int v, int lane, int& total) {
+  int incl = v;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int t = __shfl_up_sync(0xffffffffu, incl, o);
+    if (lane >= o) incl += t;
+  }
+  total = __shfl_sync(0xffffffffu, incl, 31);
+  return incl - v;
+}
+
+// Deal the outlier columns of the warp's span out to its lanes.  `n_own` = outlier columns among this
+// thread's own columns (0 for a thread beyond the last column), listed by for_each_own(f) as
+// f(slab, element, absolute column, j).  Every thread of the block must call this.
+template <typename ForEachOwn>
+__device__ __forceinline__ LaneOutliers deal_outliers(uint32_t* s_list, int col0, bool active, int n_own, ForEachOwn for_each_own) {
+  const int lane = threadIdx.x & 31;
+  // threads beyond the last column are the trailing lanes of the last warp; they serve nothing
+  const int n_act = __popc(__ballot_sync(0xffffffffu, active));
+  uint32_t* wl = s_list + (threadIdx.x >> 5) * kWarpList;
+  LaneOutliers lo;
+  lo.n = 0; lo.extra = 0u;
+#pragma unroll
+  for (int t = 0; t < kMaxOwn; ++t) { lo.col[t] = 0; lo.j[t] = 0; }
+  int total;
+  int rank = warp_excl_scan_i(n_own, lane, total);
+  lo.warp_has = total > 0;
+  if (total == 0) return lo;
+  const int cap = kMaxOwn * n_act;
+  if (n_own > 0) {
+    for_each_own([&](int slab, int e, int col, int j) {
+      if (rank < cap) wl[rank] = (uint32_t)(col - col0) | ((uint32_t)j << 16);
+      else lo.extra |= 1u << (8 * slab + e);
+      ++rank;
+    });
+  }
+  __syncwarp();
+  const int n_list = total < cap ? total : cap;
+#pragma unroll
+  for (int t = 0; t < kMaxOwn; ++t) {
+    const int i = lane + n_act * t;
+    if (active && i < n_list) {
+      const uint32_t w = wl[i];
+      lo.col[t] = col0 + (int)(w & 0xffffu);
+      lo.j[t] = (int)(w >> 16);
+      lo.n = t + 1;
+    }
+  }
+  return lo;
+}
+
+__device__ __forceinline__ void build_outlier_map(int16_t* s_map, int span_cols, int col0,
                                                   const int64_t* __restrict__ oidx, int k) {
   for (int i = threadIdx.x; i < span_cols / 2; i += blockDim.x) reinterpret_cast<uint32_t*>(s_map)[i] = 0xffffffffu;
-  if (threadIdx.x == 0) *s_overflow = 0;
   __syncthreads();
   for (int j = threadIdx.x; j < k; j += blockDim.x) {
     const int64_t c = oidx[j] - col0;
@@ -77,16 +134,12 @@ quant_pack_kernel(const __nv_bfloat16* __restrict__ x, int64_t rows, int N, int6
   int16_t* s_map = reinterpret_cast<int16_t*>(s_dyn);
   const int span_cols = blockDim.x * G::COLS_PER_THREAD;
   const int col0 = blockIdx.x * span_cols;
-  int* s_overflow = reinterpret_cast<int*>(s_dyn + 2 * span_cols);
-  if (k > 0) build_outlier_map(s_map, s_overflow, span_cols, col0, oidx, k);
+  if (k > 0) build_outlier_map(s_map, span_cols, col0, oidx, k);
 
   // without a zero point only one constant per column is needed (see fastq_code_bits); the
   // zero-point variant keeps the exact quotient (scale, reciprocal, zero point per column)
   float s[HAS_ZP ? EPP : 1][8], rc[EPP][8], z[HAS_ZP ? EPP : 1][8];
-  OwnOutliers own;
-  own.n = 0;
-#pragma unroll
-  for (int i = 0; i < kMaxOwn; ++i) { own.col[i] = 0; own.j[i] = 0; }
+  int n_own = 0;
   if (active) {
 #pragma unroll
     for (int i = 0; i < EPP; ++i) {
@@ -106,10 +159,7 @@ quant_pack_kernel(const __nv_bfloat16* __restrict__ x, int64_t rows, int N, int6
         const int jv = (int)(int16_t)((mw[e >> 1] >> (16 * (e & 1))) & 0xffffu);
         if (jv >= 0) {
           r = 0.f;     // the column encodes as zero, as if it had been cleared beforehand
-#pragma unroll
-          for (int t = 0; t < kMaxOwn; ++t)
-            if (own.n == t) { own.col[t] = c + e; own.j[t] = jv; }
-          ++own.n;
+          ++n_own;
         }
         rc[i][e] = r;
         if (HAS_ZP) {
@@ -118,10 +168,19 @@ quant_pack_kernel(const __nv_bfloat16* __restrict__ x, int64_t rows, int N, int6
         }
       }
     }
-    if (own.n > kMaxOwn) atomicOr(s_overflow, 1);
   }
-  bool overflow = false;
-  if (k > 0) { __syncthreads(); overflow = *s_overflow != 0; }
+  LaneOutliers lo;
+  lo.n = 0; lo.extra = 0u; lo.warp_has = false;
+  if (k > 0) {
+    lo = deal_outliers(reinterpret_cast<uint32_t*>(s_dyn + 2 * span_cols), col0, active, n_own, [&](auto f) {
+      for (int i = 0; i < EPP; ++i)
+        for (int e = 0; e < 8; ++e) {
+          const int col = G::slab_col(ct, i) + e;
+          const int jv = s_map[col - col0];
+          if (jv >= 0) f(i, e, col, jv);
+        }
+    });
+  }
 
   const int64_t n_groups = (rows + kRowUnroll - 1) / kRowUnroll;
   for (int64_t g = blockIdx.y; g < n_groups; g += gridDim.y) {
@@ -137,15 +196,15 @@ quant_pack_kernel(const __nv_bfloat16* __restrict__ x, int64_t rows, int N, int6
           if (ok) v[r][i] = ld_stream_v4(x + (r0 + r) * ldx + G::slab_col(ct, i));
         }
       }
-      // the owner of an outlier column fetches its full-precision value alongside the vector loads
+      // the lane's share of the outlier columns: full-precision values fetched alongside the vector loads
       // (same cache lines, so the latency is shared)
       __nv_bfloat16 ov[kRowUnroll][kMaxOwn];
-      if (own.n > 0 && !overflow) {
+      if (lo.n > 0) {
 #pragma unroll
         for (int r = 0; r < kRowUnroll; ++r)
 #pragma unroll
           for (int t = 0; t < kMaxOwn; ++t)
-            if (t < own.n && (r0 + r) < rows) ov[r][t] = x[(r0 + r) * ldx + own.col[t]];
+            if (t < lo.n && (r0 + r) < rows) ov[r][t] = x[(r0 + r) * ldx + lo.col[t]];
       }
 #pragma unroll
       for (int r = 0; r < kRowUnroll; ++r) {
@@ -183,20 +242,18 @@ quant_pack_kernel(const __nv_bfloat16* __restrict__ x, int64_t rows, int N, int6
           }
         }
         st_stream_v2(q + (r0 + r) * qld + 8 * (int64_t)ct, packed);
-        if (own.n > 0 && !overflow) {
+        if (lo.n > 0) {
 #pragma unroll
           for (int t = 0; t < kMaxOwn; ++t)
-            if (t < own.n) oout[(r0 + r) * k + own.j[t]] = ov[r][t];
+            if (t < lo.n) oout[(r0 + r) * k + lo.j[t]] = ov[r][t];
+          // columns that were not dealt out (more than two per lane in the warp's span; every lane of
+          // such a warp serves dealt entries, so the owner gets here)
+          for (uint32_t bits = lo.extra; bits; bits &= bits - 1u) {
+            const int b = __ffs(bits) - 1;
+            const int col = G::slab_col(ct, b >> 3) + (b & 7);
+            oout[(r0 + r) * k + s_map[col - col0]] = x[(r0 + r) * ldx + col];
+          }
         }
-      }
-    }
-    if (overflow) {
-      // rare: some thread owns more than kMaxOwn outlier columns; the block gathers its span together
-      for (int t = threadIdx.x; t < kRowUnroll * k; t += blockDim.x) {
-        const int64_t row = r0 + t / k;
-        const int j = t % k;
-        const int64_t c = oidx[j] - col0;
-        if (row < rows && c >= 0 && c < span_cols) oout[row * k + j] = x[row * ldx + oidx[j]];
       }
     }
   }
@@ -207,7 +264,7 @@ quant_pack_kernel(const __nv_bfloat16* __restrict__ x, int64_t rows, int N, int6
 // which is what the reference does (it zeroes x, then runs the same kernel).
 
 template <int QBIT, bool HAS_ZP>
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(kThreads, (QBIT == 8 && !HAS_ZP) ? 3 : 2)
 unpack_dequant_kernel(const uint8_t* __restrict__ q, int64_t rows, int N,
                       const __nv_bfloat16* __restrict__ scale, const int8_t* __restrict__ zp,
                       const int64_t* __restrict__ oidx, int k, const __nv_bfloat16* __restrict__ oin,
@@ -224,8 +281,7 @@ unpack_dequant_kernel(const uint8_t* __restrict__ q, int64_t rows, int N,
 
   extern __shared__ __align__(16) uint8_t s_dyn[];
   int16_t* s_map = reinterpret_cast<int16_t*>(s_dyn);
-  int* s_overflow = reinterpret_cast<int*>(s_dyn + 2 * span_cols);
-  if (k > 0) build_outlier_map(s_map, s_overflow, span_cols, col0, oidx, k);
+  if (k > 0) build_outlier_map(s_map, span_cols, col0, oidx, k);
 
   // x_hat = bf16( bf16(code - half [- z]) * s ).  (code - half - z) is an integer of magnitude
   // <= 255, exact in bf16; the product of two bf16 values rounded once to bf16 is the reference's
@@ -237,10 +293,7 @@ unpack_dequant_kernel(const uint8_t* __restrict__ q, int64_t rows, int N,
   constexpr bool PACKED = QBIT < 8;
   uint32_t s2[EPP][4], off2[(PACKED && HAS_ZP) ? EPP : 1][4];
   float s[PACKED ? 1 : EPP][8], off[PACKED ? 1 : EPP][8];
-  OwnOutliers own;
-  own.n = 0;
-#pragma unroll
-  for (int i = 0; i < kMaxOwn; ++i) { own.col[i] = 0; own.j[i] = 0; }
+  int n_own = 0;
   if (active) {
 #pragma unroll
     for (int i = 0; i < EPP; ++i) {
@@ -267,40 +320,47 @@ unpack_dequant_kernel(const uint8_t* __restrict__ q, int64_t rows, int N,
           off[i][e] = 8388608.f + (float)((1 << (QBIT - 1)) + zb);
         }
         const int jv = (int)(int16_t)((mw[e >> 1] >> (16 * (e & 1))) & 0xffffu);
-        if (jv >= 0) {
-#pragma unroll
-          for (int t = 0; t < kMaxOwn; ++t)
-            if (own.n == t) { own.col[t] = c + e; own.j[t] = jv; }
-          ++own.n;
-        }
+        if (jv >= 0) ++n_own;
       }
     }
-    if (own.n > kMaxOwn) atomicOr(s_overflow, 1);
   }
-  bool overflow = false;
-  if (k > 0) { __syncthreads(); overflow = *s_overflow != 0; }
+  LaneOutliers lo;
+  lo.n = 0; lo.extra = 0u; lo.warp_has = false;
+  if (k > 0) {
+    lo = deal_outliers(reinterpret_cast<uint32_t*>(s_dyn + 2 * span_cols), col0, active, n_own, [&](auto f) {
+      for (int i = 0; i < EPP; ++i)
+        for (int e = 0; e < 8; ++e) {
+          const int col = G::slab_col(ct, i) + e;
+          const int jv = s_map[col - col0];
+          if (jv >= 0) f(i, e, col, jv);
+        }
+    });
+  }
 
   const int64_t n_groups = (rows + kDeqUnroll - 1) / kDeqUnroll;
   for (int64_t g = blockIdx.y; g < n_groups; g += gridDim.y) {
     const int64_t r0 = g * kDeqUnroll;
+    // the lane's share of the saved outlier values, fetched ahead of the de-quantization
+    __nv_bfloat16 ov[kDeqUnroll][kMaxOwn];
+    if (lo.n > 0) {
+#pragma unroll
+      for (int r = 0; r < kDeqUnroll; ++r)
+#pragma unroll
+        for (int t = 0; t < kMaxOwn; ++t)
+          if (t < lo.n && (r0 + r) < rows) ov[r][t] = oin[(r0 + r) * k + lo.j[t]];
+    }
+    uint2 p[kDeqUnroll];
     if (active) {
-      uint2 p[kDeqUnroll];
 #pragma unroll
       for (int r = 0; r < kDeqUnroll; ++r) {
         p[r] = make_uint2(0u, 0u);
         if ((r0 + r) < rows) p[r] = ld_stream_v2(q + (r0 + r) * qld + 8 * (int64_t)ct);
       }
-      __nv_bfloat16 ov[kDeqUnroll][kMaxOwn];
-      if (own.n > 0 && !overflow) {
+    }
 #pragma unroll
-        for (int r = 0; r < kDeqUnroll; ++r)
-#pragma unroll
-          for (int t = 0; t < kMaxOwn; ++t)
-            if (t < own.n && (r0 + r) < rows) ov[r][t] = oin[(r0 + r) * k + own.j[t]];
-      }
-#pragma unroll
-      for (int r = 0; r < kDeqUnroll; ++r) {
-        if ((r0 + r) >= rows) break;
+    for (int r = 0; r < kDeqUnroll; ++r) {
+      if ((r0 + r) >= rows) break;
+      if (active) {
         uint4 prev = make_uint4(0u, 0u, 0u, 0u);
 #pragma unroll
         for (int i = 0; i < EPP; ++i) {
@@ -346,21 +406,26 @@ unpack_dequant_kernel(const uint8_t* __restrict__ q, int64_t rows, int N,
             st_stream_v4(xo + (r0 + r) * ldx + G::slab_col(ct, i), o);
           }
         }
-        // the owner of an outlier column puts the saved value back, after its own store to that spot
-        if (own.n > 0 && !overflow) {
-#pragma unroll
-          for (int t = 0; t < kMaxOwn; ++t)
-            if (t < own.n) xo[(r0 + r) * ldx + own.col[t]] = ov[r][t];
-        }
       }
     }
-    if (overflow) {
-      __syncthreads();   // the block's stores to these rows come first
-      for (int t = threadIdx.x; t < kDeqUnroll * k; t += blockDim.x) {
-        const int64_t row = r0 + t / k;
-        const int j = t % k;
-        const int64_t c = oidx[j] - col0;
-        if (row < rows && c >= 0 && c < span_cols) xo[row * ldx + oidx[j]] = oin[row * k + j];
+    // the saved values go back on top of the warp's own stores to those columns (another lane's, as a
+    // rule): the barrier orders the two.  lo.warp_has is warp-uniform.
+    if (lo.warp_has) {
+      __syncwarp();
+      if (lo.n > 0) {
+#pragma unroll
+        for (int r = 0; r < kDeqUnroll; ++r) {
+          if ((r0 + r) >= rows) break;
+#pragma unroll
+          for (int t = 0; t < kMaxOwn; ++t)
+            if (t < lo.n) xo[(r0 + r) * ldx + lo.col[t]] = ov[r][t];
+          // columns that were not dealt out stay with their owner
+          for (uint32_t bits = lo.extra; bits; bits &= bits - 1u) {
+            const int b = __ffs(bits) - 1;
+            const int col = G::slab_col(ct, b >> 3) + (b & 7);
+            xo[(r0 + r) * ldx + col] = oin[(r0 + r) * k + s_map[col - col0]];
+          }
+        }
       }
     }
   }
@@ -418,7 +483,7 @@ extern "C" HYC_API int hyc_quant_pack(const void* x, int64_t rows, int N, int64_
   cudaStream_t st = (cudaStream_t)stream;
   const int cpt = 8 * (8 / q_bit);
   const int threads = pick_threads(N / cpt);
-  size_t smem = k > 0 ? (size_t)threads * cpt * 2 + 16 : 0;   // int16 column map + overflow flag
+  size_t smem = k > 0 ? (size_t)threads * cpt * 2 + (size_t)(threads / 32) * kWarpList * 4 : 0;   // int16 column map + per-warp lists
 #define LAUNCH_Q(QB, ZP)                                                                          \
   quant_pack_kernel<QB, ZP><<<stream_grid(quant_pack_kernel<QB, ZP>, threads, smem, rows, N / cpt, kRowUnroll), threads, smem, st>>>( \
       (const __nv_bfloat16*)x, rows, N, ldx, (const __nv_bfloat16*)scale, zp, outlier_idx, k,      \
@@ -448,7 +513,7 @@ extern "C" HYC_API int hyc_unpack_dequant(const void* q, int64_t rows, int N,
   cudaStream_t st = (cudaStream_t)stream;
   const int cpt = 8 * (8 / q_bit);
   const int threads = pick_threads(N / cpt);
-  size_t smem = k > 0 ? (size_t)threads * cpt * 2 + 16 : 0;
+  size_t smem = k > 0 ? (size_t)threads * cpt * 2 + (size_t)(threads / 32) * kWarpList * 4 : 0;
 #define LAUNCH_D(QB, ZP)                                                                          \
   unpack_dequant_kernel<QB, ZP><<<stream_grid(unpack_dequant_kernel<QB, ZP>, threads, smem, rows, N / cpt, kDeqUnroll), threads, smem, st>>>(                                        \
       (const uint8_t*)q, rows, N, (const __nv_bfloat16*)scale, zp, outlier_idx, k,                 \

@@ -38,6 +38,28 @@ def test_group_mode(cf, q, shape):
     assert torch.equal(cf.decompression_group(pk, s, z, q).cpu(), oracle.group_decompress(opk, os_, oz, q))
 
 
+@pytest.mark.parametrize("q", QS)
+def test_group_mode_strided_rows(cf, q):
+    """Rows with a stride larger than N go through the C ABI directly (the Python operator always makes
+    its input contiguous); they take the warp-per-512-columns kernels instead of the flat ones."""
+    from hyc_lora_release_b200._lib import check, lib, ptr, stream_of
+    rows, N, ld = 6, 576, 640
+    g = torch.Generator().manual_seed(q)
+    full = (torch.randn(rows, ld, generator=g) * 3).to(torch.bfloat16)
+    x = full[:, :N]
+    xd = full.to(DEV)
+    pk = torch.empty(rows, N * q // 8, dtype=torch.uint8, device=DEV)
+    s = torch.empty(rows, N // 64, dtype=torch.bfloat16, device=DEV)
+    z = torch.empty(rows, N // 64, dtype=torch.int8, device=DEV)
+    check(lib.hyc_group_quant_pack(ptr(xd), rows, N, ld, ptr(pk), ptr(s), ptr(z), q, stream_of(xd)), "quant")
+    opk, os_, oz = oracle.group_compress(x.contiguous(), q)
+    assert torch.equal(s.cpu(), os_) and torch.equal(z.cpu(), oz) and torch.equal(pk.cpu(), opk)
+    out = torch.full((rows, ld), 7.0, dtype=torch.bfloat16, device=DEV)
+    check(lib.hyc_group_unpack_dequant(ptr(pk), rows, N, ptr(s), ptr(z), ptr(out), ld, q, stream_of(xd)), "dequant")
+    assert torch.equal(out[:, :N].cpu(), oracle.group_decompress(opk, os_, oz, q))
+    assert (out[:, N:] == 7.0).all()
+
+
 def test_softmax_prune_golden(cf, golden):
     d = golden["softmax"]
     a = d["a"].to(DEV)

@@ -94,6 +94,25 @@ def test_oracle_ragged_shapes(cf, q, shape):
     assert torch.equal(xr.cpu(), oracle.ref_decompress_channel_base(opk, osc, oxo, oidx, q))
 
 
+@pytest.mark.parametrize("q", QS)
+def test_clustered_outlier_channels(cf, q):
+    """Outlier channels packed next to each other: single threads own 3..8 of them (more than they keep in
+    registers), whole blocks of 32 columns are outliers, and the list is not sorted."""
+    B, M, N = 2, 37, 2048
+    g = torch.Generator().manual_seed(5 + q)
+    x = torch.randn(B, M, N, generator=g).to(torch.bfloat16)
+    cols = list(range(64, 72)) + [100, 101, 102] + list(range(512, 544)) + [1031, 1047, 1063, 1079] + [2047, 0, 33, 35, 37]
+    idx = torch.tensor(cols, dtype=torch.int64)[torch.randperm(len(cols), generator=g)]
+    s = oracle.ref_scale_per_channel(x, q)
+    s = torch.where(s == 0, torch.tensor(1e-3, dtype=torch.bfloat16), s)
+    xd, sd, idxd = x.to(DEV), s.to(DEV), idx.to(DEV)
+    xo, pk = cf.outlier_subtraction_fuse_compression_quantization(xd, sd, idxd, q)
+    oxo, opk = oracle.ref_compress_channel_base(x, s, idx, q)
+    assert torch.equal(xo.cpu(), oxo) and torch.equal(pk.cpu(), opk)
+    xr = cf.outlier_addition_fuse_decompression_dequantization(pk, sd, xo, idxd, q)
+    assert torch.equal(xr.cpu(), oracle.ref_decompress_channel_base(opk, s, oxo, idx, q))
+
+
 def test_config0_full_size(cf):
     """bf16 [4,512,4096], 0.5 % channels x30, ratio 0.005, q_bit 4 (the CPU-runnable config)."""
     g = torch.Generator().manual_seed(1234)
