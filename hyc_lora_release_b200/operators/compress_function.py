@@ -318,13 +318,14 @@ class TopkMap:
     def nbytes(self):
         return sum(t.numel() * t.element_size() for t in self.tensors())
 
-    def to_dense(self):
-        return decompression_softmax_topk(self)
+    def to_dense(self, out=None):
+        return decompression_softmax_topk(self, out=out)
 
 
-def compression_softmax_topk(x, outlier_ratio, quantize_bit=4):
+def compression_softmax_topk(x, outlier_ratio, quantize_bit=4, out=None):
     """Top-k per row (k = int(S * ratio)) as bf16 value + uint16 column, the remainder
-    group-quantized.  x [..., S] with S % 64 == 0, S <= 4096."""
+    group-quantized.  x [..., S] with S % 64 == 0, S <= 4096.  ``out``: a TopkMap of an earlier call
+    on the same shape, ratio and bit width whose buffers are overwritten (a ring of saved maps)."""
     require_cuda(x)
     _check_q(quantize_bit)
     xb = x.to(BF16).contiguous()
@@ -332,22 +333,32 @@ def compression_softmax_topk(x, outlier_ratio, quantize_bit=4):
     rows = xb.numel() // S
     k = int(S * outlier_ratio)
     dev = x.device
-    val = torch.empty((rows, k), dtype=BF16, device=dev)
-    col = torch.empty((rows, k), dtype=torch.int16, device=dev)   # holds uint16 column numbers
-    q = torch.empty((rows, S * quantize_bit // 8), dtype=torch.uint8, device=dev)
-    s = torch.empty((rows, S // 64), dtype=BF16, device=dev)
-    z = torch.empty((rows, S // 64), dtype=torch.int8, device=dev)
+    if out is not None:
+        if (out.shape != tuple(x.shape) or out.q_bit != quantize_bit or out.val.shape != (rows, k)
+                or out.q.device != dev):
+            raise ValueError("`out` was made for another shape, ratio, bit width or device")
+        val, col, q, s, z = out.tensors()
+    else:
+        val = torch.empty((rows, k), dtype=BF16, device=dev)
+        col = torch.empty((rows, k), dtype=torch.int16, device=dev)   # holds uint16 column numbers
+        q = torch.empty((rows, S * quantize_bit // 8), dtype=torch.uint8, device=dev)
+        s = torch.empty((rows, S // 64), dtype=BF16, device=dev)
+        z = torch.empty((rows, S // 64), dtype=torch.int8, device=dev)
     check(lib.hyc_softmax_topk_compress(ptr(xb), rows, S, k, ptr(val) if k else None, ptr(col) if k else None,
                                         ptr(q), ptr(s), ptr(z), quantize_bit, stream_of(x)),
           "hyc_softmax_topk_compress")
-    return TopkMap(val, col, q, s, z, x.shape, quantize_bit)
+    return out if out is not None else TopkMap(val, col, q, s, z, x.shape, quantize_bit)
 
 
-def decompression_softmax_topk(m: TopkMap):
+def decompression_softmax_topk(m: TopkMap, out=None):
+    """``out``: an existing contiguous bf16 tensor of the map's shape."""
     S = m.shape[-1]
     rows = m.q.shape[0]
     k = m.val.shape[1]
-    out = torch.empty(m.shape, dtype=BF16, device=m.q.device)
+    if out is None:
+        out = torch.empty(m.shape, dtype=BF16, device=m.q.device)
+    elif tuple(out.shape) != m.shape or out.dtype != BF16 or not out.is_contiguous() or out.device != m.q.device:
+        raise ValueError("`out` must be a contiguous bf16 tensor of shape %s on the map's device" % (m.shape,))
     check(lib.hyc_softmax_topk_restore(ptr(m.val) if k else None, ptr(m.col) if k else None, k, ptr(m.q),
                                        ptr(m.scale), ptr(m.zp), rows, S, ptr(out), m.q_bit, stream_of(m.q)),
           "hyc_softmax_topk_restore")

@@ -144,6 +144,24 @@ def test_topk_ties_lane_layout(cf, S, rows):
             assert torch.equal(m.to_dense().cpu(), oracle.topk_decompress(vals, cols, pk, sc, zp, q, x.shape))
 
 
+def test_topk_reused_buffers(cf):
+    """``out=`` writes into the buffers of an earlier handle / an existing dense tensor, bit-identically."""
+    a = _softmax_map(1, 2, 512, seed=3).to(DEV)
+    b = _softmax_map(1, 2, 512, seed=4).to(DEV)
+    ha = cf.compression_softmax_topk(a, 0.05, 4)
+    hb = cf.compression_softmax_topk(b, 0.05, 4)
+    want = [t.clone() for t in hb.tensors()]
+    dense_b = hb.to_dense().clone()
+    h = cf.compression_softmax_topk(b, 0.05, 4, out=ha)
+    assert h is ha and all(torch.equal(x, y) for x, y in zip(ha.tensors(), want))
+    buf = torch.empty_like(a)
+    assert ha.to_dense(out=buf) is buf and torch.equal(buf, dense_b)
+    with pytest.raises(ValueError):
+        cf.compression_softmax_topk(b, 0.1, 4, out=ha)
+    with pytest.raises(ValueError):
+        ha.to_dense(out=torch.empty(2, 512, 512, dtype=torch.bfloat16, device=DEV))
+
+
 def test_topk_config1_full_size_properties(cf):
     """[4,32,512,512] causal softmax map, ratio 0.05, q_bit 4: checked through size-independent
     properties plus the oracle on a slice."""
