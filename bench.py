@@ -27,6 +27,9 @@ MAP_SHAPE = (4, 32, 512, 512)
 RATIO = 0.05
 QBIT = 4
 NBUF = 4          # distinct input/output sets rotated between steps (4 x 64 MiB in, > L2)
+# dram__bytes_read.sum + dram__bytes_write.sum of ONE launch on this workload, from the ncu capture that
+# profiles/topk_lane_attention_map_4x32x512x512_q4.md summarises (bytes)
+NCU_TRAFFIC = {"hyc::topk_lane_compress_kernel<4,8>": 72.2e6, "hyc::topk_lane_restore_kernel<4,8>": 36.1e6}
 
 
 def peaks():
@@ -451,7 +454,8 @@ def main():
             "gpu_launches": 2 * args.steps,
             "frac_of_hbm_peak": value / world / hbm,
             "roofline": {"bound": "hbm", "kernel": dom, "achieved": achieved, "peak": hbm, "unit": "GB/s",
-                         "frac": achieved / hbm, "peak_source": peak_src, "traffic": None,
+                         "frac": achieved / hbm, "peak_source": peak_src,
+                         "traffic": NCU_TRAFFIC.get(dom),
                          "algorithmic_bytes_per_launch": one_way,
                          "kernel_ms": {"compress": t_c * 1e3, "decompress": t_d * 1e3}},
             "cpu_baseline": cpu, "also": also,

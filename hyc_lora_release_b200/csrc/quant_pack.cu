@@ -19,8 +19,11 @@ namespace hyc {
 #endif
 constexpr int kThreads = 256;          // upper bound; the launch picks the width that wastes fewest lanes
 constexpr int kRowUnroll = HYC_ROW_UNROLL;
+#ifndef HYC_DEQ_MINBLOCKS
+#define HYC_DEQ_MINBLOCKS 3     // resident blocks per SM the de-quantizer is compiled for (register cap 80)
+#endif
 #ifndef HYC_DEQ_UNROLL
-#define HYC_DEQ_UNROLL 8
+#define HYC_DEQ_UNROLL 4
 #endif
 constexpr int kDeqUnroll = HYC_DEQ_UNROLL;          // the de-quantizer loads only 8 bytes per row: keep more rows in flight
 
@@ -264,7 +267,7 @@ quant_pack_kernel(const __nv_bfloat16* __restrict__ x, int64_t rows, int N, int6
 // which is what the reference does (it zeroes x, then runs the same kernel).
 
 template <int QBIT, bool HAS_ZP>
-__global__ void __launch_bounds__(kThreads, (QBIT == 8 && !HAS_ZP) ? 3 : 2)
+__global__ void __launch_bounds__(kThreads, HAS_ZP ? 2 : (QBIT == 8 ? HYC_DEQ_MINBLOCKS + 1 : HYC_DEQ_MINBLOCKS))
 unpack_dequant_kernel(const uint8_t* __restrict__ q, int64_t rows, int N,
                       const __nv_bfloat16* __restrict__ scale, const int8_t* __restrict__ zp,
                       const int64_t* __restrict__ oidx, int k, const __nv_bfloat16* __restrict__ oin,
