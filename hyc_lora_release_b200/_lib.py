@@ -45,7 +45,7 @@ SIGNATURES = {
     "hyc_mlp_gateup_fwd_tcgen05": (_i, [_p, _p, _p, _i, _i, _i, _p, _p, _l, _l, _p, _p, _l, _l,
                                         _p, _p, _p, _p, _p, _p, _p, _i, _p, _p]),
     "hyc_mlp_graddown_bwd_tcgen05": (_i, [_p, _p, _i, _i, _i, _p, _p, _i, _p, _p, _l, _l, _p, _p, _l, _l,
-                                          _p, _p, _p, _p, _p, _p, _p, _i, _p, _p]),
+                                          _p, _p, _p, _p, _p, _p, _l, _p, _p, _p, _i, _p, _p]),
 }
 
 for _name, (_res, _args) in SIGNATURES.items():

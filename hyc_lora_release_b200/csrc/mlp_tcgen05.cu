@@ -22,6 +22,14 @@
 #include "hyc_common.cuh"
 #include <cuda.h>
 
+#ifdef HYC_TC_PROF
+#define TC_STAMP(role, it, j) do { if (p.prof != nullptr && blockIdx.x == 0 && (it) < 16) p.prof[((role) * 16 + (it)) * 8 + (j)] = clock64(); } while (0)
+static long long* g_tc_prof = nullptr;
+extern "C" __attribute__((visibility("default"))) void hyc_tc_debug_profile(void* buf) { g_tc_prof = (long long*)buf; }
+#else
+#define TC_STAMP(role, it, j) do { } while (0)
+#endif
+
 namespace hyc {
 namespace tc {
 
@@ -60,7 +68,13 @@ struct Params {
   uint8_t* q2;
   const __nv_bfloat16* s1;    // per-channel scales [N]
   const __nv_bfloat16* s2;
+  const __nv_bfloat16* lpre1; // GRADDOWN: optional precomputed LoRA terms bf16(xa1 B1^T), bf16(xa2 B2^T), [M, ld_pre]
+  const __nv_bfloat16* lpre2;
+  int64_t ld_pre;
   int* status;
+#ifdef HYC_TC_PROF
+  long long* prof;            // debug builds only: clock64 stamps of CTA 0, [role][tile][8]
+#endif
 };
 
 // ------------------------------------------------------------------ PTX wrappers
@@ -137,6 +151,38 @@ __device__ __forceinline__ void epi_bar_sync() { asm volatile("bar.sync 1, %0;" 
 // bits already are the float
 __device__ __forceinline__ float bfr(float v) { return __uint_as_float(pack_bf16x2_rn(0.f, v) & 0xffff0000u); }
 
+// ---- packed bf16x2 arithmetic.  The reference's element-wise chain works on bf16 tensors (every
+// operation rounds to bf16).  For bf16 operands a packed add/sub/mul is the same thing: the fp32 product of
+// two bf16 values is exact and the fp32 sum is exact unless the operands are more than 16 binades apart (then
+// both forms return the larger one), so one rounding to bf16 is all that ever happens.  Two columns per
+// instruction, no conversion instruction: those are the scarce resource of an epilogue that has only two
+// warps per scheduler.
+typedef __nv_bfloat162 bf2;
+__device__ __forceinline__ bf2 as_bf2(uint32_t v) { return *reinterpret_cast<bf2*>(&v); }
+__device__ __forceinline__ uint32_t as_u32(bf2 v) { return *reinterpret_cast<uint32_t*>(&v); }
+// (the _rn forms: a multiply followed by an add must NOT be contracted into one fused operation, the
+// reference rounds after each)
+__device__ __forceinline__ uint32_t add2(uint32_t a, uint32_t b) { return as_u32(__hadd2_rn(as_bf2(a), as_bf2(b))); }
+__device__ __forceinline__ uint32_t sub2(uint32_t a, uint32_t b) { return as_u32(__hsub2_rn(as_bf2(a), as_bf2(b))); }
+__device__ __forceinline__ uint32_t mul2(uint32_t a, uint32_t b) { return as_u32(__hmul2_rn(as_bf2(a), as_bf2(b))); }
+constexpr uint32_t kOne2 = 0x3f803f80u;   // (1.0, 1.0)
+// bf16(sigmoid(y)) of both halves; the sigmoid itself is fp32 as in the reference kernels
+__device__ __forceinline__ uint32_t sigmoid2(uint32_t y) {
+  const float a = bf16lo_to_f32(y), b = bf16hi_to_f32(y);
+  return pack_bf16x2_rn(__fdividef(1.f, 1.f + __expf(-a)), __fdividef(1.f, 1.f + __expf(-b)));
+}
+// dot with an fp32 LoRA-B row in shared memory (gate/up tiles are 128 columns wide, so fp32 rows fit)
+__device__ __forceinline__ float lora_dot_f32(const float (&xa)[16], const float* __restrict__ brow) {
+  float a = 0.f;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float4 b = *reinterpret_cast<const float4*>(brow + 4 * j);
+    a = fmaf(xa[4 * j], b.x, a); a = fmaf(xa[4 * j + 1], b.y, a);
+    a = fmaf(xa[4 * j + 2], b.z, a); a = fmaf(xa[4 * j + 3], b.w, a);
+  }
+  return a;
+}
+
 // dot of the thread's LoRA-A row (16 floats) with the bf16 LoRA-B row of a column in shared memory
 // (all lanes read the same 32 bytes: a broadcast)
 __device__ __forceinline__ float lora_dot(const float (&xa)[16], const __nv_bfloat16* __restrict__ brow) {
@@ -163,24 +209,39 @@ __device__ __forceinline__ void load_xa_row(const __nv_bfloat16* xa, int64_t row
   for (int j = 0; j < 8; ++j) { out[2 * j] = bf16lo_to_f32(w[j]); out[2 * j + 1] = bf16hi_to_f32(w[j]); }
 }
 
+// cooperative staging of a LoRA-B tile as fp32 rows (ncols x 16 floats)
+__device__ __forceinline__ void stage_lora_tile_f32(const LoraTerm& t, int n0, int ncols, float* dst, int et) {
+  if (t.bt == nullptr) return;
+  if (t.ld_r == 1 && t.ld_col == 16 && (reinterpret_cast<uintptr_t>(t.bt) & 15) == 0) {
+    // [columns, 16] row-major (the layout of a lora_B weight): 128-bit loads, eight values each
+    const uint4* src = reinterpret_cast<const uint4*>(t.bt + (int64_t)n0 * 16);
+    for (int i = et; i < ncols * 2; i += 32 * EPI_WARPS) {
+      const uint4 v = src[i];
+      float4 a, b;
+      a.x = bf16lo_to_f32(v.x); a.y = bf16hi_to_f32(v.x); a.z = bf16lo_to_f32(v.y); a.w = bf16hi_to_f32(v.y);
+      b.x = bf16lo_to_f32(v.z); b.y = bf16hi_to_f32(v.z); b.z = bf16lo_to_f32(v.w); b.w = bf16hi_to_f32(v.w);
+      reinterpret_cast<float4*>(dst)[2 * i] = a;
+      reinterpret_cast<float4*>(dst)[2 * i + 1] = b;
+    }
+    return;
+  }
+  for (int i = et; i < ncols * 16; i += 32 * EPI_WARPS) {
+    const int c = i >> 4, r = i & 15;
+    dst[i] = __bfloat162float(t.bt[(int64_t)(n0 + c) * t.ld_col + (int64_t)r * t.ld_r]);
+  }
+}
 // cooperative staging of a LoRA-B tile (ncols x 16, bf16) into shared memory
 __device__ __forceinline__ void stage_lora_tile(const LoraTerm& t, int n0, int ncols, __nv_bfloat16* dst, int et) {
   if (t.bt == nullptr) return;
+  if (t.ld_r == 1 && t.ld_col == 16 && (reinterpret_cast<uintptr_t>(t.bt) & 15) == 0) {
+    const uint4* src = reinterpret_cast<const uint4*>(t.bt + (int64_t)n0 * 16);
+    for (int i = et; i < ncols * 2; i += 32 * EPI_WARPS) reinterpret_cast<uint4*>(dst)[i] = src[i];
+    return;
+  }
   for (int i = et; i < ncols * 16; i += 32 * EPI_WARPS) {
     const int c = i >> 4, r = i & 15;
     dst[i] = t.bt[(int64_t)(n0 + c) * t.ld_col + (int64_t)r * t.ld_r];
   }
-}
-
-struct SiluTerms { float y1, sig, y1s, y2, o; };
-__device__ __forceinline__ SiluTerms silu_terms(float x1, float l1, float x2, float l2) {
-  SiluTerms r;
-  r.y1 = bfr(x1 + bfr(l1));
-  r.sig = bfr(__fdividef(1.f, 1.f + __expf(-r.y1)));
-  r.y1s = bfr(r.y1 * r.sig);
-  r.y2 = bfr(x2 + bfr(l2));
-  r.o = bfr(r.y1s * r.y2);
-  return r;
 }
 
 // The reference byte layout of a 32-column block: byte j carries, at bit QBIT*i, the code of
@@ -230,21 +291,18 @@ __device__ __forceinline__ void load_block_words(const uint8_t* src, bool valid,
   }
 }
 
-__device__ __forceinline__ void store8_bf16(__nv_bfloat16* dst, const float (&v)[8]) {
-  uint4 o;
-  o.x = pack_bf16x2_rn(v[0], v[1]); o.y = pack_bf16x2_rn(v[2], v[3]);
-  o.z = pack_bf16x2_rn(v[4], v[5]); o.w = pack_bf16x2_rn(v[6], v[7]);
-  *reinterpret_cast<uint4*>(dst) = o;
+// ------------------------------------------------------------------ epilogues (one 32-column chunk per call)
+// cb = column offset of the chunk inside the tile, ncol0 = first output column of the tile.  The thread owns
+// one row; columns are handled two at a time as packed bf16 pairs.
+__device__ __forceinline__ void store4_pairs(__nv_bfloat16* dst, const uint32_t (&v)[4]) {
+  *reinterpret_cast<uint4*>(dst) = make_uint4(v[0], v[1], v[2], v[3]);
 }
 
-// ------------------------------------------------------------------ epilogues (one 32-column chunk per call)
-// cb = column offset of the chunk inside the tile, ncol0 = first output column of the tile.
 template <int QBIT>
 __device__ __forceinline__ void epi_gateup_block(const Params& p, int64_t row, bool valid, int ncol0, int cb,
                                                  const uint32_t (&g)[32], const uint32_t (&u)[32],
                                                  const float (&xa1)[16], const float (&xa2)[16],
-                                                 const __nv_bfloat16* sB1, const __nv_bfloat16* sB2, const float* sS1, const float* sR1,
-                                                 const float* sS2, const float* sR2) {
+                                                 const float* sB1, const float* sB2, const float* sR1, const float* sR2) {
   using G = BlockGeo<QBIT>;
   const int64_t n = (int64_t)ncol0 + cb;
   uint32_t w1[G::NW], w2[G::NW];
@@ -252,17 +310,24 @@ __device__ __forceinline__ void epi_gateup_block(const Params& p, int64_t row, b
   for (int i = 0; i < G::NW; ++i) { w1[i] = 0u; w2[i] = 0u; }
 #pragma unroll
   for (int c8 = 0; c8 < 4; ++c8) {
-    float o[8];
+    uint32_t o[4];
 #pragma unroll
-    for (int e = 0; e < 8; ++e) {
-      const int c = 8 * c8 + e, tc = cb + c;
+    for (int e2 = 0; e2 < 4; ++e2) {
+      const int c = 8 * c8 + 2 * e2, tc = cb + c;
       // the frozen-weight products are bf16 tensors in the reference before anything else touches them
-      const float x1 = bfr(__uint_as_float(g[c])), x2 = bfr(__uint_as_float(u[c]));
-      put_code<QBIT>(w1, c, fastq_code_bits<QBIT>(x1, sR1[tc]) & G::CM);
-      put_code<QBIT>(w2, c, fastq_code_bits<QBIT>(x2, sR2[tc]) & G::CM);
-      o[e] = silu_terms(x1, lora_dot(xa1, sB1 + tc * 16), x2, lora_dot(xa2, sB2 + tc * 16)).o;
+      const uint32_t x1 = pack_bf16x2_rn(__uint_as_float(g[c]), __uint_as_float(g[c + 1]));
+      const uint32_t x2 = pack_bf16x2_rn(__uint_as_float(u[c]), __uint_as_float(u[c + 1]));
+      put_code<QBIT>(w1, c, fastq_code_bits<QBIT>(bf16lo_to_f32(x1), sR1[tc]) & G::CM);
+      put_code<QBIT>(w1, c + 1, fastq_code_bits<QBIT>(bf16hi_to_f32(x1), sR1[tc + 1]) & G::CM);
+      put_code<QBIT>(w2, c, fastq_code_bits<QBIT>(bf16lo_to_f32(x2), sR2[tc]) & G::CM);
+      put_code<QBIT>(w2, c + 1, fastq_code_bits<QBIT>(bf16hi_to_f32(x2), sR2[tc + 1]) & G::CM);
+      const uint32_t l1 = pack_bf16x2_rn(lora_dot_f32(xa1, sB1 + tc * 16), lora_dot_f32(xa1, sB1 + (tc + 1) * 16));
+      const uint32_t l2 = pack_bf16x2_rn(lora_dot_f32(xa2, sB2 + tc * 16), lora_dot_f32(xa2, sB2 + (tc + 1) * 16));
+      const uint32_t y1 = add2(x1, l1);
+      const uint32_t y1s = mul2(y1, sigmoid2(y1));
+      o[e2] = mul2(y1s, add2(x2, l2));
     }
-    if (valid) store8_bf16(p.out0 + row * p.N + n + 8 * c8, o);
+    if (valid) store4_pairs(p.out0 + row * p.N + n + 8 * c8, o);
   }
   if (valid) {
     store_block_words<QBIT>(p.q1 + (row * p.N + n) * QBIT / 8, w1);
@@ -270,13 +335,34 @@ __device__ __forceinline__ void epi_gateup_block(const Params& p, int64_t row, b
     if (p.dbg1 != nullptr) {
 #pragma unroll
       for (int c8 = 0; c8 < 4; ++c8) {
-        float a[8], b[8];
+        uint32_t a[4], b[4];
 #pragma unroll
-        for (int e = 0; e < 8; ++e) { a[e] = __uint_as_float(g[8 * c8 + e]); b[e] = __uint_as_float(u[8 * c8 + e]); }
-        store8_bf16(p.dbg1 + row * p.N + n + 8 * c8, a);
-        store8_bf16(p.dbg2 + row * p.N + n + 8 * c8, b);
+        for (int e2 = 0; e2 < 4; ++e2) {
+          a[e2] = pack_bf16x2_rn(__uint_as_float(g[8 * c8 + 2 * e2]), __uint_as_float(g[8 * c8 + 2 * e2 + 1]));
+          b[e2] = pack_bf16x2_rn(__uint_as_float(u[8 * c8 + 2 * e2]), __uint_as_float(u[8 * c8 + 2 * e2 + 1]));
+        }
+        store4_pairs(p.dbg1 + row * p.N + n + 8 * c8, a);
+        store4_pairs(p.dbg2 + row * p.N + n + 8 * c8, b);
       }
     }
+  }
+}
+
+// the saved codes of columns c, c + 1 of a 32-column block as the bf16 pair (x_hat[c], x_hat[c + 1]),
+// x_hat = bf16((code - half) * scale); sc2 = the two scales as a packed pair
+template <int QBIT>
+__device__ __forceinline__ uint32_t dequant_pair(const uint32_t (&w)[BlockGeo<QBIT>::NW], int c, uint32_t sc2) {
+  const uint32_t c0 = get_code<QBIT>(w, c), c1 = get_code<QBIT>(w, c + 1);
+  if constexpr (QBIT == 8) {
+    // codes reach 255: through fp32 (2^23 + code), one rounding in the packed conversion
+    const float f0 = (__uint_as_float(0x4B000000u | c0) - 8388736.f) * bf16lo_to_f32(sc2);
+    const float f1 = (__uint_as_float(0x4B000000u | c1) - 8388736.f) * bf16hi_to_f32(sc2);
+    return pack_bf16x2_rn(f0, f1);
+  } else {
+    // 0x4300 | code is the bf16 128 + code; minus (128 + half) is exact, the product rounds once
+    constexpr uint32_t C1 = 0x4300u | (uint32_t)(1 << (QBIT - 1));
+    const uint32_t pr = 0x43004300u | c0 | (c1 << 16);
+    return mul2(sub2(pr, C1 | (C1 << 16)), sc2);
   }
 }
 
@@ -285,33 +371,47 @@ __device__ __forceinline__ void epi_graddown_block(const Params& p, int64_t row,
                                                    const uint32_t (&acc)[32],
                                                    const float (&xa1)[16], const float (&xa2)[16],
                                                    const __nv_bfloat16* sB1, const __nv_bfloat16* sB2,
-                                                   const float* sS1, const float* sS2) {
+                                                   const uint32_t* sS1, const uint32_t* sS2) {
   using G = BlockGeo<QBIT>;
-  constexpr float HALF = (float)(1 << (QBIT - 1));
   const int64_t n = (int64_t)ncol0 + cb;
   uint32_t w1[G::NW], w2[G::NW];
   load_block_words<QBIT>(p.q1 + (row * p.N + n) * QBIT / 8, valid, w1);
   load_block_words<QBIT>(p.q2 + (row * p.N + n) * QBIT / 8, valid, w2);
+  const bool pre = p.lpre1 != nullptr;      // kernel-uniform
 #pragma unroll
   for (int c8 = 0; c8 < 4; ++c8) {
-    float o[8], gg[8], gu[8];
+    uint32_t o[4], gg[4], gu[4];
+    // the LoRA terms of the gate and up branches: read if a GEMM launch prepared them, else 16 FMAs each
+    uint4 pl1 = make_uint4(0u, 0u, 0u, 0u), pl2 = pl1;
+    if (pre && valid) {
+      pl1 = *reinterpret_cast<const uint4*>(p.lpre1 + row * p.ld_pre + n + 8 * c8);
+      pl2 = *reinterpret_cast<const uint4*>(p.lpre2 + row * p.ld_pre + n + 8 * c8);
+    }
+    const uint32_t pw1[4] = {pl1.x, pl1.y, pl1.z, pl1.w}, pw2[4] = {pl2.x, pl2.y, pl2.z, pl2.w};
 #pragma unroll
-    for (int e = 0; e < 8; ++e) {
-      const int c = 8 * c8 + e, tc = cb + c;
-      const float gd = bfr(__uint_as_float(acc[c]));   // the LoRA part of grad_down arrived as an extra K block
-      const float x1 = bfr(((float)get_code<QBIT>(w1, c) - HALF) * sS1[tc]);
-      const float x2 = bfr(((float)get_code<QBIT>(w2, c) - HALF) * sS2[tc]);
-      const SiluTerms t = silu_terms(x1, lora_dot(xa1, sB1 + tc * 16), x2, lora_dot(xa2, sB2 + tc * 16));
-      o[e] = t.o;
-      const float gh1 = bfr(gd * t.y2);
-      gu[e] = bfr(gd * t.y1s);
-      const float inner = bfr(1.f + bfr(t.y1 * bfr(1.f - t.sig)));
-      gg[e] = bfr(gh1 * bfr(t.sig * inner));
+    for (int e2 = 0; e2 < 4; ++e2) {
+      const int c = 8 * c8 + 2 * e2, tc = cb + c;
+      // the LoRA part of grad_down arrived as an extra K block
+      const uint32_t gd = pack_bf16x2_rn(__uint_as_float(acc[c]), __uint_as_float(acc[c + 1]));
+      const uint32_t x1 = dequant_pair<QBIT>(w1, c, sS1[tc >> 1]);
+      const uint32_t x2 = dequant_pair<QBIT>(w2, c, sS2[tc >> 1]);
+      uint32_t l1, l2;
+      if (pre) {
+        l1 = pw1[e2]; l2 = pw2[e2];
+      } else {
+        l1 = pack_bf16x2_rn(lora_dot(xa1, sB1 + tc * 16), lora_dot(xa1, sB1 + (tc + 1) * 16));
+        l2 = pack_bf16x2_rn(lora_dot(xa2, sB2 + tc * 16), lora_dot(xa2, sB2 + (tc + 1) * 16));
+      }
+      const uint32_t y1 = add2(x1, l1), sig = sigmoid2(y1), y1s = mul2(y1, sig), y2 = add2(x2, l2);
+      o[e2] = mul2(y1s, y2);
+      gu[e2] = mul2(gd, y1s);
+      const uint32_t inner = add2(kOne2, mul2(y1, sub2(kOne2, sig)));
+      gg[e2] = mul2(mul2(gd, y2), mul2(sig, inner));
     }
     if (valid) {
-      store8_bf16(p.out0 + row * p.N + n + 8 * c8, o);
-      store8_bf16(p.out1 + row * p.N + n + 8 * c8, gg);
-      store8_bf16(p.out2 + row * p.N + n + 8 * c8, gu);
+      store4_pairs(p.out0 + row * p.N + n + 8 * c8, o);
+      store4_pairs(p.out1 + row * p.N + n + 8 * c8, gg);
+      store4_pairs(p.out2 + row * p.N + n + 8 * c8, gu);
     }
   }
 }
@@ -320,27 +420,24 @@ __device__ __forceinline__ void epi_store_block(const Params& p, int64_t row, bo
                                                 const uint32_t (&acc)[32], const float (&xa0)[16], const float (&xa1)[16],
                                                 const __nv_bfloat16* sB0, const __nv_bfloat16* sB1) {
   const int64_t n = (int64_t)ncol0 + cb;
+  const bool has0 = p.l0.bt != nullptr, has1 = p.l1.bt != nullptr;
+  const bool has_res = p.residual != nullptr && valid;
 #pragma unroll
   for (int c8 = 0; c8 < 4; ++c8) {
-    float o[8], r[8];
+    uint4 rq = make_uint4(0u, 0u, 0u, 0u);
+    if (has_res) rq = *reinterpret_cast<const uint4*>(p.residual + row * p.N + n + 8 * c8);
+    const uint32_t r[4] = {rq.x, rq.y, rq.z, rq.w};
+    uint32_t o[4];
 #pragma unroll
-    for (int e = 0; e < 8; ++e) r[e] = 0.f;
-    const bool has_res = p.residual != nullptr && valid;
-    if (has_res) {
-      const uint4 q = *reinterpret_cast<const uint4*>(p.residual + row * p.N + n + 8 * c8);
-      r[0] = bf16lo_to_f32(q.x); r[1] = bf16hi_to_f32(q.x); r[2] = bf16lo_to_f32(q.y); r[3] = bf16hi_to_f32(q.y);
-      r[4] = bf16lo_to_f32(q.z); r[5] = bf16hi_to_f32(q.z); r[6] = bf16lo_to_f32(q.w); r[7] = bf16hi_to_f32(q.w);
+    for (int e2 = 0; e2 < 4; ++e2) {
+      const int c = 8 * c8 + 2 * e2, tc = cb + c;
+      uint32_t v = pack_bf16x2_rn(__uint_as_float(acc[c]), __uint_as_float(acc[c + 1]));
+      if (has0) v = add2(v, pack_bf16x2_rn(lora_dot(xa0, sB0 + tc * 16), lora_dot(xa0, sB0 + (tc + 1) * 16)));
+      if (has1) v = add2(v, pack_bf16x2_rn(lora_dot(xa1, sB1 + tc * 16), lora_dot(xa1, sB1 + (tc + 1) * 16)));
+      if (has_res) v = add2(v, r[e2]);
+      o[e2] = v;
     }
-#pragma unroll
-    for (int e = 0; e < 8; ++e) {
-      const int c = 8 * c8 + e, tc = cb + c;
-      float v = bfr(__uint_as_float(acc[c]));
-      if (p.l0.bt != nullptr) v = bfr(v + bfr(lora_dot(xa0, sB0 + tc * 16)));
-      if (p.l1.bt != nullptr) v = bfr(v + bfr(lora_dot(xa1, sB1 + tc * 16)));
-      if (has_res) v = bfr(v + r[e]);
-      o[e] = v;
-    }
-    if (valid) store8_bf16(p.out0 + row * p.N + n + 8 * c8, o);
+    if (valid) store4_pairs(p.out0 + row * p.N + n + 8 * c8, o);
   }
 }
 
@@ -392,8 +489,10 @@ mlp_gemm_kernel(const __grid_constant__ CUtensorMap mapA1, const __grid_constant
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      int pit = 0;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++pit) {
         const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * TILE_N;
+        TC_STAMP(0, pit, 0);
         for (int kb = 0; kb < kb_total; ++kb) {
           if (!mbar_wait(&empty[stage], phase ^ 1u, abort_flag)) {
             if (!*abort_flag) { *abort_flag = 1; atomicExch(p.status, ST_TIMEOUT_PRODUCER); }
@@ -424,6 +523,7 @@ mlp_gemm_kernel(const __grid_constant__ CUtensorMap mapA1, const __grid_constant
           }
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
+        TC_STAMP(0, pit, 1);
       }
     }
   } else if (warp == 1) {
@@ -439,11 +539,13 @@ mlp_gemm_kernel(const __grid_constant__ CUtensorMap mapA1, const __grid_constant
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++it) {
         const int buf = it & 1;
         const uint32_t bphase = (uint32_t)(it >> 1) & 1u;
+        TC_STAMP(1, it, 0);
         if (!mbar_wait(&tmem_empty[buf], bphase ^ 1u, abort_flag)) {
           if (!*abort_flag) { *abort_flag = 1; atomicExch(p.status, ST_TIMEOUT_MMA); }
           break;
         }
         tc_fence_after();
+        TC_STAMP(1, it, 1);
         const uint32_t d_tmem = tmem_base + (uint32_t)(buf * BN);
         for (int kb = 0; kb < kb_total; ++kb) {
           if (!mbar_wait(&full[stage], phase, abort_flag)) {
@@ -467,6 +569,7 @@ mlp_gemm_kernel(const __grid_constant__ CUtensorMap mapA1, const __grid_constant
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
         if (ok) tc_commit(&tmem_full[buf]);
+        TC_STAMP(1, it, 2);
       }
     }
   } else {
@@ -478,6 +581,8 @@ mlp_gemm_kernel(const __grid_constant__ CUtensorMap mapA1, const __grid_constant
     __nv_bfloat16* sB1 = epi_b + BN * 16;
     __nv_bfloat16* sB2 = epi_b + 2 * BN * 16;
     float* sV = reinterpret_cast<float*>(epi_b + 3 * BN * 16);    // four float vectors of BN
+    float* sF0 = reinterpret_cast<float*>(epi_b);                 // GATEUP: [TILE_N][16] floats each
+    float* sF1 = sF0 + (BN / 2) * 16;
     int it = 0;
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++it) {
       const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * TILE_N;
@@ -485,35 +590,42 @@ mlp_gemm_kernel(const __grid_constant__ CUtensorMap mapA1, const __grid_constant
       const uint32_t bphase = (uint32_t)(it >> 1) & 1u;
       const int64_t row = (int64_t)m0 + quad * 32 + lane;
       const bool valid = row < p.M;
+      if (et == 0) TC_STAMP(2, it, 0);
 
       // stage the per-tile LoRA-B rows and scales (previous tile's readers are done: barrier at the end)
       if (EPI == EPI_STORE) {
         stage_lora_tile(p.l0, n0, BN, sB0, et);
         stage_lora_tile(p.l1, n0, BN, sB1, et);
       } else if (EPI == EPI_GATEUP) {
-        stage_lora_tile(p.l0, n0, TILE_N, sB0, et);
-        stage_lora_tile(p.l1, n0, TILE_N, sB1, et);
+        // 128 output columns per tile: the two LoRA-B tiles fit as fp32 rows (2 x 8 KB)
+        stage_lora_tile_f32(p.l0, n0, TILE_N, sF0, et);
+        stage_lora_tile_f32(p.l1, n0, TILE_N, sF1, et);
         if (et < TILE_N) {
-          const float a = __bfloat162float(p.s1[n0 + et]), b = __bfloat162float(p.s2[n0 + et]);
-          sV[et] = a; sV[BN + et] = fastq_scale<QBIT>(__frcp_rn(a));
-          sV[2 * BN + et] = b; sV[3 * BN + et] = fastq_scale<QBIT>(__frcp_rn(b));
+          sV[et] = fastq_scale<QBIT>(__frcp_rn(__bfloat162float(p.s1[n0 + et])));
+          sV[BN + et] = fastq_scale<QBIT>(__frcp_rn(__bfloat162float(p.s2[n0 + et])));
         }
       } else {
-        stage_lora_tile(p.l1, n0, BN, sB1, et);
-        stage_lora_tile(p.l2, n0, BN, sB2, et);
-        sV[et] = __bfloat162float(p.s1[n0 + et]); sV[BN + et] = __bfloat162float(p.s2[n0 + et]);
+        if (p.lpre1 == nullptr) {
+          stage_lora_tile(p.l1, n0, BN, sB1, et);
+          stage_lora_tile(p.l2, n0, BN, sB2, et);
+        }
+        // the scales stay bf16: column pairs are read as one packed word
+        reinterpret_cast<__nv_bfloat16*>(sV)[et] = p.s1[n0 + et];
+        reinterpret_cast<__nv_bfloat16*>(sV + BN)[et] = p.s2[n0 + et];
       }
       float xa0[16], xa1[16], xa2[16];
       if (EPI != EPI_GRADDOWN) load_xa_row(p.l0.xa, row, valid, xa0);
       load_xa_row(p.l1.xa, row, valid, xa1);
       if (EPI == EPI_GRADDOWN) load_xa_row(p.l2.xa, row, valid, xa2);
       epi_bar_sync();
+      if (et == 0) TC_STAMP(2, it, 1);
 
       if (!mbar_wait(&tmem_full[buf], bphase, abort_flag)) {
         if (!*abort_flag) { *abort_flag = 1; atomicExch(p.status, ST_TIMEOUT_EPILOGUE); }
         break;
       }
       tc_fence_after();
+      if (et == 0) TC_STAMP(2, it, 2);
       const uint32_t t_lane = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(buf * BN);
       if (EPI == EPI_GATEUP) {
         // gate columns [0, 128) and up columns [128, 256) of the accumulator; this warp takes 64 of each
@@ -523,7 +635,7 @@ mlp_gemm_kernel(const __grid_constant__ CUtensorMap mapA1, const __grid_constant
           const int cb = 64 * chalf + 32 * ch;
           tc_ld32(t_lane + (uint32_t)cb, g);
           tc_ld32(t_lane + (uint32_t)(TILE_N + cb), u);
-          epi_gateup_block<QBIT>(p, row, valid, n0, cb, g, u, xa0, xa1, sB0, sB1, sV, sV + BN, sV + 2 * BN, sV + 3 * BN);
+          epi_gateup_block<QBIT>(p, row, valid, n0, cb, g, u, xa0, xa1, sF0, sF1, sV, sV + BN);
         }
       } else {
 #pragma unroll 1
@@ -532,13 +644,16 @@ mlp_gemm_kernel(const __grid_constant__ CUtensorMap mapA1, const __grid_constant
           const int cb = 128 * chalf + 32 * ch;
           tc_ld32(t_lane + (uint32_t)cb, acc);
           if (EPI == EPI_STORE) epi_store_block(p, row, valid, n0, cb, acc, xa0, xa1, sB0, sB1);
-          else epi_graddown_block<QBIT>(p, row, valid, n0, cb, acc, xa1, xa2, sB1, sB2, sV, sV + BN);
+          else epi_graddown_block<QBIT>(p, row, valid, n0, cb, acc, xa1, xa2, sB1, sB2,
+                                        reinterpret_cast<const uint32_t*>(sV), reinterpret_cast<const uint32_t*>(sV + BN));
         }
       }
       tc_fence_before();
       __syncwarp();
+      if (et == 0) TC_STAMP(2, it, 3);
       if (lane == 0) mbar_arrive(&tmem_empty[buf]);
       epi_bar_sync();    // everyone is done with the staged tile before the next one overwrites it
+      if (et == 0) TC_STAMP(2, it, 4);
     }
   }
 
@@ -597,7 +712,13 @@ static int launch(const CUtensorMap& a1, const CUtensorMap& b1, const CUtensorMa
   constexpr int TILE_N = (EPI == EPI_GATEUP) ? BN / 2 : BN;
   const int tiles = ((p.M + BM - 1) / BM) * (p.N / TILE_N);
   const int grid = tiles < kNumSMs ? tiles : kNumSMs;
+#ifdef HYC_TC_PROF
+  Params pp = p;
+  pp.prof = g_tc_prof;
+  kern<<<grid, THREADS, SMEM_BYTES, st>>>(a1, b1, a2, b2, a3, b3, pp);
+#else
   kern<<<grid, THREADS, SMEM_BYTES, st>>>(a1, b1, a2, b2, a3, b3, p);
+#endif
   HYC_CHECK_LAUNCH();
   return HYC_OK;
 }
@@ -695,14 +816,23 @@ extern "C" HYC_API int hyc_mlp_graddown_bwd_tcgen05(
     const void* xa1, const void* b1t, int64_t b1_ld_col, int64_t b1_ld_r,
     const void* xa2, const void* b2t, int64_t b2_ld_col, int64_t b2_ld_r,
     const void* q1, const void* s1, const void* q2, const void* s2,
+    const void* lora_gate, const void* lora_up, int64_t ld_lora,
     void* o, void* grad_gate, void* grad_up, int q_bit, int* status, void* stream) {
-  if (!g || !wd || !xa1 || !b1t || !xa2 || !b2t || !q1 || !s1 || !q2 || !s2 || !o || !grad_gate || !grad_up || !status)
+  if (!g || !wd || !q1 || !s1 || !q2 || !s2 || !o || !grad_gate || !grad_up || !status) return HYC_ERR_NULL;
+  const bool pre = lora_gate != nullptr || lora_up != nullptr;
+  if (pre) {
+    if (!lora_gate || !lora_up) return HYC_ERR_NULL;
+    if (ld_lora < I || ld_lora % 8 != 0) return HYC_ERR_SHAPE;
+    if (!aligned(lora_gate, 16) || !aligned(lora_up, 16)) return HYC_ERR_ALIGN;
+  } else if (!xa1 || !b1t || !xa2 || !b2t) {
     return HYC_ERR_NULL;
+  }
   if ((k_lora > 0) != (a_lora != nullptr && b_lora != nullptr)) return HYC_ERR_NULL;
   if (q_bit != 2 && q_bit != 4 && q_bit != 8) return HYC_ERR_QBIT;
   if (T <= 0 || H <= 0 || I <= 0 || I % BN != 0 || H % BK != 0 || k_lora < 0 || k_lora % BK != 0) return HYC_ERR_SHAPE;
-  const void* al[] = {g, wd, xa1, xa2, q1, q2, o, grad_gate, grad_up};
+  const void* al[] = {g, wd, q1, q2, o, grad_gate, grad_up};
   for (const void* q : al) if (!aligned(q, 16)) return HYC_ERR_ALIGN;
+  if (!pre && (!aligned(xa1, 16) || !aligned(xa2, 16))) return HYC_ERR_ALIGN;
   if (a_lora && (!aligned(a_lora, 16) || !aligned(b_lora, 16))) return HYC_ERR_ALIGN;
   CUtensorMap a1, b1, a2, b2;
   // wd is [H, I] row-major: the K = H rows are the reduction dimension, so B is MN-major
@@ -712,8 +842,9 @@ extern "C" HYC_API int hyc_mlp_graddown_bwd_tcgen05(
   Params p = {};
   p.M = T; p.N = I; p.K1 = H; p.K2 = k_lora; p.K3 = 0; p.epi = EPI_GRADDOWN; p.q_bit = q_bit;
   p.l0 = make_term(nullptr, nullptr, 0, 0);
-  p.l1 = make_term(xa1, b1t, b1_ld_col, b1_ld_r);
-  p.l2 = make_term(xa2, b2t, b2_ld_col, b2_ld_r);
+  p.l1 = pre ? make_term(nullptr, nullptr, 0, 0) : make_term(xa1, b1t, b1_ld_col, b1_ld_r);
+  p.l2 = pre ? make_term(nullptr, nullptr, 0, 0) : make_term(xa2, b2t, b2_ld_col, b2_ld_r);
+  p.lpre1 = (const __nv_bfloat16*)lora_gate; p.lpre2 = (const __nv_bfloat16*)lora_up; p.ld_pre = ld_lora;
   p.out0 = (__nv_bfloat16*)o; p.out1 = (__nv_bfloat16*)grad_gate; p.out2 = (__nv_bfloat16*)grad_up;
   p.q1 = (uint8_t*)const_cast<void*>(q1); p.q2 = (uint8_t*)const_cast<void*>(q2);
   p.s1 = (const __nv_bfloat16*)s1; p.s2 = (const __nv_bfloat16*)s2;

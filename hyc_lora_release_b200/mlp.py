@@ -102,7 +102,7 @@ class MLPWeights:
           ad_cols  [I, 64]  columns 0..15 = Ad^T       (projects hadamard to the padded down LoRA activation)
           bd_cols  [H, 64]  columns 0..15 = Bd         (second operand of the down projection's LoRA part, [N, K])
           agu_rows [64, H]  rows 0..15 = Ag, 16..31 = Au (second operand of grad_x's LoRA part, [K, N])"""
-        key = tuple(t._version for t in (self.ag, self.au, self.ad, self.bd))
+        key = tuple(t._version for t in (self.ag, self.au, self.ad, self.bd, self.bg, self.bu))
         if getattr(self, "_pad_key", None) != key:
             r, I = self.ad.shape
             H = self.bd.shape[0]
@@ -217,6 +217,7 @@ def mlp_backward(grad_out, saved, w: MLPWeights, status=None):
         ptr(g), ptr(w.wd), T, H, I, ptr(gdm64), ptr(pad["ad_rows"]), 64,
         ptr(gate_xa), ptr(w.bg), 16, 1, ptr(up_xa), ptr(w.bu), 16, 1,
         ptr(saved['gate_q']), ptr(saved['gate_scale']), ptr(saved['up_q']), ptr(saved['up_scale']),
+        None, None, 0,
         ptr(had), ptr(gg), ptr(gu), q, ptr(st), stream_of(grad_out)), "hyc_mlp_graddown_bwd_tcgen05")
     grad_ad = gdm.t() @ had                        # [r, I]
 

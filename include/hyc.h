@@ -205,12 +205,17 @@ int hyc_mlp_gateup_fwd_tcgen05(const void* x, const void* wg, const void* wu, in
  * o (hadamard), grad_gate, grad_up [T,I].  g [T,H], wd [H,I] (the down weight as stored).  I % 256 == 0.
  * The LoRA part of grad_down, (g * Bd^T) * Ad, is passed as a zero-padded extra K block:
  * a_lora [T, k_lora] (the rank-16 product g * Bd^T in its first columns), b_lora [k_lora, I] (Ad in its
- * first rows), k_lora a multiple of 64 or 0. */
+ * first rows), k_lora a multiple of 64 or 0.
+ * The LoRA terms of the gate and up branches that the recomputation needs, bf16(xa1 * b1t^T) and
+ * bf16(xa2 * b2t^T), are either computed in the epilogue (16 FMAs per element each: lora_gate = lora_up = NULL)
+ * or read from lora_gate / lora_up ([T, ld_lora] bf16, ld_lora >= I, a multiple of 8), which one launch of
+ * hyc_gemm_bf16_tcgen05 on the zero-padded rank-16 operands prepares; xa1/b1t/xa2/b2t may then be NULL. */
 int hyc_mlp_graddown_bwd_tcgen05(const void* g, const void* wd, int T, int H, int I,
                                  const void* a_lora, const void* b_lora, int k_lora,
                                  const void* xa1, const void* b1t, int64_t b1_ld_col, int64_t b1_ld_r,
                                  const void* xa2, const void* b2t, int64_t b2_ld_col, int64_t b2_ld_r,
                                  const void* q1, const void* s1, const void* q2, const void* s2,
+                                 const void* lora_gate, const void* lora_up, int64_t ld_lora,
                                  void* o, void* grad_gate, void* grad_up, int q_bit, int* status, void* stream);
 
 /* LoRA-A gradient with the de-quantizer inside the contraction:

@@ -133,15 +133,30 @@ def test_gateup_and_graddown_epilogues(mlp, q):
     gdm64 = torch.zeros(T, 64, dtype=BF16); gdm64[:, :R] = gdm      # the LoRA part rides along as a padded K block
     ad64 = torch.zeros(64, I, dtype=BF16); ad64[:R] = ad
     goutd, gdmd, add = map(d, (gout, gdm64, ad64))
-    check(lib.hyc_mlp_graddown_bwd_tcgen05(ptr(goutd), ptr(wdd), T, H, I, ptr(gdmd), ptr(add), 64,
-                                           ptr(xa1d), ptr(bgd), 16, 1, ptr(xa2d), ptr(bud), 16, 1,
-                                           ptr(q1), ptr(s1d), ptr(q2), ptr(s2d), ptr(had), ptr(gg), ptr(gu), q,
-                                           ptr(st), stream_of(xd)), "graddown")
-    mlp.check_status(st, "graddown")
     grad_down = (gout.float() @ wd.float() + gdm.float() @ ad.float()).to(BF16)
     ob, ogg, ogu = oracle.ref_fused_silu_backward(xa1[None], bg.t(), q1.cpu()[None], s1[None], xa2[None], bu.t(),
                                                   q2.cpu()[None], s2[None], grad_down[None], q)
+    # (a) LoRA terms of the recomputation inside the epilogue
+    check(lib.hyc_mlp_graddown_bwd_tcgen05(ptr(goutd), ptr(wdd), T, H, I, ptr(gdmd), ptr(add), 64,
+                                           ptr(xa1d), ptr(bgd), 16, 1, ptr(xa2d), ptr(bud), 16, 1,
+                                           ptr(q1), ptr(s1d), ptr(q2), ptr(s2d), None, None, 0,
+                                           ptr(had), ptr(gg), ptr(gu), q, ptr(st), stream_of(xd)), "graddown")
+    mlp.check_status(st, "graddown")
     assert close(had, ob[0]) and close(gg, ogg[0]) and close(gu, ogu[0])
+    # (b) LoRA terms prepared by one GEMM launch on the zero-padded rank-16 operands
+    xa12 = torch.zeros(T, 128, dtype=BF16, device=DEV); xa12[:, :R] = xa1d; xa12[:, 64:64 + R] = xa2d
+    bdiag = torch.zeros(2 * I, 128, dtype=BF16, device=DEV); bdiag[:I, :R] = bgd; bdiag[I:, 64:64 + R] = bud
+    l12 = mlp.gemm(xa12, bdiag, status=st)
+    assert close(l12[:, :I], xa1.float() @ bg.float().t(), rel=4e-3) and close(l12[:, I:], xa2.float() @ bu.float().t(), rel=4e-3)
+    had2 = torch.empty_like(had); gg2 = torch.empty_like(had); gu2 = torch.empty_like(had)
+    import ctypes
+    check(lib.hyc_mlp_graddown_bwd_tcgen05(ptr(goutd), ptr(wdd), T, H, I, ptr(gdmd), ptr(add), 64,
+                                           None, None, 0, 0, None, None, 0, 0,
+                                           ptr(q1), ptr(s1d), ptr(q2), ptr(s2d),
+                                           ptr(l12), ctypes.c_void_p(l12.data_ptr() + 2 * I), 2 * I,
+                                           ptr(had2), ptr(gg2), ptr(gu2), q, ptr(st), stream_of(xd)), "graddown pre")
+    mlp.check_status(st, "graddown pre")
+    assert close(had2, ob[0]) and close(gg2, ogg[0]) and close(gu2, ogu[0])
 
 
 @pytest.mark.parametrize("q", (2, 4, 8))
