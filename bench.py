@@ -239,7 +239,36 @@ def extra_workloads(dev, hbm):
                         "ms_per_step": t / (reps * nbuf) * 1e3, "launch": "CUDA graph replay of %d compress+decompress pairs" % nbuf})
             del graph, qb, ob, xb
         del xs
+    out.append(fused_elementwise_workload(dev, hbm))
     return out
+
+
+def fused_elementwise_workload(dev, hbm):
+    """The two stand-alone fused LoRA-SiLU-Hadamard kernels behind the reference's launch wrappers
+    (triton_fuse_silu_forward / triton_fuse_silu_backward) at the Mistral MLP width, 8192 tokens, q_bit 4.
+    Algorithmic bytes per element: forward 2+2 in, 2 + 2*q/8 out; backward 2*q/8 + 2 in, 6 out."""
+    from hyc_lora_release_b200.operators import compress_function as cf
+    from hyc_lora_release_b200.operators.triton_fuse_lora_silu_hadamard_forward_kernels import triton_fuse_silu_forward
+    from hyc_lora_release_b200.operators.triton_fuse_lora_silu_hadamard_backward_kernels import triton_fuse_silu_backward
+    g = torch.Generator().manual_seed(77)
+    T, N, R, q = 8192, 14336, 16, 4
+    rn = lambda *sh, sc=1.0: (torch.randn(*sh, generator=g) * sc).to(torch.bfloat16).to(dev)
+    xa1, xa2 = rn(1, T, R), rn(1, T, R)
+    b1, b2 = rn(N, R, sc=.05).t(), rn(N, R, sc=.05).t()
+    x1, x2, go = rn(1, T, N), rn(1, T, N), rn(1, T, N)
+    s1 = cf.get_statistics_only_quant(x1, q, "per-channel")
+    s2 = cf.get_statistics_only_quant(x2, q, "per-channel")
+    q1, q2, _ = triton_fuse_silu_forward(xa1, b1, x1, s1, xa2, b2, x2, s2, q)
+    tf = time_loop(lambda i: triton_fuse_silu_forward(xa1, b1, x1, s1, xa2, b2, x2, s2, q), 8, 3) / 8
+    tb = time_loop(lambda i: triton_fuse_silu_backward(xa1, b1, q1, s1, xa2, b2, q2, s2, go, q), 8, 3) / 8
+    nel = T * N
+    bf, bb = nel * (4 + 2 + 2 * q / 8), nel * (2 * q / 8 + 2 + 6)
+    return {"workload": "stand-alone fused LoRA-SiLU-Hadamard kernels (triton_fuse_silu_forward/backward drop-ins), "
+                        "[1,8192,14336] bf16, q_bit 4",
+            "q_bit": q, "value": (bf + bb) / (tf + tb) / 1e9, "unit": "GB/s",
+            "frac_of_hbm": (bf + bb) / (tf + tb) / 1e9 / hbm, "ms_per_step": (tf + tb) * 1e3,
+            "forward": {"ms": tf * 1e3, "GBps": bf / tf / 1e9}, "backward": {"ms": tb * 1e3, "GBps": bb / tb / 1e9},
+            "launch": "one forward + one backward call through the operator wrappers (inputs 3 x 235 MB > L2)"}
 
 
 def run_profile(args):
