@@ -37,6 +37,8 @@ SIGNATURES = {
     "hyc_fused_lora_silu_hadamard_bwd": (_i, [_p] * 12 + [_l, _i, _i, _i, _p]),
     "hyc_rmsnorm_fwd": (_i, [_p, _p, _f, _p, _p, _l, _i, _p]),
     "hyc_rmsnorm_bwd": (_i, [_p, _p, _p, _p, _p, _l, _i, _p]),
+    "hyc_rmsnorm_fwd_save": (_i, [_p, _p, _f, _l, _i, _p, _p, _i, _p, _p, _p, _p, _p, _p, _i, _p]),
+    "hyc_rmsnorm_bwd_packed": (_i, [_p, _p, _p, _p, _i, _p, _p, _p, _p, _p, _l, _i, _i, _p]),
     "hyc_softmax_bwd": (_i, [_p, _p, _p, _l, _i, _p]),
     "hyc_lora_grad_a_workspace_bytes": (_z, [_i, _i, _i]),
     "hyc_lora_grad_a_dequant": (_i, [_p, _p, _p, _l, _i, _i, _i, _i, _p, _p, _z, _p]),

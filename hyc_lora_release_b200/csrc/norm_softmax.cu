@@ -1,7 +1,7 @@
 // RMSNorm forward/backward and softmax backward: the producers and consumers of the
 // compressed tensors.  Plain streaming kernels, one row per block (norm) or per warp
 // (softmax), the row held in registers between the reduction and the second pass.
-#include "hyc_common.cuh"
+#include "octet_codes.cuh"
 
 namespace hyc {
 
@@ -116,6 +116,203 @@ rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __
   }
 }
 
+// ---------------------------------------------------------------- RMSNorm fused with the activation saves
+// Forward: one pass over x produces x_norm, rstd AND the saved forms of the layer's fused MLP path: the packed
+// per-channel codes of x with its outlier channels moved to the outlier slab, and (optionally) the packed
+// codes of x_norm.  The results are bit-identical to rmsnorm_fwd_kernel followed by quant_pack_kernel on x
+// and on the bf16 x_norm.  A thread owns octets (8 columns); see octet_codes.cuh for the byte layout.
+// s_map (dynamic shared memory, N int16): column -> position in the outlier list, -1 = none.
+__device__ __forceinline__ void build_full_map(int16_t* s_map, int N, const int64_t* __restrict__ oidx, int k) {
+  for (int i = threadIdx.x; i < N / 2; i += blockDim.x) reinterpret_cast<uint32_t*>(s_map)[i] = 0xffffffffu;
+  __syncthreads();
+  for (int j = threadIdx.x; j < k; j += blockDim.x) {
+    const int64_t c = oidx[j];
+    if (c >= 0 && c < N) s_map[c] = (int16_t)j;
+  }
+  __syncthreads();
+}
+
+// NV = octets per thread the kernel is built for (N <= NV * 2048 columns).  With NV <= 2 (hidden sizes up to
+// 4096) the per-column quantizer constants and the norm weights of the thread's octets stay in registers
+// across rows; wider rows form them on the fly.
+template <int QBIT, int NV>
+__global__ void __launch_bounds__(kNormThreads)
+rmsnorm_fwd_save_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w, float eps,
+                        const __nv_bfloat16* __restrict__ scale_x, const int64_t* __restrict__ oidx, int k,
+                        const __nv_bfloat16* __restrict__ scale_y,
+                        __nv_bfloat16* __restrict__ y, float* __restrict__ rstd, uint8_t* __restrict__ qx,
+                        __nv_bfloat16* __restrict__ oout, uint8_t* __restrict__ qy, int64_t rows, int N) {
+  extern __shared__ __align__(16) int16_t s_map[];
+  constexpr bool CACHED = NV <= 2;
+  if (k > 0) build_full_map(s_map, N, oidx, k);
+  const int nvec = N / 8;
+  const int64_t qld = (int64_t)N * QBIT / 8;
+  const uint4 one = make_uint4(0x3f803f80u, 0x3f803f80u, 0x3f803f80u, 0x3f803f80u);
+  // per-octet state that does not depend on the row
+  uint32_t zmask[NV];
+  float rx[CACHED ? NV : 1][8], ry[CACHED ? NV : 1][8];
+  uint4 wv[CACHED ? NV : 1];
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int v = threadIdx.x + i * kNormThreads;
+    zmask[i] = 0u;
+    if (v < nvec && k > 0) {
+      const uint4 mv = *reinterpret_cast<const uint4*>(s_map + 8 * v);
+      const uint32_t mw[4] = {mv.x, mv.y, mv.z, mv.w};
+#pragma unroll
+      for (int e = 0; e < 8; ++e)
+        if ((int)(int16_t)((mw[e >> 1] >> (16 * (e & 1))) & 0xffffu) >= 0) zmask[i] |= 1u << e;
+    }
+    if (CACHED) {
+      const bool ok = v < nvec;
+      octet_rcs<QBIT>(ok ? *reinterpret_cast<const uint4*>(scale_x + 8 * v) : one, zmask[i], rx[i]);
+      octet_rcs<QBIT>(ok && qy != nullptr ? *reinterpret_cast<const uint4*>(scale_y + 8 * v) : one, 0u, ry[i]);
+      wv[i] = ok ? *reinterpret_cast<const uint4*>(w + 8 * v) : one;
+    }
+  }
+  for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
+    uint4 xv[NV];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int v = threadIdx.x + i * kNormThreads;
+      if (v < nvec) {
+        xv[i] = ld_stream_v4(x + row * N + 8 * v);
+        float f[8]; unpack8(xv[i], f);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) ss = fmaf(f[e], f[e], ss);
+      }
+    }
+    const float var = block_sum(ss) / (float)N;
+    const float rs = 1.f / sqrtf(var + eps);
+    if (threadIdx.x == 0) rstd[row] = rs;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      if (i * kNormThreads < nvec) {             // block-uniform: every lane takes part in the shuffles below
+        const int v = threadIdx.x + i * kNormThreads;
+        const bool ok = v < nvec;
+        const int col = 8 * v;
+        uint32_t xw[4] = {0u, 0u, 0u, 0u}, yw[4] = {0u, 0u, 0u, 0u};
+        if (ok) {
+          xw[0] = xv[i].x; xw[1] = xv[i].y; xw[2] = xv[i].z; xw[3] = xv[i].w;
+          float f[8], wf[8];
+          unpack8(xv[i], f);
+          unpack8(CACHED ? wv[CACHED ? i : 0] : *reinterpret_cast<const uint4*>(w + col), wf);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) f[e] = (f[e] * rs) * wf[e];
+          const uint4 yv = pack8(f);
+          st_stream_v4(y + row * N + col, yv);
+          yw[0] = yv.x; yw[1] = yv.y; yw[2] = yv.z; yw[3] = yv.w;
+          if (zmask[i] != 0u) {                  // rare: outlier columns in this octet go to the slab
+            for (uint32_t bits = zmask[i]; bits; bits &= bits - 1u) {
+              const int e = __ffs(bits) - 1;
+              oout[row * k + s_map[col + e]] = __ushort_as_bfloat16((uint16_t)((xw[e >> 1] >> (16 * (e & 1))) & 0xffffu));
+            }
+          }
+        }
+        uint32_t kx[2];
+        if (CACHED) {
+          octet_quant_rcs<QBIT>(xw, rx[CACHED ? i : 0], kx);
+        } else {
+          octet_quant<QBIT>(xw, ok ? *reinterpret_cast<const uint4*>(scale_x + col) : one, zmask[i], kx);
+        }
+        octet_store<QBIT>(qx + row * qld, col, kx, ok);
+        if (qy != nullptr) {
+          uint32_t ky[2];
+          if (CACHED) {
+            octet_quant_rcs<QBIT>(yw, ry[CACHED ? i : 0], ky);
+          } else {
+            octet_quant<QBIT>(yw, ok ? *reinterpret_cast<const uint4*>(scale_y + col) : one, 0u, ky);
+          }
+          octet_store<QBIT>(qy + row * qld, col, ky, ok);
+        }
+      }
+    }
+  }
+}
+
+// Backward reading the packed x directly: x_hat = de-quantized codes with the outlier columns put back,
+// then the arithmetic of rmsnorm_bwd_kernel; `res` (optional) is added to the result as a bf16 tensor add
+// (the residual branch of the layer's input gradient).
+template <int QBIT>
+__global__ void __launch_bounds__(kNormThreads)
+rmsnorm_bwd_packed_kernel(const __nv_bfloat16* __restrict__ dy, const uint8_t* __restrict__ qx,
+                          const __nv_bfloat16* __restrict__ scale_x, const int64_t* __restrict__ oidx, int k,
+                          const __nv_bfloat16* __restrict__ oin, const __nv_bfloat16* __restrict__ w,
+                          const float* __restrict__ rstd, const __nv_bfloat16* __restrict__ res,
+                          __nv_bfloat16* __restrict__ dx, int64_t rows, int N) {
+  extern __shared__ __align__(16) int16_t s_map[];
+  if (k > 0) build_full_map(s_map, N, oidx, k);
+  const int nvec = N / 8;
+  const int64_t qld = (int64_t)N * QBIT / 8;
+  for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
+    const float rs = rstd[row];
+    uint4 xv[kNormMaxVec], gv[kNormMaxVec];
+    float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+    for (int i = 0; i < kNormMaxVec; ++i) {
+      const int v = threadIdx.x + i * kNormThreads;
+      if (v < nvec) {
+        const int col = 8 * v;
+        gv[i] = ld_stream_v4(dy + row * N + col);
+        uint32_t xw[4];
+        octet_load_dequant<QBIT>(qx + row * qld, col, *reinterpret_cast<const uint4*>(scale_x + col), xw);
+        if (k > 0) {
+          const uint4 mv = *reinterpret_cast<const uint4*>(s_map + col);
+          if ((mv.x & mv.y & mv.z & mv.w) != 0xffffffffu) {
+            const uint32_t mw[4] = {mv.x, mv.y, mv.z, mv.w};
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+              const int jv = (int)(int16_t)((mw[e >> 1] >> (16 * (e & 1))) & 0xffffu);
+              if (jv >= 0) {
+                const uint32_t val = (uint32_t)__bfloat16_as_ushort(oin[row * k + jv]);
+                xw[e >> 1] = (e & 1) ? ((xw[e >> 1] & 0x0000ffffu) | (val << 16)) : ((xw[e >> 1] & 0xffff0000u) | val);
+              }
+            }
+          }
+        }
+        xv[i] = make_uint4(xw[0], xw[1], xw[2], xw[3]);
+        float xf[8], gf[8], wf[8];
+        unpack8(xv[i], xf); unpack8(gv[i], gf);
+        unpack8(*reinterpret_cast<const uint4*>(w + col), wf);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          const float wdy = wf[e] * gf[e];
+          s1 = fmaf(xf[e] * rs, wdy, s1);
+          s2 += wdy;
+        }
+      }
+    }
+    const float c1 = block_sum(s1) / (float)N;
+    const float c2 = block_sum(s2) / (float)N;
+#pragma unroll
+    for (int i = 0; i < kNormMaxVec; ++i) {
+      const int v = threadIdx.x + i * kNormThreads;
+      if (v < nvec) {
+        float xf[8], gf[8], wf[8];
+        unpack8(xv[i], xf); unpack8(gv[i], gf);
+        unpack8(*reinterpret_cast<const uint4*>(w + 8 * v), wf);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          const float wdy = wf[e] * gf[e];
+          xf[e] = (wdy - ((xf[e] * rs) * c1 + c2)) * rs;
+        }
+        uint4 o = pack8(xf);
+        if (res != nullptr) {
+          const uint4 r = ld_stream_v4(res + row * N + 8 * v);
+          const __nv_bfloat162* op = reinterpret_cast<const __nv_bfloat162*>(&o);
+          const __nv_bfloat162* rp = reinterpret_cast<const __nv_bfloat162*>(&r);
+          __nv_bfloat162 t[4];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) t[j] = __hadd2_rn(op[j], rp[j]);
+          o = *reinterpret_cast<const uint4*>(t);
+        }
+        st_stream_v4(dx + row * N + 8 * v, o);
+      }
+    }
+  }
+}
+
 constexpr int kSmMaxVec = 16;   // 16 x (32 lanes x 8 elements) = 4096 columns
 __global__ void __launch_bounds__(256)
 softmax_bwd_kernel(const __nv_bfloat16* __restrict__ y, const __nv_bfloat16* __restrict__ g,
@@ -166,6 +363,54 @@ extern "C" HYC_API int hyc_rmsnorm_fwd(const void* x, const void* w, float eps, 
   int64_t grid = rows < (int64_t)kNumSMs * 8 ? rows : (int64_t)kNumSMs * 8;
   rmsnorm_fwd_kernel<<<(int)grid, kNormThreads, 0, (cudaStream_t)stream>>>(
       (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, eps, (__nv_bfloat16*)y, rstd, rows, N);
+  HYC_CHECK_LAUNCH();
+  return HYC_OK;
+}
+
+extern "C" HYC_API int hyc_rmsnorm_fwd_save(const void* x, const void* w, float eps, int64_t rows, int N,
+                                            const void* scale_x, const int64_t* outlier_idx, int k, const void* scale_y,
+                                            void* y, float* rstd, void* qx, void* outlier_out, void* qy, int q_bit,
+                                            void* stream) {
+  if (!x || !w || !y || !rstd || !scale_x || !qx) return HYC_ERR_NULL;
+  if ((qy != nullptr) != (scale_y != nullptr)) return HYC_ERR_NULL;
+  if (q_bit != 2 && q_bit != 4 && q_bit != 8) return HYC_ERR_QBIT;
+  if (rows < 0 || N <= 0 || N % 32 != 0 || N > kNormThreads * 8 * kNormMaxVec || k < 0 || k > N || k > 32767) return HYC_ERR_SHAPE;
+  if (k > 0 && (!outlier_idx || !outlier_out)) return HYC_ERR_NULL;
+  if (!aligned(x, 16) || !aligned(w, 16) || !aligned(y, 16) || !aligned(scale_x, 16) || !aligned(qx, 8) ||
+      (qy && (!aligned(qy, 8) || !aligned(scale_y, 16)))) return HYC_ERR_ALIGN;
+  if (rows == 0) return HYC_OK;
+  const int64_t grid = rows < (int64_t)kNumSMs * 8 ? rows : (int64_t)kNumSMs * 8;
+  const size_t smem = k > 0 ? (size_t)N * 2 : 0;
+#define FS(QB) if (N <= 2 * kNormThreads * 8) FSV(QB, 2); else FSV(QB, kNormMaxVec)
+#define FSV(QB, NVV) rmsnorm_fwd_save_kernel<QB, NVV><<<(int)grid, kNormThreads, smem, (cudaStream_t)stream>>>(       \
+      (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, eps, (const __nv_bfloat16*)scale_x, outlier_idx, k,          \
+      (const __nv_bfloat16*)scale_y, (__nv_bfloat16*)y, rstd, (uint8_t*)qx, (__nv_bfloat16*)outlier_out, (uint8_t*)qy, rows, N)
+  if (q_bit == 2) { FS(2); } else if (q_bit == 4) { FS(4); } else { FS(8); }
+#undef FS
+#undef FSV
+  HYC_CHECK_LAUNCH();
+  return HYC_OK;
+}
+
+extern "C" HYC_API int hyc_rmsnorm_bwd_packed(const void* dy, const void* qx, const void* scale_x,
+                                              const int64_t* outlier_idx, int k, const void* outlier, const void* w,
+                                              const float* rstd, const void* residual_grad, void* dx,
+                                              int64_t rows, int N, int q_bit, void* stream) {
+  if (!dy || !qx || !scale_x || !w || !rstd || !dx) return HYC_ERR_NULL;
+  if (q_bit != 2 && q_bit != 4 && q_bit != 8) return HYC_ERR_QBIT;
+  if (rows < 0 || N <= 0 || N % 32 != 0 || N > kNormThreads * 8 * kNormMaxVec || k < 0 || k > N || k > 32767) return HYC_ERR_SHAPE;
+  if (k > 0 && (!outlier_idx || !outlier)) return HYC_ERR_NULL;
+  if (!aligned(dy, 16) || !aligned(w, 16) || !aligned(dx, 16) || !aligned(scale_x, 16) || !aligned(qx, 8) ||
+      (residual_grad && !aligned(residual_grad, 16))) return HYC_ERR_ALIGN;
+  if (rows == 0) return HYC_OK;
+  const int64_t grid = rows < (int64_t)kNumSMs * 8 ? rows : (int64_t)kNumSMs * 8;
+  const size_t smem = k > 0 ? (size_t)N * 2 : 0;
+#define BP(QB) rmsnorm_bwd_packed_kernel<QB><<<(int)grid, kNormThreads, smem, (cudaStream_t)stream>>>(               \
+      (const __nv_bfloat16*)dy, (const uint8_t*)qx, (const __nv_bfloat16*)scale_x, outlier_idx, k,                   \
+      (const __nv_bfloat16*)outlier, (const __nv_bfloat16*)w, rstd, (const __nv_bfloat16*)residual_grad,             \
+      (__nv_bfloat16*)dx, rows, N)
+  if (q_bit == 2) BP(2); else if (q_bit == 4) BP(4); else BP(8);
+#undef BP
   HYC_CHECK_LAUNCH();
   return HYC_OK;
 }

@@ -23,7 +23,7 @@ import torch
 
 from ._lib import HycError, check, lib, ptr, require_cuda, stream_of
 from .operators import compress_function as cf
-from .operators.rmsnorm_kernels import rmsnorm_backward, rmsnorm_forward
+from .operators.rmsnorm_kernels import rmsnorm_backward_packed, rmsnorm_forward, rmsnorm_forward_save
 
 BF16 = torch.bfloat16
 _KERNEL_STATUS = {1: "TMA producer wait timed out", 2: "MMA issuer wait timed out", 3: "epilogue wait timed out"}
@@ -137,10 +137,17 @@ def mlp_forward(x_medium, w: MLPWeights, state: MLPState, eps=1e-5, status=None)
     calib = state.iteration < state.iteration_threshold
     sv = state.static_value
 
-    x_norm, _, rstd, _, _ = rmsnorm_forward(x_medium, w.norm_w, eps)
-    xm_o, xm_q, xm_idx, xm_scale = cf.compression_pack_channel_base(
-        x_medium, state.layernorm_outlier_ratio, q, 'per-channel', state.iteration, state.iteration_threshold,
-        sv['x_medium'])
+    if calib:
+        x_norm, _, rstd, _, _ = rmsnorm_forward(x_medium, w.norm_w, eps)
+        xm_o, xm_q, xm_idx, xm_scale = cf.compression_pack_channel_base(
+            x_medium, state.layernorm_outlier_ratio, q, 'per-channel', state.iteration, state.iteration_threshold,
+            sv['x_medium'])
+        xn_q = None
+    else:
+        # steady state: the norm, the save of its input (codes + outlier channels) and the save of its output
+        # are one pass over x_medium
+        xm_idx, xm_scale, xn_scale = sv['x_medium']['outlier_channel_index'], sv['x_medium']['scale'], sv['x_norm_2']['scale']
+        x_norm, rstd, xm_o, xm_q, xn_q = rmsnorm_forward_save(x_medium, w.norm_w, eps, q, xm_scale, xm_idx, xn_scale)
     xn2 = x_norm.reshape(T, H)
     gate_xa = xn2 @ w.ag.t()
     up_xa = xn2 @ w.au.t()
@@ -173,8 +180,9 @@ def mlp_forward(x_medium, w: MLPWeights, state: MLPState, eps=1e-5, status=None)
     us = up_scale.to(BF16).reshape(-1).contiguous()
     gateup(gs, us)
 
-    xn_q, xn_scale = cf.compression_pack_quant_base(x_norm, q, 'per-channel', state.iteration,
-                                                    state.iteration_threshold, sv['x_norm_2'])
+    if xn_q is None:
+        xn_q, xn_scale = cf.compression_pack_quant_base(x_norm, q, 'per-channel', state.iteration,
+                                                        state.iteration_threshold, sv['x_norm_2'])
     had2 = had.reshape(T, I)
     pad = w.padded()
     down_xa64 = had2 @ pad["ad_cols"]              # [T, 64]: the LoRA-A activation of the down projection, zero-padded
@@ -232,9 +240,8 @@ def mlp_backward(grad_out, saved, w: MLPWeights, status=None):
     grad_bu = gu.t() @ up_xa
     # grad wrt x_norm: gate and up products accumulate in one tensor-memory tile
     grad_xn = gemm(gg, w.wg, b_is_kn=True, a2=gu, b2=w.wu, a3=gm64, b3=pad["agu_rows"], status=st)
-    x_medium = cf.outlier_addition_fuse_decompression_dequantization(
-        saved['xm_q'], saved['xm_scale'], saved['xm_o'], saved['xm_idx'], q)
-    grad_norm, _ = rmsnorm_backward(grad_xn.reshape(B, M, H), x_medium, w.norm_w, None, saved['rstd'], True, 1e-5, 0, 0)
-    grad_x = grad_norm + g.reshape(B, M, H)
+    # RMSNorm backward straight from the saved form of x_medium, residual gradient added in the same pass
+    grad_x = rmsnorm_backward_packed(grad_xn.reshape(B, M, H), saved['xm_q'], saved['xm_scale'], saved['xm_o'],
+                                     saved['xm_idx'], w.norm_w, saved['rstd'], q, residual_grad=g.reshape(B, M, H))
     return dict(grad_x=grad_x, grad_ag=grad_ag, grad_bg=grad_bg, grad_au=grad_au, grad_bu=grad_bu,
                 grad_ad=grad_ad, grad_bd=grad_bd, hadamard=had, g_gate=gg, g_up=gu)

@@ -161,6 +161,25 @@ int hyc_rmsnorm_fwd(const void* x, const void* w, float eps, void* y, float* rst
                     int64_t rows, int N, void* stream);
 int hyc_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd, void* dx,
                     int64_t rows, int N, void* stream);
+
+/* RMSNorm fused with the saves of the fused layer (fused_llama_layer_intra_inter_full_fuse.py:203-216: the
+ * norm, `compression_pack_channel_base(x_medium)` and `compression_pack_quant_base(x_norm)` of the MLP half; the
+ * attention half has the same pattern at :99-112): one pass over x writes y = x_norm and rstd, the packed
+ * per-channel codes of x (qx [rows, N*q_bit/8]) with its outlier channels moved to outlier_out [rows, k], and,
+ * when scale_y/qy are given, the packed codes of the bf16 y.  Bit-identical to hyc_rmsnorm_fwd followed by
+ * hyc_quant_pack on x (with the outlier list) and on y.  Statistics are the caller's (steady state of the
+ * calibration): scale_x [N] (zero-guarded), outlier_idx int64 [k], scale_y [N].  N % 32 == 0, N <= 16384. */
+int hyc_rmsnorm_fwd_save(const void* x, const void* w, float eps, int64_t rows, int N,
+                         const void* scale_x, const int64_t* outlier_idx, int k, const void* scale_y_or_null,
+                         void* y, float* rstd, void* qx, void* outlier_out, void* qy_or_null, int q_bit, void* stream);
+
+/* RMSNorm backward reading the packed x directly (:388-395, :484-491: `outlier_addition_fuse_decompression_
+ * dequantization` followed by `rmsnorm_backward`): x is de-quantized and its outlier channels restored inside
+ * the kernel, then the arithmetic of hyc_rmsnorm_bwd.  residual_grad (optional, [rows, N] bf16) is added to the
+ * result as a bf16 tensor add (the residual branch of the layer input's gradient). */
+int hyc_rmsnorm_bwd_packed(const void* dy, const void* qx, const void* scale_x, const int64_t* outlier_idx, int k,
+                           const void* outlier, const void* w, const float* rstd, const void* residual_grad_or_null,
+                           void* dx, int64_t rows, int N, int q_bit, void* stream);
 /* softmax_backward (operators/softmax_kernels.py:7-56): o = (g - sum(y*g)) * y per row. */
 int hyc_softmax_bwd(const void* y, const void* g, void* o, int64_t rows, int S, void* stream);
 

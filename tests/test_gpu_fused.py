@@ -108,6 +108,48 @@ def test_rmsnorm(ops, shape):
     assert none is None and close(dx, oracle.ref_rmsnorm_backward(dy, x, w, orstd), rel=4e-3)
 
 
+@pytest.mark.parametrize("q", (2, 4, 8))
+@pytest.mark.parametrize("shape", [(3, 64), (2, 7, 4096), (1, 33, 11008), (5, 16384), (1, 300, 4128)])
+def test_rmsnorm_fused_with_saves(ops, q, shape):
+    """One-pass norm + saves and the backward on the packed x: bit-identical to the separate operators, which
+    the other tests tie to the oracle; the packed x is also checked against the oracle directly."""
+    from hyc_lora_release_b200.operators import compress_function as cf
+    _, _, rn, _ = ops
+    N = shape[-1]
+    g = torch.Generator().manual_seed(sum(shape) + q)
+    x = torch.randn(*shape, generator=g)
+    n_out = max(1, N // 100)
+    x[..., torch.randperm(N, generator=g)[:n_out]] *= 25.0
+    x[..., 40:43] *= 30.0                       # three outlier channels inside one octet
+    x = x.bfloat16().reshape(-1, shape[-2] if len(shape) > 1 else 1, N)
+    w = (1 + 0.1 * torch.randn(N, generator=g)).bfloat16()
+    xd, wd = x.to(DEV), w.to(DEV)
+    ratio = 0.02
+    idx, sx = cf.get_statistics_channel_base(xd, ratio, q, "per-channel")
+    y0, _, rstd0, _, _ = rn.rmsnorm_forward(xd, wd, 1e-5)
+    sy = cf.get_statistics_only_quant(y0, q, "per-channel")
+    xo0, qx0 = cf.outlier_subtraction_fuse_compression_quantization(xd, sx, idx, q)
+    qy0 = cf.compression_quantization(y0, sy, q)
+    y, rstd, xo, qx, qy = rn.rmsnorm_forward_save(xd, wd, 1e-5, q, sx, idx, sy)
+    assert torch.equal(y, y0) and torch.equal(rstd, rstd0.reshape(-1))
+    assert torch.equal(qx, qx0) and torch.equal(xo, xo0) and torch.equal(qy, qy0)
+    oxo, oqx = oracle.ref_compress_channel_base(x, sx.cpu(), idx.cpu(), q)
+    assert torch.equal(qx.cpu(), oqx) and torch.equal(xo.cpu(), oxo)
+    # without the second save and without outlier channels
+    y1, rstd1, xo1, qx1, qy1 = rn.rmsnorm_forward_save(xd, wd, 1e-5, q, sx, None, None)
+    assert qy1 is None and xo1.shape[-1] == 0 and torch.equal(y1, y0)
+    assert torch.equal(qx1, cf.compression_quantization(xd, sx, q))
+    # backward on the packed x
+    dy = torch.randn(*x.shape, generator=g).bfloat16().to(DEV)
+    res = torch.randn(*x.shape, generator=g).bfloat16().to(DEV)
+    x_hat = cf.outlier_addition_fuse_decompression_dequantization(qx0, sx, xo0, idx, q)
+    dx0, _ = rn.rmsnorm_backward(dy, x_hat, wd, None, rstd0, True, 1e-5, 0, 0)
+    dx = rn.rmsnorm_backward_packed(dy, qx, sx, xo, idx, wd, rstd, q)
+    assert torch.equal(dx, dx0)
+    dx_r = rn.rmsnorm_backward_packed(dy, qx, sx, xo, idx, wd, rstd, q, residual_grad=res)
+    assert torch.equal(dx_r, dx0 + res)
+
+
 @pytest.mark.parametrize("shape", [(1, 2, 8, 8), (2, 3, 100, 104), (1, 4, 512, 512), (1, 1, 16, 4096)])
 def test_softmax_backward(ops, shape):
     _, _, _, sm = ops
