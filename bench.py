@@ -329,9 +329,10 @@ def mlp_workload(dev, dist=None, steps=20, warmup=4):
 
     def step(i):
         out, saved = mlp.mlp_forward(x, W, state, status=st)
-        grads = mlp.mlp_backward(gout, saved, W, status=st)
-        lora = {k: v for k, v in grads.items() if k in ("grad_ag", "grad_bg", "grad_au", "grad_bu", "grad_ad", "grad_bd")}
-        parallel.allreduce_lora_grads(lora)
+        pending = []
+        # the LoRA-gradient all-reduce starts inside the backward pass and overlaps its last two kernels
+        mlp.mlp_backward(gout, saved, W, status=st, on_lora_grads=lambda g_: pending.append(parallel.allreduce_lora_grads_async(g_)))
+        pending[0].wait()
     for i in range(6):          # calibration iterations
         step(i)
     mlp.check_status(st, "mlp")

@@ -204,9 +204,11 @@ def mlp_forward(x_medium, w: MLPWeights, state: MLPState, eps=1e-5, status=None)
     return x_out.reshape(B, M, H), saved
 
 
-def mlp_backward(grad_out, saved, w: MLPWeights, status=None):
+def mlp_backward(grad_out, saved, w: MLPWeights, status=None, on_lora_grads=None):
     """-> dict(grad_x, grad_ag, grad_bg, grad_au, grad_bu, grad_ad, grad_bd); LoRA gradients in the
-    layout of the weights they belong to ([r, in] / [out, r])."""
+    layout of the weights they belong to ([r, in] / [out, r]).  ``on_lora_grads(dict)`` (optional) is called
+    as soon as the six LoRA gradients are enqueued, before the grad_x GEMM and the RMSNorm backward: the
+    place to start their all-reduce so that it overlaps the rest of the pass."""
     B, M, H = saved['shape']
     T, I, q = B * M, w.wg.shape[0], saved['q_bit']
     dev = grad_out.device
@@ -238,6 +240,9 @@ def mlp_backward(grad_out, saved, w: MLPWeights, status=None):
     grad_ag, grad_au = ga[:16], ga[16:32]          # [r, H] each
     grad_bg = gg.t() @ gate_xa                     # [I, r]
     grad_bu = gu.t() @ up_xa
+    if on_lora_grads is not None:
+        on_lora_grads(dict(grad_ag=grad_ag, grad_bg=grad_bg, grad_au=grad_au, grad_bu=grad_bu, grad_ad=grad_ad,
+                           grad_bd=grad_bd))
     # grad wrt x_norm: gate and up products accumulate in one tensor-memory tile
     grad_xn = gemm(gg, w.wg, b_is_kn=True, a2=gu, b2=w.wu, a3=gm64, b3=pad["agu_rows"], status=st)
     # RMSNorm backward straight from the saved form of x_medium, residual gradient added in the same pass

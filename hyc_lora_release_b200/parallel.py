@@ -49,6 +49,35 @@ def allreduce_lora_grads(grads: Dict[str, torch.Tensor], group=None, average=Tru
     return dict(zip(names, unflatten_grads(flat, meta, [grads[n] for n in names])))
 
 
+class PendingLoraGrads:
+    """Handle of an all-reduce that is in flight; ``wait()`` returns the averaged gradients."""
+
+    def __init__(self, names, flat, meta, like, work, world, average):
+        self._names, self._flat, self._meta, self._like = names, flat, meta, like
+        self._work, self._world, self._average = work, world, average
+
+    def wait(self) -> Dict[str, torch.Tensor]:
+        if self._work is not None:
+            self._work.wait()          # the current stream waits for the collective
+        flat = self._flat
+        if self._average and self._world > 1:
+            flat = flat / self._world
+        return dict(zip(self._names, unflatten_grads(flat, self._meta, self._like)))
+
+
+def allreduce_lora_grads_async(grads: Dict[str, torch.Tensor], group=None, average=True) -> PendingLoraGrads:
+    """Start the all-reduce of the flattened LoRA gradients and return at once: the collective runs beside
+    whatever the caller enqueues next (``mlp_backward`` calls this through its ``on_lora_grads`` hook before the
+    grad_x GEMM and the RMSNorm backward, which do not need the reduced values)."""
+    names = sorted(grads)
+    like = [grads[n] for n in names]
+    flat, meta = flatten_grads(like)
+    if not dist.is_initialized() or dist.get_world_size(group) == 1:
+        return PendingLoraGrads(names, flat, meta, like, None, 1, average)
+    work = dist.all_reduce(flat, op=dist.ReduceOp.SUM, group=group, async_op=True)
+    return PendingLoraGrads(names, flat, meta, like, work, dist.get_world_size(group), average)
+
+
 def sync_calibration(static_value: dict, group=None) -> dict:
     """Make calibration statistics identical on all ranks: floating-point entries are averaged,
     the outlier channel index of rank 0 wins."""

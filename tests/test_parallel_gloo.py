@@ -31,6 +31,11 @@ def _worker(rank, world, port, ret):
         full_a = (gm.t() @ x)
         ok = torch.allclose(red["grad_a"].float(), full_a, atol=0.25, rtol=2e-2) and \
             torch.allclose(red["grad_b"], x.t() @ gm, atol=1e-4) and red["grad_a"].dtype == torch.bfloat16
+        # the asynchronous form gives the same sums (and the average when asked)
+        pend = parallel.allreduce_lora_grads_async(grads, average=True)
+        other = torch.randn(8, 8, generator=g) @ torch.randn(8, 8, generator=g)     # work enqueued meanwhile
+        avg = pend.wait()
+        ok = ok and torch.allclose(avg["grad_b"], (x.t() @ gm) / world, atol=1e-4) and other.shape == (8, 8)
         sv = {"x": {"outlier_channel_index": torch.tensor([rank, rank + 5]), "scale": torch.full((1, 4), float(rank + 1))}}
         sv = parallel.sync_calibration(sv)
         ok = ok and sv["x"]["outlier_channel_index"].tolist() == [0, 5] and \
