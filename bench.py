@@ -240,7 +240,34 @@ def extra_workloads(dev, hbm):
             del graph, qb, ob, xb
         del xs
     out.append(fused_elementwise_workload(dev, hbm))
+    out.append(attention_backward_workload(dev, hbm))
     return out
+
+
+def attention_backward_workload(dev, hbm):
+    """Backward side of the attention-map save: restore of the top-k + 4-bit map fused with softmax_backward
+    (the restored map never reaches HBM), on the headline's [4,32,512,512] map.  Algorithmic bytes: the saved
+    form (codes, group parameters, outlier list) + the upstream gradient in, the gradient out."""
+    from hyc_lora_release_b200.operators import compress_function as cf
+    maps = [make_map(2000 + i, dev) for i in range(NBUF)]
+    g = torch.Generator().manual_seed(5)
+    grads = [torch.randn(*MAP_SHAPE, generator=g).to(torch.bfloat16).to(dev) for _ in range(NBUF)]
+    hs = [cf.compression_softmax_topk(m, RATIO, QBIT) for m in maps]
+    outs = [torch.empty_like(m) for m in maps]
+    del maps
+    for j in range(NBUF):
+        hs[j].softmax_backward(grads[j], out=outs[j])
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for j in range(NBUF):
+            hs[j].softmax_backward(grads[j], out=outs[j])
+    t = time_loop(lambda i: graph.replay(), 10, 3) / (10 * NBUF)
+    numel = grads[0].numel()
+    nbytes = algo_bytes(MAP_SHAPE, QBIT, RATIO) - 2.0 * numel + 4.0 * numel
+    return {"workload": "attention-map backward: top-k restore fused with softmax_backward, [4,32,512,512] (BASELINE configs[1] map)",
+            "q_bit": QBIT, "value": nbytes / t / 1e9, "unit": "GB/s", "frac_of_hbm": nbytes / t / 1e9 / hbm,
+            "ms_per_step": t * 1e3, "launch": "CUDA graph replay over %d buffer sets" % NBUF}
 
 
 def fused_elementwise_workload(dev, hbm):

@@ -2,6 +2,7 @@
 // compressed tensors.  Plain streaming kernels, one row per block (norm) or per warp
 // (softmax), the row held in registers between the reduction and the second pass.
 #include "octet_codes.cuh"
+#include "topk_lane.cuh"
 
 namespace hyc {
 
@@ -433,6 +434,10 @@ extern "C" HYC_API int hyc_softmax_bwd(const void* y, const void* g, void* o, in
   if (rows < 0 || S <= 0 || S % 8 != 0 || S > 32 * 8 * kSmMaxVec) return HYC_ERR_SHAPE;
   if (!aligned(y, 16) || !aligned(g, 16) || !aligned(o, 16)) return HYC_ERR_ALIGN;
   if (rows == 0) return HYC_OK;
+  if (softmax_bwd_lane(y, g, rows, S, o, (cudaStream_t)stream)) {   // rows of 64 * 2^n columns: staged, coalesced
+    HYC_CHECK_LAUNCH();
+    return HYC_OK;
+  }
   int64_t grid = (rows + 7) / 8;
   if (grid > (int64_t)kNumSMs * 8) grid = (int64_t)kNumSMs * 8;
   softmax_bwd_kernel<<<(int)grid, 256, 0, (cudaStream_t)stream>>>(

@@ -189,11 +189,15 @@ topk_lane_compress_kernel(const __nv_bfloat16* __restrict__ a, int64_t rows, int
 }
 
 // ---------------------------------------------------------------- restore
-template <int QBIT, int LPR>
+// SMBWD: instead of the restored map y itself, write the softmax backward of it for the upstream gradient
+// `grad`:  out = (g - sum_row(bf16(y * g))) * y  (operators/softmax_kernels.py:7-38: the product is a bf16
+// operation, the row sum and the rest fp32).  The restored map never goes to HBM.
+template <int QBIT, int LPR, bool SMBWD>
 __global__ void __launch_bounds__(256, HYC_LANE_MINB)
 topk_lane_restore_kernel(const __nv_bfloat16* __restrict__ val, const uint16_t* __restrict__ colv, int k, float inv_k,
                          const uint8_t* __restrict__ q, const __nv_bfloat16* __restrict__ scale,
-                         const int8_t* __restrict__ zp, int64_t rows, __nv_bfloat16* __restrict__ ao) {
+                         const int8_t* __restrict__ zp, int64_t rows, const __nv_bfloat16* __restrict__ grad,
+                         __nv_bfloat16* __restrict__ ao) {
   constexpr int RPW = 32 / LPR;
   constexpr int S = 64 * LPR;
   constexpr int64_t QLD = (int64_t)S * QBIT / 8;
@@ -252,10 +256,100 @@ topk_lane_restore_kernel(const __nv_bfloat16* __restrict__ val, const uint16_t* 
       sw16[owner * 64 + ((c & 63) ^ ((owner & 7) << 3))] = __bfloat16_as_ushort(vrun[j]);
     }
     __syncwarp();
+    if (SMBWD) {
+      uint32_t yv[32], gv[32];
+      lane_slot_load(sx, lane, yv);                       // the lane's own group of the restored row
+      __syncwarp();
+      lane_run_to_shared(grad + row0 * S, n_rows * (S / 16), s_x[warp], lane);
+      __syncwarp();
+      lane_slot_load(sx, lane, gv);
+      float acc = 0.f;
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        const __nv_bfloat162 p = __hmul2_rn(*reinterpret_cast<const __nv_bfloat162*>(&yv[j]),
+                                            *reinterpret_cast<const __nv_bfloat162*>(&gv[j]));
+        acc += __bfloat162float(p.x) + __bfloat162float(p.y);
+      }
+#pragma unroll
+      for (int o = 1; o < LPR; o <<= 1) acc += __shfl_xor_sync(kFull, acc, o);     // stays inside the row's lanes
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        gv[j] = pack_bf16x2_rn((bf16lo_to_f32(gv[j]) - acc) * bf16lo_to_f32(yv[j]),
+                               (bf16hi_to_f32(gv[j]) - acc) * bf16hi_to_f32(yv[j]));
+      __syncwarp();
+      lane_slot_store(sx, lane, gv);
+      __syncwarp();
+    }
     // the warp's rows leave as four fully coalesced 1 KB stores
     lane_shared_to_run(s_x[warp], ao + row0 * S, n_rows * (S / 16), lane);
     __syncwarp();
   }
+}
+
+// ---------------------------------------------------------------- softmax backward on dense maps
+// out = (g - sum_row(bf16(y * g))) * y for rows of 64 * LPR columns, same layout and staging as above
+template <int LPR>
+__global__ void __launch_bounds__(256, HYC_LANE_MINB)
+softmax_bwd_lane_kernel(const __nv_bfloat16* __restrict__ y, const __nv_bfloat16* __restrict__ g, int64_t rows,
+                        __nv_bfloat16* __restrict__ out) {
+  constexpr int RPW = 32 / LPR;
+  constexpr int S = 64 * LPR;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  __shared__ __align__(16) uint32_t s_x[8][32 * 32];
+  uint32_t* sx = s_x[warp] + lane * 32;
+  const int64_t items = (rows + RPW - 1) / RPW;
+  for (int64_t item = (int64_t)blockIdx.x * nwarps + warp; item < items; item += (int64_t)gridDim.x * nwarps) {
+    const int64_t row0 = item * RPW, left = rows - row0;
+    const int n_pieces = (int)(left < RPW ? left : RPW) * (S / 16);
+    uint32_t yv[32], gv[32];
+    lane_run_to_shared(y + row0 * S, n_pieces, s_x[warp], lane);
+    __syncwarp();
+    lane_slot_load(sx, lane, yv);
+    __syncwarp();
+    lane_run_to_shared(g + row0 * S, n_pieces, s_x[warp], lane);
+    __syncwarp();
+    lane_slot_load(sx, lane, gv);
+    float acc = 0.f;
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      const __nv_bfloat162 p = __hmul2_rn(*reinterpret_cast<const __nv_bfloat162*>(&yv[j]),
+                                          *reinterpret_cast<const __nv_bfloat162*>(&gv[j]));
+      acc += __bfloat162float(p.x) + __bfloat162float(p.y);
+    }
+#pragma unroll
+    for (int o = 1; o < LPR; o <<= 1) acc += __shfl_xor_sync(kFull, acc, o);
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      gv[j] = pack_bf16x2_rn((bf16lo_to_f32(gv[j]) - acc) * bf16lo_to_f32(yv[j]),
+                             (bf16hi_to_f32(gv[j]) - acc) * bf16hi_to_f32(yv[j]));
+    __syncwarp();
+    lane_slot_store(sx, lane, gv);
+    __syncwarp();
+    lane_shared_to_run(s_x[warp], out + row0 * S, n_pieces, lane);
+    __syncwarp();
+  }
+}
+
+template <int LPR>
+static void launch_softmax_bwd(const void* y, const void* g, int64_t rows, void* out, cudaStream_t st) {
+  auto kern = softmax_bwd_lane_kernel<LPR>;
+  int grid, threads;
+  lane_launch_shape(kern, rows, 32 / LPR, grid, threads);
+  kern<<<grid, threads, 0, st>>>((const __nv_bfloat16*)y, (const __nv_bfloat16*)g, rows, (__nv_bfloat16*)out);
+}
+
+// rows of 64 * 2^n <= 2048 columns, 32-byte aligned tensors; false = not covered (nothing launched)
+bool softmax_bwd_lane(const void* y, const void* g, int64_t rows, int S, void* out, cudaStream_t st) {
+  if (S < 64 || S > 2048 || (S & (S - 1)) != 0 || !aligned(y, 32) || !aligned(g, 32) || !aligned(out, 32)) return false;
+  switch (S / 64) {
+    case 1: launch_softmax_bwd<1>(y, g, rows, out, st); break;
+    case 2: launch_softmax_bwd<2>(y, g, rows, out, st); break;
+    case 4: launch_softmax_bwd<4>(y, g, rows, out, st); break;
+    case 8: launch_softmax_bwd<8>(y, g, rows, out, st); break;
+    case 16: launch_softmax_bwd<16>(y, g, rows, out, st); break;
+    default: launch_softmax_bwd<32>(y, g, rows, out, st); break;
+  }
+  return true;
 }
 
 // ---------------------------------------------------------------- launchers
@@ -270,12 +364,20 @@ static void launch_compress(const void* a, int64_t rows, int k, void* val, uint1
 }
 template <int QBIT, int LPR>
 static void launch_restore(const void* val, const uint16_t* col, int k, const void* q, const void* scale,
-                           const int8_t* zp, int64_t rows, void* ao, cudaStream_t st) {
-  auto kern = topk_lane_restore_kernel<QBIT, LPR>;
+                           const int8_t* zp, int64_t rows, const void* grad, void* ao, cudaStream_t st) {
   int grid, threads;
-  lane_launch_shape(kern, rows, 32 / LPR, grid, threads);
-  kern<<<grid, threads, 0, st>>>((const __nv_bfloat16*)val, col, k, k > 0 ? 1.0f / (float)k : 0.f,
-                                 (const uint8_t*)q, (const __nv_bfloat16*)scale, zp, rows, (__nv_bfloat16*)ao);
+  if (grad == nullptr) {
+    auto kern = topk_lane_restore_kernel<QBIT, LPR, false>;
+    lane_launch_shape(kern, rows, 32 / LPR, grid, threads);
+    kern<<<grid, threads, 0, st>>>((const __nv_bfloat16*)val, col, k, k > 0 ? 1.0f / (float)k : 0.f,
+                                   (const uint8_t*)q, (const __nv_bfloat16*)scale, zp, rows, nullptr, (__nv_bfloat16*)ao);
+  } else {
+    auto kern = topk_lane_restore_kernel<QBIT, LPR, true>;
+    lane_launch_shape(kern, rows, 32 / LPR, grid, threads);
+    kern<<<grid, threads, 0, st>>>((const __nv_bfloat16*)val, col, k, k > 0 ? 1.0f / (float)k : 0.f,
+                                   (const uint8_t*)q, (const __nv_bfloat16*)scale, zp, rows,
+                                   (const __nv_bfloat16*)grad, (__nv_bfloat16*)ao);
+  }
 }
 
 #define HYC_LANE_DISPATCH(FN, ...)                                            \
@@ -297,8 +399,8 @@ static int compress_q(const void* a, int64_t rows, int S, int k, void* val, uint
 }
 template <int QB>
 static int restore_q(const void* val, const uint16_t* col, int k, const void* q, const void* scale, const int8_t* zp,
-                     int64_t rows, int S, void* ao, cudaStream_t st) {
-  HYC_LANE_DISPATCH(launch_restore, val, col, k, q, scale, zp, rows, ao, st);
+                     int64_t rows, int S, const void* grad, void* ao, cudaStream_t st) {
+  HYC_LANE_DISPATCH(launch_restore, val, col, k, q, scale, zp, rows, grad, ao, st);
   return HYC_OK;
 }
 
@@ -310,11 +412,12 @@ int topk_lane_compress(const void* a, int64_t rows, int S, int k, void* val_out,
   return compress_q<8>(a, rows, S, k, val_out, col_out, q_out, scale_out, zp_out, st);
 }
 int topk_lane_restore(const void* val, const uint16_t* col, int k, const void* q, const void* scale,
-                      const int8_t* zp, int64_t rows, int S, void* a_out, int q_bit, cudaStream_t st) {
+                      const int8_t* zp, int64_t rows, int S, const void* grad_or_null, void* a_out, int q_bit,
+                      cudaStream_t st) {
   if (!topk_lane_ok(S, k)) return HYC_ERR_SHAPE;
-  if (q_bit == 2) return restore_q<2>(val, col, k, q, scale, zp, rows, S, a_out, st);
-  if (q_bit == 4) return restore_q<4>(val, col, k, q, scale, zp, rows, S, a_out, st);
-  return restore_q<8>(val, col, k, q, scale, zp, rows, S, a_out, st);
+  if (q_bit == 2) return restore_q<2>(val, col, k, q, scale, zp, rows, S, grad_or_null, a_out, st);
+  if (q_bit == 4) return restore_q<4>(val, col, k, q, scale, zp, rows, S, grad_or_null, a_out, st);
+  return restore_q<8>(val, col, k, q, scale, zp, rows, S, grad_or_null, a_out, st);
 }
 
 }  // namespace hyc

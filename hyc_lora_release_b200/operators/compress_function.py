@@ -321,6 +321,27 @@ class TopkMap:
     def to_dense(self, out=None):
         return decompression_softmax_topk(self, out=out)
 
+    def softmax_backward(self, grad, out=None):
+        """``softmax_backward(self.to_dense(), grad)`` (operators/softmax_kernels.py:41) without writing the
+        restored map: one kernel where the shapes allow it, restore + softmax backward otherwise."""
+        require_cuda(grad, self.q)
+        g = grad.to(BF16).contiguous()
+        if tuple(g.shape) != self.shape:
+            raise ValueError("the gradient must have the map's shape %s" % (self.shape,))
+        S, rows, k = self.shape[-1], self.q.shape[0], self.val.shape[1]
+        if out is None:
+            out = torch.empty(self.shape, dtype=BF16, device=self.q.device)
+        rc = lib.hyc_softmax_topk_restore_bwd(ptr(self.val) if k else None, ptr(self.col) if k else None, k, ptr(self.q),
+                                              ptr(self.scale), ptr(self.zp), rows, S, ptr(g), ptr(out), self.q_bit,
+                                              stream_of(self.q))
+        if rc == -8:      # HYC_ERR_UNSUPPORTED: shape outside the fused kernel
+            from .softmax_kernels import softmax_backward as _sb
+            res = _sb(self.to_dense(), g)
+            out.copy_(res.reshape(self.shape))
+            return out
+        check(rc, "hyc_softmax_topk_restore_bwd")
+        return out
+
 
 def compression_softmax_topk(x, outlier_ratio, quantize_bit=4, out=None):
     """Top-k per row (k = int(S * ratio)) as bf16 value + uint16 column, the remainder

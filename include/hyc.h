@@ -135,6 +135,13 @@ int hyc_softmax_topk_compress(const void* a, int64_t rows, int S, int k,
 int hyc_softmax_topk_restore(const void* val, const uint16_t* col, int k,
                              const void* q, const void* scale, const int8_t* zp,
                              int64_t rows, int S, void* a_out, int q_bit, void* stream);
+/* Restore fused with softmax_backward (fused_llama_layer_intra_inter_full_fuse.py:414-433: `a_o.to_dense()`
+ * followed by `softmax_backward`): out = (g - sum_row(bf16(y * g))) * y with y the restored map, which is
+ * never written to HBM.  grad, out [rows, S] bf16.  Returns HYC_ERR_UNSUPPORTED for shapes outside the
+ * lane-per-group kernels (S not 64 * 2^n <= 2048, very large k): restore, then hyc_softmax_bwd. */
+int hyc_softmax_topk_restore_bwd(const void* val, const uint16_t* col, int k,
+                                 const void* q, const void* scale, const int8_t* zp,
+                                 int64_t rows, int S, const void* grad, void* out, int q_bit, void* stream);
 
 /* ---- fused LoRA-SiLU-Hadamard elementwise kernels ------------------------------------- */
 

@@ -162,6 +162,29 @@ def test_topk_reused_buffers(cf):
         ha.to_dense(out=torch.empty(2, 512, 512, dtype=torch.bfloat16, device=DEV))
 
 
+@pytest.mark.parametrize("q", QS)
+@pytest.mark.parametrize("shape", [(1, 2, 512, 512), (1, 1, 13, 128), (1, 1, 5, 2048), (1, 1, 320, 320)])
+def test_topk_restore_fused_with_softmax_backward(cf, q, shape):
+    """out = softmax_backward(restored map, grad) without the restored map in HBM; the last shape takes the
+    two-kernel fallback.  Against the oracle (tolerance: the fp32 row sum has another order) and against the
+    two separate device kernels."""
+    from hyc_lora_release_b200.operators.softmax_kernels import softmax_backward
+    b, h, r, s = shape
+    g = torch.Generator().manual_seed(s + q + r)
+    a = torch.softmax(3 * torch.randn(b, h, r, s, generator=g), -1).to(torch.bfloat16)
+    grad = torch.randn(b, h, r, s, generator=g).to(torch.bfloat16)
+    m = cf.compression_softmax_topk(a.to(DEV), 0.05, q)
+    out = m.softmax_backward(grad.to(DEV))
+    y = m.to_dense()
+    ref = oracle.ref_softmax_backward(y.cpu(), grad)
+    two = softmax_backward(y, grad.to(DEV))
+    scale = ref.float().abs().max()
+    assert (out.float().cpu() - ref.float()).abs().max() <= 1e-2 * scale
+    assert (out.float() - two.float()).abs().max() <= 1e-2 * scale
+    buf = torch.empty_like(y)
+    assert m.softmax_backward(grad.to(DEV), out=buf) is buf and torch.equal(buf, out)
+
+
 def test_topk_config1_full_size_properties(cf):
     """[4,32,512,512] causal softmax map, ratio 0.05, q_bit 4: checked through size-independent
     properties plus the oracle on a slice."""
