@@ -57,6 +57,8 @@ class PendingLoraGrads:
         self._work, self._world, self._average = work, world, average
 
     def wait(self) -> Dict[str, torch.Tensor]:
+        if self._flat is None:
+            return dict(zip(self._names, self._like))
         if self._work is not None:
             self._work.wait()          # the current stream waits for the collective
         flat = self._flat
@@ -71,9 +73,9 @@ def allreduce_lora_grads_async(grads: Dict[str, torch.Tensor], group=None, avera
     grad_x GEMM and the RMSNorm backward, which do not need the reduced values)."""
     names = sorted(grads)
     like = [grads[n] for n in names]
-    flat, meta = flatten_grads(like)
     if not dist.is_initialized() or dist.get_world_size(group) == 1:
-        return PendingLoraGrads(names, flat, meta, like, None, 1, average)
+        return PendingLoraGrads(names, None, None, like, None, 1, average)      # nothing to exchange
+    flat, meta = flatten_grads(like)
     work = dist.all_reduce(flat, op=dist.ReduceOp.SUM, group=group, async_op=True)
     return PendingLoraGrads(names, flat, meta, like, work, dist.get_world_size(group), average)
 
