@@ -5,7 +5,7 @@
 
 Headline workload (N = 1): the attention-map save/restore of a [4,32,512,512] bf16 causal
 softmax map, per-row top-k (ratio 0.05) + 4-bit 64-wide groups; one step = compress +
-decompress of one map.  Prints ONE JSON line (see DESIGN.md for every field).
+decompress of one map.  Prints ONE JSON line.
 Under torchrun every rank works on its own shard of maps (weak scaling, no data-path
 collective); the time is the maximum over ranks.
 """
