@@ -36,6 +36,7 @@ SIGNATURES = {
     "hyc_softmax_topk_restore_bwd": (_i, [_p, _p, _i, _p, _p, _p, _l, _i, _p, _p, _i, _p]),
     "hyc_fused_lora_silu_hadamard_fwd": (_i, [_p] * 11 + [_l, _i, _i, _i, _p]),
     "hyc_fused_lora_silu_hadamard_bwd": (_i, [_p] * 12 + [_l, _i, _i, _i, _p]),
+    "hyc_dequant_lora_add": (_i, [_p, _p, _p, _p, _p, _l, _i, _i, _i, _p]),
     "hyc_rmsnorm_fwd": (_i, [_p, _p, _f, _p, _p, _l, _i, _p]),
     "hyc_rmsnorm_bwd": (_i, [_p, _p, _p, _p, _p, _l, _i, _p]),
     "hyc_rmsnorm_fwd_save": (_i, [_p, _p, _f, _l, _i, _p, _p, _i, _p, _p, _p, _p, _p, _p, _i, _p]),
@@ -47,6 +48,7 @@ SIGNATURES = {
                                    _p, _p, _l, _l, _p, _p, _l, _l, _p, _p, _p, _p]),
     "hyc_mlp_gateup_fwd_tcgen05": (_i, [_p, _p, _p, _i, _i, _i, _p, _p, _l, _l, _p, _p, _l, _l,
                                         _p, _p, _p, _p, _p, _p, _p, _i, _p, _p]),
+    "hyc_linear_lora_save_fwd_tcgen05": (_i, [_p, _p, _i, _i, _i, _p, _p, _l, _l, _p, _p, _p, _p, _i, _p, _p]),
     "hyc_mlp_graddown_bwd_tcgen05": (_i, [_p, _p, _i, _i, _i, _p, _p, _i, _p, _p, _l, _l, _p, _p, _l, _l,
                                           _p, _p, _p, _p, _p, _p, _l, _p, _p, _p, _i, _p, _p]),
 }

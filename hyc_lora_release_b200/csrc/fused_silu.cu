@@ -453,6 +453,101 @@ fused_silu_wide_kernel(const __nv_bfloat16* __restrict__ xa1, const __nv_bfloat1
   }
 }
 
+// ---------------------------------------------------------------- de-quantize + LoRA re-add
+// y = bf16( dequant(q, s) + bf16(xa * bt^T) ): the backward-side reconstruction of a LoRA projection whose
+// main branch was saved as codes (the q/k/v projections: `decompression_dequantization` followed by
+// `+ x_lora_a @ w_lora_b`, fused_llama_layer_intra_inter_full_fuse.py:416-452).  Same layout as the wide
+// kernel above with one branch.
+template <int QBIT>
+__global__ void __launch_bounds__(256, HYC_FUSED_MINB)
+dequant_lora_add_kernel(const __nv_bfloat16* __restrict__ xa, const __nv_bfloat16* __restrict__ bt,
+                        const __nv_bfloat16* __restrict__ sv, const uint8_t* __restrict__ q,
+                        __nv_bfloat16* __restrict__ y, int64_t rows, int N) {
+  constexpr int EPP = 8 / QBIT;
+  constexpr uint32_t CM = (1u << QBIT) - 1u, BM = CM * 0x01010101u;
+  __shared__ __align__(16) uint32_t s_l[8][16 * kWideLd];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  const int c0 = 64 * (blockIdx.x * 8 + warp);
+  if (c0 >= N) return;
+  const int64_t qld = (int64_t)N / EPP;
+  uint32_t* sl = s_l[warp];
+  const int cl = lane & 7, rsub = lane >> 3;
+  const int col = c0 + 8 * cl;
+  const bool col_ok = col < N;
+  const int blk = col >> 5, cg = (col >> 3) & 3;
+  uint32_t sp[4] = {0u, 0u, 0u, 0u};
+  if (col_ok) {
+    const uint4 a = *reinterpret_cast<const uint4*>(sv + col);
+    sp[0] = a.x; sp[1] = a.y; sp[2] = a.z; sp[3] = a.w;
+  }
+  const int64_t n_tiles = (rows + 15) / 16;
+  for (int64_t rt = blockIdx.y; rt < n_tiles; rt += gridDim.y) {
+    uint2 pq[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int64_t row = rt * 16 + 4 * i + rsub;
+      pq[i] = make_uint2(0u, 0u);
+      if (row < rows && col_ok) {
+        if (QBIT == 8) pq[i] = ld_stream_v2(q + row * qld + col);
+        else if (QBIT == 4) pq[i] = ld_stream_v2(q + row * qld + 16 * blk + 8 * (cg & 1));
+        else pq[i] = ld_stream_v2(q + row * qld + 8 * blk);
+      }
+    }
+    {
+      const int64_t ra = rt * 16 + g, rb = ra + 8;
+      uint32_t a[4] = {0u, 0u, 0u, 0u};
+      if (ra < rows) {
+        a[0] = *reinterpret_cast<const uint32_t*>(xa + ra * 16 + 2 * t);
+        a[2] = *reinterpret_cast<const uint32_t*>(xa + ra * 16 + 2 * t + 8);
+      }
+      if (rb < rows) {
+        a[1] = *reinterpret_cast<const uint32_t*>(xa + rb * 16 + 2 * t);
+        a[3] = *reinterpret_cast<const uint32_t*>(xa + rb * 16 + 2 * t + 8);
+      }
+#pragma unroll 2
+      for (int nt = 0; nt < 8; ++nt) {
+        const int n = c0 + 8 * nt + g;
+        uint32_t ba = 0u, bb = 0u;
+        if (n < N) {
+          ba = *reinterpret_cast<const uint32_t*>(bt + (int64_t)n * 16 + 2 * t);
+          bb = *reinterpret_cast<const uint32_t*>(bt + (int64_t)n * 16 + 2 * t + 8);
+        }
+        float l[4];
+        mma_bf16_16816(l, a, ba, bb);
+        sl[g * kWideLd + 4 * nt + t] = pack_bf16x2_rn(l[0], l[1]);
+        sl[(g + 8) * kWideLd + 4 * nt + t] = pack_bf16x2_rn(l[2], l[3]);
+      }
+    }
+    __syncwarp();
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int lr = 4 * i + rsub;
+      const int64_t row = rt * 16 + lr;
+      const uint4 lq = *reinterpret_cast<const uint4*>(sl + lr * kWideLd + 4 * cl);
+      const uint32_t lw[4] = {lq.x, lq.y, lq.z, lq.w};
+      const int sh = QBIT == 8 ? 0 : (QBIT == 4 ? 4 * (cg >> 1) : 2 * cg);
+      const uint32_t k[2] = {(pq[i].x >> sh) & BM, (pq[i].y >> sh) & BM};
+      uint32_t o[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const uint32_t w = k[j >> 1];
+        uint32_t x;
+        if (QBIT == 8) {
+          const float a0 = (byte_to_magic_float(w, (2 * j) & 3) - 8388736.f) * bf16lo_to_f32(sp[j]);
+          const float a1 = (byte_to_magic_float(w, ((2 * j) & 3) + 1) - 8388736.f) * bf16hi_to_f32(sp[j]);
+          x = pack_bf16x2_rn(a0, a1);
+        } else {
+          constexpr uint32_t C1 = 0x4300u | (uint32_t)(1 << (QBIT - 1));
+          x = mul2(sub2(__byte_perm(w, 0x43434343u, (j & 1) ? 0x4342u : 0x4140u), C1 | (C1 << 16)), sp[j]);
+        }
+        o[j] = add2(x, lw[j]);
+      }
+      if (row < rows && col_ok) st_stream_v4(y + row * N + col, make_uint4(o[0], o[1], o[2], o[3]));
+    }
+    __syncwarp();
+  }
+}
+
 // one resident wave: every block walks down the rows with a fixed stride, so a second, partial wave would
 // only add a tail
 template <typename K>
@@ -553,6 +648,21 @@ extern "C" HYC_API int hyc_fused_lora_silu_hadamard_bwd(const void* xa1, const v
       (__nv_bfloat16*)grad_up, rows, N)
   if (q_bit == 2) BW(2); else if (q_bit == 4) BW(4); else BW(8);
 #undef BW
+  HYC_CHECK_LAUNCH();
+  return HYC_OK;
+}
+
+extern "C" HYC_API int hyc_dequant_lora_add(const void* q, const void* scale, const void* xa, const void* bt,
+                                            void* y, int64_t rows, int N, int R, int q_bit, void* stream) {
+  if (!q || !scale || !xa || !bt || !y) return HYC_ERR_NULL;
+  int rc = check_fused(rows, N, R, q_bit);
+  if (rc) return rc;
+  if (!aligned(q, 8) || !aligned(scale, 16) || !aligned(xa, 4) || !aligned(bt, 4) || !aligned(y, 16)) return HYC_ERR_ALIGN;
+  if (rows == 0) return HYC_OK;
+#define DL(QB) dequant_lora_add_kernel<QB><<<fused_wide_grid(dequant_lora_add_kernel<QB>, rows, N), 256, 0, (cudaStream_t)stream>>>( \
+      (const __nv_bfloat16*)xa, (const __nv_bfloat16*)bt, (const __nv_bfloat16*)scale, (const uint8_t*)q, (__nv_bfloat16*)y, rows, N)
+  if (q_bit == 2) DL(2); else if (q_bit == 4) DL(4); else DL(8);
+#undef DL
   HYC_CHECK_LAUNCH();
   return HYC_OK;
 }

@@ -416,29 +416,46 @@ __device__ __forceinline__ void epi_graddown_block(const Params& p, int64_t row,
   }
 }
 
+// p.q1 != NULL: the bf16 main product (before the LoRA term and the residual) is also quantized with the
+// per-channel constants sR (staged per tile) and packed: the "linear + save" of a LoRA projection.
+template <int QBIT>
 __device__ __forceinline__ void epi_store_block(const Params& p, int64_t row, bool valid, int ncol0, int cb,
                                                 const uint32_t (&acc)[32], const float (&xa0)[16], const float (&xa1)[16],
-                                                const __nv_bfloat16* sB0, const __nv_bfloat16* sB1) {
+                                                const __nv_bfloat16* sB0, const __nv_bfloat16* sB1, const float* sR) {
+  using G = BlockGeo<QBIT>;
   const int64_t n = (int64_t)ncol0 + cb;
   const bool has0 = p.l0.bt != nullptr, has1 = p.l1.bt != nullptr;
   const bool has_res = p.residual != nullptr && valid;
+  const bool save = p.q1 != nullptr;
+  uint32_t w1[G::NW];
+#pragma unroll
+  for (int i = 0; i < G::NW; ++i) w1[i] = 0u;
 #pragma unroll
   for (int c8 = 0; c8 < 4; ++c8) {
     uint4 rq = make_uint4(0u, 0u, 0u, 0u);
     if (has_res) rq = *reinterpret_cast<const uint4*>(p.residual + row * p.N + n + 8 * c8);
     const uint32_t r[4] = {rq.x, rq.y, rq.z, rq.w};
-    uint32_t o[4];
+    uint32_t o[4], m[4];
 #pragma unroll
     for (int e2 = 0; e2 < 4; ++e2) {
       const int c = 8 * c8 + 2 * e2, tc = cb + c;
       uint32_t v = pack_bf16x2_rn(__uint_as_float(acc[c]), __uint_as_float(acc[c + 1]));
+      m[e2] = v;
+      if (save) {
+        put_code<QBIT>(w1, c, fastq_code_bits<QBIT>(bf16lo_to_f32(v), sR[tc]) & G::CM);
+        put_code<QBIT>(w1, c + 1, fastq_code_bits<QBIT>(bf16hi_to_f32(v), sR[tc + 1]) & G::CM);
+      }
       if (has0) v = add2(v, pack_bf16x2_rn(lora_dot(xa0, sB0 + tc * 16), lora_dot(xa0, sB0 + (tc + 1) * 16)));
       if (has1) v = add2(v, pack_bf16x2_rn(lora_dot(xa1, sB1 + tc * 16), lora_dot(xa1, sB1 + (tc + 1) * 16)));
       if (has_res) v = add2(v, r[e2]);
       o[e2] = v;
     }
-    if (valid) store4_pairs(p.out0 + row * p.N + n + 8 * c8, o);
+    if (valid) {
+      store4_pairs(p.out0 + row * p.N + n + 8 * c8, o);
+      if (p.dbg1 != nullptr) store4_pairs(p.dbg1 + row * p.N + n + 8 * c8, m);
+    }
   }
+  if (save && valid) store_block_words<QBIT>(p.q1 + (row * p.N + n) * QBIT / 8, w1);
 }
 
 // ------------------------------------------------------------------ the kernel
@@ -596,6 +613,7 @@ mlp_gemm_kernel(const __grid_constant__ CUtensorMap mapA1, const __grid_constant
       if (EPI == EPI_STORE) {
         stage_lora_tile(p.l0, n0, BN, sB0, et);
         stage_lora_tile(p.l1, n0, BN, sB1, et);
+        if (p.q1 != nullptr) sV[et] = fastq_scale<QBIT>(__frcp_rn(__bfloat162float(p.s1[n0 + et])));
       } else if (EPI == EPI_GATEUP) {
         // 128 output columns per tile: the two LoRA-B tiles fit as fp32 rows (2 x 8 KB)
         stage_lora_tile_f32(p.l0, n0, TILE_N, sF0, et);
@@ -643,7 +661,7 @@ mlp_gemm_kernel(const __grid_constant__ CUtensorMap mapA1, const __grid_constant
           uint32_t acc[32];
           const int cb = 128 * chalf + 32 * ch;
           tc_ld32(t_lane + (uint32_t)cb, acc);
-          if (EPI == EPI_STORE) epi_store_block(p, row, valid, n0, cb, acc, xa0, xa1, sB0, sB1);
+          if (EPI == EPI_STORE) epi_store_block<QBIT>(p, row, valid, n0, cb, acc, xa0, xa1, sB0, sB1, sV);
           else epi_graddown_block<QBIT>(p, row, valid, n0, cb, acc, xa1, xa2, sB1, sB2,
                                         reinterpret_cast<const uint32_t*>(sV), reinterpret_cast<const uint32_t*>(sV + BN));
         }
@@ -853,4 +871,32 @@ extern "C" HYC_API int hyc_mlp_graddown_bwd_tcgen05(
   if (q_bit == 2) return launch<EPI_GRADDOWN, 2, true>(a1, b1, a2, b2, a1, b1, p, st);
   if (q_bit == 4) return launch<EPI_GRADDOWN, 4, true>(a1, b1, a2, b2, a1, b1, p, st);
   return launch<EPI_GRADDOWN, 8, true>(a1, b1, a2, b2, a1, b1, p, st);
+}
+
+extern "C" HYC_API int hyc_linear_lora_save_fwd_tcgen05(
+    const void* x, const void* w, int T, int K, int N,
+    const void* xa, const void* bt, int64_t bt_ld_col, int64_t bt_ld_r,
+    const void* scale, void* q_out, void* y, void* main_or_null, int q_bit, int* status, void* stream) {
+  if (!x || !w || !scale || !q_out || !y || !status) return HYC_ERR_NULL;
+  if ((xa != nullptr) != (bt != nullptr)) return HYC_ERR_NULL;
+  if (q_bit != 2 && q_bit != 4 && q_bit != 8) return HYC_ERR_QBIT;
+  if (T <= 0 || N <= 0 || K <= 0 || N % BN != 0 || K % BK != 0) return HYC_ERR_SHAPE;
+  if (!aligned(x, 16) || !aligned(w, 16) || !aligned(y, 16) || !aligned(q_out, 16) || (xa && !aligned(xa, 16)) ||
+      (main_or_null && !aligned(main_or_null, 16))) return HYC_ERR_ALIGN;
+  CUtensorMap a1, b1;
+  if (!make_map(&a1, x, T, K, BM) || !make_map(&b1, w, N, K, 64)) return HYC_ERR_UNSUPPORTED;
+  Params p = {};
+  p.M = T; p.N = N; p.K1 = K; p.K2 = 0; p.K3 = 0; p.epi = EPI_STORE; p.q_bit = q_bit;
+  p.l0 = make_term(xa, bt, bt_ld_col, bt_ld_r);
+  p.l1 = make_term(nullptr, nullptr, 0, 0);
+  p.l2 = make_term(nullptr, nullptr, 0, 0);
+  p.out0 = (__nv_bfloat16*)y;
+  p.dbg1 = (__nv_bfloat16*)main_or_null;
+  p.q1 = (uint8_t*)q_out;
+  p.s1 = (const __nv_bfloat16*)scale;
+  p.status = status;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (q_bit == 2) return launch<EPI_STORE, 2, false>(a1, b1, a1, b1, a1, b1, p, st);
+  if (q_bit == 4) return launch<EPI_STORE, 4, false>(a1, b1, a1, b1, a1, b1, p, st);
+  return launch<EPI_STORE, 8, false>(a1, b1, a1, b1, a1, b1, p, st);
 }

@@ -67,6 +67,26 @@ def gemm(a, b, *, b_is_kn=False, a2=None, b2=None, a3=None, b3=None, lora0=None,
     return d
 
 
+def linear_lora_save(x, w, a, b, scale, q_bit, *, want_main=False, status=None):
+    """A LoRA projection with the save of its main branch in the GEMM epilogue (steady state of the q/k/v/o
+    projections): x [T,K], w [N,K], a = lora_A.weight [r,K], b = lora_B.weight [N,r], scale [N] ->
+    (y [T,N], q_main [T, N*q_bit/8], xa [T,r][, main])."""
+    require_cuda(x, w, a, b, scale)
+    T, K = x.shape
+    N = w.shape[0]
+    xa = (x @ a.t()).contiguous()
+    dev = x.device
+    y = torch.empty((T, N), dtype=BF16, device=dev)
+    qm = torch.empty((T, N * q_bit // 8), dtype=torch.uint8, device=dev)
+    main = torch.empty((T, N), dtype=BF16, device=dev) if want_main else None
+    st = status if status is not None else _status_tensor(dev)
+    sc = scale.to(BF16).reshape(-1).contiguous()
+    check(lib.hyc_linear_lora_save_fwd_tcgen05(ptr(x), ptr(w), T, K, N, ptr(xa), ptr(b.contiguous()), b.shape[1], 1,
+                                               ptr(sc), ptr(qm), ptr(y), ptr(main), q_bit, ptr(st), stream_of(x)),
+          "hyc_linear_lora_save_fwd_tcgen05")
+    return (y, qm, xa, main) if want_main else (y, qm, xa)
+
+
 def lora_grad_a(q, scale, gm, r2, q_bit):
     """out [r2, H] = gm[:, :r2]^T @ dequant(q, scale), the packed activation de-quantized inside the kernel.
     q [T, H*q_bit/8] uint8, scale [H] bf16, gm [T, >= r2] bf16 (row stride a multiple of 8)."""

@@ -225,6 +225,25 @@ def decompression_dequantization(q, s, quantize_bit=8, is_head=False, num_heads=
     return hidden_to_head_shape(x, num_heads=num_heads) if is_head else x
 
 
+def decompression_dequantization_lora_add(q, s, x_lora_a, w_lora_b, quantize_bit=8):
+    """``decompression_dequantization(q, s, quantize_bit) + x_lora_a @ w_lora_b`` in one kernel (no counterpart
+    in the reference, which runs the two steps: fused_llama_layer_intra_inter_full_fuse.py:416-452).
+    q [B, M, N*bit/8], s [.., N], x_lora_a [B, M, 16], w_lora_b [16, N] (``lora_B.weight.T``) -> [B, M, N] bf16."""
+    from ._fused_common import lora_b_transposed
+    require_cuda(q, s, x_lora_a, w_lora_b)
+    _check_q(quantize_bit)
+    B, M, _ = q.shape
+    N = s.shape[-1]
+    sc = _scale_vec(s, N)
+    xa = x_lora_a.to(BF16).contiguous()
+    bt = lora_b_transposed(w_lora_b)
+    y = torch.empty((B, M, N), dtype=BF16, device=q.device)
+    if B * M:
+        check(lib.hyc_dequant_lora_add(ptr(q.contiguous()), ptr(sc), ptr(xa), ptr(bt), ptr(y), B * M, N, xa.shape[-1],
+                                       quantize_bit, stream_of(q)), "hyc_dequant_lora_add")
+    return y
+
+
 def compression_quantization_with_zero_point(x, s, z, quantize_bit=8, dtype=torch.bfloat16):
     """compress_function.py:245-275."""
     return _quant(x, s, quantize_bit, z=z)[0]

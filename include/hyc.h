@@ -160,6 +160,13 @@ int hyc_fused_lora_silu_hadamard_bwd(const void* xa1, const void* bt1, const voi
                                      const void* grad_o, void* o, void* grad_gate, void* grad_up,
                                      int64_t rows, int N, int R, int q_bit, void* stream);
 
+/* De-quantize + LoRA re-add: y = bf16( decompression_dequantization(q, scale) + bf16(xa * bt^T) ), the
+ * backward-side reconstruction of a LoRA projection whose main branch was saved as codes (q/k/v:
+ * fused_llama_layer_intra_inter_full_fuse.py:416-452, `decompression_dequantization` then `+ x_lora_a @ w_lora_b`).
+ * q [rows, N*q_bit/8], scale [N] bf16, xa [rows, 16] bf16, bt [N, 16] bf16, y [rows, N] bf16.  N % 32 == 0. */
+int hyc_dequant_lora_add(const void* q, const void* scale, const void* xa, const void* bt,
+                         void* y, int64_t rows, int N, int R, int q_bit, void* stream);
+
 /* ---- producers / consumers of the saved tensors ----------------------------------------- */
 
 /* rmsnorm_forward / rmsnorm_backward (operators/rmsnorm_kernels.py:10-54, 58-113, wrappers
@@ -212,6 +219,19 @@ int hyc_gemm_bf16_tcgen05(const void* A, const void* B, int M, int N, int K, int
                           const void* xa0, const void* bt0, int64_t bt0_ld_col, int64_t bt0_ld_r,
                           const void* xa1, const void* bt1, int64_t bt1_ld_col, int64_t bt1_ld_r,
                           const void* residual, void* D, int* status, void* stream);
+
+/* A LoRA projection with the save of its main branch in the GEMM epilogue (the q/k/v/o projections of the
+ * attention half: `lora_forward` followed by `compression_pack_quant_base(x=q_main, ...)`,
+ * fused_llama_layer_intra_inter_full_fuse.py:112-142; models/utils/compute_utils.py:18-25):
+ *   main = bf16(x * w^T)   q_out = quantize + pack(main, scale)   y = bf16(main + bf16(xa * bt^T))
+ * x [T,K], w [N,K] (nn.Linear layout), xa [T,16] = x * A^T (or NULL: no LoRA term), bt element (col, r) at
+ * bt[col*bt_ld_col + r*bt_ld_r], scale [N] bf16 (calibrated; during calibration run hyc_gemm_bf16_tcgen05, the
+ * statistics and hyc_quant_pack instead), q_out [T, N*q_bit/8], y [T,N]; main_or_null receives the bf16 main
+ * branch for inspection.  N % 256 == 0, K % 64 == 0. */
+int hyc_linear_lora_save_fwd_tcgen05(const void* x, const void* w, int T, int K, int N,
+                                     const void* xa, const void* bt, int64_t bt_ld_col, int64_t bt_ld_r,
+                                     const void* scale, void* q_out, void* y, void* main_or_null, int q_bit,
+                                     int* status, void* stream);
 
 /* gate/up projections and triton_fuse_silu_forward in one kernel
  * (fused_llama_layer_intra_inter_full_fuse.py:218-235 + triton_fuse_lora_silu_hadamard_forward_kernels.py):

@@ -150,6 +150,34 @@ def test_rmsnorm_fused_with_saves(ops, q, shape):
     assert torch.equal(dx_r, dx0 + res)
 
 
+@pytest.mark.parametrize("q", (2, 4, 8))
+@pytest.mark.parametrize("shape", [(1, 5, 32), (2, 33, 96), (1, 300, 4096), (1, 17, 11008)])
+def test_dequant_lora_add(ops, q, shape):
+    """decompression_dequantization + LoRA re-add in one kernel: bit-exact against the oracle's de-quantizer
+    followed by a bf16 add of the bf16 LoRA term computed by the same tensor-core product as the fused kernels
+    (checked here against fp32 within one bf16 rounding)."""
+    from hyc_lora_release_b200.operators import compress_function as cf
+    B, M, N = shape
+    g = torch.Generator().manual_seed(sum(shape) + q)
+    x = torch.randn(B, M, N, generator=g).bfloat16()
+    xa = torch.randn(B, M, 16, generator=g).bfloat16()
+    b = (torch.randn(16, N, generator=g) * 0.05).bfloat16()
+    s = oracle.ref_scale_per_channel(x, q)
+    s = torch.where(s == 0, torch.tensor(1e-3, dtype=torch.bfloat16), s)
+    pk = oracle.ref_compress(x, s, q)
+    y = cf.decompression_dequantization_lora_add(pk.to(DEV), s.to(DEV), xa.to(DEV), b.to(DEV), q)
+    xh = oracle.ref_decompress(pk, s, q)
+    lora = (xa.float() @ b.float()).to(torch.bfloat16)
+    ref = (xh.float() + lora.float()).to(torch.bfloat16)
+    yc = y.cpu()
+    mism = (yc != ref)
+    # the only freedom is the summation order of the rank-16 product before its bf16 rounding
+    assert mism.float().mean() < 2e-3 and close(y, ref, rel=4e-3)
+    plain = cf.decompression_dequantization(pk.to(DEV), s.to(DEV), q)
+    zero = cf.decompression_dequantization_lora_add(pk.to(DEV), s.to(DEV), torch.zeros_like(xa).to(DEV), b.to(DEV), q)
+    assert torch.equal(zero, plain)
+
+
 @pytest.mark.parametrize("shape", [(1, 2, 8, 8), (2, 3, 100, 104), (1, 4, 512, 512), (1, 1, 16, 4096)])
 def test_softmax_backward(ops, shape):
     _, _, _, sm = ops

@@ -160,6 +160,30 @@ def test_gateup_and_graddown_epilogues(mlp, q):
 
 
 @pytest.mark.parametrize("q", (2, 4, 8))
+def test_linear_lora_save_epilogue(mlp, q):
+    """LoRA projection with the quantized save of its main branch in the epilogue: codes bit-exact against the
+    oracle quantizer on the emitted bf16 main branch, y and main within tolerance of fp32."""
+    from hyc_lora_release_b200.operators import compress_function as cf
+    g = torch.Generator().manual_seed(90 + q)
+    T, K, N, R = 300, 512, 768, 16
+    x = _randn(g, T, K)
+    w, a, b = _randn(g, N, K, scale=0.05), _randn(g, R, K, scale=0.05), _randn(g, N, R, scale=0.05)
+    main_ref = x.float() @ w.float().t()
+    scale = oracle.ref_scale_per_channel(main_ref.to(BF16)[None], q).reshape(-1)
+    scale = torch.where(scale == 0, torch.tensor(1e-3, dtype=BF16), scale)
+    st = torch.zeros(1, dtype=torch.int32, device=DEV)
+    y, qm, xa, main = mlp.linear_lora_save(x.to(DEV), w.to(DEV), a.to(DEV), b.to(DEV), scale.to(DEV), q,
+                                           want_main=True, status=st)
+    mlp.check_status(st, "linear_lora_save")
+    assert close(main, main_ref, rel=4e-3)
+    assert torch.equal(qm.cpu(), oracle.ref_compress(main.cpu()[None], scale[None], q)[0])
+    assert torch.equal(qm, cf.compression_quantization(main[None], scale.to(DEV), q)[0])
+    y_ref = (main.cpu().float() + (xa.cpu().float() @ b.float().t()).to(BF16).float()).to(BF16)
+    assert close(y, y_ref.float(), rel=4e-3)
+    assert close(y, main_ref + (x.float() @ a.float().t()) @ b.float().t())
+
+
+@pytest.mark.parametrize("q", (2, 4, 8))
 def test_mlp_block_forward_backward(mlp, q):
     g = torch.Generator().manual_seed(7 + q)
     B, M, H, I = 2, 128, 512, 1024
