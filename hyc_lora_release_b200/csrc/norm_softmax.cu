@@ -36,18 +36,29 @@ __device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
   return make_uint4(pack_bf16x2_rn(f[0], f[1]), pack_bf16x2_rn(f[2], f[3]), pack_bf16x2_rn(f[4], f[5]), pack_bf16x2_rn(f[6], f[7]));
 }
 
+template <int NV>
 __global__ void __launch_bounds__(kNormThreads)
 rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w, float eps,
                    __nv_bfloat16* __restrict__ y, float* __restrict__ rstd, int64_t rows, int N) {
   const int nvec = N / 8;
-  for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
-    uint4 xv[kNormMaxVec];
-    float ss = 0.f;
+  // NV octets per thread; the next row of the block is in flight while the current one is reduced and written
+  uint4 xnext[NV];
 #pragma unroll
-    for (int i = 0; i < kNormMaxVec; ++i) {
+  for (int i = 0; i < NV; ++i) {
+    const int v = threadIdx.x + i * kNormThreads;
+    xnext[i] = make_uint4(0u, 0u, 0u, 0u);
+    if (v < nvec && (int64_t)blockIdx.x < rows) xnext[i] = ld_stream_v4(x + (int64_t)blockIdx.x * N + 8 * v);
+  }
+  for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
+    uint4 xv[NV];
+    float ss = 0.f;
+    const int64_t nrow = row + gridDim.x;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
       const int v = threadIdx.x + i * kNormThreads;
+      xv[i] = xnext[i];
       if (v < nvec) {
-        xv[i] = ld_stream_v4(x + row * N + 8 * v);
+        if (nrow < rows) xnext[i] = ld_stream_v4(x + nrow * N + 8 * v);
         float f[8]; unpack8(xv[i], f);
 #pragma unroll
         for (int e = 0; e < 8; ++e) ss = fmaf(f[e], f[e], ss);
@@ -57,7 +68,7 @@ rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
     const float rs = 1.f / sqrtf(var + eps);
     if (threadIdx.x == 0) rstd[row] = rs;
 #pragma unroll
-    for (int i = 0; i < kNormMaxVec; ++i) {
+    for (int i = 0; i < NV; ++i) {
       const int v = threadIdx.x + i * kNormThreads;
       if (v < nvec) {
         float f[8], wf[8];
@@ -137,7 +148,7 @@ __device__ __forceinline__ void build_full_map(int16_t* s_map, int N, const int6
 // 4096) the per-column quantizer constants and the norm weights of the thread's octets stay in registers
 // across rows; wider rows form them on the fly.
 template <int QBIT, int NV>
-__global__ void __launch_bounds__(kNormThreads)
+__global__ void __launch_bounds__(kNormThreads, NV <= 2 ? 3 : 1)
 rmsnorm_fwd_save_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w, float eps,
                         const __nv_bfloat16* __restrict__ scale_x, const int64_t* __restrict__ oidx, int k,
                         const __nv_bfloat16* __restrict__ scale_y,
@@ -171,14 +182,25 @@ rmsnorm_fwd_save_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16
       wv[i] = ok ? *reinterpret_cast<const uint4*>(w + 8 * v) : one;
     }
   }
+  // the next row of the block is fetched while the current one is reduced and written (a block holds one
+  // row at a time, so without this every row pays a full memory latency)
+  uint4 xnext[NV];
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int v = threadIdx.x + i * kNormThreads;
+    xnext[i] = make_uint4(0u, 0u, 0u, 0u);
+    if (v < nvec && (int64_t)blockIdx.x < rows) xnext[i] = ld_stream_v4(x + (int64_t)blockIdx.x * N + 8 * v);
+  }
   for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
     uint4 xv[NV];
     float ss = 0.f;
+    const int64_t nrow = row + gridDim.x;
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
       const int v = threadIdx.x + i * kNormThreads;
+      xv[i] = xnext[i];
       if (v < nvec) {
-        xv[i] = ld_stream_v4(x + row * N + 8 * v);
+        if (nrow < rows) xnext[i] = ld_stream_v4(x + nrow * N + 8 * v);
         float f[8]; unpack8(xv[i], f);
 #pragma unroll
         for (int e = 0; e < 8; ++e) ss = fmaf(f[e], f[e], ss);
@@ -362,8 +384,12 @@ extern "C" HYC_API int hyc_rmsnorm_fwd(const void* x, const void* w, float eps, 
   if (!aligned(x, 16) || !aligned(w, 16) || !aligned(y, 16)) return HYC_ERR_ALIGN;
   if (rows == 0) return HYC_OK;
   int64_t grid = rows < (int64_t)kNumSMs * 8 ? rows : (int64_t)kNumSMs * 8;
-  rmsnorm_fwd_kernel<<<(int)grid, kNormThreads, 0, (cudaStream_t)stream>>>(
-      (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, eps, (__nv_bfloat16*)y, rstd, rows, N);
+  if (N <= 2 * kNormThreads * 8)
+    rmsnorm_fwd_kernel<2><<<(int)grid, kNormThreads, 0, (cudaStream_t)stream>>>(
+        (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, eps, (__nv_bfloat16*)y, rstd, rows, N);
+  else
+    rmsnorm_fwd_kernel<kNormMaxVec><<<(int)grid, kNormThreads, 0, (cudaStream_t)stream>>>(
+        (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, eps, (__nv_bfloat16*)y, rstd, rows, N);
   HYC_CHECK_LAUNCH();
   return HYC_OK;
 }

@@ -94,6 +94,33 @@ def test_fused_linearity_at_full_width(ops):
     assert torch.equal(gu2, gu * 2)
 
 
+def test_fused_unaligned_tensors_take_the_narrow_kernel(ops):
+    """Tensors that are only 4-byte aligned (a view into a larger buffer) go through the fragment-layout kernel;
+    its results are bit-identical to the wide kernel's."""
+    from hyc_lora_release_b200._lib import check, lib, ptr, stream_of
+    import ctypes
+    g = torch.Generator().manual_seed(3)
+    rows, N, q = 45, 160, 4
+    x1, x2 = torch.randn(rows, N, generator=g).bfloat16(), torch.randn(rows, N, generator=g).bfloat16()
+    xa1, xa2 = torch.randn(rows, 16, generator=g).bfloat16(), torch.randn(rows, 16, generator=g).bfloat16()
+    bt1, bt2 = (torch.randn(N, 16, generator=g) * 0.05).bfloat16(), (torch.randn(N, 16, generator=g) * 0.05).bfloat16()
+    s1, s2 = oracle.ref_scale_per_channel(x1[None], q).reshape(-1), oracle.ref_scale_per_channel(x2[None], q).reshape(-1)
+    d = lambda t: t.to(DEV)
+    xa1d, xa2d, bt1d, bt2d, s1d, s2d, x2d = map(d, (xa1, xa2, bt1, bt2, s1, s2, x2))
+    outs = []
+    for shift in (0, 2):        # elements: 0 -> 16-byte aligned, 2 -> 4-byte aligned
+        base = torch.zeros(rows * N + 8, dtype=torch.bfloat16, device=DEV)
+        x1d = base[shift:shift + rows * N].view(rows, N)
+        x1d.copy_(x1)
+        q1 = torch.empty(rows, N // 2, dtype=torch.uint8, device=DEV); q2 = torch.empty_like(q1)
+        o = torch.empty(rows, N, dtype=torch.bfloat16, device=DEV)
+        check(lib.hyc_fused_lora_silu_hadamard_fwd(ptr(xa1d), ptr(bt1d), ctypes.c_void_p(x1d.data_ptr()), ptr(s1d), ptr(xa2d),
+                                                   ptr(bt2d), ptr(x2d), ptr(s2d), ptr(q1), ptr(q2), ptr(o), rows, N, 16, q,
+                                                   stream_of(o)), "fwd")
+        outs.append((q1, q2, o))
+    assert all(torch.equal(a, b) for a, b in zip(outs[0], outs[1]))
+
+
 @pytest.mark.parametrize("shape", [(3, 64), (2, 7, 4096), (1, 33, 11008), (5, 16384)])
 def test_rmsnorm(ops, shape):
     _, _, rn, _ = ops
