@@ -308,6 +308,10 @@ def run_profile(args):
         print(json.dumps({"profile": "mlp", "steps": args.steps, "ms_per_step": line["ms_per_step"],
                           "tokens_per_s": line["value"], "tflops": line["roofline"]["achieved"]}))
         return
+    if args.profile == "fused":
+        line = fused_elementwise_workload(dev, peaks()[0])
+        print(json.dumps({"profile": "fused", "forward": line["forward"], "backward": line["backward"]}))
+        return
     if args.profile == "attn_topk":
         maps = [make_map(1000 + i, dev) for i in range(NBUF)]
         nbytes = 2 * algo_bytes(MAP_SHAPE, QBIT, RATIO)
@@ -390,7 +394,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-extras", action="store_true", help="skip the secondary workloads and the CPU sample")
-    ap.add_argument("--profile", default=None, choices=["attn_topk", "channel_q4", "channel_q2", "channel_q8", "mlp"],
+    ap.add_argument("--profile", default=None, choices=["attn_topk", "channel_q4", "channel_q2", "channel_q8", "mlp", "fused"],
                     help="run only W+K steps of one workload and print timing (for a profiler capture)")
     args = ap.parse_args()
     if args.warmup < 3:
