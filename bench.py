@@ -29,7 +29,7 @@ QBIT = 4
 NBUF = 4          # distinct input/output sets rotated between steps (4 x 64 MiB in, > L2)
 # dram__bytes_read.sum + dram__bytes_write.sum of ONE launch on this workload, from the ncu capture that
 # profiles/topk_lane_attention_map_4x32x512x512_q4.md summarises (bytes)
-NCU_TRAFFIC = {"hyc::topk_lane_compress_kernel<4,8>": 72.2e6, "hyc::topk_lane_restore_kernel<4,8>": 36.1e6}
+NCU_TRAFFIC = {"hyc::topk_lane_compress_kernel<4,8>": 72.2e6, "hyc::topk_lane_restore_kernel<4,8,false>": 36.1e6}
 
 
 def peaks():
@@ -472,7 +472,7 @@ def main():
     t_c = graph_avg(lambda j: cf.compression_softmax_topk(maps[j], RATIO, QBIT, out=handles[j]))
     t_d = graph_avg(lambda j: handles[j].to_dense(out=dense[j]))
     dom, t_dom = (("hyc::topk_lane_compress_kernel<4,8>", t_c) if t_c >= t_d
-                  else ("hyc::topk_lane_restore_kernel<4,8>", t_d))
+                  else ("hyc::topk_lane_restore_kernel<4,8,false>", t_d))
     achieved = one_way / t_dom / 1e9
 
     # end to end: pinned host map -> device -> compress -> decompress -> pinned host map, every step through the
