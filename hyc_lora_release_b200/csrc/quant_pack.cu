@@ -341,6 +341,18 @@ unpack_dequant_kernel(const uint8_t* __restrict__ q, int64_t rows, int N,
   }
 
   const int64_t n_groups = (rows + kDeqUnroll - 1) / kDeqUnroll;
+  // 2- and 8-bit codes: the codes of the block's next row group are in flight while the current one is expanded
+  // and stored (measured: +3 % and +6 %; the 4-bit instantiation loses 18 % with it and loads in place)
+  constexpr bool PIPE = QBIT != 4;
+  uint2 pnext[PIPE ? kDeqUnroll : 1];
+  if constexpr (PIPE) {
+#pragma unroll
+    for (int r = 0; r < kDeqUnroll; ++r) {
+      const int64_t row = (int64_t)blockIdx.y * kDeqUnroll + r;
+      pnext[r] = make_uint2(0u, 0u);
+      if (active && row < rows) pnext[r] = ld_stream_v2(q + row * qld + 8 * (int64_t)ct);
+    }
+  }
   for (int64_t g = blockIdx.y; g < n_groups; g += gridDim.y) {
     const int64_t r0 = g * kDeqUnroll;
     // the lane's share of the saved outlier values, fetched ahead of the de-quantization
@@ -353,11 +365,20 @@ unpack_dequant_kernel(const uint8_t* __restrict__ q, int64_t rows, int N,
           if (t < lo.n && (r0 + r) < rows) ov[r][t] = oin[(r0 + r) * k + lo.j[t]];
     }
     uint2 p[kDeqUnroll];
-    if (active) {
+    if constexpr (PIPE) {
+      const int64_t n0 = (g + gridDim.y) * kDeqUnroll;
 #pragma unroll
       for (int r = 0; r < kDeqUnroll; ++r) {
-        p[r] = make_uint2(0u, 0u);
-        if ((r0 + r) < rows) p[r] = ld_stream_v2(q + (r0 + r) * qld + 8 * (int64_t)ct);
+        p[r] = pnext[r];
+        if (active && (n0 + r) < rows) pnext[r] = ld_stream_v2(q + (n0 + r) * qld + 8 * (int64_t)ct);
+      }
+    } else {
+      if (active) {
+#pragma unroll
+        for (int r = 0; r < kDeqUnroll; ++r) {
+          p[r] = make_uint2(0u, 0u);
+          if ((r0 + r) < rows) p[r] = ld_stream_v2(q + (r0 + r) * qld + 8 * (int64_t)ct);
+        }
       }
     }
 #pragma unroll
