@@ -29,7 +29,7 @@ QBIT = 4
 NBUF = 4          # distinct input/output sets rotated between steps (4 x 64 MiB in, > L2)
 # dram__bytes_read.sum + dram__bytes_write.sum of ONE launch on this workload, from the ncu capture that
 # profiles/topk_lane_attention_map_4x32x512x512_q4.md summarises (bytes)
-NCU_TRAFFIC = {"hyc::topk_lane_compress_kernel<4,8>": 72.2e6, "hyc::topk_lane_restore_kernel<4,8,false>": 36.1e6}
+NCU_TRAFFIC = {"hyc::topk_lane_compress_kernel<4,8>": 70.0e6, "hyc::topk_lane_restore_kernel<4,8,false>": 35.9e6}
 
 
 def peaks():

@@ -23,10 +23,15 @@
 
 namespace hyc {
 
+// sum over the LPR lanes of a row.  A whole warp uses the hardware reduction; for a part of a warp
+// __reduce_add_sync with a partial mask is expanded into some twenty instructions, log2(LPR) butterfly
+// steps are far cheaper (measured: 4.4 M of the kernel's 31 M warp instructions, 8 us of 47)
 template <int LPR>
-__device__ __forceinline__ int seg_add(unsigned segmask, int v) {
-  if (LPR == 1) return v;
-  return (int)__reduce_add_sync(segmask, (unsigned)v);
+__device__ __forceinline__ int seg_add(int v) {
+  if (LPR == 32) return (int)__reduce_add_sync(kFull, (unsigned)v);
+#pragma unroll
+  for (int o = 1; o < LPR; o <<= 1) v += __shfl_xor_sync(kFull, v, o);
+  return v;
 }
 template <int LPR>
 __device__ __forceinline__ int seg_excl_scan(int v, int lr) {
@@ -57,7 +62,6 @@ topk_lane_compress_kernel(const __nv_bfloat16* __restrict__ a, int64_t rows, int
   constexpr int64_t QLD = (int64_t)S * QBIT / 8;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
   const int lr = lane & (LPR - 1), rw = lane / LPR;
-  const unsigned segmask = (LPR == 32) ? kFull : (((1u << LPR) - 1u) << (lane & ~(LPR - 1)));
   __shared__ __align__(16) uint32_t s_x[8][32 * 32];          // the warp's rows, 128 bytes per lane
   __shared__ uint32_t s_out[8][kLaneStageEntries];            // staged (column << 16 | value) words
   uint32_t* sx = s_x[warp] + lane * 32;
@@ -125,7 +129,7 @@ topk_lane_compress_kernel(const __nv_bfloat16* __restrict__ a, int64_t rows, int
 #pragma unroll
       for (int b = 14; b >= 0; --b) {
         const uint32_t x0 = m[b] & A0, x1 = m[16 + b] & A1;
-        const int tot = seg_add<LPR>(segmask, __popc(x0) + __popc(x1));
+        const int tot = seg_add<LPR>(__popc(x0) + __popc(x1));
         const uint32_t drop = (tot >= rem) ? 0u : kFull;   // all ones: the threshold has a 0 here, the ones are above it
         G0 |= x0 & drop; G1 |= x1 & drop;
         A0 &= m[b] ^ drop; A1 &= m[16 + b] ^ drop;
