@@ -42,6 +42,8 @@ SIGNATURES = {
     "hyc_rmsnorm_fwd_save": (_i, [_p, _p, _f, _l, _i, _p, _p, _i, _p, _p, _p, _p, _p, _p, _i, _p]),
     "hyc_rmsnorm_bwd_packed": (_i, [_p, _p, _p, _p, _i, _p, _p, _p, _p, _p, _l, _i, _i, _p]),
     "hyc_softmax_bwd": (_i, [_p, _p, _p, _l, _i, _p]),
+    "hyc_softmax_fwd_scale_mask": (_i, [_p, _f, _p, _l, _l, _l, _i, _i, _p, _l, _i, _p]),
+    "hyc_rope": (_i, [_p, _l, _p, _l, _p, _p, _l, _i, _l, _i, _i, _i, _i, _p]),
     "hyc_lora_grad_a_workspace_bytes": (_z, [_i, _i, _i]),
     "hyc_lora_grad_a_dequant": (_i, [_p, _p, _p, _l, _i, _i, _i, _i, _p, _p, _z, _p]),
     "hyc_gemm_bf16_tcgen05": (_i, [_p, _p, _i, _i, _i, _i, _p, _p, _i, _p, _p, _i,

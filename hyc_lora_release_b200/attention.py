@@ -1,0 +1,292 @@
+"""Attention half of the HyC-LoRA fused decoder layer.
+
+Mirrors the attention part of ``FusedLlamaLayerIntraInterFullFuseFunc.forward/backward``
+(models/llama/fused_llama_layer_intra_inter_full_fuse.py:99-201 and :400-493; the Mistral twin differs only
+in its grouped key/value heads, which are covered) with plain bf16 frozen weights:
+
+  forward : RMSNorm fused with the saves of x (outlier channels + codes) and x_norm (codes) -> q/k/v
+            projections on the tcgen05 GEMM whose epilogue also packs the codes of the main branch ->
+            rotary embedding in place -> scores (library batched GEMM) -> scale + mask + softmax in one pass
+            -> save of the probability map (per-row top-k + 4-bit groups, or the reference's threshold
+            prune) -> P.V (library batched GEMM) -> save of o -> o projection with the LoRA product as one
+            more K block and the residual in the GEMM epilogue;
+  backward: o projection backward (LoRA-A gradient straight from the packed o) -> restored map -> grad_v,
+            grad_a -> restore fused with the softmax backward -> q, k rebuilt by de-quantize + LoRA re-add +
+            rotary -> grad_q, grad_k -> inverse rotary -> LoRA gradients of q/k/v (A side from the packed
+            x_norm in one pass for the three adapters) -> grad_x as ONE GEMM over the three K segments ->
+            RMSNorm backward from the packed x with the residual gradient added in the same pass.
+
+Weights use the nn.Linear layout ([out, in]); LoRA factors are ``lora_A.weight`` [r, in] and
+``lora_B.weight`` [out, r].  The two batched attention products are plain library GEMMs (torch.matmul).
+"""
+import math
+from dataclasses import dataclass, field
+
+import torch
+
+from ._lib import require_cuda
+from .mlp import _status_tensor, gemm, linear_lora_save, lora_grad_a
+from .operators import compress_function as cf
+from .operators.rmsnorm_kernels import rmsnorm_backward_packed, rmsnorm_forward, rmsnorm_forward_save
+from .operators.rope_kernels import rope_inplace
+from .operators.softmax_kernels import softmax_backward, softmax_forward_scale_mask
+
+BF16 = torch.bfloat16
+
+
+@dataclass
+class AttnWeights:
+    """Frozen bf16 weights ([out, in]) and LoRA factors of one attention block."""
+    norm_w: torch.Tensor   # [H]
+    wq: torch.Tensor       # [heads*d, H]
+    wk: torch.Tensor       # [kv_heads*d, H]
+    wv: torch.Tensor       # [kv_heads*d, H]
+    wo: torch.Tensor       # [H, heads*d]
+    aq: torch.Tensor       # q lora_A.weight [r, H]
+    bq: torch.Tensor       # q lora_B.weight [heads*d, r]
+    ak: torch.Tensor
+    bk: torch.Tensor
+    av: torch.Tensor
+    bv: torch.Tensor
+    ao: torch.Tensor       # o lora_A.weight [r, heads*d]
+    bo: torch.Tensor       # o lora_B.weight [H, r]
+
+    def padded(self):
+        """LoRA factors zero-padded to a K of 64 so that a rank-16 product rides along a GEMM as one more K block
+        (rebuilt when a factor changes):
+          ao_cols  [heads*d, 64]  columns 0..15 = Ao^T   (o -> padded LoRA activation of the o projection)
+          bo_cols  [H, 64]        columns 0..15 = Bo     ([N, K] operand of the o projection's LoRA block)
+          ao_rows  [64, heads*d]  rows 0..15 = Ao        ([K, N] operand of grad_o's LoRA block)
+          aqkv_rows [64, H]       rows 0..15 = Aq, 16..31 = Ak, 32..47 = Av ([K, N] operand of grad_x's LoRA block)"""
+        ts = (self.aq, self.ak, self.av, self.ao, self.bo)
+        key = tuple((t.data_ptr(), t._version) for t in ts)
+        if getattr(self, "_pad_key", None) != key:
+            r, D = self.ao.shape
+            H = self.bo.shape[0]
+            dev, dt = self.ao.device, self.ao.dtype
+            ao_rows = torch.zeros(64, D, dtype=dt, device=dev); ao_rows[:r] = self.ao
+            bo_cols = torch.zeros(H, 64, dtype=dt, device=dev); bo_cols[:, :r] = self.bo
+            aqkv = torch.zeros(64, self.aq.shape[1], dtype=dt, device=dev)
+            aqkv[:r] = self.aq; aqkv[r:2 * r] = self.ak; aqkv[2 * r:3 * r] = self.av
+            self._pad = dict(ao_rows=ao_rows, ao_cols=ao_rows.t().contiguous(), bo_cols=bo_cols, aqkv_rows=aqkv)
+            self._pad_key = key
+        return self._pad
+
+
+@dataclass
+class AttnState:
+    """Calibration state of the attention part of a layer (the reference keeps the same entries in
+    ``static_value``, fused_llama_layer_intra_inter_full_fuse.py:557-565).  ``map_mode``: "prune" = the
+    reference's global-threshold prune of the probability map, "topk" = per-row top-k + ``map_q_bit`` groups."""
+    iteration: int = 0
+    iteration_threshold: int = 5
+    q_bit: int = 4
+    layernorm_outlier_ratio: float = 0.005
+    softmax_outlier_ratio: float = 0.05
+    map_mode: str = "topk"
+    map_q_bit: int = 4
+    static_value: dict = field(default_factory=lambda: {
+        'x': {'outlier_channel_index': None, 'scale': None}, 'x_norm_1': {'scale': None},
+        'q': {'scale': None}, 'k': {'scale': None}, 'v': {'scale': None}, 'a': {'outlier': None},
+        'o': {'scale': None}})
+
+
+def _repeat_kv(x, n_rep):
+    """[B, kv, M, d] -> [B, kv * n_rep, M, d] (each key/value head serves n_rep query heads)."""
+    if n_rep == 1:
+        return x
+    b, n, m, d = x.shape
+    return x[:, :, None].expand(b, n, n_rep, m, d).reshape(b, n * n_rep, m, d)
+
+
+def _repeat_kv_backward(g, n_rep):
+    if n_rep == 1:
+        return g
+    b, n, m, d = g.shape
+    return g.reshape(b, n // n_rep, n_rep, m, d).sum(dim=2)
+
+
+def _heads(x2, B, M, n):
+    """[B*M, n*d] (contiguous) -> [B, n, M, d] view."""
+    return x2.view(B, M, n, -1).transpose(1, 2)
+
+
+def _hidden(xh):
+    """[B, n, M, d] -> contiguous [B*M, n*d]."""
+    b, n, m, d = xh.shape
+    return xh.transpose(1, 2).reshape(b * m, n * d)
+
+
+def _project(xn2, w, a, b, q_bit, calib, sv, it, thd, status, B):
+    """One LoRA projection and the save of its main branch -> (y [T,N], q_main, scale, xa [T,r])."""
+    if not calib:
+        scale = sv['scale']
+        y, qm, xa = linear_lora_save(xn2, w, a, b, scale, q_bit, status=status)
+        return y, qm, scale, xa
+    # calibration iterations: the scale depends on the finished main branch
+    main = gemm(xn2, w, status=status)
+    qm, scale = cf.compression_pack_quant_base(main.view(B, main.shape[0] // B, -1), q_bit, 'per-channel', it, thd, sv)
+    xa = (xn2 @ a.t()).contiguous()
+    y = main + xa @ b.t()
+    return y, qm.reshape(main.shape[0], -1), scale, xa
+
+
+def attention_forward(x, w: AttnWeights, state: AttnState, cos, sin, attention_mask, num_heads, head_dim,
+                      num_key_value_heads, eps=1e-5, status=None):
+    """-> (x_medium [B,M,H], saved dict).  Advances the calibration state like the layer does."""
+    require_cuda(x)
+    B, M, H = x.shape
+    T, q = B * M, state.q_bit
+    st = status if status is not None else _status_tensor(x.device)
+    it, thd = state.iteration, state.iteration_threshold
+    calib = it < thd
+    sv = state.static_value
+    n_rep = num_heads // num_key_value_heads
+
+    if calib:
+        x_norm, _, rstd, _, _ = rmsnorm_forward(x, w.norm_w, eps)
+        x_o, x_q, x_idx, x_scale = cf.compression_pack_channel_base(x, state.layernorm_outlier_ratio, q, 'per-channel',
+                                                                    it, thd, sv['x'])
+        xn_q, xn_scale = cf.compression_pack_quant_base(x_norm, q, 'per-channel', it, thd, sv['x_norm_1'])
+    else:
+        x_idx, x_scale, xn_scale = sv['x']['outlier_channel_index'], sv['x']['scale'], sv['x_norm_1']['scale']
+        x_norm, rstd, x_o, x_q, xn_q = rmsnorm_forward_save(x, w.norm_w, eps, q, x_scale, x_idx, xn_scale)
+    xn2 = x_norm.reshape(T, H)
+
+    qy, q_q, q_scale, q_xa = _project(xn2, w.wq, w.aq, w.bq, q, calib, sv['q'], it, thd, st, B)
+    ky, k_q, k_scale, k_xa = _project(xn2, w.wk, w.ak, w.bk, q, calib, sv['k'], it, thd, st, B)
+    vy, v_q, v_scale, v_xa = _project(xn2, w.wv, w.av, w.bv, q, calib, sv['v'], it, thd, st, B)
+    del x_norm, xn2
+
+    rope_inplace(qy.view(B, M, num_heads, head_dim), cos, sin)
+    rope_inplace(ky.view(B, M, num_key_value_heads, head_dim), cos, sin)
+    qh = _heads(qy, B, M, num_heads)
+    kh = _repeat_kv(_heads(ky, B, M, num_key_value_heads), n_rep)
+    vh = _repeat_kv(_heads(vy, B, M, num_key_value_heads), n_rep)
+    scores = torch.matmul(qh, kh.transpose(-2, -1))
+    a = softmax_forward_scale_mask(scores, 1.0 / math.sqrt(head_dim), attention_mask, inplace=True)
+    del scores
+
+    if state.map_mode == "topk":
+        a_saved = cf.compression_softmax_topk(a, state.softmax_outlier_ratio, state.map_q_bit)
+        a_thr = None
+    elif state.map_mode == "prune":
+        a_saved, a_thr = cf.compression_pack_softmax_base(a, state.softmax_outlier_ratio, it, thd, sv['a'])
+    else:
+        raise ValueError("map_mode must be 'topk' or 'prune'")
+    o2 = _hidden(torch.matmul(a, vh))
+    a_shape = tuple(a.shape)
+    del a
+
+    pad = w.padded()
+    o_xa64 = o2 @ pad["ao_cols"]
+    x_medium = gemm(o2, w.wo, a2=o_xa64, b2=pad["bo_cols"], residual=x.reshape(T, H).to(BF16).contiguous(), status=st)
+    o_q, o_scale = cf.compression_pack_quant_base(o2.view(B, M, -1), q, 'per-channel', it, thd, sv['o'])
+
+    if calib:
+        sv['x'] = cf.update_dict(sv['x'], {'outlier_channel_index': x_idx, 'scale': x_scale}, it)
+        sv['x_norm_1'] = cf.update_dict(sv['x_norm_1'], {'scale': xn_scale}, it)
+        sv['q'] = cf.update_dict(sv['q'], {'scale': q_scale}, it)
+        sv['k'] = cf.update_dict(sv['k'], {'scale': k_scale}, it)
+        sv['v'] = cf.update_dict(sv['v'], {'scale': v_scale}, it)
+        if a_thr is not None:
+            sv['a'] = cf.update_dict(sv['a'], {'outlier': a_thr}, it)
+        sv['o'] = cf.update_dict(sv['o'], {'scale': o_scale}, it)
+    state.iteration += 1
+
+    saved = dict(rstd=rstd, x_o=x_o, x_q=x_q, x_scale=x_scale, x_idx=x_idx, xn_q=xn_q, xn_scale=xn_scale,
+                 q_q=q_q, q_scale=q_scale, k_q=k_q, k_scale=k_scale, v_q=v_q, v_scale=v_scale,
+                 q_xa=q_xa, k_xa=k_xa, v_xa=v_xa, a_saved=a_saved, a_shape=a_shape, map_mode=state.map_mode,
+                 o_q=o_q.reshape(T, -1), o_scale=o_scale, o_xa=o_xa64[:, :w.ao.shape[0]], q_bit=q, shape=(B, M, H),
+                 cos=cos, sin=sin, num_heads=num_heads, head_dim=head_dim, num_key_value_heads=num_key_value_heads)
+    return x_medium.reshape(B, M, H), saved
+
+
+def _rebuild(codes, scale, xa, b, q_bit):
+    """De-quantized main branch + LoRA product of a projection, [T, N] (b = lora_B.weight [N, r])."""
+    T = codes.shape[0]
+    return cf.decompression_dequantization_lora_add(codes.view(1, T, -1), scale, xa.view(1, T, -1), b.t(), q_bit).view(T, -1)
+
+
+def _vec(s):
+    return s.to(BF16).reshape(-1).contiguous()
+
+
+def attention_backward(grad_medium, saved, w: AttnWeights, status=None, on_lora_grads=None):
+    """-> dict(grad_x, grad_aq, grad_bq, grad_ak, grad_bk, grad_av, grad_bv, grad_ao, grad_bo), the LoRA
+    gradients in the layout of the weights they belong to ([r, in] / [out, r]).  ``on_lora_grads(dict)`` is
+    called once the eight LoRA gradients are enqueued (before the grad_x GEMM and the RMSNorm backward)."""
+    B, M, H = saved['shape']
+    T, q = B * M, saved['q_bit']
+    nh, d, nkv = saved['num_heads'], saved['head_dim'], saved['num_key_value_heads']
+    n_rep = nh // nkv
+    cos, sin = saved['cos'], saved['sin']
+    dev = grad_medium.device
+    st = status if status is not None else _status_tensor(dev)
+    g = grad_medium.to(BF16).reshape(T, H).contiguous()
+    pad = w.padded()
+    r = w.ao.shape[0]
+
+    # ---- o projection
+    gm64 = g @ pad["bo_cols"]                                # [T, 64]; first r columns = g @ Bo
+    grad_bo = g.t() @ saved['o_xa']                          # [H, r]
+    grad_ao = lora_grad_a(saved['o_q'], _vec(saved['o_scale']), gm64, 16, q)[:r]     # [r, heads*d], o de-quantized in the kernel
+    grad_o2 = gemm(g, w.wo, b_is_kn=True, a2=gm64, b2=pad["ao_rows"], status=st)      # [T, heads*d]
+    grad_oh = _heads(grad_o2, B, M, nh)
+
+    # ---- P.V backward on the restored map
+    m = saved['a_saved']
+    if saved['map_mode'] == "topk":
+        a = m.to_dense()
+    else:
+        a = cf.decompression_softmax(m).reshape(saved['a_shape'])
+    v2 = _rebuild(saved['v_q'], saved['v_scale'], saved['v_xa'], w.bv, q)
+    vh = _repeat_kv(_heads(v2, B, M, nkv), n_rep)
+    grad_vh = _repeat_kv_backward(torch.matmul(a.transpose(-2, -1), grad_oh), n_rep)
+    grad_a = torch.matmul(grad_oh, vh.transpose(-2, -1))
+    del vh, v2
+    # ---- softmax backward (for the top-k form fused with a second restore: the map is not re-read)
+    if saved['map_mode'] == "topk":
+        del a
+        grad_s = m.softmax_backward(grad_a)
+        del grad_a
+    else:
+        grad_s = softmax_backward(a, grad_a)
+        del a
+    grad_s.mul_(1.0 / math.sqrt(d))
+
+    # ---- q, k rebuilt from their codes, rotary re-applied
+    q2 = _rebuild(saved['q_q'], saved['q_scale'], saved['q_xa'], w.bq, q)
+    rope_inplace(q2.view(B, M, nh, d), cos, sin)
+    grad_kh = _repeat_kv_backward(torch.matmul(grad_s.transpose(-2, -1), _heads(q2, B, M, nh)), n_rep)
+    del q2
+    k2 = _rebuild(saved['k_q'], saved['k_scale'], saved['k_xa'], w.bk, q)
+    rope_inplace(k2.view(B, M, nkv, d), cos, sin)
+    grad_qh = torch.matmul(grad_s, _repeat_kv(_heads(k2, B, M, nkv), n_rep))
+    del k2, grad_s
+    grad_q = _hidden(grad_qh)
+    grad_k = _hidden(grad_kh)
+    grad_v = _hidden(grad_vh)
+    rope_inplace(grad_q.view(B, M, nh, d), cos, sin, backward=True)
+    rope_inplace(grad_k.view(B, M, nkv, d), cos, sin, backward=True)
+
+    # ---- q/k/v projections: LoRA gradients, then grad_x_norm as one GEMM over the three K segments
+    gmq = torch.zeros((T, 64), dtype=BF16, device=dev)       # g_q @ Bq | g_k @ Bk | g_v @ Bv side by side
+    gmq[:, :r] = grad_q @ w.bq
+    gmq[:, r:2 * r] = grad_k @ w.bk
+    gmq[:, 2 * r:3 * r] = grad_v @ w.bv
+    ga = lora_grad_a(saved['xn_q'].reshape(T, -1), _vec(saved['xn_scale']), gmq, 48, q)
+    grad_aq, grad_ak, grad_av = ga[:r], ga[r:2 * r], ga[2 * r:3 * r]
+    grad_bq = grad_q.t() @ saved['q_xa']
+    grad_bk = grad_k.t() @ saved['k_xa']
+    grad_bv = grad_v.t() @ saved['v_xa']
+    if on_lora_grads is not None:
+        on_lora_grads(dict(grad_aq=grad_aq, grad_bq=grad_bq, grad_ak=grad_ak, grad_bk=grad_bk, grad_av=grad_av,
+                           grad_bv=grad_bv, grad_ao=grad_ao, grad_bo=grad_bo))
+    lora_x = gmq @ pad["aqkv_rows"]                          # [T, H]: the three LoRA-A back-projections
+    grad_xn = gemm(grad_q, w.wq, b_is_kn=True, a2=grad_k, b2=w.wk, a3=grad_v, b3=w.wv, residual=lora_x, status=st)
+    grad_x = rmsnorm_backward_packed(grad_xn.reshape(B, M, H), saved['x_q'], saved['x_scale'], saved['x_o'],
+                                     saved['x_idx'], w.norm_w, saved['rstd'], q, residual_grad=g.reshape(B, M, H))
+    return dict(grad_x=grad_x, grad_aq=grad_aq, grad_bq=grad_bq, grad_ak=grad_ak, grad_bk=grad_bk,
+                grad_av=grad_av, grad_bv=grad_bv, grad_ao=grad_ao, grad_bo=grad_bo,
+                grad_q=grad_q, grad_k=grad_k, grad_v=grad_v)

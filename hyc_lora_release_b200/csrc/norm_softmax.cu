@@ -373,6 +373,65 @@ softmax_bwd_kernel(const __nv_bfloat16* __restrict__ y, const __nv_bfloat16* __r
   }
 }
 
+
+// Attention probabilities from raw scores in one pass (fused_llama_layer_intra_inter_full_fuse.py:150-160:
+// `s = q @ k^T / sqrt(d)`, `s = s + attention_mask`, `a = softmax(s, dim=-1, dtype=bf16)`), with the
+// reference's rounding points: t = bf16(s * scale), u = bf16(t + mask), fp32 softmax of u, bf16 result.
+// One warp per row, the row in registers (NV chunks of 32 lanes x 8 columns).  The mask is addressed as
+// mask[b * mb + head * mh + m * mr + column] for row = (b * heads + head) * M + m.
+template <int NV>
+__global__ void __launch_bounds__(256)
+softmax_fwd_kernel(const __nv_bfloat16* __restrict__ sc, float scale, const __nv_bfloat16* __restrict__ mask,
+                   int64_t mb, int64_t mh, int64_t mr, int heads, int M, __nv_bfloat16* __restrict__ a,
+                   int64_t rows, int S) {
+  const int lane = threadIdx.x & 31;
+  const int nvec = S / 8;
+  for (int64_t row = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5); row < rows; row += (int64_t)gridDim.x * 8) {
+    const int m = (int)(row % M);
+    const int64_t bh = row / M;
+    const __nv_bfloat16* mrow = mask ? mask + (bh / heads) * mb + (bh % heads) * mh + (int64_t)m * mr : nullptr;
+    float u[NV][8];
+    float mx = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int v = lane + 32 * i;
+      if (v < nvec) {
+        unpack8(ld_stream_v4(sc + row * S + 8 * v), u[i]);
+        float mk[8];
+        if (mrow) unpack8(*reinterpret_cast<const uint4*>(mrow + 8 * v), mk);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          float t = bf16bits_to_f32(f32_to_bf16bits_rn(u[i][e] * scale));
+          if (mrow) t = bf16bits_to_f32(f32_to_bf16bits_rn(t + mk[e]));
+          u[i][e] = t;
+          mx = fmaxf(mx, t);
+        }
+      }
+    }
+#pragma unroll
+    for (int of = 16; of > 0; of >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, of));
+    float sum = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i)
+      if (lane + 32 * i < nvec) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) { u[i][e] = __expf(u[i][e] - mx); sum += u[i][e]; }
+      }
+#pragma unroll
+    for (int of = 16; of > 0; of >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, of);
+    const float inv = 1.0f / sum;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int v = lane + 32 * i;
+      if (v < nvec) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) u[i][e] *= inv;
+        st_stream_v4(a + row * S + 8 * v, pack8(u[i]));
+      }
+    }
+  }
+}
+
 }  // namespace hyc
 
 using namespace hyc;
@@ -468,6 +527,24 @@ extern "C" HYC_API int hyc_softmax_bwd(const void* y, const void* g, void* o, in
   if (grid > (int64_t)kNumSMs * 8) grid = (int64_t)kNumSMs * 8;
   softmax_bwd_kernel<<<(int)grid, 256, 0, (cudaStream_t)stream>>>(
       (const __nv_bfloat16*)y, (const __nv_bfloat16*)g, (__nv_bfloat16*)o, rows, S);
+  HYC_CHECK_LAUNCH();
+  return HYC_OK;
+}
+
+extern "C" HYC_API int hyc_softmax_fwd_scale_mask(const void* scores, float scale, const void* mask_or_null, int64_t mask_stride_b,
+                                                  int64_t mask_stride_h, int64_t mask_stride_row, int heads, int M, void* a,
+                                                  int64_t rows, int S, void* stream) {
+  if (!scores || !a) return HYC_ERR_NULL;
+  if (rows < 0 || S <= 0 || S % 8 != 0 || S > 32 * 8 * kSmMaxVec || heads < 1 || M < 1) return HYC_ERR_SHAPE;
+  if (!aligned(scores, 16) || !aligned(a, 16)) return HYC_ERR_ALIGN;
+  if (mask_or_null && (!aligned(mask_or_null, 16) || (mask_stride_b & 7) || (mask_stride_h & 7) || (mask_stride_row & 7))) return HYC_ERR_ALIGN;
+  if (rows == 0) return HYC_OK;
+  int64_t grid = (rows + 7) / 8;
+  if (grid > (int64_t)kNumSMs * 8) grid = (int64_t)kNumSMs * 8;
+#define SF(NV) softmax_fwd_kernel<NV><<<(int)grid, 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)scores, scale, \
+      (const __nv_bfloat16*)mask_or_null, mask_stride_b, mask_stride_h, mask_stride_row, heads, M, (__nv_bfloat16*)a, rows, S)
+  if (S <= 512) SF(2); else if (S <= 1024) SF(4); else if (S <= 2048) SF(8); else SF(16);
+#undef SF
   HYC_CHECK_LAUNCH();
   return HYC_OK;
 }

@@ -1,0 +1,153 @@
+"""The fused decoder layer: drop-in for ``FusedLlamaLayerIntraInterFullFuse`` / ``...Func``
+(models/llama/fused_llama_layer_intra_inter_full_fuse.py:29-708) and its Mistral twin
+(models/mistral/fused_mistral_layer_intra_inter_full_fuse.py), on the sm_100a kernels.
+
+The module keeps the reference's interface: ``set_hyclora_config(cfg)``, the ``iteration`` counter and the
+``static_value`` dictionary of calibrated statistics, and a ``forward`` that takes the norm weights, the rotary
+tables, the frozen ``*_proj_base`` modules and their ``*_proj_lora_a/b`` adapter dictionaries, the additive
+attention mask and the head geometry.  Differences, all deliberate:
+
+  * frozen weights are plain bf16 ``[out, in]`` matrices; a 4-bit ``quant_state`` is refused (the NF4
+    de-quantizer of the reference is a third-party library that is not part of this build);
+  * projection biases are refused (the Llama and Mistral layers the reference drives have none);
+  * ``hyclora_config.softmax_map_mode`` (optional, default ``"prune"`` = the reference's threshold prune) may
+    be ``"topk"`` for the per-row top-k + 4-bit-group form of the saved probability map.
+
+After the calibration iterations a step launches a fixed sequence of kernels with no host synchronisation in
+``"topk"`` mode (the ``"prune"`` mode reads the number of kept entries back, as ``to_sparse`` does).
+"""
+import torch
+
+from .attention import AttnState, AttnWeights, attention_backward, attention_forward
+from .mlp import MLPState, MLPWeights, _status_tensor, check_status, mlp_backward, mlp_forward
+
+BF16 = torch.bfloat16
+
+_LORA_ORDER = ("aq", "bq", "ak", "bk", "av", "bv", "ao", "bo", "ag", "bg", "au", "bu", "ad", "bd")
+
+
+class FusedLayerFunction(torch.autograd.Function):
+    """forward(x, module, aw, mw, cos, sin, mask, heads, head_dim, kv_heads, *fourteen LoRA weights).
+    The LoRA weights are listed as inputs only so that autograd routes their gradients; the computation reads
+    them from ``aw`` / ``mw``.  Gradients come back in the layout of the weights ([r, in] and [out, r])."""
+
+    @staticmethod
+    def forward(ctx, x, module, aw, mw, cos, sin, attention_mask, num_heads, head_dim, num_key_value_heads, *lora):
+        st = _status_tensor(x.device)
+        x_medium, sa = attention_forward(x, aw, module.attn_state, cos, sin, attention_mask, num_heads, head_dim,
+                                         num_key_value_heads, status=st)
+        y, sm = mlp_forward(x_medium, mw, module.mlp_state, status=st)
+        ctx.hyc = (sa, sm, aw, mw, st, module)
+        return y
+
+    @staticmethod
+    def backward(ctx, grad_y):
+        sa, sm, aw, mw, st, module = ctx.hyc
+        ctx.hyc = None
+        hook = module.on_lora_grads
+        gm = mlp_backward(grad_y, sm, mw, status=st, on_lora_grads=hook)
+        ga = attention_backward(gm['grad_x'], sa, aw, status=st, on_lora_grads=hook)
+        if module.check_kernel_status:
+            check_status(st, "fused layer")
+        grads = [ga['grad_aq'], ga['grad_bq'], ga['grad_ak'], ga['grad_bk'], ga['grad_av'], ga['grad_bv'],
+                 ga['grad_ao'], ga['grad_bo'], gm['grad_ag'], gm['grad_bg'], gm['grad_au'], gm['grad_bu'],
+                 gm['grad_ad'], gm['grad_bd']]
+        return (ga['grad_x'],) + (None,) * 9 + tuple(grads)
+
+
+def _frozen(base, name):
+    w = base.weight
+    if getattr(w, "quant_state", None) is not None or w.dtype != BF16:
+        raise NotImplementedError("%s: frozen weights must be plain bf16 [out, in] matrices (4-bit quant_state "
+                                  "weights are not supported)" % name)
+    if getattr(base, "bias", None) is not None:
+        raise NotImplementedError("%s: projection biases are not supported" % name)
+    return w
+
+
+def _adapter(mod):
+    """``lora_A`` / ``lora_B`` module dictionary of a PEFT layer (``.default``) or a bare ``nn.Linear``."""
+    inner = getattr(mod, "default", mod)
+    return inner.weight
+
+
+class FusedLlamaLayerIntraInterFullFuse(torch.nn.Module):
+    """One decoder layer (attention + MLP) with compressed saved activations."""
+
+    def __init__(self):
+        super().__init__()
+        self.attn_state = AttnState()
+        self.mlp_state = MLPState()
+        self.use_hyclora = True
+        self.on_lora_grads = None          # optional callable(dict of LoRA gradients): start their all-reduce early
+        self.check_kernel_status = False   # True: read the bounded-wait status word back after every backward pass
+        self._weights = None
+
+    # ---- the reference's attributes
+    @property
+    def iteration(self):
+        return self.attn_state.iteration
+
+    @iteration.setter
+    def iteration(self, v):
+        self.attn_state.iteration = v
+        self.mlp_state.iteration = v
+
+    @property
+    def static_value(self):
+        d = dict(self.attn_state.static_value)
+        d.update(self.mlp_state.static_value)
+        return d
+
+    def set_hyclora_config(self, hyclora_config):
+        self.hyclora_config = hyclora_config
+        self.use_hyclora = hyclora_config.use_hyclora
+        self.iteration_threshold = hyclora_config.iteration_threshold
+        self.softmax_outlier_ratio = hyclora_config.softmax_outlier_ratio
+        self.layernorm_outlier_ratio = hyclora_config.layernorm_outlier_ratio
+        self.q_bit = hyclora_config.q_bit
+        a, m = self.attn_state, self.mlp_state
+        a.iteration_threshold = m.iteration_threshold = self.iteration_threshold
+        a.q_bit = m.q_bit = self.q_bit
+        a.layernorm_outlier_ratio = m.layernorm_outlier_ratio = self.layernorm_outlier_ratio
+        a.softmax_outlier_ratio = self.softmax_outlier_ratio
+        a.map_mode = getattr(hyclora_config, "softmax_map_mode", "prune")
+        a.map_q_bit = getattr(hyclora_config, "softmax_map_q_bit", 4)
+
+    def _bind(self, norm_w1, norm_w2, mods):
+        """Weight records for the two halves, rebuilt only when a tensor was replaced."""
+        tensors = [norm_w1, norm_w2]
+        for name in ("q", "k", "v", "o", "gate", "up", "down"):
+            base, la, lb = mods[name]
+            tensors += [_frozen(base, name + "_proj"), _adapter(la), _adapter(lb)]
+        key = tuple(id(t) for t in tensors)
+        if self._weights is None or self._weights[0] != key:
+            (n1, n2, wq, aq, bq, wk, ak, bk, wv, av, bv, wo, ao, bo, wg, ag, bg, wu, au, bu, wd, ad, bd) = tensors
+            aw = AttnWeights(norm_w=n1, wq=wq, wk=wk, wv=wv, wo=wo, aq=aq, bq=bq, ak=ak, bk=bk, av=av, bv=bv, ao=ao, bo=bo)
+            mw = MLPWeights(norm_w=n2, wg=wg, wu=wu, wd=wd, ag=ag, bg=bg, au=au, bu=bu, ad=ad, bd=bd)
+            lora = (aq, bq, ak, bk, av, bv, ao, bo, ag, bg, au, bu, ad, bd)
+            self._weights = (key, aw, mw, lora)
+        return self._weights[1:]
+
+    def forward(self, input, norm_weight_1, norm_bias_1, cos, sin,
+                q_proj_base, q_proj_lora_a, q_proj_lora_b, k_proj_base, k_proj_lora_a, k_proj_lora_b,
+                v_proj_base, v_proj_lora_a, v_proj_lora_b, o_proj_base, o_proj_lora_a, o_proj_lora_b,
+                norm_weight_2, norm_bias_2,
+                gate_proj_base, gate_proj_lora_a, gate_proj_lora_b, up_proj_base, up_proj_lora_a, up_proj_lora_b,
+                down_proj_base, down_proj_lora_a, down_proj_lora_b,
+                attention_mask, num_heads, head_dim, num_key_value_heads):
+        if norm_bias_1 is not None or norm_bias_2 is not None:
+            raise NotImplementedError("RMSNorm has no bias")
+        mods = dict(q=(q_proj_base, q_proj_lora_a, q_proj_lora_b), k=(k_proj_base, k_proj_lora_a, k_proj_lora_b),
+                    v=(v_proj_base, v_proj_lora_a, v_proj_lora_b), o=(o_proj_base, o_proj_lora_a, o_proj_lora_b),
+                    gate=(gate_proj_base, gate_proj_lora_a, gate_proj_lora_b),
+                    up=(up_proj_base, up_proj_lora_a, up_proj_lora_b),
+                    down=(down_proj_base, down_proj_lora_a, down_proj_lora_b))
+        aw, mw, lora = self._bind(norm_weight_1, norm_weight_2, mods)
+        return FusedLayerFunction.apply(input, self, aw, mw, cos, sin, attention_mask, num_heads, head_dim,
+                                        num_key_value_heads, *lora)
+
+
+# The Mistral layer of the reference differs from the Llama one only in its head geometry (grouped key/value
+# heads), which is an argument of forward here.
+FusedMistralLayerIntraInterFullFuse = FusedLlamaLayerIntraInterFullFuse

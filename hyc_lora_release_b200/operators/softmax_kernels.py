@@ -15,3 +15,38 @@ def softmax_backward(y, grad_y):
     o = torch.empty_like(yc)
     check(lib.hyc_softmax_bwd(ptr(yc), ptr(gc), ptr(o), yc.numel() // S, S, stream_of(y)), "hyc_softmax_bwd")
     return o
+
+
+def softmax_forward_scale_mask(scores, scale, attention_mask=None, inplace=False):
+    """a = softmax(scores * scale + attention_mask, dim=-1) for raw scores [b, h, n, S] in one pass, with the
+    rounding points of the layer's three tensor operations (the scaling and the mask addition are bf16
+    operations, the softmax is fp32 inside with a bf16 result;
+    models/llama/fused_llama_layer_intra_inter_full_fuse.py:150-160).  ``attention_mask``: additive, broadcastable
+    as [b, 1 or h, n, S].  ``inplace`` overwrites ``scores`` (which must then be contiguous bf16)."""
+    require_cuda(scores, attention_mask)
+    if scores.dim() != 4:
+        raise ValueError("scores must be [batch, heads, n, S]")
+    if inplace and (scores.dtype != BF16 or not scores.is_contiguous()):
+        raise ValueError("inplace needs contiguous bf16 scores")
+    sc = scores.to(BF16).contiguous()
+    b, h, n, S = sc.shape
+    out = sc if inplace else torch.empty_like(sc)
+    mb = mh = mr = 0
+    mk = None
+    if attention_mask is not None:
+        mk = attention_mask.to(BF16)
+        if mk.dim() != 4 or mk.shape[-1] != S or mk.shape[-2] != n or mk.shape[0] not in (1, b) or mk.shape[1] not in (1, h):
+            raise ValueError("attention_mask must be [b or 1, h or 1, n, S]")
+        if mk.stride(-1) != 1:
+            mk = mk.contiguous()
+        mb = 0 if mk.shape[0] == 1 else mk.stride(0)
+        mh = 0 if mk.shape[1] == 1 else mk.stride(1)
+        mr = mk.stride(2)
+        if (mb | mh | mr) & 7 or mk.data_ptr() & 15:
+            mk = mk.contiguous()
+            mb = 0 if mk.shape[0] == 1 else mk.stride(0)
+            mh = 0 if mk.shape[1] == 1 else mk.stride(1)
+            mr = mk.stride(2)
+    check(lib.hyc_softmax_fwd_scale_mask(ptr(sc), float(scale), ptr(mk), mb, mh, mr, h, n, ptr(out), b * h * n, S,
+                                         stream_of(scores)), "hyc_softmax_fwd_scale_mask")
+    return out

@@ -194,6 +194,24 @@ int hyc_rmsnorm_fwd_save(const void* x, const void* w, float eps, int64_t rows, 
 int hyc_rmsnorm_bwd_packed(const void* dy, const void* qx, const void* scale_x, const int64_t* outlier_idx, int k,
                            const void* outlier, const void* w, const float* rstd, const void* residual_grad_or_null,
                            void* dx, int64_t rows, int N, int q_bit, void* stream);
+/* rope_forward / rope_backward (operators/rope_kernels.py:81-131, called from
+ * fused_llama_layer_intra_inter_full_fuse.py:142-143, 441, 449, 459-460): rotary embedding in the rotate-half
+ * form on the hidden layout.  x, out [rows, n_heads*head_dim] bf16 with row strides ldx / ldo (elements,
+ * multiples of 8; out may alias x), position of a row = row % seq_len, cos/sin tables [>= seq_len, ld_table]
+ * of which the first head_dim/2 columns are read, bf16 (table_is_f32 = 0) or fp32 (1).
+ *   out[j] = x[j]*cos[j] - x[j+h]*sin[j];  out[j+h] = x[j+h]*cos[j] + x[j]*sin[j];  backward: sin negated.
+ * fp32 arithmetic, one rounding to bf16.  head_dim % 16 == 0. */
+int hyc_rope(const void* x, int64_t ldx, void* out, int64_t ldo, const void* cos_table, const void* sin_table,
+             int64_t ld_table, int table_is_f32, int64_t rows, int seq_len, int n_heads, int head_dim,
+             int backward, void* stream);
+/* Attention probabilities from raw scores in one pass (fused_llama_layer_intra_inter_full_fuse.py:150-160:
+ * `s = q @ k^T / sqrt(d)`, `s + attention_mask`, `softmax(s, -1, dtype=bf16)`): a = softmax(bf16(bf16(scores * scale)
+ * + mask)) per row, fp32 inside, bf16 result.  scores, a [rows, S] bf16 (a may alias scores), rows = batch * heads * M;
+ * the optional additive bf16 mask is read at mask[b*stride_b + head*stride_h + m*stride_row + column] (strides in
+ * elements, multiples of 8; stride_h = 0 for a mask shared by the heads).  S % 8 == 0, S <= 4096. */
+int hyc_softmax_fwd_scale_mask(const void* scores, float scale, const void* mask_or_null, int64_t mask_stride_b,
+                               int64_t mask_stride_h, int64_t mask_stride_row, int heads, int M, void* a,
+                               int64_t rows, int S, void* stream);
 /* softmax_backward (operators/softmax_kernels.py:7-56): o = (g - sum(y*g)) * y per row. */
 int hyc_softmax_bwd(const void* y, const void* g, void* o, int64_t rows, int S, void* stream);
 

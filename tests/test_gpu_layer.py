@@ -1,0 +1,220 @@
+"""Attention half and whole fused decoder layer on the GPU against the CPU oracle: rotary embedding and
+scale + mask + softmax kernels, the attention block forward/backward (calibration iterations and steady state,
+both forms of the saved probability map, grouped key/value heads), and the layer module through autograd.
+Tolerances as for the MLP path: max |err| <= 1e-2 * max|ref| and cosine > 0.999 for activations."""
+import math
+import types
+
+import pytest
+import torch
+
+import oracle
+from oracle.attention import (ref_attention_block_backward, ref_attention_block_forward, ref_layer_backward,
+                              ref_layer_forward, ref_rope)
+from test_oracle_layer import layer_problem
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+BF16 = torch.bfloat16
+
+
+def close(a, b, rel=1e-2, cos=0.999):
+    a, b = a.float().cpu().flatten(), b.float().cpu().flatten()
+    scale = b.abs().max().clamp(min=1e-30)
+    c = torch.nn.functional.cosine_similarity(a, b, dim=0)
+    ok = bool((a - b).abs().max() <= rel * scale) and bool(c > cos)
+    if not ok:
+        print("max rel err %.4g (bound %g), cosine %.5f (bound %g)" % (float((a - b).abs().max() / scale), rel, float(c), cos))
+    return ok
+
+
+@pytest.mark.parametrize("table_dtype", [BF16, torch.float32])
+@pytest.mark.parametrize("B,M,heads,d", [(2, 64, 4, 32), (1, 100, 3, 128), (3, 17, 8, 64)])
+def test_rope_forward_backward(B, M, heads, d, table_dtype):
+    from hyc_lora_release_b200.operators import rope_kernels as rk
+    g = torch.Generator().manual_seed(B * M + d)
+    pos = torch.arange(M + 5, dtype=torch.float32)
+    inv = 1.0 / (10000.0 ** (torch.arange(0, d, 2, dtype=torch.float32) / d))
+    emb = torch.cat([torch.outer(pos, inv)] * 2, dim=-1)
+    cos, sin = emb.cos().to(table_dtype), emb.sin().to(table_dtype)
+    x = torch.randn(B, M, heads, d, generator=g).to(BF16)
+    for backward in (False, True):
+        ref = ref_rope(x, cos, sin, backward=backward)
+        fn = rk.rope_backward if backward else rk.rope_forward
+        out = fn(x.to(DEV), cos.to(DEV).unsqueeze(0), sin.to(DEV).unsqueeze(0))
+        assert out.shape == x.shape
+        diff = (out.cpu().float() - ref.float()).abs()
+        # fp32 arithmetic on both sides; a product rounded before the subtraction may move a value by one bf16 step
+        assert bool((diff <= ref.float().abs() * 2 ** -7 + 1e-30).all())
+        assert float((out.cpu() != ref).float().mean()) < 2e-3
+    xin = x.to(DEV).clone()
+    rk.rope_inplace(xin, cos.to(DEV), sin.to(DEV))
+    assert torch.equal(xin, rk.rope_forward(x.to(DEV), cos.to(DEV), sin.to(DEV)))
+    # head geometry and tables are checked before any launch
+    with pytest.raises(Exception):
+        rk.rope_forward(torch.zeros(1, 4, 2, 24, dtype=BF16, device=DEV), cos.to(DEV), sin.to(DEV))
+
+
+@pytest.mark.parametrize("B,h,M,S,mask_kind", [(2, 4, 64, 64, "causal"), (1, 3, 40, 520, None), (2, 2, 33, 1024, "batch"),
+                                               (1, 2, 16, 4096, "head")])
+def test_softmax_forward_scale_mask(B, h, M, S, mask_kind):
+    from hyc_lora_release_b200.operators.softmax_kernels import softmax_forward_scale_mask
+    g = torch.Generator().manual_seed(S + M)
+    sc = (torch.randn(B, h, M, S, generator=g) * 8).to(BF16)
+    mask = None
+    if mask_kind == "causal":
+        mask = torch.full((M, S), torch.finfo(BF16).min).triu(1).to(BF16).reshape(1, 1, M, S)
+    elif mask_kind == "batch":
+        mask = (torch.randn(B, 1, M, S, generator=g) * 3).to(BF16)
+    elif mask_kind == "head":
+        mask = (torch.randn(1, h, M, S, generator=g) * 3).to(BF16)
+    scale = 1.0 / math.sqrt(128)
+    t = (sc.float() * scale).to(BF16)
+    if mask is not None:
+        t = (t + mask).to(BF16)
+    ref = torch.softmax(t.float(), dim=-1)
+    out = softmax_forward_scale_mask(sc.to(DEV), scale, None if mask is None else mask.to(DEV))
+    assert out.dtype == BF16 and out.shape == sc.shape
+    assert close(out, ref, rel=5e-3)
+    assert float((out.float().sum(-1).cpu() - 1).abs().max()) < 2e-2
+    sc_d = sc.to(DEV).clone()
+    out2 = softmax_forward_scale_mask(sc_d, scale, None if mask is None else mask.to(DEV), inplace=True)
+    assert out2.data_ptr() == sc_d.data_ptr() and torch.equal(out2, out)
+
+
+def _attn_weights(p):
+    from hyc_lora_release_b200.attention import AttnWeights
+    t = lambda k: p[k].t().contiguous().to(DEV)
+    return AttnWeights(norm_w=p["norm_w1"].to(DEV), wq=t("wq"), wk=t("wk"), wv=t("wv"), wo=t("wo"), aq=t("aq"), bq=t("bq"),
+                       ak=t("ak"), bk=t("bk"), av=t("av"), bv=t("bv"), ao=t("ao"), bo=t("bo"))
+
+
+def _attn_static(sv):
+    c = lambda v: v.cpu().to(BF16)
+    st = dict(x_idx=sv["x"]["outlier_channel_index"].cpu(), x_scale=c(sv["x"]["scale"]),
+              x_norm_1_scale=c(sv["x_norm_1"]["scale"]), q_scale=c(sv["q"]["scale"]), k_scale=c(sv["k"]["scale"]),
+              v_scale=c(sv["v"]["scale"]), o_scale=c(sv["o"]["scale"]))
+    if sv["a"]["outlier"] is not None:
+        st["a_threshold"] = sv["a"]["outlier"].cpu().float()
+    return st
+
+
+ATTN_ARGS = ("wq", "wk", "wv", "wo", "aq", "bq", "ak", "bk", "av", "bv", "ao", "bo")
+
+
+@pytest.mark.parametrize("q,heads,kv,map_mode", [(4, 4, 4, "topk"), (8, 4, 2, "topk"), (4, 4, 4, "prune"), (2, 4, 2, "prune")])
+def test_attention_block_forward_backward(q, heads, kv, map_mode):
+    from hyc_lora_release_b200 import attention as at
+    from hyc_lora_release_b200.mlp import check_status
+    g = torch.Generator().manual_seed(3 * q + kv)
+    B, M, d, I = 2, 128, 128, 256
+    H = heads * d
+    x, p, cos, sin, mask = layer_problem(g, B, M, H, heads, d, kv, I)
+    W = _attn_weights(p)
+    state = at.AttnState(q_bit=q, layernorm_outlier_ratio=0.01, softmax_outlier_ratio=0.05, map_mode=map_mode)
+    st = torch.zeros(1, dtype=torch.int32, device=DEV)
+    ow = [p[k] for k in ATTN_ARGS]
+    gout = (torch.randn(B, M, H, generator=g)).to(BF16)
+    xd, cosd, sind, maskd, goutd = x.to(DEV), cos.to(DEV), sin.to(DEV), mask.to(DEV), gout.to(DEV)
+    static = None
+    # 2-bit codes of COMPUTED tensors (q/k/v main branches, o) flip where the device and the CPU sums differ in the
+    # last bit, and one flip is a third of the range: looser bounds for q = 2
+    ra, ca, rl, cl = (2e-2, 0.998, 3e-2, 0.995) if q > 2 else (6e-2, 0.99, 1.5e-1, 0.98)
+    for it in range(7):      # 5 calibration iterations, then the steady-state branch
+        if it >= 5:
+            static = _attn_static(state.static_value)
+        ref_out, ref_saved = ref_attention_block_forward(x, p["norm_w1"], cos, sin, *ow, mask, heads, d, kv, q, 0.01, 0.05,
+                                                         map_mode=map_mode, static=static)
+        ref_g = ref_attention_block_backward(gout, ref_saved, p["norm_w1"], cos, sin, *ow, heads, d, kv, q)
+        out, saved = at.attention_forward(xd, W, state, cosd, sind, maskd, heads, d, kv, status=st)
+        grads = at.attention_backward(goutd, saved, W, status=st)
+        check_status(st, "attention")
+        assert close(out, ref_out), it
+        assert torch.equal(saved["x_q"].cpu(), ref_saved["x_q"]) and torch.equal(saved["x_o"].cpu(), ref_saved["x_o"])
+        assert close(grads["grad_x"], ref_g["grad_x"], rel=ra, cos=ca), it
+        for name in ("q", "k", "v"):
+            assert close(grads["grad_" + name], ref_g["grad_" + name], rel=ra, cos=ca), (it, name)
+        for name in ("aq", "bq", "ak", "bk", "av", "bv", "ao", "bo"):   # oracle [in, r] / [r, out] -> weight layout
+            assert close(grads["grad_" + name], ref_g["grad_" + name].t(), rel=rl, cos=cl), (it, name)
+    assert state.iteration == 7
+
+
+class _Holder(torch.nn.Module):
+    """Stand-in for a PEFT module dictionary: ``.default`` is the adapter's nn.Linear."""
+    def __init__(self, w):
+        super().__init__()
+        self.default = torch.nn.Linear(w.shape[1], w.shape[0], bias=False, device=DEV, dtype=BF16)
+        with torch.no_grad():
+            self.default.weight.copy_(w)
+
+
+def _base(w):
+    lin = torch.nn.Linear(w.shape[1], w.shape[0], bias=False, device=DEV, dtype=BF16)
+    with torch.no_grad():
+        lin.weight.copy_(w)
+    lin.weight.requires_grad_(False)
+    return lin
+
+
+@pytest.mark.parametrize("heads,kv,map_mode", [(4, 4, "topk"), (4, 2, "prune")])
+def test_layer_module_through_autograd(heads, kv, map_mode):
+    from hyc_lora_release_b200.layer import FusedLlamaLayerIntraInterFullFuse, FusedMistralLayerIntraInterFullFuse
+    assert FusedMistralLayerIntraInterFullFuse is FusedLlamaLayerIntraInterFullFuse
+    g = torch.Generator().manual_seed(21 + kv)
+    B, M, d, I, q = 2, 128, 128, 1024, 4
+    H = heads * d
+    x, p, cos, sin, mask = layer_problem(g, B, M, H, heads, d, kv, I)
+    mods = {}
+    for n in ("q", "k", "v", "o", "gate", "up", "down"):
+        mods[n] = (_base(p["w" + n].t().to(DEV)), _Holder(p["a" + n].t().to(DEV)), _Holder(p["b" + n].t().to(DEV)))
+    layer = FusedLlamaLayerIntraInterFullFuse()
+    cfg = types.SimpleNamespace(use_hyclora=True, iteration_threshold=5, softmax_outlier_ratio=0.05,
+                                layernorm_outlier_ratio=0.01, q_bit=q, softmax_map_mode=map_mode)
+    layer.set_hyclora_config(cfg)
+    layer.check_kernel_status = True
+    n1 = torch.nn.Parameter(p["norm_w1"].to(DEV), requires_grad=False)
+    n2 = torch.nn.Parameter(p["norm_w2"].to(DEV), requires_grad=False)
+    gy = torch.randn(B, M, H, generator=g).to(BF16)
+
+    def run():
+        xin = x.to(DEV).requires_grad_(True)
+        args = [xin, n1, None, cos.to(DEV), sin.to(DEV)]
+        for n in ("q", "k", "v", "o"):
+            args += list(mods[n])
+        args += [n2, None]
+        for n in ("gate", "up", "down"):
+            args += list(mods[n])
+        y = layer(*args, mask.to(DEV), heads, d, kv)
+        for m3 in mods.values():
+            m3[1].default.weight.grad = None
+            m3[2].default.weight.grad = None
+        y.backward(gy.to(DEV))
+        return xin, y
+
+    for it in range(6):
+        xin, y = run()
+    assert layer.iteration == 6
+    sv = layer.static_value
+    assert set(sv) == {"x", "x_norm_1", "q", "k", "v", "a", "o", "x_medium", "x_norm_2", "gate", "up"}
+    static = dict(attention=_attn_static(sv),
+                  mlp=dict(x_medium_idx=sv["x_medium"]["outlier_channel_index"].cpu(),
+                           x_medium_scale=sv["x_medium"]["scale"].cpu().to(BF16),
+                           gate_scale=sv["gate"]["scale"].cpu().to(BF16), up_scale=sv["up"]["scale"].cpu().to(BF16),
+                           x_norm_2_scale=sv["x_norm_2"]["scale"].cpu().to(BF16)))
+    ref_y, ref_saved = ref_layer_forward(x, p, cos, sin, mask, heads, d, kv, q, 0.01, 0.05, map_mode=map_mode, static=static)
+    ref_g = ref_layer_backward(gy, ref_saved, p, cos, sin, heads, d, kv, q)
+    assert close(y, ref_y)
+    # the saved tensors downstream of the first GEMM are codes of COMPUTED activations, so a few 4-bit codes differ
+    # between the device and the CPU sums (one step = 1/15 of a channel's range): the cosine stays tight, the
+    # largest single deviation does not
+    assert close(xin.grad, ref_g["grad_x"], rel=6e-2, cos=0.998)
+    for n in ("q", "k", "v", "o", "gate", "up", "down"):
+        ga, gb = mods[n][1].default.weight.grad, mods[n][2].default.weight.grad
+        assert ga is not None and gb is not None, n
+        assert close(ga, ref_g["grad_a" + n].t(), rel=1e-1, cos=0.995), n
+        assert close(gb, ref_g["grad_b" + n].t(), rel=1e-1, cos=0.995), n
+    # a 4-bit quant_state or a bias is refused, not silently ignored
+    bad = _base(p["wq"].t().to(DEV))
+    bad.weight.quant_state = object()
+    with pytest.raises(NotImplementedError):
+        layer._bind(n1, n2, {**mods, "q": (bad, mods["q"][1], mods["q"][2])})
