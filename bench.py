@@ -308,6 +308,11 @@ def run_profile(args):
         print(json.dumps({"profile": "mlp", "steps": args.steps, "ms_per_step": line["ms_per_step"],
                           "tokens_per_s": line["value"], "tflops": line["roofline"]["achieved"]}))
         return
+    if args.profile == "layer":
+        line = layer_workload(dev, None, steps=args.steps, warmup=args.warmup)
+        print(json.dumps({"profile": "layer", "steps": args.steps, "ms_per_step": line["ms_per_step"],
+                          "tokens_per_s": line["value"], "tflops": line["roofline"]["achieved"]}))
+        return
     if args.profile == "fused":
         line = fused_elementwise_workload(dev, peaks()[0])
         print(json.dumps({"profile": "fused", "forward": line["forward"], "backward": line["backward"]}))
@@ -387,6 +392,99 @@ def mlp_workload(dev, dist=None, steps=20, warmup=4):
             "LoRA-gradient all-reduce inside the step when n_gpus > 1"}
 
 
+def layer_workload(dev, dist=None, steps=10, warmup=3):
+    """One fused decoder layer (attention + MLP) forward + backward at the Llama-2-7B geometry of BASELINE
+    configs[4]: hidden 4096, 32 heads of 128, intermediate 11008, sequence 2048, batch 1 per GPU, causal mask,
+    LoRA rank 16 on q/k/v/o/gate/up/down, saved activations 4-bit with 0.5 % outlier channels, the probability
+    map [1,32,2048,2048] saved as per-row top-k (5 %) + 4-bit groups.  Driven through the layer module and
+    autograd (the call a model fork makes); calibration happens before the timed region."""
+    import types
+    from hyc_lora_release_b200 import mlp, parallel
+    from hyc_lora_release_b200.layer import FusedLlamaLayerIntraInterFullFuse
+    g = torch.Generator().manual_seed(777)
+    B, M, H, heads, d, I, R = 1, 2048, 4096, 32, 128, 11008, 16
+    bf = torch.bfloat16
+
+    def lin(out, inp, sc=None, grad=False):
+        m = torch.nn.Linear(inp, out, bias=False, device=dev, dtype=bf)
+        with torch.no_grad():
+            if sc is None:
+                m.weight.copy_(((torch.rand(out, inp, generator=g) * 2 - 1) * (1.0 / inp) ** 0.5).to(bf))
+            else:
+                m.weight.copy_((torch.randn(out, inp, generator=g) * sc).to(bf))
+        m.weight.requires_grad_(grad)
+        return m
+
+    def adapter(out, inp):
+        a, b = torch.nn.Module(), torch.nn.Module()
+        a.default, b.default = lin(R, inp, grad=True), lin(out, R, sc=.02, grad=True)
+        return a, b
+    dims = dict(q=(H, H), k=(H, H), v=(H, H), o=(H, H), gate=(I, H), up=(I, H), down=(H, I))
+    mods = {n: (lin(o_, i_, sc=.02),) + adapter(o_, i_) for n, (o_, i_) in dims.items()}
+    x = torch.randn(B, M, H, generator=g)
+    x[:, :, torch.randperm(H, generator=g)[:20]] *= 30
+    x = x.to(bf).to(dev)
+    pos = torch.arange(M, dtype=torch.float32)
+    inv = 1.0 / (10000.0 ** (torch.arange(0, d, 2, dtype=torch.float32) / d))
+    emb = torch.cat([torch.outer(pos, inv)] * 2, -1)
+    cos, sin = emb.cos().to(bf).to(dev), emb.sin().to(bf).to(dev)
+    mask = torch.full((M, M), torch.finfo(bf).min).triu(1).to(bf).reshape(1, 1, M, M).to(dev)
+    n1 = torch.ones(H, dtype=bf, device=dev)
+    n2 = torch.ones(H, dtype=bf, device=dev)
+    gy = (torch.randn(B, M, H, generator=g)).to(bf).to(dev)
+    layer = FusedLlamaLayerIntraInterFullFuse()
+    layer.set_hyclora_config(types.SimpleNamespace(use_hyclora=True, iteration_threshold=5, softmax_outlier_ratio=0.05,
+                                                   layernorm_outlier_ratio=0.005, q_bit=4, softmax_map_mode="topk"))
+    pending = []
+    layer.on_lora_grads = lambda gr: pending.append(parallel.allreduce_lora_grads_async(gr))
+    args = [None, n1, None, cos, sin]
+    for n in ("q", "k", "v", "o"):
+        args += list(mods[n])
+    args += [n2, None]
+    for n in ("gate", "up", "down"):
+        args += list(mods[n])
+    args += [mask, heads, d, heads]
+
+    def step(i):
+        xin = x.detach().requires_grad_(True)
+        args[0] = xin
+        y = layer(*args)
+        y.backward(gy)
+        for p_ in pending:
+            p_.wait()
+        pending.clear()
+        for m3 in mods.values():
+            m3[1].default.weight.grad = None
+            m3[2].default.weight.grad = None
+    for i in range(6):
+        step(i)
+    layer.check_kernel_status = True
+    step(6)
+    layer.check_kernel_status = False
+    t = time_loop(step, steps, warmup)
+    world = 1
+    if dist is not None:
+        world = dist.get_world_size()
+        tt = torch.tensor([t], device=dev)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        t = float(tt.item())
+    T = B * M
+    # frozen GEMMs (no weight gradient): 2 flop x (fwd + bwd) per weight element; attention products 4 M d per
+    # head and token forward (scores + P.V over the full, unskipped square), twice that backward; rank-16 terms:
+    # 12 H R per attention projection, R (18 H + 22 I) for the MLP
+    flop_per_token = 4 * (4 * H * H + 3 * H * I) + 12 * M * heads * d + R * (48 * H + 18 * H + 22 * I)
+    burst, sustained, src = tensor_peaks()
+    tf = T * flop_per_token * steps / t / 1e12
+    return {"workload": "fused decoder layer fwd+bwd through the layer module, Llama-2-7B geometry, seq 2048, batch 1 per GPU, "
+                        "q_bit 4, map top-k 5 % (one of the 32 layers of BASELINE configs[4])",
+            "metric": "tokens/s", "value": world * T * steps / t, "unit": "tokens/s (one layer)", "ms_per_step": t / steps * 1e3,
+            "tokens_per_gpu": T, "flop_per_token": flop_per_token,
+            "roofline": {"bound": "tensor", "achieved": tf, "peak": sustained, "unit": "TFLOP/s", "frac": tf / sustained,
+                         "peak_source": src + " (sustained)"},
+            "note": "the two attention products per direction are library batched GEMMs and, like every pass over the "
+                    "[1,32,2048,2048] map (softmax, save, restore, softmax backward), bound by HBM, not by the tensor cores"}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -394,7 +492,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-extras", action="store_true", help="skip the secondary workloads and the CPU sample")
-    ap.add_argument("--profile", default=None, choices=["attn_topk", "channel_q4", "channel_q2", "channel_q8", "mlp", "fused"],
+    ap.add_argument("--profile", default=None, choices=["attn_topk", "channel_q4", "channel_q2", "channel_q8", "mlp", "fused", "layer"],
                     help="run only W+K steps of one workload and print timing (for a profiler capture)")
     args = ap.parse_args()
     if args.warmup < 3:
@@ -527,10 +625,12 @@ def main():
            "api": "compress_function.compression_softmax_topk + TopkMap.to_dense on pinned host maps, four streams "
                   "(the read-back of one step overlaps the upload of the next)"}
 
-    mlp_line = None
+    mlp_line = layer_line = None
     if not args.no_extras:
         barrier()
         mlp_line = mlp_workload(dev, dist)      # every rank takes part (all-reduce inside)
+        barrier()
+        layer_line = layer_workload(dev, dist)
     if rank == 0:
         also, cpu = [], None
         if not args.no_extras and world == 1:
@@ -538,6 +638,8 @@ def main():
             cpu, _, _ = cpu_port_sample()
         if mlp_line is not None:
             also.append(mlp_line)
+        if layer_line is not None:
+            also.append(layer_line)
         line = {
             "metric": "activation compress+decompress GB/s", "value": value, "unit": "GB/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": secs / args.steps * 1e3,

@@ -33,7 +33,7 @@ SIGNATURES = {
     "hyc_softmax_prune_static": (_i, [_p, _l, _f, _p, _p, _l, _p, _p]),
     "hyc_softmax_topk_compress": (_i, [_p, _l, _i, _i, _p, _p, _p, _p, _p, _i, _p]),
     "hyc_softmax_topk_restore": (_i, [_p, _p, _i, _p, _p, _p, _l, _i, _p, _i, _p]),
-    "hyc_softmax_topk_restore_bwd": (_i, [_p, _p, _i, _p, _p, _p, _l, _i, _p, _p, _i, _p]),
+    "hyc_softmax_topk_restore_bwd": (_i, [_p, _p, _i, _p, _p, _p, _l, _i, _p, _p, _i, _f, _p]),
     "hyc_fused_lora_silu_hadamard_fwd": (_i, [_p] * 11 + [_l, _i, _i, _i, _p]),
     "hyc_fused_lora_silu_hadamard_bwd": (_i, [_p] * 12 + [_l, _i, _i, _i, _p]),
     "hyc_dequant_lora_add": (_i, [_p, _p, _p, _p, _p, _l, _i, _i, _i, _p]),
@@ -41,7 +41,7 @@ SIGNATURES = {
     "hyc_rmsnorm_bwd": (_i, [_p, _p, _p, _p, _p, _l, _i, _p]),
     "hyc_rmsnorm_fwd_save": (_i, [_p, _p, _f, _l, _i, _p, _p, _i, _p, _p, _p, _p, _p, _p, _i, _p]),
     "hyc_rmsnorm_bwd_packed": (_i, [_p, _p, _p, _p, _i, _p, _p, _p, _p, _p, _l, _i, _i, _p]),
-    "hyc_softmax_bwd": (_i, [_p, _p, _p, _l, _i, _p]),
+    "hyc_softmax_bwd": (_i, [_p, _p, _p, _l, _i, _f, _p]),
     "hyc_softmax_fwd_scale_mask": (_i, [_p, _f, _p, _l, _l, _l, _i, _i, _p, _l, _i, _p]),
     "hyc_rope": (_i, [_p, _l, _p, _l, _p, _p, _l, _i, _l, _i, _i, _i, _i, _p]),
     "hyc_lora_grad_a_workspace_bytes": (_z, [_i, _i, _i]),

@@ -248,12 +248,11 @@ def attention_backward(grad_medium, saved, w: AttnWeights, status=None, on_lora_
     # ---- softmax backward (for the top-k form fused with a second restore: the map is not re-read)
     if saved['map_mode'] == "topk":
         del a
-        grad_s = m.softmax_backward(grad_a)
+        grad_s = m.softmax_backward(grad_a, scale=1.0 / math.sqrt(d))
         del grad_a
     else:
-        grad_s = softmax_backward(a, grad_a)
+        grad_s = softmax_backward(a, grad_a, scale=1.0 / math.sqrt(d))
         del a
-    grad_s.mul_(1.0 / math.sqrt(d))
 
     # ---- q, k rebuilt from their codes, rotary re-applied
     q2 = _rebuild(saved['q_q'], saved['q_scale'], saved['q_xa'], w.bq, q)

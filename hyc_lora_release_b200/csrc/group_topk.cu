@@ -574,7 +574,7 @@ extern "C" HYC_API int hyc_softmax_topk_restore(const void* val, const uint16_t*
   if (rows == 0) return HYC_OK;
   cudaStream_t st = (cudaStream_t)stream;
   if (topk_lane_ok(S, k) && aligned(q, 32)) {
-    const int rc = topk_lane_restore(val, col, k, q, scale, zp, rows, S, nullptr, a_out, q_bit, st);
+    const int rc = topk_lane_restore(val, col, k, q, scale, zp, rows, S, nullptr, 1.f, a_out, q_bit, st);
     if (rc) return rc;
     HYC_CHECK_LAUNCH();
     return HYC_OK;
@@ -590,7 +590,7 @@ extern "C" HYC_API int hyc_softmax_topk_restore(const void* val, const uint16_t*
 extern "C" HYC_API int hyc_softmax_topk_restore_bwd(const void* val, const uint16_t* col, int k,
                                                     const void* q, const void* scale, const int8_t* zp,
                                                     int64_t rows, int S, const void* grad, void* out, int q_bit,
-                                                    void* stream) {
+                                                    float out_scale, void* stream) {
   if (!q || !scale || !zp || !grad || !out) return HYC_ERR_NULL;
   if (k > 0 && (!val || !col)) return HYC_ERR_NULL;
   if (q_bit != 2 && q_bit != 4 && q_bit != 8) return HYC_ERR_QBIT;
@@ -598,7 +598,7 @@ extern "C" HYC_API int hyc_softmax_topk_restore_bwd(const void* val, const uint1
   if (!aligned(out, 32) || !aligned(grad, 32) || !aligned(q, 16)) return HYC_ERR_ALIGN;
   if (!topk_lane_ok(S, k) || !aligned(q, 32)) return HYC_ERR_UNSUPPORTED;   // caller: restore, then hyc_softmax_bwd
   if (rows == 0) return HYC_OK;
-  const int rc = topk_lane_restore(val, col, k, q, scale, zp, rows, S, grad, out, q_bit, (cudaStream_t)stream);
+  const int rc = topk_lane_restore(val, col, k, q, scale, zp, rows, S, grad, out_scale, out, q_bit, (cudaStream_t)stream);
   if (rc) return rc;
   HYC_CHECK_LAUNCH();
   return HYC_OK;

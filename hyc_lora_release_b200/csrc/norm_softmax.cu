@@ -339,7 +339,7 @@ rmsnorm_bwd_packed_kernel(const __nv_bfloat16* __restrict__ dy, const uint8_t* _
 constexpr int kSmMaxVec = 16;   // 16 x (32 lanes x 8 elements) = 4096 columns
 __global__ void __launch_bounds__(256)
 softmax_bwd_kernel(const __nv_bfloat16* __restrict__ y, const __nv_bfloat16* __restrict__ g,
-                   __nv_bfloat16* __restrict__ o, int64_t rows, int S) {
+                   __nv_bfloat16* __restrict__ o, int64_t rows, int S, float oscale) {
   const int lane = threadIdx.x & 31;
   const int nvec = S / 8;
   for (int64_t row = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5); row < rows; row += (int64_t)gridDim.x * 8) {
@@ -367,7 +367,14 @@ softmax_bwd_kernel(const __nv_bfloat16* __restrict__ y, const __nv_bfloat16* __r
         unpack8(yv[i], yf); unpack8(gv[i], gf);
 #pragma unroll
         for (int e = 0; e < 8; ++e) gf[e] = (gf[e] - acc) * yf[e];
-        st_stream_v4(o + row * S + 8 * v, pack8(gf));
+        uint4 r = pack8(gf);
+        if (oscale != 1.f) {       // a second bf16 operation on the result
+          unpack8(r, gf);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) gf[e] *= oscale;
+          r = pack8(gf);
+        }
+        st_stream_v4(o + row * S + 8 * v, r);
       }
     }
   }
@@ -380,54 +387,71 @@ softmax_bwd_kernel(const __nv_bfloat16* __restrict__ y, const __nv_bfloat16* __r
 // One warp per row, the row in registers (NV chunks of 32 lanes x 8 columns).  The mask is addressed as
 // mask[b * mb + head * mh + m * mr + column] for row = (b * heads + head) * M + m.
 template <int NV>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, NV <= 8 ? 2 : 1)
 softmax_fwd_kernel(const __nv_bfloat16* __restrict__ sc, float scale, const __nv_bfloat16* __restrict__ mask,
                    int64_t mb, int64_t mh, int64_t mr, int heads, int M, __nv_bfloat16* __restrict__ a,
                    int64_t rows, int S) {
   const int lane = threadIdx.x & 31;
   const int nvec = S / 8;
+  constexpr float kLog2e = 1.4426950408889634f;
   for (int64_t row = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5); row < rows; row += (int64_t)gridDim.x * 8) {
     const int m = (int)(row % M);
     const int64_t bh = row / M;
     const __nv_bfloat16* mrow = mask ? mask + (bh / heads) * mb + (bh % heads) * mh + (int64_t)m * mr : nullptr;
-    float u[NV][8];
-    float mx = -INFINITY;
+    // every load of the row is issued before the first use (the scores stream from HBM, the mask comes from L2)
+    uint4 raw[NV], mk[NV];
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
       const int v = lane + 32 * i;
-      if (v < nvec) {
-        unpack8(ld_stream_v4(sc + row * S + 8 * v), u[i]);
-        float mk[8];
-        if (mrow) unpack8(*reinterpret_cast<const uint4*>(mrow + 8 * v), mk);
+      raw[i] = make_uint4(0xff80ff80u, 0xff80ff80u, 0xff80ff80u, 0xff80ff80u);      // -inf: columns beyond S
+      if (v < nvec) raw[i] = ld_stream_v4(sc + row * S + 8 * v);
+    }
 #pragma unroll
-        for (int e = 0; e < 8; ++e) {
-          float t = bf16bits_to_f32(f32_to_bf16bits_rn(u[i][e] * scale));
-          if (mrow) t = bf16bits_to_f32(f32_to_bf16bits_rn(t + mk[e]));
-          u[i][e] = t;
-          mx = fmaxf(mx, t);
-        }
+    for (int i = 0; i < NV; ++i) {
+      const int v = lane + 32 * i;
+      mk[i] = make_uint4(0u, 0u, 0u, 0u);
+      if (mrow && v < nvec) mk[i] = __ldg(reinterpret_cast<const uint4*>(mrow + 8 * v));
+    }
+    // t = bf16(bf16(s * scale) + mask), kept as packed bf16 in place of the raw scores
+    float mx = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      float u[8], mf[8];
+      unpack8(raw[i], u);
+      unpack8(mk[i], mf);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) u[e] *= scale;
+      raw[i] = pack8(u);
+      if (mrow) {
+        unpack8(raw[i], u);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) u[e] += mf[e];
+        raw[i] = pack8(u);
       }
+      unpack8(raw[i], u);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) mx = fmaxf(mx, u[e]);
     }
 #pragma unroll
     for (int of = 16; of > 0; of >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, of));
+    const float mxl = mx * kLog2e;
+    float ef[NV][8];
     float sum = 0.f;
 #pragma unroll
-    for (int i = 0; i < NV; ++i)
-      if (lane + 32 * i < nvec) {
+    for (int i = 0; i < NV; ++i) {
+      unpack8(raw[i], ef[i]);
 #pragma unroll
-        for (int e = 0; e < 8; ++e) { u[i][e] = __expf(u[i][e] - mx); sum += u[i][e]; }
-      }
+      for (int e = 0; e < 8; ++e) { ef[i][e] = exp2f(fmaf(ef[i][e], kLog2e, -mxl)); sum += ef[i][e]; }
+    }
 #pragma unroll
     for (int of = 16; of > 0; of >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, of);
     const float inv = 1.0f / sum;
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
       const int v = lane + 32 * i;
-      if (v < nvec) {
 #pragma unroll
-        for (int e = 0; e < 8; ++e) u[i][e] *= inv;
-        st_stream_v4(a + row * S + 8 * v, pack8(u[i]));
-      }
+      for (int e = 0; e < 8; ++e) ef[i][e] *= inv;
+      if (v < nvec) st_stream_v4(a + row * S + 8 * v, pack8(ef[i]));
     }
   }
 }
@@ -514,19 +538,19 @@ extern "C" HYC_API int hyc_rmsnorm_bwd(const void* dy, const void* x, const void
   return HYC_OK;
 }
 
-extern "C" HYC_API int hyc_softmax_bwd(const void* y, const void* g, void* o, int64_t rows, int S, void* stream) {
+extern "C" HYC_API int hyc_softmax_bwd(const void* y, const void* g, void* o, int64_t rows, int S, float out_scale, void* stream) {
   if (!y || !g || !o) return HYC_ERR_NULL;
   if (rows < 0 || S <= 0 || S % 8 != 0 || S > 32 * 8 * kSmMaxVec) return HYC_ERR_SHAPE;
   if (!aligned(y, 16) || !aligned(g, 16) || !aligned(o, 16)) return HYC_ERR_ALIGN;
   if (rows == 0) return HYC_OK;
-  if (softmax_bwd_lane(y, g, rows, S, o, (cudaStream_t)stream)) {   // rows of 64 * 2^n columns: staged, coalesced
+  if (softmax_bwd_lane(y, g, rows, S, out_scale, o, (cudaStream_t)stream)) {   // rows of 64 * 2^n columns: staged, coalesced
     HYC_CHECK_LAUNCH();
     return HYC_OK;
   }
   int64_t grid = (rows + 7) / 8;
   if (grid > (int64_t)kNumSMs * 8) grid = (int64_t)kNumSMs * 8;
   softmax_bwd_kernel<<<(int)grid, 256, 0, (cudaStream_t)stream>>>(
-      (const __nv_bfloat16*)y, (const __nv_bfloat16*)g, (__nv_bfloat16*)o, rows, S);
+      (const __nv_bfloat16*)y, (const __nv_bfloat16*)g, (__nv_bfloat16*)o, rows, S, out_scale);
   HYC_CHECK_LAUNCH();
   return HYC_OK;
 }

@@ -201,7 +201,7 @@ __global__ void __launch_bounds__(256, HYC_LANE_MINB)
 topk_lane_restore_kernel(const __nv_bfloat16* __restrict__ val, const uint16_t* __restrict__ colv, int k, float inv_k,
                          const uint8_t* __restrict__ q, const __nv_bfloat16* __restrict__ scale,
                          const int8_t* __restrict__ zp, int64_t rows, const __nv_bfloat16* __restrict__ grad,
-                         __nv_bfloat16* __restrict__ ao) {
+                         float oscale, __nv_bfloat16* __restrict__ ao) {
   constexpr int RPW = 32 / LPR;
   constexpr int S = 64 * LPR;
   constexpr int64_t QLD = (int64_t)S * QBIT / 8;
@@ -280,6 +280,10 @@ topk_lane_restore_kernel(const __nv_bfloat16* __restrict__ val, const uint16_t* 
       for (int j = 0; j < 32; ++j)
         gv[j] = pack_bf16x2_rn((bf16lo_to_f32(gv[j]) - acc) * bf16lo_to_f32(yv[j]),
                                (bf16hi_to_f32(gv[j]) - acc) * bf16hi_to_f32(yv[j]));
+      if (oscale != 1.f) {        // a second bf16 operation on the result (the layer's `grad_s / sqrt(d)`)
+#pragma unroll
+        for (int j = 0; j < 32; ++j) gv[j] = pack_bf16x2_rn(bf16lo_to_f32(gv[j]) * oscale, bf16hi_to_f32(gv[j]) * oscale);
+      }
       __syncwarp();
       lane_slot_store(sx, lane, gv);
       __syncwarp();
@@ -295,7 +299,7 @@ topk_lane_restore_kernel(const __nv_bfloat16* __restrict__ val, const uint16_t* 
 template <int LPR>
 __global__ void __launch_bounds__(256, HYC_LANE_MINB)
 softmax_bwd_lane_kernel(const __nv_bfloat16* __restrict__ y, const __nv_bfloat16* __restrict__ g, int64_t rows,
-                        __nv_bfloat16* __restrict__ out) {
+                        float oscale, __nv_bfloat16* __restrict__ out) {
   constexpr int RPW = 32 / LPR;
   constexpr int S = 64 * LPR;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
@@ -326,6 +330,10 @@ softmax_bwd_lane_kernel(const __nv_bfloat16* __restrict__ y, const __nv_bfloat16
     for (int j = 0; j < 32; ++j)
       gv[j] = pack_bf16x2_rn((bf16lo_to_f32(gv[j]) - acc) * bf16lo_to_f32(yv[j]),
                              (bf16hi_to_f32(gv[j]) - acc) * bf16hi_to_f32(yv[j]));
+    if (oscale != 1.f) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) gv[j] = pack_bf16x2_rn(bf16lo_to_f32(gv[j]) * oscale, bf16hi_to_f32(gv[j]) * oscale);
+    }
     __syncwarp();
     lane_slot_store(sx, lane, gv);
     __syncwarp();
@@ -335,23 +343,23 @@ softmax_bwd_lane_kernel(const __nv_bfloat16* __restrict__ y, const __nv_bfloat16
 }
 
 template <int LPR>
-static void launch_softmax_bwd(const void* y, const void* g, int64_t rows, void* out, cudaStream_t st) {
+static void launch_softmax_bwd(const void* y, const void* g, int64_t rows, float oscale, void* out, cudaStream_t st) {
   auto kern = softmax_bwd_lane_kernel<LPR>;
   int grid, threads;
   lane_launch_shape(kern, rows, 32 / LPR, grid, threads);
-  kern<<<grid, threads, 0, st>>>((const __nv_bfloat16*)y, (const __nv_bfloat16*)g, rows, (__nv_bfloat16*)out);
+  kern<<<grid, threads, 0, st>>>((const __nv_bfloat16*)y, (const __nv_bfloat16*)g, rows, oscale, (__nv_bfloat16*)out);
 }
 
 // rows of 64 * 2^n <= 2048 columns, 32-byte aligned tensors; false = not covered (nothing launched)
-bool softmax_bwd_lane(const void* y, const void* g, int64_t rows, int S, void* out, cudaStream_t st) {
+bool softmax_bwd_lane(const void* y, const void* g, int64_t rows, int S, float oscale, void* out, cudaStream_t st) {
   if (S < 64 || S > 2048 || (S & (S - 1)) != 0 || !aligned(y, 32) || !aligned(g, 32) || !aligned(out, 32)) return false;
   switch (S / 64) {
-    case 1: launch_softmax_bwd<1>(y, g, rows, out, st); break;
-    case 2: launch_softmax_bwd<2>(y, g, rows, out, st); break;
-    case 4: launch_softmax_bwd<4>(y, g, rows, out, st); break;
-    case 8: launch_softmax_bwd<8>(y, g, rows, out, st); break;
-    case 16: launch_softmax_bwd<16>(y, g, rows, out, st); break;
-    default: launch_softmax_bwd<32>(y, g, rows, out, st); break;
+    case 1: launch_softmax_bwd<1>(y, g, rows, oscale, out, st); break;
+    case 2: launch_softmax_bwd<2>(y, g, rows, oscale, out, st); break;
+    case 4: launch_softmax_bwd<4>(y, g, rows, oscale, out, st); break;
+    case 8: launch_softmax_bwd<8>(y, g, rows, oscale, out, st); break;
+    case 16: launch_softmax_bwd<16>(y, g, rows, oscale, out, st); break;
+    default: launch_softmax_bwd<32>(y, g, rows, oscale, out, st); break;
   }
   return true;
 }
@@ -368,19 +376,19 @@ static void launch_compress(const void* a, int64_t rows, int k, void* val, uint1
 }
 template <int QBIT, int LPR>
 static void launch_restore(const void* val, const uint16_t* col, int k, const void* q, const void* scale,
-                           const int8_t* zp, int64_t rows, const void* grad, void* ao, cudaStream_t st) {
+                           const int8_t* zp, int64_t rows, const void* grad, float oscale, void* ao, cudaStream_t st) {
   int grid, threads;
   if (grad == nullptr) {
     auto kern = topk_lane_restore_kernel<QBIT, LPR, false>;
     lane_launch_shape(kern, rows, 32 / LPR, grid, threads);
     kern<<<grid, threads, 0, st>>>((const __nv_bfloat16*)val, col, k, k > 0 ? 1.0f / (float)k : 0.f,
-                                   (const uint8_t*)q, (const __nv_bfloat16*)scale, zp, rows, nullptr, (__nv_bfloat16*)ao);
+                                   (const uint8_t*)q, (const __nv_bfloat16*)scale, zp, rows, nullptr, 1.f, (__nv_bfloat16*)ao);
   } else {
     auto kern = topk_lane_restore_kernel<QBIT, LPR, true>;
     lane_launch_shape(kern, rows, 32 / LPR, grid, threads);
     kern<<<grid, threads, 0, st>>>((const __nv_bfloat16*)val, col, k, k > 0 ? 1.0f / (float)k : 0.f,
                                    (const uint8_t*)q, (const __nv_bfloat16*)scale, zp, rows,
-                                   (const __nv_bfloat16*)grad, (__nv_bfloat16*)ao);
+                                   (const __nv_bfloat16*)grad, oscale, (__nv_bfloat16*)ao);
   }
 }
 
@@ -403,8 +411,8 @@ static int compress_q(const void* a, int64_t rows, int S, int k, void* val, uint
 }
 template <int QB>
 static int restore_q(const void* val, const uint16_t* col, int k, const void* q, const void* scale, const int8_t* zp,
-                     int64_t rows, int S, const void* grad, void* ao, cudaStream_t st) {
-  HYC_LANE_DISPATCH(launch_restore, val, col, k, q, scale, zp, rows, grad, ao, st);
+                     int64_t rows, int S, const void* grad, float oscale, void* ao, cudaStream_t st) {
+  HYC_LANE_DISPATCH(launch_restore, val, col, k, q, scale, zp, rows, grad, oscale, ao, st);
   return HYC_OK;
 }
 
@@ -416,12 +424,12 @@ int topk_lane_compress(const void* a, int64_t rows, int S, int k, void* val_out,
   return compress_q<8>(a, rows, S, k, val_out, col_out, q_out, scale_out, zp_out, st);
 }
 int topk_lane_restore(const void* val, const uint16_t* col, int k, const void* q, const void* scale,
-                      const int8_t* zp, int64_t rows, int S, const void* grad_or_null, void* a_out, int q_bit,
-                      cudaStream_t st) {
+                      const int8_t* zp, int64_t rows, int S, const void* grad_or_null, float out_scale, void* a_out,
+                      int q_bit, cudaStream_t st) {
   if (!topk_lane_ok(S, k)) return HYC_ERR_SHAPE;
-  if (q_bit == 2) return restore_q<2>(val, col, k, q, scale, zp, rows, S, grad_or_null, a_out, st);
-  if (q_bit == 4) return restore_q<4>(val, col, k, q, scale, zp, rows, S, grad_or_null, a_out, st);
-  return restore_q<8>(val, col, k, q, scale, zp, rows, S, grad_or_null, a_out, st);
+  if (q_bit == 2) return restore_q<2>(val, col, k, q, scale, zp, rows, S, grad_or_null, out_scale, a_out, st);
+  if (q_bit == 4) return restore_q<4>(val, col, k, q, scale, zp, rows, S, grad_or_null, out_scale, a_out, st);
+  return restore_q<8>(val, col, k, q, scale, zp, rows, S, grad_or_null, out_scale, a_out, st);
 }
 
 }  // namespace hyc

@@ -16,12 +16,13 @@ inline bool topk_lane_ok(int S, int k) {
 // both return 0 or a negative HYC_ERR_* (arguments already validated by the caller)
 int topk_lane_compress(const void* a, int64_t rows, int S, int k, void* val_out, uint16_t* col_out,
                        void* q_out, void* scale_out, int8_t* zp_out, int q_bit, cudaStream_t st);
-// grad_or_null != NULL: a_out receives softmax_backward(restored map, grad) instead of the restored map
+// grad_or_null != NULL: a_out receives bf16(softmax_backward(restored map, grad) * out_scale) instead of the
+// restored map (out_scale == 1: no second operation)
 int topk_lane_restore(const void* val, const uint16_t* col, int k, const void* q, const void* scale,
-                      const int8_t* zp, int64_t rows, int S, const void* grad_or_null, void* a_out, int q_bit,
-                      cudaStream_t st);
+                      const int8_t* zp, int64_t rows, int S, const void* grad_or_null, float out_scale, void* a_out,
+                      int q_bit, cudaStream_t st);
 
 // softmax backward on dense maps in the same layout; false = shape or alignment not covered, nothing launched
-bool softmax_bwd_lane(const void* y, const void* g, int64_t rows, int S, void* out, cudaStream_t st);
+bool softmax_bwd_lane(const void* y, const void* g, int64_t rows, int S, float out_scale, void* out, cudaStream_t st);
 
 }  // namespace hyc

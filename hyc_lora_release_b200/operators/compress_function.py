@@ -340,9 +340,10 @@ class TopkMap:
     def to_dense(self, out=None):
         return decompression_softmax_topk(self, out=out)
 
-    def softmax_backward(self, grad, out=None):
+    def softmax_backward(self, grad, out=None, scale=1.0):
         """``softmax_backward(self.to_dense(), grad)`` (operators/softmax_kernels.py:41) without writing the
-        restored map: one kernel where the shapes allow it, restore + softmax backward otherwise."""
+        restored map: one kernel where the shapes allow it, restore + softmax backward otherwise.  ``scale``: the
+        bf16 result times ``scale`` as a second bf16 operation (the layer's ``grad_s / sqrt(head_dim)``)."""
         require_cuda(grad, self.q)
         g = grad.to(BF16).contiguous()
         if tuple(g.shape) != self.shape:
@@ -352,10 +353,10 @@ class TopkMap:
             out = torch.empty(self.shape, dtype=BF16, device=self.q.device)
         rc = lib.hyc_softmax_topk_restore_bwd(ptr(self.val) if k else None, ptr(self.col) if k else None, k, ptr(self.q),
                                               ptr(self.scale), ptr(self.zp), rows, S, ptr(g), ptr(out), self.q_bit,
-                                              stream_of(self.q))
+                                              float(scale), stream_of(self.q))
         if rc == -8:      # HYC_ERR_UNSUPPORTED: shape outside the fused kernel
             from .softmax_kernels import softmax_backward as _sb
-            res = _sb(self.to_dense(), g)
+            res = _sb(self.to_dense(), g, scale)
             out.copy_(res.reshape(self.shape))
             return out
         check(rc, "hyc_softmax_topk_restore_bwd")

@@ -6,14 +6,15 @@ from .._lib import check, lib, ptr, require_cuda, stream_of
 BF16 = torch.bfloat16
 
 
-def softmax_backward(y, grad_y):
-    """o = (grad_y - sum(y * grad_y, -1)) * y for a [b, h, n, n] map."""
+def softmax_backward(y, grad_y, scale=1.0):
+    """o = (grad_y - sum(y * grad_y, -1)) * y for a [b, h, n, n] map.  ``scale`` (extension): the bf16 result
+    times ``scale`` as a second bf16 operation, for the layer's ``grad_s / sqrt(head_dim)``."""
     require_cuda(y, grad_y)
     assert grad_y.shape == y.shape
     yc, gc = y.to(BF16).contiguous(), grad_y.to(BF16).contiguous()
     S = yc.shape[-1]
     o = torch.empty_like(yc)
-    check(lib.hyc_softmax_bwd(ptr(yc), ptr(gc), ptr(o), yc.numel() // S, S, stream_of(y)), "hyc_softmax_bwd")
+    check(lib.hyc_softmax_bwd(ptr(yc), ptr(gc), ptr(o), yc.numel() // S, S, float(scale), stream_of(y)), "hyc_softmax_bwd")
     return o
 
 

@@ -137,11 +137,13 @@ int hyc_softmax_topk_restore(const void* val, const uint16_t* col, int k,
                              int64_t rows, int S, void* a_out, int q_bit, void* stream);
 /* Restore fused with softmax_backward (fused_llama_layer_intra_inter_full_fuse.py:414-433: `a_o.to_dense()`
  * followed by `softmax_backward`): out = (g - sum_row(bf16(y * g))) * y with y the restored map, which is
- * never written to HBM.  grad, out [rows, S] bf16.  Returns HYC_ERR_UNSUPPORTED for shapes outside the
+ * never written to HBM.  grad, out [rows, S] bf16.  out_scale != 1 multiplies the bf16 result once more (a second
+ * bf16 operation: the layer's `grad_s / sqrt(head_dim)`, :436).  Returns HYC_ERR_UNSUPPORTED for shapes outside the
  * lane-per-group kernels (S not 64 * 2^n <= 2048, very large k): restore, then hyc_softmax_bwd. */
 int hyc_softmax_topk_restore_bwd(const void* val, const uint16_t* col, int k,
                                  const void* q, const void* scale, const int8_t* zp,
-                                 int64_t rows, int S, const void* grad, void* out, int q_bit, void* stream);
+                                 int64_t rows, int S, const void* grad, void* out, int q_bit, float out_scale,
+                                 void* stream);
 
 /* ---- fused LoRA-SiLU-Hadamard elementwise kernels ------------------------------------- */
 
@@ -212,8 +214,9 @@ int hyc_rope(const void* x, int64_t ldx, void* out, int64_t ldo, const void* cos
 int hyc_softmax_fwd_scale_mask(const void* scores, float scale, const void* mask_or_null, int64_t mask_stride_b,
                                int64_t mask_stride_h, int64_t mask_stride_row, int heads, int M, void* a,
                                int64_t rows, int S, void* stream);
-/* softmax_backward (operators/softmax_kernels.py:7-56): o = (g - sum(y*g)) * y per row. */
-int hyc_softmax_bwd(const void* y, const void* g, void* o, int64_t rows, int S, void* stream);
+/* softmax_backward (operators/softmax_kernels.py:7-56): o = (g - sum(y*g)) * y per row; out_scale != 1 multiplies
+ * the bf16 result once more (o = bf16(o * out_scale)). */
+int hyc_softmax_bwd(const void* y, const void* g, void* o, int64_t rows, int S, float out_scale, void* stream);
 
 /* ---- tcgen05 / TMEM GEMMs of the LoRA MLP (activation compression in the epilogue) ------------
  * bf16 operands, fp32 accumulation in tensor memory, operands staged by TMA.  `status` is a

@@ -183,6 +183,11 @@ def test_topk_restore_fused_with_softmax_backward(cf, q, shape):
     assert (out.float() - two.float()).abs().max() <= 1e-2 * scale
     buf = torch.empty_like(y)
     assert m.softmax_backward(grad.to(DEV), out=buf) is buf and torch.equal(buf, out)
+    # the optional output scale is a second bf16 operation on the unscaled result
+    sc = 1.0 / 128 ** 0.5
+    want = (out.float() * torch.tensor(sc, dtype=torch.float32)).to(torch.bfloat16)
+    assert torch.equal(m.softmax_backward(grad.to(DEV), scale=sc), want)
+    assert torch.equal(softmax_backward(y, grad.to(DEV), scale=sc), (two.float() * torch.tensor(sc, dtype=torch.float32)).to(torch.bfloat16))
 
 
 def test_topk_config1_full_size_properties(cf):
