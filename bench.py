@@ -463,11 +463,24 @@ def layer_workload(dev, dist=None, steps=10, warmup=3):
     layer.check_kernel_status = False
     t = time_loop(step, steps, warmup)
     world = 1
+    graph_ms = None
     if dist is not None:
         world = dist.get_world_size()
         tt = torch.tensor([t], device=dev)
         dist.all_reduce(tt, op=dist.ReduceOp.MAX)
         t = float(tt.item())
+    else:
+        # the steady-state step (module forward + autograd backward) is a fixed launch sequence: captured once,
+        # replayed without host work between the launches
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            step(0)
+        torch.cuda.current_stream().wait_stream(side)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            step(0)
+        graph_ms = time_loop(lambda i: graph.replay(), steps, warmup) / steps * 1e3
     T = B * M
     # frozen GEMMs (no weight gradient): 2 flop x (fwd + bwd) per weight element; attention products 4 M d per
     # head and token forward (scores + P.V over the full, unskipped square), twice that backward; rank-16 terms:
@@ -478,7 +491,7 @@ def layer_workload(dev, dist=None, steps=10, warmup=3):
     return {"workload": "fused decoder layer fwd+bwd through the layer module, Llama-2-7B geometry, seq 2048, batch 1 per GPU, "
                         "q_bit 4, map top-k 5 % (one of the 32 layers of BASELINE configs[4])",
             "metric": "tokens/s", "value": world * T * steps / t, "unit": "tokens/s (one layer)", "ms_per_step": t / steps * 1e3,
-            "tokens_per_gpu": T, "flop_per_token": flop_per_token,
+            "tokens_per_gpu": T, "flop_per_token": flop_per_token, "cuda_graph_replay_ms_per_step": graph_ms,
             "roofline": {"bound": "tensor", "achieved": tf, "peak": sustained, "unit": "TFLOP/s", "frac": tf / sustained,
                          "peak_source": src + " (sustained)"},
             "note": "the two attention products per direction are library batched GEMMs and, like every pass over the "

@@ -117,6 +117,17 @@ def _hidden(xh):
     return xh.transpose(1, 2).reshape(b * m, n * d)
 
 
+def _matmul_to_hidden(a4, b4):
+    """[B, n, M, K] @ [B, n, K, d] -> contiguous [B*M, n*d]: every batch's product is written by the library GEMM
+    straight into the hidden layout (an [n, M, d] view with strides (d, n*d, 1)), no transposing copy."""
+    B, n, M, _ = a4.shape
+    d = b4.shape[-1]
+    out = torch.empty((B, M, n, d), dtype=a4.dtype, device=a4.device)
+    for b in range(B):
+        torch.bmm(a4[b], b4[b], out=out[b].transpose(0, 1))
+    return out.view(B * M, n * d)
+
+
 def _project(xn2, w, a, b, q_bit, calib, sv, it, thd, status, B):
     """One LoRA projection and the save of its main branch -> (y [T,N], q_main, scale, xa [T,r])."""
     if not calib:
@@ -174,7 +185,7 @@ def attention_forward(x, w: AttnWeights, state: AttnState, cos, sin, attention_m
         a_saved, a_thr = cf.compression_pack_softmax_base(a, state.softmax_outlier_ratio, it, thd, sv['a'])
     else:
         raise ValueError("map_mode must be 'topk' or 'prune'")
-    o2 = _hidden(torch.matmul(a, vh))
+    o2 = _matmul_to_hidden(a, vh)
     a_shape = tuple(a.shape)
     del a
 
@@ -242,7 +253,10 @@ def attention_backward(grad_medium, saved, w: AttnWeights, status=None, on_lora_
         a = cf.decompression_softmax(m).reshape(saved['a_shape'])
     v2 = _rebuild(saved['v_q'], saved['v_scale'], saved['v_xa'], w.bv, q)
     vh = _repeat_kv(_heads(v2, B, M, nkv), n_rep)
-    grad_vh = _repeat_kv_backward(torch.matmul(a.transpose(-2, -1), grad_oh), n_rep)
+    if n_rep == 1:
+        grad_v = _matmul_to_hidden(a.transpose(-2, -1), grad_oh)
+    else:
+        grad_v = _hidden(_repeat_kv_backward(torch.matmul(a.transpose(-2, -1), grad_oh), n_rep))
     grad_a = torch.matmul(grad_oh, vh.transpose(-2, -1))
     del vh, v2
     # ---- softmax backward (for the top-k form fused with a second restore: the map is not re-read)
@@ -257,15 +271,15 @@ def attention_backward(grad_medium, saved, w: AttnWeights, status=None, on_lora_
     # ---- q, k rebuilt from their codes, rotary re-applied
     q2 = _rebuild(saved['q_q'], saved['q_scale'], saved['q_xa'], w.bq, q)
     rope_inplace(q2.view(B, M, nh, d), cos, sin)
-    grad_kh = _repeat_kv_backward(torch.matmul(grad_s.transpose(-2, -1), _heads(q2, B, M, nh)), n_rep)
+    if n_rep == 1:
+        grad_k = _matmul_to_hidden(grad_s.transpose(-2, -1), _heads(q2, B, M, nh))
+    else:
+        grad_k = _hidden(_repeat_kv_backward(torch.matmul(grad_s.transpose(-2, -1), _heads(q2, B, M, nh)), n_rep))
     del q2
     k2 = _rebuild(saved['k_q'], saved['k_scale'], saved['k_xa'], w.bk, q)
     rope_inplace(k2.view(B, M, nkv, d), cos, sin)
-    grad_qh = torch.matmul(grad_s, _repeat_kv(_heads(k2, B, M, nkv), n_rep))
+    grad_q = _matmul_to_hidden(grad_s, _repeat_kv(_heads(k2, B, M, nkv), n_rep))
     del k2, grad_s
-    grad_q = _hidden(grad_qh)
-    grad_k = _hidden(grad_kh)
-    grad_v = _hidden(grad_vh)
     rope_inplace(grad_q.view(B, M, nh, d), cos, sin, backward=True)
     rope_inplace(grad_k.view(B, M, nkv, d), cos, sin, backward=True)
 
