@@ -309,7 +309,7 @@ def run_profile(args):
                           "tokens_per_s": line["value"], "tflops": line["roofline"]["achieved"]}))
         return
     if args.profile == "layer":
-        line = layer_workload(dev, None, steps=args.steps, warmup=args.warmup)
+        line = layer_workload(dev, None, steps=args.steps, warmup=args.warmup, graph=False)
         print(json.dumps({"profile": "layer", "steps": args.steps, "ms_per_step": line["ms_per_step"],
                           "tokens_per_s": line["value"], "tflops": line["roofline"]["achieved"]}))
         return
@@ -392,7 +392,7 @@ def mlp_workload(dev, dist=None, steps=20, warmup=4):
             "LoRA-gradient all-reduce inside the step when n_gpus > 1"}
 
 
-def layer_workload(dev, dist=None, steps=10, warmup=3):
+def layer_workload(dev, dist=None, steps=10, warmup=3, graph=True):
     """One fused decoder layer (attention + MLP) forward + backward at the Llama-2-7B geometry of BASELINE
     configs[4]: hidden 4096, 32 heads of 128, intermediate 11008, sequence 2048, batch 1 per GPU, causal mask,
     LoRA rank 16 on q/k/v/o/gate/up/down, saved activations 4-bit with 0.5 % outlier channels, the probability
@@ -469,7 +469,7 @@ def layer_workload(dev, dist=None, steps=10, warmup=3):
         tt = torch.tensor([t], device=dev)
         dist.all_reduce(tt, op=dist.ReduceOp.MAX)
         t = float(tt.item())
-    else:
+    elif graph:
         # the steady-state step (module forward + autograd backward) is a fixed launch sequence: captured once,
         # replayed without host work between the launches
         side = torch.cuda.Stream()
