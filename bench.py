@@ -459,8 +459,14 @@ def layer_workload(dev, dist=None, steps=10, warmup=3, graph=True):
     for i in range(6):
         step(i)
     layer.check_kernel_status = True
+    layer.track_saved_bytes = True
     step(6)
     layer.check_kernel_status = False
+    layer.track_saved_bytes = False
+    saved_bytes = layer.last_saved_bytes
+    # the same tensors kept as plain bf16 (x, x_norm_1, q, k, v, o, x_medium, x_norm_2: T x H each; gate and up main
+    # branches: T x I each; the probability map)
+    dense_bytes = 2 * (8 * B * M * H + 2 * B * M * I + B * heads * M * M)
     t = time_loop(step, steps, warmup)
     world = 1
     graph_ms = None
@@ -492,6 +498,7 @@ def layer_workload(dev, dist=None, steps=10, warmup=3, graph=True):
                         "q_bit 4, map top-k 5 % (one of the 32 layers of BASELINE configs[4])",
             "metric": "tokens/s", "value": world * T * steps / t, "unit": "tokens/s (one layer)", "ms_per_step": t / steps * 1e3,
             "tokens_per_gpu": T, "flop_per_token": flop_per_token, "cuda_graph_replay_ms_per_step": graph_ms,
+            "saved_for_backward_bytes": saved_bytes, "same_tensors_in_bf16_bytes": dense_bytes,
             "roofline": {"bound": "tensor", "achieved": tf, "peak": sustained, "unit": "TFLOP/s", "frac": tf / sustained,
                          "peak_source": src + " (sustained)"},
             "note": "the two attention products per direction are library batched GEMMs and, like every pass over the "

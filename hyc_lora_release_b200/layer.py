@@ -23,7 +23,21 @@ from .mlp import MLPState, MLPWeights, _status_tensor, check_status, mlp_backwar
 
 BF16 = torch.bfloat16
 
-_LORA_ORDER = ("aq", "bq", "ak", "bk", "av", "bv", "ao", "bo", "ag", "bg", "au", "bu", "ad", "bd")
+def saved_nbytes(saved):
+    """Bytes of device memory a ``saved`` dictionary of ``attention_forward`` / ``mlp_forward`` keeps alive between
+    the two passes (tensors, the top-k map handle, a sparse COO map); the shared rotary tables are not counted."""
+    total = 0
+    for key, v in saved.items():
+        if key in ("cos", "sin"):
+            continue
+        if isinstance(v, torch.Tensor):
+            if v.is_sparse:
+                total += v.indices().numel() * 8 + v.values().numel() * v.values().element_size()
+            else:
+                total += v.numel() * v.element_size()
+        elif hasattr(v, "nbytes") and callable(v.nbytes):
+            total += v.nbytes()
+    return total
 
 
 class FusedLayerFunction(torch.autograd.Function):
@@ -37,6 +51,8 @@ class FusedLayerFunction(torch.autograd.Function):
         x_medium, sa = attention_forward(x, aw, module.attn_state, cos, sin, attention_mask, num_heads, head_dim,
                                          num_key_value_heads, status=st)
         y, sm = mlp_forward(x_medium, mw, module.mlp_state, status=st)
+        if module.track_saved_bytes:
+            module.last_saved_bytes = saved_nbytes(sa) + saved_nbytes(sm)
         ctx.hyc = (sa, sm, aw, mw, st, module)
         return y
 
@@ -81,6 +97,8 @@ class FusedLlamaLayerIntraInterFullFuse(torch.nn.Module):
         self.use_hyclora = True
         self.on_lora_grads = None          # optional callable(dict of LoRA gradients): start their all-reduce early
         self.check_kernel_status = False   # True: read the bounded-wait status word back after every backward pass
+        self.track_saved_bytes = False     # True: forward records the bytes kept for backward in last_saved_bytes
+        self.last_saved_bytes = None
         self._weights = None
 
     # ---- the reference's attributes
