@@ -39,6 +39,16 @@ def test_argument_validation_without_device():
     assert lib.hyc_softmax_topk_compress(p, 1, 8192, 10, p, p, p, p, p, 4, None) == -3     # S too large
     assert lib.hyc_fused_lora_silu_hadamard_fwd(p, p, p, p, p, p, p, p, p, p, p, 16, 64, 8, 4, None) == -8
     assert lib.hyc_softmax_prune_workspace_bytes(4096 * 3 + 1) == 8 * 5
+    # rotary embedding and scale + mask + softmax: geometry and alignment are checked before any launch
+    assert lib.hyc_rope(None, 128, p, 128, p, p, 64, 0, 4, 4, 1, 128, 0, None) == -1
+    assert lib.hyc_rope(p, 128, p, 128, p, p, 64, 0, 4, 4, 1, 24, 0, None) == -3           # head_dim % 16
+    assert lib.hyc_rope(p, 64, p, 128, p, p, 64, 0, 4, 4, 1, 128, 0, None) == -3           # row stride < heads * head_dim
+    assert lib.hyc_rope(p, 132, p, 132, p, p, 64, 0, 4, 4, 1, 128, 0, None) == -4          # stride not a multiple of 8
+    assert lib.hyc_rope(p, 128, p, 128, p, p, 64, 0, 0, 4, 1, 128, 0, None) == 0           # no rows
+    assert lib.hyc_softmax_fwd_scale_mask(p, 1.0, None, 0, 0, 0, 1, 4, p, 4, 60, None) == -3       # S % 8
+    assert lib.hyc_softmax_fwd_scale_mask(p, 1.0, p, 0, 0, 68, 1, 4, p, 4, 64, None) == -4         # mask row stride
+    assert lib.hyc_softmax_fwd_scale_mask(p, 1.0, None, 0, 0, 0, 1, 4, p, 0, 64, None) == 0        # no rows
+    assert lib.hyc_softmax_bwd(p, p, None, 4, 64, 1.0, None) == -1
     assert b"q_bit" in lib.hyc_strerror(-2)
 
 
