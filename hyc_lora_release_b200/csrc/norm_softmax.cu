@@ -28,6 +28,25 @@ __device__ __forceinline__ float block_sum(float v) {
   return r;
 }
 
+// two sums with one pair of barriers
+__device__ __forceinline__ void block_sum2(float a, float b, float& ra, float& rb) {
+  __shared__ float2 s_p2[kNormThreads / 32];
+  __shared__ float2 s_tot2;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) { a += __shfl_xor_sync(0xffffffffu, a, o); b += __shfl_xor_sync(0xffffffffu, b, o); }
+  if ((threadIdx.x & 31) == 0) s_p2[threadIdx.x >> 5] = make_float2(a, b);
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float ta = 0.f, tb = 0.f;
+#pragma unroll
+    for (int i = 0; i < kNormThreads / 32; ++i) { ta += s_p2[i].x; tb += s_p2[i].y; }
+    s_tot2 = make_float2(ta, tb);
+  }
+  __syncthreads();
+  ra = s_tot2.x; rb = s_tot2.y;
+  __syncthreads();
+}
+
 __device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
   f[0] = bf16lo_to_f32(v.x); f[1] = bf16hi_to_f32(v.x); f[2] = bf16lo_to_f32(v.y); f[3] = bf16hi_to_f32(v.y);
   f[4] = bf16lo_to_f32(v.z); f[5] = bf16hi_to_f32(v.z); f[6] = bf16lo_to_f32(v.w); f[7] = bf16hi_to_f32(v.w);
@@ -82,17 +101,18 @@ rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
   }
 }
 
-__global__ void __launch_bounds__(kNormThreads)
+template <int NV>
+__global__ void __launch_bounds__(kNormThreads, NV <= 2 ? 4 : 1)
 rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
                    const __nv_bfloat16* __restrict__ w, const float* __restrict__ rstd,
                    __nv_bfloat16* __restrict__ dx, int64_t rows, int N) {
   const int nvec = N / 8;
   for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
     const float rs = rstd[row];
-    uint4 xv[kNormMaxVec], gv[kNormMaxVec];
+    uint4 xv[NV], gv[NV];
     float s1 = 0.f, s2 = 0.f;
 #pragma unroll
-    for (int i = 0; i < kNormMaxVec; ++i) {
+    for (int i = 0; i < NV; ++i) {
       const int v = threadIdx.x + i * kNormThreads;
       if (v < nvec) {
         xv[i] = ld_stream_v4(x + row * N + 8 * v);
@@ -108,10 +128,11 @@ rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __
         }
       }
     }
-    const float c1 = block_sum(s1) / (float)N;
-    const float c2 = block_sum(s2) / (float)N;
+    float c1, c2;
+    block_sum2(s1, s2, c1, c2);
+    c1 /= (float)N; c2 /= (float)N;
 #pragma unroll
-    for (int i = 0; i < kNormMaxVec; ++i) {
+    for (int i = 0; i < NV; ++i) {
       const int v = threadIdx.x + i * kNormThreads;
       if (v < nvec) {
         float xf[8], gf[8], wf[8];
@@ -257,8 +278,10 @@ rmsnorm_fwd_save_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16
 // Backward reading the packed x directly: x_hat = de-quantized codes with the outlier columns put back,
 // then the arithmetic of rmsnorm_bwd_kernel; `res` (optional) is added to the result as a bf16 tensor add
 // (the residual branch of the layer's input gradient).
-template <int QBIT>
-__global__ void __launch_bounds__(kNormThreads)
+// NV = octets of a row per thread: rows of up to 4096 columns (NV = 2) leave room for four resident blocks per SM,
+// which matters because a block's row is one dependent chain (loads -> two block sums -> stores)
+template <int QBIT, int NV>
+__global__ void __launch_bounds__(kNormThreads, NV <= 2 ? 4 : 1)
 rmsnorm_bwd_packed_kernel(const __nv_bfloat16* __restrict__ dy, const uint8_t* __restrict__ qx,
                           const __nv_bfloat16* __restrict__ scale_x, const int64_t* __restrict__ oidx, int k,
                           const __nv_bfloat16* __restrict__ oin, const __nv_bfloat16* __restrict__ w,
@@ -270,14 +293,15 @@ rmsnorm_bwd_packed_kernel(const __nv_bfloat16* __restrict__ dy, const uint8_t* _
   const int64_t qld = (int64_t)N * QBIT / 8;
   for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
     const float rs = rstd[row];
-    uint4 xv[kNormMaxVec], gv[kNormMaxVec];
+    uint4 xv[NV], gv[NV], rv[NV];
     float s1 = 0.f, s2 = 0.f;
 #pragma unroll
-    for (int i = 0; i < kNormMaxVec; ++i) {
+    for (int i = 0; i < NV; ++i) {
       const int v = threadIdx.x + i * kNormThreads;
       if (v < nvec) {
         const int col = 8 * v;
         gv[i] = ld_stream_v4(dy + row * N + col);
+        if (res != nullptr) rv[i] = ld_stream_v4(res + row * N + col);     // needed last, fetched with the rest
         uint32_t xw[4];
         octet_load_dequant<QBIT>(qx + row * qld, col, *reinterpret_cast<const uint4*>(scale_x + col), xw);
         if (k > 0) {
@@ -306,10 +330,11 @@ rmsnorm_bwd_packed_kernel(const __nv_bfloat16* __restrict__ dy, const uint8_t* _
         }
       }
     }
-    const float c1 = block_sum(s1) / (float)N;
-    const float c2 = block_sum(s2) / (float)N;
+    float c1, c2;
+    block_sum2(s1, s2, c1, c2);
+    c1 /= (float)N; c2 /= (float)N;
 #pragma unroll
-    for (int i = 0; i < kNormMaxVec; ++i) {
+    for (int i = 0; i < NV; ++i) {
       const int v = threadIdx.x + i * kNormThreads;
       if (v < nvec) {
         float xf[8], gf[8], wf[8];
@@ -322,7 +347,7 @@ rmsnorm_bwd_packed_kernel(const __nv_bfloat16* __restrict__ dy, const uint8_t* _
         }
         uint4 o = pack8(xf);
         if (res != nullptr) {
-          const uint4 r = ld_stream_v4(res + row * N + 8 * v);
+          const uint4 r = rv[i];
           const __nv_bfloat162* op = reinterpret_cast<const __nv_bfloat162*>(&o);
           const __nv_bfloat162* rp = reinterpret_cast<const __nv_bfloat162*>(&r);
           __nv_bfloat162 t[4];
@@ -489,7 +514,10 @@ extern "C" HYC_API int hyc_rmsnorm_fwd_save(const void* x, const void* w, float 
   if (!aligned(x, 16) || !aligned(w, 16) || !aligned(y, 16) || !aligned(scale_x, 16) || !aligned(qx, 8) ||
       (qy && (!aligned(qy, 8) || !aligned(scale_y, 16)))) return HYC_ERR_ALIGN;
   if (rows == 0) return HYC_OK;
-  const int64_t grid = rows < (int64_t)kNumSMs * 8 ? rows : (int64_t)kNumSMs * 8;
+  // resident blocks only: a block computes its per-column constants and the outlier-column map once, then walks
+  // rows with the next row's loads in flight
+  const int64_t cap = (int64_t)kNumSMs * (N <= 2 * kNormThreads * 8 ? 3 : 1);
+  const int64_t grid = rows < cap ? rows : cap;
   const size_t smem = k > 0 ? (size_t)N * 2 : 0;
 #define FS(QB) if (N <= 2 * kNormThreads * 8) FSV(QB, 2); else FSV(QB, kNormMaxVec)
 #define FSV(QB, NVV) rmsnorm_fwd_save_kernel<QB, NVV><<<(int)grid, kNormThreads, smem, (cudaStream_t)stream>>>(       \
@@ -513,13 +541,17 @@ extern "C" HYC_API int hyc_rmsnorm_bwd_packed(const void* dy, const void* qx, co
   if (!aligned(dy, 16) || !aligned(w, 16) || !aligned(dx, 16) || !aligned(scale_x, 16) || !aligned(qx, 8) ||
       (residual_grad && !aligned(residual_grad, 16))) return HYC_ERR_ALIGN;
   if (rows == 0) return HYC_OK;
-  const int64_t grid = rows < (int64_t)kNumSMs * 8 ? rows : (int64_t)kNumSMs * 8;
+  // resident blocks only (each block builds the outlier-column map once and then walks rows)
+  const int64_t cap = (int64_t)kNumSMs * (N <= 2 * kNormThreads * 8 ? 4 : 1);
+  const int64_t grid = rows < cap ? rows : cap;
   const size_t smem = k > 0 ? (size_t)N * 2 : 0;
-#define BP(QB) rmsnorm_bwd_packed_kernel<QB><<<(int)grid, kNormThreads, smem, (cudaStream_t)stream>>>(               \
+#define BPN(QB, NV) rmsnorm_bwd_packed_kernel<QB, NV><<<(int)grid, kNormThreads, smem, (cudaStream_t)stream>>>(      \
       (const __nv_bfloat16*)dy, (const uint8_t*)qx, (const __nv_bfloat16*)scale_x, outlier_idx, k,                   \
       (const __nv_bfloat16*)outlier, (const __nv_bfloat16*)w, rstd, (const __nv_bfloat16*)residual_grad,             \
       (__nv_bfloat16*)dx, rows, N)
+#define BP(QB) do { if (N <= 2 * kNormThreads * 8) BPN(QB, 2); else BPN(QB, kNormMaxVec); } while (0)
   if (q_bit == 2) BP(2); else if (q_bit == 4) BP(4); else BP(8);
+#undef BPN
 #undef BP
   HYC_CHECK_LAUNCH();
   return HYC_OK;
@@ -532,8 +564,12 @@ extern "C" HYC_API int hyc_rmsnorm_bwd(const void* dy, const void* x, const void
   if (!aligned(x, 16) || !aligned(w, 16) || !aligned(dy, 16) || !aligned(dx, 16)) return HYC_ERR_ALIGN;
   if (rows == 0) return HYC_OK;
   int64_t grid = rows < (int64_t)kNumSMs * 8 ? rows : (int64_t)kNumSMs * 8;
-  rmsnorm_bwd_kernel<<<(int)grid, kNormThreads, 0, (cudaStream_t)stream>>>(
-      (const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, rstd, (__nv_bfloat16*)dx, rows, N);
+  if (N <= 2 * kNormThreads * 8)
+    rmsnorm_bwd_kernel<2><<<(int)grid, kNormThreads, 0, (cudaStream_t)stream>>>(
+        (const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, rstd, (__nv_bfloat16*)dx, rows, N);
+  else
+    rmsnorm_bwd_kernel<kNormMaxVec><<<(int)grid, kNormThreads, 0, (cudaStream_t)stream>>>(
+        (const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, rstd, (__nv_bfloat16*)dx, rows, N);
   HYC_CHECK_LAUNCH();
   return HYC_OK;
 }
