@@ -41,7 +41,12 @@ constexpr int STAGE_BYTES = STAGE_A_BYTES + STAGE_B_BYTES;
 constexpr int EPI_WARPS = 8;
 constexpr int THREADS = 64 + 32 * EPI_WARPS;
 constexpr int TMEM_COLS = 512;
-constexpr int EPI_SMEM_BYTES = 3 * BN * 16 * 2 + 4 * BN * 4;   // three bf16 LoRA-B tiles + four float vectors
+// epilogue scratch: 32 KB of tiles followed by BN floats of per-column constants.
+//   STORE    two fp32 LoRA-B tiles [BN][16], then BN quantizer constants
+//   GATEUP   two fp32 LoRA-B tiles [BN/2][16], then (inside the 32 KB) two float vectors of BN/2 constants
+//   GRADDOWN per epilogue warp two [32 rows][32 columns] bf16 tiles (LoRA terms in, results out), then two bf16
+//            scale vectors of BN
+constexpr int EPI_SMEM_BYTES = 2 * BN * 16 * 4 + BN * 4;
 constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + EPI_SMEM_BYTES + 256;
 constexpr uint32_t SPIN_LIMIT = 1u << 22;
 
@@ -171,31 +176,32 @@ __device__ __forceinline__ uint32_t sigmoid2(uint32_t y) {
   const float a = bf16lo_to_f32(y), b = bf16hi_to_f32(y);
   return pack_bf16x2_rn(__fdividef(1.f, 1.f + __expf(-a)), __fdividef(1.f, 1.f + __expf(-b)));
 }
-// dot with an fp32 LoRA-B row in shared memory (gate/up tiles are 128 columns wide, so fp32 rows fit)
+// dot with an fp32 LoRA-B row in shared memory: eight packed two-wide fp32 FMAs (even and odd ranks accumulate
+// side by side, one add joins them) on four 128-bit broadcast loads
+__device__ __forceinline__ uint64_t pair_f32(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
 __device__ __forceinline__ float lora_dot_f32(const float (&xa)[16], const float* __restrict__ brow) {
-  float a = 0.f;
+  uint64_t acc = 0ull;
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
     const float4 b = *reinterpret_cast<const float4*>(brow + 4 * j);
-    a = fmaf(xa[4 * j], b.x, a); a = fmaf(xa[4 * j + 1], b.y, a);
-    a = fmaf(xa[4 * j + 2], b.z, a); a = fmaf(xa[4 * j + 3], b.w, a);
+    asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(acc) : "l"(pair_f32(xa[4 * j], xa[4 * j + 1])), "l"(pair_f32(b.x, b.y)));
+    asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(acc) : "l"(pair_f32(xa[4 * j + 2], xa[4 * j + 3])), "l"(pair_f32(b.z, b.w)));
   }
-  return a;
+  float lo, hi;
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(acc));
+  return lo + hi;
 }
 
-// dot of the thread's LoRA-A row (16 floats) with the bf16 LoRA-B row of a column in shared memory
-// (all lanes read the same 32 bytes: a broadcast)
-__device__ __forceinline__ float lora_dot(const float (&xa)[16], const __nv_bfloat16* __restrict__ brow) {
-  const uint4 u = *reinterpret_cast<const uint4*>(brow), v = *reinterpret_cast<const uint4*>(brow + 8);
-  const uint32_t w[8] = {u.x, u.y, u.z, u.w, v.x, v.y, v.z, v.w};
-  float a = xa[0] * bf16lo_to_f32(w[0]);
-  a = fmaf(xa[1], bf16hi_to_f32(w[0]), a);
-#pragma unroll
-  for (int j = 1; j < 8; ++j) {
-    a = fmaf(xa[2 * j], bf16lo_to_f32(w[j]), a);
-    a = fmaf(xa[2 * j + 1], bf16hi_to_f32(w[j]), a);
-  }
-  return a;
+// LoRA terms of the GRADDOWN epilogue on the legacy tensor path (a rank-16 side product of a tcgen05 kernel)
+__device__ __forceinline__ void mma_bf16_16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};"
+      : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "f"(0.f), "f"(0.f), "f"(0.f), "f"(0.f));
 }
 
 __device__ __forceinline__ void load_xa_row(const __nv_bfloat16* xa, int64_t row, bool valid, float (&out)[16]) {
@@ -230,20 +236,6 @@ __device__ __forceinline__ void stage_lora_tile_f32(const LoraTerm& t, int n0, i
     dst[i] = __bfloat162float(t.bt[(int64_t)(n0 + c) * t.ld_col + (int64_t)r * t.ld_r]);
   }
 }
-// cooperative staging of a LoRA-B tile (ncols x 16, bf16) into shared memory
-__device__ __forceinline__ void stage_lora_tile(const LoraTerm& t, int n0, int ncols, __nv_bfloat16* dst, int et) {
-  if (t.bt == nullptr) return;
-  if (t.ld_r == 1 && t.ld_col == 16 && (reinterpret_cast<uintptr_t>(t.bt) & 15) == 0) {
-    const uint4* src = reinterpret_cast<const uint4*>(t.bt + (int64_t)n0 * 16);
-    for (int i = et; i < ncols * 2; i += 32 * EPI_WARPS) reinterpret_cast<uint4*>(dst)[i] = src[i];
-    return;
-  }
-  for (int i = et; i < ncols * 16; i += 32 * EPI_WARPS) {
-    const int c = i >> 4, r = i & 15;
-    dst[i] = t.bt[(int64_t)(n0 + c) * t.ld_col + (int64_t)r * t.ld_r];
-  }
-}
-
 // The reference byte layout of a 32-column block: byte j carries, at bit QBIT*i, the code of
 // column j + i*SLAB (SLAB = 32/EPP columns, EPP = 8/QBIT).  A block is SLAB bytes = NW words.
 template <int QBIT> struct BlockGeo {
@@ -366,26 +358,108 @@ __device__ __forceinline__ uint32_t dequant_pair(const uint32_t (&w)[BlockGeo<QB
   }
 }
 
+// Word index of 16-byte chunk c (eight columns) of a row in a [32 rows][32 columns] bf16 tile of one epilogue warp.
+// The chunks of a row are permuted by the row number so that the three access patterns of the GRADDOWN epilogue
+// are free of bank conflicts: 32-bit stores in the mma fragment layout (rows g, g + 8 / word t of chunk nt), 128-bit
+// accesses of a lane to its own row, and 128-bit reads of eight rows x four chunks for the coalesced flush.
+__device__ __forceinline__ int gd_chunk(int row, int c) { return row * 16 + ((c ^ ((row >> 1) & 3)) << 2); }
+
+// rows [8k, 8k + 8) of the warp's tile leave as 64 contiguous bytes per row (four lanes per row)
+__device__ __forceinline__ void gd_flush(const uint32_t* R, __nv_bfloat16* out, int64_t row0, int64_t M, int64_t ldo,
+                                         int64_t n, int lane) {
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const int r = 8 * k + (lane >> 2), c = lane & 3;
+    const uint4 v = *reinterpret_cast<const uint4*>(R + gd_chunk(r, c));
+    if (row0 + r < M) *reinterpret_cast<uint4*>(out + (row0 + r) * ldo + n + 8 * c) = v;
+  }
+}
+
+// What a GRADDOWN block reads from global memory, fetched one block ahead: the packed codes of the lane's row and
+// the LoRA-B fragments (mma B operands) of the block's 32 columns for both branches.
 template <int QBIT>
-__device__ __forceinline__ void epi_graddown_block(const Params& p, int64_t row, bool valid, int ncol0, int cb,
-                                                   const uint32_t (&acc)[32],
-                                                   const float (&xa1)[16], const float (&xa2)[16],
-                                                   const __nv_bfloat16* sB1, const __nv_bfloat16* sB2,
+struct GdInputs {
+  uint32_t w1[BlockGeo<QBIT>::NW], w2[BlockGeo<QBIT>::NW];
+  uint32_t bf[16];      // [nt][b1a, b1b, b2a, b2b]
+};
+template <int QBIT>
+__device__ __forceinline__ void gd_fetch(const Params& p, int64_t row0, int lane, int64_t n, GdInputs<QBIT>& in) {
+  const int64_t row = row0 + lane;
+  const bool valid = row < p.M;
+  const int g = lane >> 2, t = lane & 3;
+  load_block_words<QBIT>(p.q1 + (row * p.N + n) * QBIT / 8, valid, in.w1);
+  load_block_words<QBIT>(p.q2 + (row * p.N + n) * QBIT / 8, valid, in.w2);
+  if (p.lpre1 != nullptr) return;      // kernel-uniform: the LoRA terms come from a launch that prepared them
+  const bool fast = p.l1.ld_r == 1 && p.l2.ld_r == 1 && ((p.l1.ld_col | p.l2.ld_col) & 1) == 0;
+#pragma unroll
+  for (int nt = 0; nt < 4; ++nt) {
+    const int64_t nn = n + 8 * nt + g;
+    const __nv_bfloat16* b1p = p.l1.bt + nn * p.l1.ld_col;
+    const __nv_bfloat16* b2p = p.l2.bt + nn * p.l2.ld_col;
+    if (fast) {
+      in.bf[4 * nt] = *reinterpret_cast<const uint32_t*>(b1p + 2 * t);
+      in.bf[4 * nt + 1] = *reinterpret_cast<const uint32_t*>(b1p + 2 * t + 8);
+      in.bf[4 * nt + 2] = *reinterpret_cast<const uint32_t*>(b2p + 2 * t);
+      in.bf[4 * nt + 3] = *reinterpret_cast<const uint32_t*>(b2p + 2 * t + 8);
+    } else {
+      auto two = [](const __nv_bfloat16* q, int64_t r, int64_t ld) {
+        return (uint32_t)__bfloat16_as_ushort(q[r * ld]) | ((uint32_t)__bfloat16_as_ushort(q[(r + 1) * ld]) << 16);
+      };
+      in.bf[4 * nt] = two(b1p, 2 * t, p.l1.ld_r); in.bf[4 * nt + 1] = two(b1p, 2 * t + 8, p.l1.ld_r);
+      in.bf[4 * nt + 2] = two(b2p, 2 * t, p.l2.ld_r); in.bf[4 * nt + 3] = two(b2p, 2 * t + 8, p.l2.ld_r);
+    }
+  }
+}
+
+// One block of 32 rows x 32 columns of the GRADDOWN epilogue, a whole warp at a time (lane = row for the
+// accumulator and the element-wise chain).  The LoRA terms of the two branches are rank-16 products on the legacy
+// tensor path: fragments -> bf16 pairs -> the warp's two shared-memory tiles, from which every lane reads its own
+// row.  The same tiles then collect the results so that they leave as coalesced 64-byte row segments: a lane
+// storing 16 bytes of its own row would make every store instruction touch 32 lines, which throttled the
+// load/store unit and slowed the TMA loads of the main loop.
+template <int QBIT>
+__device__ __forceinline__ void epi_graddown_block(const Params& p, int64_t row0, int lane, int ncol0, int cb,
+                                                   const uint32_t (&acc)[32], const GdInputs<QBIT>& in,
+                                                   const uint32_t (&fa1)[2][4], const uint32_t (&fa2)[2][4],
+                                                   uint32_t* R1, uint32_t* R2,
                                                    const uint32_t* sS1, const uint32_t* sS2) {
-  using G = BlockGeo<QBIT>;
   const int64_t n = (int64_t)ncol0 + cb;
-  uint32_t w1[G::NW], w2[G::NW];
-  load_block_words<QBIT>(p.q1 + (row * p.N + n) * QBIT / 8, valid, w1);
-  load_block_words<QBIT>(p.q2 + (row * p.N + n) * QBIT / 8, valid, w2);
+  const int64_t row = row0 + lane;
+  const bool valid = row < p.M;
+  const int g = lane >> 2, t = lane & 3;
   const bool pre = p.lpre1 != nullptr;      // kernel-uniform
+  if (!pre) {
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt) {
+#pragma unroll
+      for (int mt = 0; mt < 2; ++mt) {
+        float c1[4], c2[4];
+        mma_bf16_16816(c1, fa1[mt], in.bf[4 * nt], in.bf[4 * nt + 1]);
+        mma_bf16_16816(c2, fa2[mt], in.bf[4 * nt + 2], in.bf[4 * nt + 3]);
+        // fragment: (row 16 mt + g, columns 8 nt + 2t, +1) and (row 16 mt + g + 8, same columns)
+        R1[gd_chunk(16 * mt + g, nt) + t] = pack_bf16x2_rn(c1[0], c1[1]);
+        R1[gd_chunk(16 * mt + g + 8, nt) + t] = pack_bf16x2_rn(c1[2], c1[3]);
+        R2[gd_chunk(16 * mt + g, nt) + t] = pack_bf16x2_rn(c2[0], c2[1]);
+        R2[gd_chunk(16 * mt + g + 8, nt) + t] = pack_bf16x2_rn(c2[2], c2[3]);
+      }
+    }
+    __syncwarp();
+  }
+  uint32_t gu_all[16];
 #pragma unroll
   for (int c8 = 0; c8 < 4; ++c8) {
-    uint32_t o[4], gg[4], gu[4];
-    // the LoRA terms of the gate and up branches: read if a GEMM launch prepared them, else 16 FMAs each
-    uint4 pl1 = make_uint4(0u, 0u, 0u, 0u), pl2 = pl1;
-    if (pre && valid) {
-      pl1 = *reinterpret_cast<const uint4*>(p.lpre1 + row * p.ld_pre + n + 8 * c8);
-      pl2 = *reinterpret_cast<const uint4*>(p.lpre2 + row * p.ld_pre + n + 8 * c8);
+    uint32_t o[4], gg[4];
+    // the LoRA terms of the lane's row: from the warp's tiles, or from a launch that prepared them
+    uint4 pl1, pl2;
+    if (pre) {
+      pl1 = make_uint4(0u, 0u, 0u, 0u); pl2 = pl1;
+      if (valid) {
+        pl1 = *reinterpret_cast<const uint4*>(p.lpre1 + row * p.ld_pre + n + 8 * c8);
+        pl2 = *reinterpret_cast<const uint4*>(p.lpre2 + row * p.ld_pre + n + 8 * c8);
+      }
+    } else {
+      pl1 = *reinterpret_cast<const uint4*>(R1 + gd_chunk(lane, c8));
+      pl2 = *reinterpret_cast<const uint4*>(R2 + gd_chunk(lane, c8));
     }
     const uint32_t pw1[4] = {pl1.x, pl1.y, pl1.z, pl1.w}, pw2[4] = {pl2.x, pl2.y, pl2.z, pl2.w};
 #pragma unroll
@@ -393,35 +467,34 @@ __device__ __forceinline__ void epi_graddown_block(const Params& p, int64_t row,
       const int c = 8 * c8 + 2 * e2, tc = cb + c;
       // the LoRA part of grad_down arrived as an extra K block
       const uint32_t gd = pack_bf16x2_rn(__uint_as_float(acc[c]), __uint_as_float(acc[c + 1]));
-      const uint32_t x1 = dequant_pair<QBIT>(w1, c, sS1[tc >> 1]);
-      const uint32_t x2 = dequant_pair<QBIT>(w2, c, sS2[tc >> 1]);
-      uint32_t l1, l2;
-      if (pre) {
-        l1 = pw1[e2]; l2 = pw2[e2];
-      } else {
-        l1 = pack_bf16x2_rn(lora_dot(xa1, sB1 + tc * 16), lora_dot(xa1, sB1 + (tc + 1) * 16));
-        l2 = pack_bf16x2_rn(lora_dot(xa2, sB2 + tc * 16), lora_dot(xa2, sB2 + (tc + 1) * 16));
-      }
-      const uint32_t y1 = add2(x1, l1), sig = sigmoid2(y1), y1s = mul2(y1, sig), y2 = add2(x2, l2);
+      const uint32_t x1 = dequant_pair<QBIT>(in.w1, c, sS1[tc >> 1]);
+      const uint32_t x2 = dequant_pair<QBIT>(in.w2, c, sS2[tc >> 1]);
+      const uint32_t y1 = add2(x1, pw1[e2]), sig = sigmoid2(y1), y1s = mul2(y1, sig), y2 = add2(x2, pw2[e2]);
       o[e2] = mul2(y1s, y2);
-      gu[e2] = mul2(gd, y1s);
+      gu_all[4 * c8 + e2] = mul2(gd, y1s);
       const uint32_t inner = add2(kOne2, mul2(y1, sub2(kOne2, sig)));
       gg[e2] = mul2(mul2(gd, y2), mul2(sig, inner));
     }
-    if (valid) {
-      store4_pairs(p.out0 + row * p.N + n + 8 * c8, o);
-      store4_pairs(p.out1 + row * p.N + n + 8 * c8, gg);
-      store4_pairs(p.out2 + row * p.N + n + 8 * c8, gu);
-    }
+    // chunk c8 of the lane's own row is dead now: the results take its place
+    *reinterpret_cast<uint4*>(R1 + gd_chunk(lane, c8)) = make_uint4(o[0], o[1], o[2], o[3]);
+    *reinterpret_cast<uint4*>(R2 + gd_chunk(lane, c8)) = make_uint4(gg[0], gg[1], gg[2], gg[3]);
   }
+  __syncwarp();
+  gd_flush(R1, p.out0, row0, p.M, p.N, n, lane);
+  gd_flush(R2, p.out1, row0, p.M, p.N, n, lane);
+  __syncwarp();
+#pragma unroll
+  for (int c8 = 0; c8 < 4; ++c8)
+    *reinterpret_cast<uint4*>(R1 + gd_chunk(lane, c8)) = make_uint4(gu_all[4 * c8], gu_all[4 * c8 + 1], gu_all[4 * c8 + 2], gu_all[4 * c8 + 3]);
+  __syncwarp();
+  gd_flush(R1, p.out2, row0, p.M, p.N, n, lane);
+  __syncwarp();     // the tiles are rewritten by the next block
 }
 
-// p.q1 != NULL: the bf16 main product (before the LoRA term and the residual) is also quantized with the
-// per-channel constants sR (staged per tile) and packed: the "linear + save" of a LoRA projection.
 template <int QBIT>
 __device__ __forceinline__ void epi_store_block(const Params& p, int64_t row, bool valid, int ncol0, int cb,
                                                 const uint32_t (&acc)[32], const float (&xa0)[16], const float (&xa1)[16],
-                                                const __nv_bfloat16* sB0, const __nv_bfloat16* sB1, const float* sR) {
+                                                const float* sB0, const float* sB1, const float* sR) {
   using G = BlockGeo<QBIT>;
   const int64_t n = (int64_t)ncol0 + cb;
   const bool has0 = p.l0.bt != nullptr, has1 = p.l1.bt != nullptr;
@@ -445,8 +518,8 @@ __device__ __forceinline__ void epi_store_block(const Params& p, int64_t row, bo
         put_code<QBIT>(w1, c, fastq_code_bits<QBIT>(bf16lo_to_f32(v), sR[tc]) & G::CM);
         put_code<QBIT>(w1, c + 1, fastq_code_bits<QBIT>(bf16hi_to_f32(v), sR[tc + 1]) & G::CM);
       }
-      if (has0) v = add2(v, pack_bf16x2_rn(lora_dot(xa0, sB0 + tc * 16), lora_dot(xa0, sB0 + (tc + 1) * 16)));
-      if (has1) v = add2(v, pack_bf16x2_rn(lora_dot(xa1, sB1 + tc * 16), lora_dot(xa1, sB1 + (tc + 1) * 16)));
+      if (has0) v = add2(v, pack_bf16x2_rn(lora_dot_f32(xa0, sB0 + tc * 16), lora_dot_f32(xa0, sB0 + (tc + 1) * 16)));
+      if (has1) v = add2(v, pack_bf16x2_rn(lora_dot_f32(xa1, sB1 + tc * 16), lora_dot_f32(xa1, sB1 + (tc + 1) * 16)));
       if (has_res) v = add2(v, r[e2]);
       o[e2] = v;
     }
@@ -594,12 +667,16 @@ mlp_gemm_kernel(const __grid_constant__ CUtensorMap mapA1, const __grid_constant
     const int et = threadIdx.x - 64;
     const int quad = warp & 3;
     const int chalf = (warp - 2) >> 2;
-    __nv_bfloat16* sB0 = epi_b;                  // [BN][16]
-    __nv_bfloat16* sB1 = epi_b + BN * 16;
-    __nv_bfloat16* sB2 = epi_b + 2 * BN * 16;
-    float* sV = reinterpret_cast<float*>(epi_b + 3 * BN * 16);    // four float vectors of BN
-    float* sF0 = reinterpret_cast<float*>(epi_b);                 // GATEUP: [TILE_N][16] floats each
+    // scratch of the epilogue warps (layout: see EPI_SMEM_BYTES)
+    float* sG1 = reinterpret_cast<float*>(epi_b);                 // STORE: two fp32 LoRA-B tiles of BN columns
+    float* sG2 = sG1 + BN * 16;
+    float* sGV = sG2 + BN * 16;                                   // STORE: BN quantizer constants
+    __nv_bfloat16* sGS = reinterpret_cast<__nv_bfloat16*>(sGV);   // GRADDOWN: two bf16 scale vectors of BN
+    uint32_t* sR1 = reinterpret_cast<uint32_t*>(epi_b) + (warp - 2) * 1024;   // GRADDOWN: this warp's two tiles
+    uint32_t* sR2 = sR1 + 512;
+    float* sF0 = sG1;                                             // GATEUP: two tiles of BN/2 columns ...
     float* sF1 = sF0 + (BN / 2) * 16;
+    float* sV = sG2;                                              // ... and two float vectors at sV, sV + BN
     int it = 0;
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++it) {
       const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * TILE_N;
@@ -611,9 +688,9 @@ mlp_gemm_kernel(const __grid_constant__ CUtensorMap mapA1, const __grid_constant
 
       // stage the per-tile LoRA-B rows and scales (previous tile's readers are done: barrier at the end)
       if (EPI == EPI_STORE) {
-        stage_lora_tile(p.l0, n0, BN, sB0, et);
-        stage_lora_tile(p.l1, n0, BN, sB1, et);
-        if (p.q1 != nullptr) sV[et] = fastq_scale<QBIT>(__frcp_rn(__bfloat162float(p.s1[n0 + et])));
+        stage_lora_tile_f32(p.l0, n0, BN, sG1, et);
+        stage_lora_tile_f32(p.l1, n0, BN, sG2, et);
+        if (p.q1 != nullptr) sGV[et] = fastq_scale<QBIT>(__frcp_rn(__bfloat162float(p.s1[n0 + et])));
       } else if (EPI == EPI_GATEUP) {
         // 128 output columns per tile: the two LoRA-B tiles fit as fp32 rows (2 x 8 KB)
         stage_lora_tile_f32(p.l0, n0, TILE_N, sF0, et);
@@ -623,18 +700,41 @@ mlp_gemm_kernel(const __grid_constant__ CUtensorMap mapA1, const __grid_constant
           sV[BN + et] = fastq_scale<QBIT>(__frcp_rn(__bfloat162float(p.s2[n0 + et])));
         }
       } else {
-        if (p.lpre1 == nullptr) {
-          stage_lora_tile(p.l1, n0, BN, sB1, et);
-          stage_lora_tile(p.l2, n0, BN, sB2, et);
-        }
         // the scales stay bf16: column pairs are read as one packed word
-        reinterpret_cast<__nv_bfloat16*>(sV)[et] = p.s1[n0 + et];
-        reinterpret_cast<__nv_bfloat16*>(sV + BN)[et] = p.s2[n0 + et];
+        sGS[et] = p.s1[n0 + et];
+        sGS[BN + et] = p.s2[n0 + et];
       }
-      float xa0[16], xa1[16], xa2[16];
-      if (EPI != EPI_GRADDOWN) load_xa_row(p.l0.xa, row, valid, xa0);
-      load_xa_row(p.l1.xa, row, valid, xa1);
-      if (EPI == EPI_GRADDOWN) load_xa_row(p.l2.xa, row, valid, xa2);
+      float xa0[16], xa1[16];
+      uint32_t fa1[2][4], fa2[2][4];       // GRADDOWN: the warp's LoRA-A rows as mma A fragments (two tiles of 16 rows)
+      GdInputs<QBIT> gin;                  // GRADDOWN: global inputs of the next block, fetched one block ahead
+      if (EPI != EPI_GRADDOWN) {
+        load_xa_row(p.l0.xa, row, valid, xa0);
+        load_xa_row(p.l1.xa, row, valid, xa1);
+      } else {
+        const int g = lane >> 2, t = lane & 3;
+#pragma unroll
+        for (int mt = 0; mt < 2; ++mt) {
+          const int64_t ra = (int64_t)m0 + quad * 32 + 16 * mt + g, rb = ra + 8;
+#pragma unroll
+          for (int j = 0; j < 4; ++j) { fa1[mt][j] = 0u; fa2[mt][j] = 0u; }
+          if (p.l1.xa != nullptr && p.l2.xa != nullptr) {
+            if (ra < p.M) {
+              fa1[mt][0] = *reinterpret_cast<const uint32_t*>(p.l1.xa + ra * 16 + 2 * t);
+              fa1[mt][2] = *reinterpret_cast<const uint32_t*>(p.l1.xa + ra * 16 + 2 * t + 8);
+              fa2[mt][0] = *reinterpret_cast<const uint32_t*>(p.l2.xa + ra * 16 + 2 * t);
+              fa2[mt][2] = *reinterpret_cast<const uint32_t*>(p.l2.xa + ra * 16 + 2 * t + 8);
+            }
+            if (rb < p.M) {
+              fa1[mt][1] = *reinterpret_cast<const uint32_t*>(p.l1.xa + rb * 16 + 2 * t);
+              fa1[mt][3] = *reinterpret_cast<const uint32_t*>(p.l1.xa + rb * 16 + 2 * t + 8);
+              fa2[mt][1] = *reinterpret_cast<const uint32_t*>(p.l2.xa + rb * 16 + 2 * t);
+              fa2[mt][3] = *reinterpret_cast<const uint32_t*>(p.l2.xa + rb * 16 + 2 * t + 8);
+            }
+          }
+        }
+        // the first block's inputs are on their way while the warp waits for the accumulator
+        gd_fetch<QBIT>(p, (int64_t)m0 + quad * 32, lane, (int64_t)n0 + 128 * chalf, gin);
+      }
       epi_bar_sync();
       if (et == 0) TC_STAMP(2, it, 1);
 
@@ -661,9 +761,14 @@ mlp_gemm_kernel(const __grid_constant__ CUtensorMap mapA1, const __grid_constant
           uint32_t acc[32];
           const int cb = 128 * chalf + 32 * ch;
           tc_ld32(t_lane + (uint32_t)cb, acc);
-          if (EPI == EPI_STORE) epi_store_block<QBIT>(p, row, valid, n0, cb, acc, xa0, xa1, sB0, sB1, sV);
-          else epi_graddown_block<QBIT>(p, row, valid, n0, cb, acc, xa1, xa2, sB1, sB2,
-                                        reinterpret_cast<const uint32_t*>(sV), reinterpret_cast<const uint32_t*>(sV + BN));
+          if (EPI == EPI_STORE) {
+            epi_store_block<QBIT>(p, row, valid, n0, cb, acc, xa0, xa1, sG1, sG2, sGV);
+          } else {
+            const GdInputs<QBIT> cur = gin;
+            if (ch < 3) gd_fetch<QBIT>(p, (int64_t)m0 + quad * 32, lane, (int64_t)n0 + cb + 32, gin);
+            epi_graddown_block<QBIT>(p, (int64_t)m0 + quad * 32, lane, n0, cb, acc, cur, fa1, fa2, sR1, sR2,
+                                     reinterpret_cast<const uint32_t*>(sGS), reinterpret_cast<const uint32_t*>(sGS + BN));
+          }
         }
       }
       tc_fence_before();

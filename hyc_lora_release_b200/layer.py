@@ -53,12 +53,12 @@ class FusedLayerFunction(torch.autograd.Function):
         y, sm = mlp_forward(x_medium, mw, module.mlp_state, status=st)
         if module.track_saved_bytes:
             module.last_saved_bytes = saved_nbytes(sa) + saved_nbytes(sm)
-        ctx.hyc = (sa, sm, aw, mw, st, module)
-        return y
+        ctx.hyc = (sa, sm, aw, mw, st, module, x.dtype)
+        return y.to(x.dtype)
 
     @staticmethod
     def backward(ctx, grad_y):
-        sa, sm, aw, mw, st, module = ctx.hyc
+        sa, sm, aw, mw, st, module, x_dtype = ctx.hyc
         ctx.hyc = None
         hook = module.on_lora_grads
         gm = mlp_backward(grad_y, sm, mw, status=st, on_lora_grads=hook)
@@ -68,7 +68,7 @@ class FusedLayerFunction(torch.autograd.Function):
         grads = [ga['grad_aq'], ga['grad_bq'], ga['grad_ak'], ga['grad_bk'], ga['grad_av'], ga['grad_bv'],
                  ga['grad_ao'], ga['grad_bo'], gm['grad_ag'], gm['grad_bg'], gm['grad_au'], gm['grad_bu'],
                  gm['grad_ad'], gm['grad_bd']]
-        return (ga['grad_x'],) + (None,) * 9 + tuple(grads)
+        return (ga['grad_x'].to(x_dtype),) + (None,) * 9 + tuple(grads)
 
 
 def _frozen(base, name):
