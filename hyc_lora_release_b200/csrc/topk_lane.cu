@@ -158,13 +158,22 @@ topk_lane_compress_kernel(const __nv_bfloat16* __restrict__ a, int64_t rows, int
       for (int h = 1; h >= 0; --h) {
         uint32_t bits = h ? sel1 : sel0;
         const uint32_t colh = (64u * (uint32_t)lr + 32u * h) << 16;
+        // two elements per trip: the busiest lane of the warp sets the number of trips (the large entries of a
+        // causal row sit in few groups), and each trip is a load -> store chain
         while (bits) {
-          const uint32_t e = 31u - (uint32_t)__clz(bits);
-          bits ^= 1u << e;
-          uint16_t* at = sx16 + ((e + 32u * h) ^ sw8);
-          const uint32_t v = *at;
-          *at = 0;
-          *--slot = (colh + (e << 16)) | v;
+          const uint32_t e0 = 31u - (uint32_t)__clz(bits);
+          bits ^= 1u << e0;
+          const bool two = bits != 0u;
+          const uint32_t e1 = two ? 31u - (uint32_t)__clz(bits) : e0;
+          bits &= ~(1u << e1);
+          uint16_t* at0 = sx16 + ((e0 + 32u * h) ^ sw8);
+          uint16_t* at1 = sx16 + ((e1 + 32u * h) ^ sw8);
+          const uint32_t v0 = *at0, v1 = *at1;
+          *at0 = 0;
+          *at1 = 0;                      // the same halfword again when there was only one
+          slot[-1] = (colh + (e0 << 16)) | v0;
+          if (two) slot[-2] = (colh + (e1 << 16)) | v1;
+          slot -= two ? 2 : 1;
         }
       }
       __syncwarp();
