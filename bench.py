@@ -342,24 +342,30 @@ def run_profile(args):
                       "GBps": args.steps * nbytes / t / 1e9}))
 
 
-def mlp_workload(dev, dist=None, steps=20, warmup=4):
-    """Fused LoRA-SiLU-Hadamard MLP forward + backward at Llama-2-7B shapes (BASELINE configs[2]):
-    x [4,512,4096] per GPU, frozen W ~ N(0, .02), LoRA rank 16, saved activations 4-bit with 0.5 % outlier
-    channels; calibration (5 iterations) happens before the timed region.  With several ranks every rank
-    runs its own token shard and the LoRA gradients are all-reduced inside the timed step."""
+def mlp_workload(dev, dist=None, steps=20, warmup=4, shape="llama", q_bit=4):
+    """Fused LoRA-SiLU-Hadamard MLP forward + backward.  shape "llama" = BASELINE configs[2]: x [4,512,4096] per
+    GPU, intermediate 11008, 0.5 % outlier channels x30; shape "mistral" = BASELINE configs[3]: 8192 tokens per GPU,
+    intermediate 14336, 1 % outlier channels x20.  Frozen W ~ N(0, .02), LoRA rank 16, saved activations q_bit
+    wide; calibration (5 iterations) happens before the timed region.  With several ranks every rank runs its
+    own token shard and the LoRA gradients are all-reduced inside the timed step."""
     from hyc_lora_release_b200 import mlp, parallel
     g = torch.Generator().manual_seed(4321)
-    B, M, H, I, R = 4, 512, 4096, 11008, 16
+    if shape == "llama":
+        B, M, H, I, R, n_out, amp, ratio = 4, 512, 4096, 11008, 16, 20, 30, 0.005
+        name = "Llama-2-7B shapes, x [4,512,4096] per GPU, q_bit %d (BASELINE configs[2])" % q_bit
+    else:
+        B, M, H, I, R, n_out, amp, ratio = 1, 8192, 4096, 14336, 16, 41, 20, 0.01
+        name = "Mistral-7B shapes, x [1,8192,4096] per GPU, q_bit %d (BASELINE configs[3])" % q_bit
     T = B * M
     rn = lambda *sh, sc=1.0: (torch.randn(*sh, generator=g) * sc).to(torch.bfloat16).to(dev)
     x = torch.randn(B, M, H, generator=g)
-    x[:, :, torch.randperm(H, generator=g)[:20]] *= 30
+    x[:, :, torch.randperm(H, generator=g)[:n_out]] *= amp
     x = x.to(torch.bfloat16).to(dev)
     ku = lambda out, inp: ((torch.rand(out, inp, generator=g) * 2 - 1) * (1.0 / inp) ** 0.5).to(torch.bfloat16).to(dev)
     W = mlp.MLPWeights(norm_w=torch.ones(H, dtype=torch.bfloat16, device=dev),
                        wg=rn(I, H, sc=.02), wu=rn(I, H, sc=.02), wd=rn(H, I, sc=.02),
                        ag=ku(R, H), bg=rn(I, R, sc=.02), au=ku(R, H), bu=rn(I, R, sc=.02), ad=ku(R, I), bd=rn(H, R, sc=.02))
-    state = mlp.MLPState(q_bit=4, layernorm_outlier_ratio=0.005)
+    state = mlp.MLPState(q_bit=q_bit, layernorm_outlier_ratio=ratio)
     st = torch.zeros(1, dtype=torch.int32, device=dev)
     gout = rn(B, M, H)
 
@@ -383,7 +389,7 @@ def mlp_workload(dev, dist=None, steps=20, warmup=4):
     flop_per_token = 12 * H * I + R * (18 * H + 22 * I)
     burst, sustained, src = tensor_peaks()
     tf = T * flop_per_token * steps / t / 1e12
-    return {"workload": "fused LoRA-SiLU-Hadamard MLP fwd+bwd, Llama-2-7B shapes, x [4,512,4096] per GPU, q_bit 4 (BASELINE configs[2])",
+    return {"workload": "fused LoRA-SiLU-Hadamard MLP fwd+bwd, " + name, "q_bit": q_bit,
             "metric": "tokens/s", "value": world * T * steps / t, "unit": "tokens/s", "ms_per_step": t / steps * 1e3,
             "tokens_per_gpu": T, "flop_per_token": flop_per_token,
             "roofline": {"bound": "tensor", "achieved": tf, "peak": sustained, "unit": "TFLOP/s", "frac": tf / sustained,
@@ -646,9 +652,14 @@ def main():
                   "(the read-back of one step overlaps the upload of the next)"}
 
     mlp_line = layer_line = None
+    sweep_lines = []
     if not args.no_extras:
         barrier()
         mlp_line = mlp_workload(dev, dist)      # every rank takes part (all-reduce inside)
+        sweep_lines = []
+        for qb in (2, 4, 8):
+            barrier()
+            sweep_lines.append(mlp_workload(dev, dist, steps=10, warmup=3, shape="mistral", q_bit=qb))
         barrier()
         layer_line = layer_workload(dev, dist)
     if rank == 0:
@@ -658,6 +669,7 @@ def main():
             cpu, _, _ = cpu_port_sample()
         if mlp_line is not None:
             also.append(mlp_line)
+        also.extend(sweep_lines)
         if layer_line is not None:
             also.append(layer_line)
         line = {
