@@ -81,10 +81,16 @@ def _frozen(base, name):
     return w
 
 
-def _adapter(mod):
-    """``lora_A`` / ``lora_B`` module dictionary of a PEFT layer (``.default``) or a bare ``nn.Linear``."""
+def _adapter(mod, name, rank_dim):
+    """``lora_A`` / ``lora_B`` module dictionary of a PEFT layer (``.default``) or a bare ``nn.Linear``.
+    The kernels are built for bf16 adapters of rank 16."""
     inner = getattr(mod, "default", mod)
-    return inner.weight
+    w = inner.weight
+    if w.dtype != BF16:
+        raise NotImplementedError("%s: LoRA adapters must be bf16 (got %s)" % (name, w.dtype))
+    if w.dim() != 2 or w.shape[rank_dim] != 16:
+        raise NotImplementedError("%s: LoRA rank must be 16 (weight shape %s)" % (name, tuple(w.shape)))
+    return w
 
 
 class FusedLlamaLayerIntraInterFullFuse(torch.nn.Module):
@@ -137,7 +143,8 @@ class FusedLlamaLayerIntraInterFullFuse(torch.nn.Module):
         tensors = [norm_w1, norm_w2]
         for name in ("q", "k", "v", "o", "gate", "up", "down"):
             base, la, lb = mods[name]
-            tensors += [_frozen(base, name + "_proj"), _adapter(la), _adapter(lb)]
+            tensors += [_frozen(base, name + "_proj"), _adapter(la, name + "_proj lora_A", 0),
+                        _adapter(lb, name + "_proj lora_B", 1)]
         key = tuple(id(t) for t in tensors)
         if self._weights is None or self._weights[0] != key:
             (n1, n2, wq, aq, bq, wk, ak, bk, wv, av, bv, wo, ao, bo, wg, ag, bg, wu, au, bu, wd, ad, bd) = tensors

@@ -218,3 +218,10 @@ def test_layer_module_through_autograd(heads, kv, map_mode):
     bad.weight.quant_state = object()
     with pytest.raises(NotImplementedError):
         layer._bind(n1, n2, {**mods, "q": (bad, mods["q"][1], mods["q"][2])})
+    # so are adapters of another rank or dtype
+    with pytest.raises(NotImplementedError):
+        layer._bind(n1, n2, {**mods, "q": (mods["q"][0], _Holder(torch.zeros(8, H, dtype=BF16)), mods["q"][2])})
+    f32 = _Holder(p["aq"].t().to(DEV))
+    f32.default = f32.default.float()
+    with pytest.raises(NotImplementedError):
+        layer._bind(n1, n2, {**mods, "q": (mods["q"][0], f32, mods["q"][2])})
