@@ -481,7 +481,7 @@ def layer_workload(dev, dist=None, steps=10, warmup=3, graph=True):
         tt = torch.tensor([t], device=dev)
         dist.all_reduce(tt, op=dist.ReduceOp.MAX)
         t = float(tt.item())
-    elif graph:
+    if graph:
         # the steady-state step (module forward + autograd backward) is a fixed launch sequence: captured once,
         # replayed without host work between the launches
         side = torch.cuda.Stream()
@@ -492,7 +492,12 @@ def layer_workload(dev, dist=None, steps=10, warmup=3, graph=True):
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph):
             step(0)
-        graph_ms = time_loop(lambda i: graph.replay(), steps, warmup) / steps * 1e3
+        tg = time_loop(lambda i: graph.replay(), steps, warmup)
+        if dist is not None:       # the captured step holds the all-reduce of the LoRA gradients too
+            tt = torch.tensor([tg], device=dev)
+            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+            tg = float(tt.item())
+        graph_ms = tg / steps * 1e3
     T = B * M
     # frozen GEMMs (no weight gradient): 2 flop x (fwd + bwd) per weight element; attention products 4 M d per
     # head and token forward (scores + P.V over the full, unskipped square), twice that backward; rank-16 terms:
