@@ -598,18 +598,15 @@ mlp_gemm_kernel(const __grid_constant__ CUtensorMap mapA1, const __grid_constant
           mbar_expect_tx(&full[stage], STAGE_BYTES);
           tma_load_2d(sa, ma, &full[stage], k0, m0);
           if (EPI == EPI_GATEUP) {
-            // 128 rows of Wg then 128 rows of Wu: one K-major 256-row B tile (boxes of 64 rows)
+            // 128 rows of Wg then 128 rows of Wu: one K-major 256-row B tile (two boxes of 128 rows)
             tma_load_2d(sb, &mapB1, &full[stage], k0, n0);
-            tma_load_2d(sb + 8192, &mapB1, &full[stage], k0, n0 + 64);
             tma_load_2d(sb + 16384, &mapB2, &full[stage], k0, n0);
-            tma_load_2d(sb + 24576, &mapB2, &full[stage], k0, n0 + 64);
           } else if (B_MN) {
             // [K, N] row-major: four boxes of 64 k-rows x 64 columns (8 KB each)
 #pragma unroll
             for (int j = 0; j < BN / 64; ++j) tma_load_2d(sb + j * 8192, mb, &full[stage], n0 + 64 * j, k0);
           } else {
-#pragma unroll
-            for (int j = 0; j < BN / 64; ++j) tma_load_2d(sb + j * 8192, mb, &full[stage], k0, n0 + 64 * j);
+            tma_load_2d(sb, mb, &full[stage], k0, n0);      // one box of 256 rows x 64 k (fewer, larger requests)
           }
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
@@ -878,16 +875,16 @@ extern "C" HYC_API int hyc_gemm_bf16_tcgen05(
   if ((bt0 != nullptr) != (xa0 != nullptr) || (bt1 != nullptr) != (xa1 != nullptr)) return HYC_ERR_NULL;
   CUtensorMap a1, b1, a2, b2, a3, b3;
   bool ok = make_map(&a1, A, M, K, BM);
-  ok = ok && (b_is_kn ? make_map(&b1, B, K, N, 64) : make_map(&b1, B, N, K, 64));
+  ok = ok && (b_is_kn ? make_map(&b1, B, K, N, 64) : make_map(&b1, B, N, K, 256));
   a2 = a1; b2 = b1;
   if (K2 > 0) {
     ok = ok && make_map(&a2, A2, M, K2, BM);
-    ok = ok && (b_is_kn ? make_map(&b2, B2, K2, N, 64) : make_map(&b2, B2, N, K2, 64));
+    ok = ok && (b_is_kn ? make_map(&b2, B2, K2, N, 64) : make_map(&b2, B2, N, K2, 256));
   }
   a3 = a1; b3 = b1;
   if (K3 > 0) {
     ok = ok && make_map(&a3, A3, M, K3, BM);
-    ok = ok && (b_is_kn ? make_map(&b3, B3, K3, N, 64) : make_map(&b3, B3, N, K3, 64));
+    ok = ok && (b_is_kn ? make_map(&b3, B3, K3, N, 64) : make_map(&b3, B3, N, K3, 256));
   }
   if (!ok) return HYC_ERR_UNSUPPORTED;
   Params p = {};
@@ -915,7 +912,7 @@ extern "C" HYC_API int hyc_mlp_gateup_fwd_tcgen05(
   const void* al[] = {x, wg, wu, xa1, xa2, q1, q2, o};
   for (const void* q : al) if (!aligned(q, 16)) return HYC_ERR_ALIGN;
   CUtensorMap a1, bg, bu;
-  if (!make_map(&a1, x, T, H, BM) || !make_map(&bg, wg, I, H, 64) || !make_map(&bu, wu, I, H, 64)) return HYC_ERR_UNSUPPORTED;
+  if (!make_map(&a1, x, T, H, BM) || !make_map(&bg, wg, I, H, 128) || !make_map(&bu, wu, I, H, 128)) return HYC_ERR_UNSUPPORTED;
   Params p = {};
   p.M = T; p.N = I; p.K1 = H; p.K2 = 0; p.K3 = 0; p.epi = EPI_GATEUP; p.q_bit = q_bit;
   p.l0 = make_term(xa1, b1t, b1_ld_col, b1_ld_r);
@@ -989,7 +986,7 @@ extern "C" HYC_API int hyc_linear_lora_save_fwd_tcgen05(
   if (!aligned(x, 16) || !aligned(w, 16) || !aligned(y, 16) || !aligned(q_out, 16) || (xa && !aligned(xa, 16)) ||
       (main_or_null && !aligned(main_or_null, 16))) return HYC_ERR_ALIGN;
   CUtensorMap a1, b1;
-  if (!make_map(&a1, x, T, K, BM) || !make_map(&b1, w, N, K, 64)) return HYC_ERR_UNSUPPORTED;
+  if (!make_map(&a1, x, T, K, BM) || !make_map(&b1, w, N, K, 256)) return HYC_ERR_UNSUPPORTED;
   Params p = {};
   p.M = T; p.N = N; p.K1 = K; p.K2 = 0; p.K3 = 0; p.epi = EPI_STORE; p.q_bit = q_bit;
   p.l0 = make_term(xa, bt, bt_ld_col, bt_ld_r);
