@@ -241,7 +241,39 @@ def extra_workloads(dev, hbm):
         del xs
     out.append(fused_elementwise_workload(dev, hbm))
     out.append(attention_backward_workload(dev, hbm))
+    out.append(prune_workload(dev, hbm))
     return out
+
+
+def prune_workload(dev, hbm):
+    """The reference's own form of the saved probability map (compress_function.py:309-317): entries above a
+    calibrated global threshold as a sparse COO tensor (int64 index + bf16 value), restored by to_dense.  Headline
+    map [4,32,512,512], ratio 0.05, through the operator API (which reads the number of kept entries back once per
+    call, as to_sparse does).  Algorithmic bytes: the dense map read once and written once, the list written and
+    read (10 bytes per kept entry each way)."""
+    from hyc_lora_release_b200.operators import compress_function as cf
+    maps = [make_map(2000 + i, dev) for i in range(NBUF)]
+    thr = cf.get_statistics_softmax(maps[0], RATIO)
+    handles = [cf.compression_softmax(m, thr) for m in maps]
+    nnz = sum(h.values().numel() for h in handles) / NBUF
+    numel = maps[0].numel()
+    nbytes = numel * 4 + 2 * 10 * nnz
+    t_c = time_loop(lambda i: cf.compression_softmax(maps[i % NBUF], thr), 20, 3) / 20
+    t_d = time_loop(lambda i: cf.decompression_softmax(handles[i % NBUF]), 20, 3) / 20
+    gbs = nbytes / (t_c + t_d) / 1e9
+    # the form the fused layer uses in steady state: fixed-capacity buffers, the count stays on the device
+    thr_f = float(thr)
+    pm = [cf.compression_softmax_static(m, thr_f, ratio=RATIO) for m in maps]
+    dense = [torch.empty(MAP_SHAPE, dtype=torch.bfloat16, device=dev) for _ in range(NBUF)]
+    t_cs = time_loop(lambda i: cf.compression_softmax_static(maps[i % NBUF], thr_f, ratio=RATIO), 20, 3) / 20
+    t_ds = time_loop(lambda i: pm[i % NBUF].to_dense(out=dense[i % NBUF]), 20, 3) / 20
+    return {"workload": "attention-map save/restore in the reference's form: global-threshold prune to sparse COO + to_dense, "
+                        "[4,32,512,512] (BASELINE configs[1] map)", "value": gbs, "unit": "GB/s", "frac_of_hbm": gbs / hbm,
+            "ms_per_step": (t_c + t_d) * 1e3, "kept_fraction": nnz / numel,
+            "kernel_ms": {"compress": t_c * 1e3, "restore": t_d * 1e3},
+            "without_host_sync": {"GBps": nbytes / (t_cs + t_ds) / 1e9, "compress_ms": t_cs * 1e3, "restore_ms": t_ds * 1e3,
+                                  "api": "compression_softmax_static -> PrunedMap.to_dense (count left on the device)"},
+            "launch": "operator calls, CUDA events (compress includes one device-to-host read of the count)"}
 
 
 def attention_backward_workload(dev, hbm):
@@ -514,6 +546,160 @@ def layer_workload(dev, dist=None, steps=10, warmup=3, graph=True):
                          "peak_source": src + " (sustained)"},
             "note": "the two attention products per direction are library batched GEMMs and, like every pass over the "
                     "[1,32,2048,2048] map (softmax, save, restore, softmax backward), bound by HBM, not by the tensor cores"}
+
+
+def model_workload(dev, dist=None, steps=4, warmup=3, n_layers=32, graph=True):
+    """One training step (forward + backward) of the whole 32-layer stack of BASELINE configs[4]: token embedding
+    (vocabulary 32000, hidden 4096), 32 fused decoder layers driven through the layer module (32 heads of 128,
+    intermediate 11008, LoRA rank 16 on q/k/v/o/gate/up/down, 4-bit saves, top-k map), final RMSNorm, the
+    vocabulary projection and a cross-entropy loss on random token ids uniform in [0,32000), sequence 2048,
+    batch 1 per GPU.  Only the adapters train (frozen embedding, norms and head).  Frozen weights are random-init
+    bf16 drawn on the device, distinct per layer.  The LoRA gradients of every layer are all-reduced over NCCL
+    when there are several ranks.  The loss is read back to the host at the end of every step."""
+    import types
+    from hyc_lora_release_b200 import mlp, parallel
+    from hyc_lora_release_b200.layer import FusedLlamaLayerIntraInterFullFuse
+    from hyc_lora_release_b200.operators.rmsnorm_kernels import rmsnorm_backward, rmsnorm_forward
+    B, M, H, heads, d, I, R, V = 1, 2048, 4096, 32, 128, 11008, 16, 32000
+    bf = torch.bfloat16
+    g = torch.Generator(device=dev).manual_seed(4242 + (dist.get_rank() if dist is not None else 0))
+
+    def lin(out, inp, sc=None, grad=False):
+        m = torch.nn.Linear(inp, out, bias=False, device=dev, dtype=bf)
+        with torch.no_grad():
+            if sc is None:
+                m.weight.copy_((torch.rand(out, inp, generator=g, device=dev) * 2 - 1) * (1.0 / inp) ** 0.5)
+            else:
+                m.weight.copy_(torch.randn(out, inp, generator=g, device=dev) * sc)
+        m.weight.requires_grad_(grad)
+        return m
+
+    def adapter(out, inp):
+        a, b = torch.nn.Module(), torch.nn.Module()
+        a.default, b.default = lin(R, inp, grad=True), lin(out, R, sc=.02, grad=True)
+        return a, b
+    dims = dict(q=(H, H), k=(H, H), v=(H, H), o=(H, H), gate=(I, H), up=(I, H), down=(H, I))
+    pos = torch.arange(M, dtype=torch.float32)
+    inv = 1.0 / (10000.0 ** (torch.arange(0, d, 2, dtype=torch.float32) / d))
+    emb_t = torch.cat([torch.outer(pos, inv)] * 2, -1)
+    cos, sin = emb_t.cos().to(bf).to(dev), emb_t.sin().to(bf).to(dev)
+    mask = torch.full((M, M), torch.finfo(bf).min).triu(1).to(bf).reshape(1, 1, M, M).to(dev)
+    cfg = types.SimpleNamespace(use_hyclora=True, iteration_threshold=5, softmax_outlier_ratio=0.05,
+                                layernorm_outlier_ratio=0.005, q_bit=4, softmax_map_mode="topk")
+    pending = []
+    layers, adapters = [], []
+    for _ in range(n_layers):
+        mods = {n: (lin(o_, i_, sc=.02),) + adapter(o_, i_) for n, (o_, i_) in dims.items()}
+        layer = FusedLlamaLayerIntraInterFullFuse()
+        layer.set_hyclora_config(cfg)
+        layer.on_lora_grads = lambda gr: pending.append(parallel.allreduce_lora_grads_async(gr))
+        args = [None, torch.ones(H, dtype=bf, device=dev), None, cos, sin]
+        for n in ("q", "k", "v", "o"):
+            args += list(mods[n])
+        args += [torch.ones(H, dtype=bf, device=dev), None]
+        for n in ("gate", "up", "down"):
+            args += list(mods[n])
+        args += [mask, heads, d, heads]
+        layers.append((layer, args))
+        adapters += [m3[j].default.weight for m3 in mods.values() for j in (1, 2)]
+    embed = (torch.randn(V, H, generator=g, device=dev) * 0.02).to(bf)
+    head_w = (torch.randn(V, H, generator=g, device=dev) * 0.02).to(bf)
+    norm_w = torch.ones(H, dtype=bf, device=dev)
+    status = mlp._status_tensor(dev)
+
+    class NormHead(torch.autograd.Function):
+        """final RMSNorm + vocabulary projection: the norm kernels of the path and the tcgen05 GEMM in both
+        weight orientations (logits = h W^T, grad_h = grad_logits W); frozen weights, so no weight gradient"""
+
+        @staticmethod
+        def forward(ctx, h):
+            h2 = h.reshape(-1, H)
+            y, mean, rstd, blk, warps = rmsnorm_forward(h2, norm_w, 1e-5)
+            ctx.save_for_backward(h2, rstd)
+            ctx.meta = (mean, blk, warps, h.shape)
+            return mlp.gemm(y.reshape(-1, H), head_w, status=status)
+
+        @staticmethod
+        def backward(ctx, g_logits):
+            h2, rstd = ctx.saved_tensors
+            mean, blk, warps, shape = ctx.meta
+            gy = mlp.gemm(g_logits.contiguous(), head_w, b_is_kn=True, status=status)
+            dx, _ = rmsnorm_backward(gy, h2, norm_w, mean, rstd, (True, False), 1e-5, warps, blk)
+            return dx.reshape(shape)
+
+    n_ids = 4
+    ids = [torch.randint(0, V, (B, M), generator=g, device=dev) for _ in range(n_ids)]
+    labels = [torch.randint(0, V, (B * M,), generator=g, device=dev) for _ in range(n_ids)]
+    loss_box = [None]
+
+    def fwd_bwd(i):
+        x = embed[ids[i % n_ids]].requires_grad_(True)
+        for layer, args in layers:
+            args[0] = x
+            x = layer(*args)
+        logits = NormHead.apply(x)
+        loss = torch.nn.functional.cross_entropy(logits.float(), labels[i % n_ids])
+        loss.backward()
+        for p_ in pending:
+            p_.wait()
+        pending.clear()
+        for w_ in adapters:
+            w_.grad = None
+        loss_box[0] = loss.detach()
+
+    def step(i):
+        fwd_bwd(i)
+        return float(loss_box[0].item())      # the device-to-host read of the step's result
+    for i in range(6):                         # calibration iterations of every layer
+        step(i)
+    mlp.check_status(status, "model step")
+    torch.cuda.reset_peak_memory_stats(dev)
+    t = time_loop(step, steps, warmup)
+    peak_mem = torch.cuda.max_memory_allocated(dev)
+    loss_value = step(0)
+    world = 1
+    if dist is not None:
+        world = dist.get_world_size()
+        tt = torch.tensor([t], device=dev)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        t = float(tt.item())
+    graph_ms = None
+    if graph:
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            fwd_bwd(0)
+        torch.cuda.current_stream().wait_stream(side)
+        cg = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(cg):
+            fwd_bwd(0)
+
+        def replay(i):
+            cg.replay()
+            return float(loss_box[0].item())
+        tg = time_loop(replay, steps, warmup)
+        if dist is not None:
+            tt = torch.tensor([tg], device=dev)
+            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+            tg = float(tt.item())
+        graph_ms = tg / steps * 1e3
+        mlp.check_status(status, "model step (graph)")
+    T = B * M
+    per_layer = 4 * (4 * H * H + 3 * H * I) + 12 * M * heads * d + R * (48 * H + 18 * H + 22 * I)
+    flop_per_token = n_layers * per_layer + 4 * H * V
+    burst, sustained, src = tensor_peaks()
+    tf = T * flop_per_token * steps / t / 1e12
+    out = {"workload": "one training step fwd+bwd of the %d-layer Llama-2-7B stack (embedding, fused layers, final norm, "
+                       "vocabulary projection, cross-entropy), random-init bf16, LoRA r=16 on all seven projections, q_bit 4, "
+                       "seq 2048, batch 1 per GPU (BASELINE configs[4])" % n_layers,
+           "metric": "tokens/s", "value": world * T * steps / t, "unit": "tokens/s", "ms_per_step": t / steps * 1e3,
+           "tokens_per_gpu": T, "flop_per_token": flop_per_token, "cuda_graph_replay_ms_per_step": graph_ms,
+           "loss": loss_value, "peak_memory_bytes": peak_mem,
+           "roofline": {"bound": "tensor", "achieved": tf, "peak": sustained, "unit": "TFLOP/s", "frac": tf / sustained,
+                        "peak_source": src + " (sustained)"},
+           "note": "embedding lookup and the cross-entropy are torch glue; every other launch is a kernel of this library "
+                   "except the batched attention products and the rank-16 skinny products (library GEMMs)"}
+    return out
 
 
 def main():

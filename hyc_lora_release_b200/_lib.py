@@ -30,6 +30,7 @@ SIGNATURES = {
     "hyc_softmax_prune_count": (_i, [_p, _l, _f, _p, _z, _p]),
     "hyc_softmax_prune_fill": (_i, [_p, _l, _f, _p, _p, _p, _l, _p]),
     "hyc_softmax_prune_restore": (_i, [_p, _p, _l, _p, _l, _p]),
+    "hyc_softmax_prune_restore_counted": (_i, [_p, _p, _p, _l, _p, _l, _p]),
     "hyc_softmax_prune_static": (_i, [_p, _l, _f, _p, _p, _l, _p, _p]),
     "hyc_softmax_topk_compress": (_i, [_p, _l, _i, _i, _p, _p, _p, _p, _p, _i, _p]),
     "hyc_softmax_topk_restore": (_i, [_p, _p, _i, _p, _p, _p, _l, _i, _p, _i, _p]),

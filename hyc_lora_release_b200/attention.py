@@ -85,6 +85,8 @@ class AttnState:
     softmax_outlier_ratio: float = 0.05
     map_mode: str = "topk"
     map_q_bit: int = 4
+    prune_capacity_margin: float = 1.5     # "prune" steady state: buffers hold margin x ratio x numel entries
+    threshold_host: float = None           # the calibrated threshold as a host number (set after calibration)
     static_value: dict = field(default_factory=lambda: {
         'x': {'outlier_channel_index': None, 'scale': None}, 'x_norm_1': {'scale': None},
         'q': {'scale': None}, 'k': {'scale': None}, 'v': {'scale': None}, 'a': {'outlier': None},
@@ -182,7 +184,16 @@ def attention_forward(x, w: AttnWeights, state: AttnState, cos, sin, attention_m
         a_saved = cf.compression_softmax_topk(a, state.softmax_outlier_ratio, state.map_q_bit)
         a_thr = None
     elif state.map_mode == "prune":
-        a_saved, a_thr = cf.compression_pack_softmax_base(a, state.softmax_outlier_ratio, it, thd, sv['a'])
+        if calib:
+            a_saved, a_thr = cf.compression_pack_softmax_base(a, state.softmax_outlier_ratio, it, thd, sv['a'])
+        else:
+            # steady state: the calibrated threshold as a host number (read once), fixed-capacity buffers and the
+            # count left on the device -> no host synchronisation in the step
+            if state.threshold_host is None:
+                state.threshold_host = float(sv['a']['outlier'])
+            a_thr = None
+            a_saved = cf.compression_softmax_static(a, state.threshold_host, ratio=state.softmax_outlier_ratio,
+                                                    margin=state.prune_capacity_margin)
     else:
         raise ValueError("map_mode must be 'topk' or 'prune'")
     o2 = _matmul_to_hidden(a, vh)
@@ -250,7 +261,8 @@ def attention_backward(grad_medium, saved, w: AttnWeights, status=None, on_lora_
     if saved['map_mode'] == "topk":
         a = m.to_dense()
     else:
-        a = cf.decompression_softmax(m).reshape(saved['a_shape'])
+        a = m.to_dense().reshape(saved['a_shape']) if isinstance(m, cf.PrunedMap) else \
+            cf.decompression_softmax(m).reshape(saved['a_shape'])
     v2 = _rebuild(saved['v_q'], saved['v_scale'], saved['v_xa'], w.bv, q)
     vh = _repeat_kv(_heads(v2, B, M, nkv), n_rep)
     if n_rep == 1:

@@ -125,6 +125,19 @@ prune_scatter_kernel(const int64_t* __restrict__ idx, const __nv_bfloat16* __res
   }
 }
 
+// the same with the number of entries read from device memory (a count that was never copied to the host)
+__global__ void __launch_bounds__(256)
+prune_scatter_counted_kernel(const int64_t* __restrict__ idx, const __nv_bfloat16* __restrict__ val,
+                             const int64_t* __restrict__ nnz_dev, int64_t capacity,
+                             __nv_bfloat16* __restrict__ out, int64_t numel) {
+  int64_t nnz = *nnz_dev;
+  if (nnz > capacity) nnz = capacity;
+  for (int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x; i < nnz; i += (int64_t)gridDim.x * 256) {
+    const int64_t p = idx[i];
+    if (p >= 0 && p < numel) out[p] = val[i];
+  }
+}
+
 static inline int64_t n_tiles_of(int64_t numel) { return (numel + kTileElems - 1) / kTileElems; }
 static inline int tile_grid(int64_t n_tiles) {
   int64_t g = n_tiles < (int64_t)kNumSMs * 8 ? n_tiles : (int64_t)kNumSMs * 8;
@@ -190,6 +203,22 @@ extern "C" HYC_API int hyc_softmax_prune_restore(const int64_t* idx, const void*
     int64_t g = (nnz + 255) / 256;
     if (g > (int64_t)kNumSMs * 16) g = (int64_t)kNumSMs * 16;
     prune_scatter_kernel<<<(int)g, 256, 0, st>>>(idx, (const __nv_bfloat16*)val, nnz, (__nv_bfloat16*)a_out, numel);
+    HYC_CHECK_LAUNCH();
+  }
+  return HYC_OK;
+}
+
+extern "C" HYC_API int hyc_softmax_prune_restore_counted(const int64_t* idx, const void* val, const int64_t* nnz_dev,
+                                                         int64_t capacity, void* a_out, int64_t numel, void* stream) {
+  if (!a_out || !nnz_dev || (capacity > 0 && (!idx || !val))) return HYC_ERR_NULL;
+  if (numel <= 0 || capacity < 0) return HYC_ERR_SHAPE;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (cudaMemsetAsync(a_out, 0, (size_t)numel * 2, st) != cudaSuccess) { hyc_set_last_cuda_error((int)cudaGetLastError()); return HYC_ERR_LAUNCH; }
+  if (capacity > 0) {
+    int64_t g = (capacity + 255) / 256;
+    if (g > (int64_t)kNumSMs * 16) g = (int64_t)kNumSMs * 16;
+    prune_scatter_counted_kernel<<<(int)g, 256, 0, st>>>(idx, (const __nv_bfloat16*)val, nnz_dev, capacity,
+                                                         (__nv_bfloat16*)a_out, numel);
     HYC_CHECK_LAUNCH();
   }
   return HYC_OK;

@@ -14,7 +14,9 @@ attention mask and the head geometry.  Differences, all deliberate:
     be ``"topk"`` for the per-row top-k + 4-bit-group form of the saved probability map.
 
 After the calibration iterations a step launches a fixed sequence of kernels with no host synchronisation in
-``"topk"`` mode (the ``"prune"`` mode reads the number of kept entries back, as ``to_sparse`` does).
+either mode: the ``"prune"`` mode then keeps its list in buffers of a fixed capacity (1.5 x ratio x numel entries,
+``AttnState.prune_capacity_margin``) with the count left on the device, instead of a sparse tensor whose size the
+host has to read back.
 """
 import torch
 

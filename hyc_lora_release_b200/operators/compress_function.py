@@ -290,6 +290,62 @@ def decompression_softmax(x_sparse: torch.Tensor):
     return out
 
 
+class PrunedMap:
+    """The threshold-pruned map with its length left on the device: index and value buffers of a fixed
+    capacity plus a device-side count.  ``to_dense()`` is what the layers call on their sparse handle; nothing
+    here synchronises with the host, so a training step that uses it is a fixed launch sequence."""
+
+    def __init__(self, idx, val, nnz, shape):
+        self.idx, self.val, self.nnz, self.shape = idx, val, nnz, tuple(shape)
+
+    @property
+    def capacity(self):
+        return self.idx.numel()
+
+    def nbytes(self):
+        return self.idx.numel() * 8 + self.val.numel() * 2 + 8
+
+    def overflowed(self):
+        """True if more entries passed the threshold than the buffers hold (synchronises)."""
+        return int(self.nnz.item()) > self.capacity
+
+    def to_dense(self, out=None):
+        numel = 1
+        for d in self.shape:
+            numel *= d
+        if out is None:
+            out = torch.empty(self.shape, dtype=BF16, device=self.val.device)
+        elif out.numel() != numel or out.dtype != BF16 or not out.is_contiguous():
+            raise ValueError("`out` must be a contiguous bf16 tensor with the map's number of elements")
+        check(lib.hyc_softmax_prune_restore_counted(ptr(self.idx), ptr(self.val), ptr(self.nnz), self.capacity, ptr(out),
+                                                    numel, stream_of(self.val)), "hyc_softmax_prune_restore_counted")
+        return out
+
+
+def compression_softmax_static(x: torch.Tensor, outlier, capacity=None, margin=1.5, ratio=None):
+    """``compression_softmax`` (compress_function.py:309-313) without the device-to-host read of the count: the
+    kept entries go into buffers of a fixed ``capacity`` (default: ``margin`` x ``ratio`` x numel + 1024, for a
+    threshold calibrated to keep ``ratio`` of the entries) and the count stays on the device.  Entries beyond the
+    capacity are dropped; ``PrunedMap.overflowed()`` tells.  ``outlier``: a Python float or a tensor (one
+    synchronisation if it lives on the device: pass the calibrated threshold as a float in steady state).
+    Maps of up to 268,435,456 elements; calls on one GPU must not overlap (they share scratch inside the library);
+    the first call on a device must be made outside of stream capture."""
+    require_cuda(x)
+    xf = x.to(BF16).contiguous()
+    numel = xf.numel()
+    if capacity is None:
+        if ratio is None:
+            raise ValueError("give `capacity` or the calibrated `ratio`")
+        capacity = int(numel * ratio * margin) + 1024
+    capacity = min(int(capacity), numel)
+    idx = torch.empty(capacity, dtype=torch.int64, device=x.device)
+    val = torch.empty(capacity, dtype=BF16, device=x.device)
+    nnz = torch.empty(1, dtype=torch.int64, device=x.device)
+    check(lib.hyc_softmax_prune_static(ptr(xf), numel, float(outlier), ptr(idx), ptr(val), capacity, ptr(nnz),
+                                       stream_of(x)), "hyc_softmax_prune_static")
+    return PrunedMap(idx, val, nnz, x.shape)
+
+
 # ---- modes without a counterpart in the reference ----
 
 def compression_group(x, quantize_bit=4):

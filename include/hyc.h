@@ -112,6 +112,11 @@ int hyc_softmax_prune_fill(const void* a, int64_t numel, float threshold,
 int hyc_softmax_prune_restore(const int64_t* idx, const void* val, int64_t nnz,
                               void* a_out, int64_t numel, void* stream);
 
+/* to_dense for a list whose length lives in device memory (the count hyc_softmax_prune_static left in nnz_out and
+ * nobody copied to the host): zero-fill, then scatter min(*nnz_dev, capacity) entries.  No host synchronisation. */
+int hyc_softmax_prune_restore_counted(const int64_t* idx, const void* val, const int64_t* nnz_dev, int64_t capacity,
+                                      void* a_out, int64_t numel, void* stream);
+
 /* No counterpart in the reference.  The same threshold prune for callers that must not allocate
  * device memory at call time (a fixed up-front memory plan, or a host that forbids allocation inside
  * operator callbacks) and so have no workspace to pass: the tile offsets live in a 512 KiB array built

@@ -214,3 +214,24 @@ def test_topk_config1_full_size_properties(cf):
     vals, oc, pk, sc, zp = oracle.topk_compress(a2[sl].cpu(), 0.05, 4)
     assert torch.equal(cols[sl].cpu(), oc) and torch.equal(m.q[sl].cpu(), pk) and torch.equal(m.scale[sl].cpu(), sc)
     assert m.nbytes() < 0.45 * a.numel() * 2
+
+
+def test_softmax_prune_with_the_count_left_on_the_device(cf):
+    """``compression_softmax_static`` -> ``PrunedMap``: the same entries as the sparse-tensor form, restored without
+    a host synchronisation; a capacity that is too small drops the tail and says so."""
+    a = _softmax_map(2, 3, 256, seed=9).to(DEV)
+    thr = float(cf.get_statistics_softmax(a, 0.05))
+    sp = cf.compression_softmax(a, thr)
+    nnz = sp.values().numel()
+    m = cf.compression_softmax_static(a, thr, ratio=0.05)
+    assert m.capacity >= nnz and int(m.nnz.item()) == nnz and not m.overflowed()
+    assert torch.equal(m.idx[:nnz], sp.indices().reshape(-1)) and torch.equal(m.val[:nnz], sp.values())
+    dense = cf.decompression_softmax(sp).reshape(a.shape)
+    assert torch.equal(m.to_dense(), dense)
+    buf = torch.full(a.shape, 3.0, dtype=torch.bfloat16, device=DEV)
+    assert m.to_dense(out=buf) is buf and torch.equal(buf, dense)
+    small = cf.compression_softmax_static(a, thr, capacity=nnz // 2)
+    assert small.overflowed() and int(small.nnz.item()) == nnz
+    part = torch.zeros(a.numel(), dtype=torch.bfloat16, device=DEV)
+    part[sp.indices().reshape(-1)[: nnz // 2]] = sp.values()[: nnz // 2]
+    assert torch.equal(small.to_dense().reshape(-1), part)
