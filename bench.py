@@ -345,6 +345,10 @@ def run_profile(args):
         print(json.dumps({"profile": "layer", "steps": args.steps, "ms_per_step": line["ms_per_step"],
                           "tokens_per_s": line["value"], "tflops": line["roofline"]["achieved"]}))
         return
+    if args.profile == "model":
+        line = model_workload(dev, None, steps=args.steps, warmup=args.warmup, n_layers=args.layers)
+        print(json.dumps(line))
+        return
     if args.profile == "fused":
         line = fused_elementwise_workload(dev, peaks()[0])
         print(json.dumps({"profile": "fused", "forward": line["forward"], "backward": line["backward"]}))
@@ -630,21 +634,18 @@ def model_workload(dev, dist=None, steps=4, warmup=3, n_layers=32, graph=True):
     n_ids = 4
     ids = [torch.randint(0, V, (B, M), generator=g, device=dev) for _ in range(n_ids)]
     labels = [torch.randint(0, V, (B * M,), generator=g, device=dev) for _ in range(n_ids)]
-    loss_box = [None]
+    loss_box, grads_box = [None], [None]
 
     def fwd_bwd(i):
-        x = embed[ids[i % n_ids]].requires_grad_(True)
+        x = embed[ids[i % n_ids]]
         for layer, args in layers:
-            args[0] = x
-            x = layer(*args)
+            x = layer(x, *args[1:])       # (no reference to x is kept: a stale autograd graph would outlive the step)
         logits = NormHead.apply(x)
         loss = torch.nn.functional.cross_entropy(logits.float(), labels[i % n_ids])
-        loss.backward()
+        grads_box[0] = torch.autograd.grad(loss, adapters)      # the 14 x n_layers adapter gradients of this rank
         for p_ in pending:
             p_.wait()
         pending.clear()
-        for w_ in adapters:
-            w_.grad = None
         loss_box[0] = loss.detach()
 
     def step(i):
@@ -709,8 +710,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-extras", action="store_true", help="skip the secondary workloads and the CPU sample")
-    ap.add_argument("--profile", default=None, choices=["attn_topk", "channel_q4", "channel_q2", "channel_q8", "mlp", "fused", "layer"],
+    ap.add_argument("--profile", default=None, choices=["attn_topk", "channel_q4", "channel_q2", "channel_q8", "mlp", "fused", "layer", "model"],
                     help="run only W+K steps of one workload and print timing (for a profiler capture)")
+    ap.add_argument("--layers", type=int, default=32, help="decoder layers of --profile model")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3
@@ -842,7 +844,7 @@ def main():
            "api": "compress_function.compression_softmax_topk + TopkMap.to_dense on pinned host maps, four streams "
                   "(the read-back of one step overlaps the upload of the next)"}
 
-    mlp_line = layer_line = None
+    mlp_line = layer_line = model_line = None
     sweep_lines = []
     if not args.no_extras:
         barrier()
@@ -853,6 +855,8 @@ def main():
             sweep_lines.append(mlp_workload(dev, dist, steps=10, warmup=3, shape="mistral", q_bit=qb))
         barrier()
         layer_line = layer_workload(dev, dist)
+        barrier()
+        model_line = model_workload(dev, dist)
     if rank == 0:
         also, cpu = [], None
         if not args.no_extras and world == 1:
@@ -863,6 +867,8 @@ def main():
         also.extend(sweep_lines)
         if layer_line is not None:
             also.append(layer_line)
+        if model_line is not None:
+            also.append(model_line)
         line = {
             "metric": "activation compress+decompress GB/s", "value": value, "unit": "GB/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": secs / args.steps * 1e3,
