@@ -8,109 +8,187 @@
 namespace hyc {
 
 constexpr int kTileThreads = 256;
-constexpr int kTileElems = kTileThreads * 16;   // 4096 elements (8 KiB) per tile
+constexpr int kTileElems = 4096;                // elements (8 KiB) per tile: the unit of the offsets in the workspace
+constexpr int kWarpsPerBlock = kTileThreads / 32;
+constexpr int kBatch = 8;                       // 16-byte chunks a lane has in flight; a tile is two batches per lane
 
-__device__ __forceinline__ uint32_t keep_mask16(const uint32_t (&w)[8], float thr, int64_t base, int64_t numel) {
+// A WARP owns a tile.  Chunk c of the tile (8 elements, 16 bytes) is read by lane c % 32 in trip c / 32, so that every
+// load instruction of the warp covers 512 contiguous bytes and a lane has kBatch independent loads in flight.
+
+// one chunk of 8 elements starting at element `base` (a multiple of 8); elements at or beyond numel read as zero.
+// LAST: the final read of the map (evict-first); the counting pass reads with the default policy so that a map
+// smaller than the L2 is still there when the fill pass comes.
+template <bool LAST>
+__device__ __forceinline__ uint4 load_chunk(const __nv_bfloat16* a, int64_t base, int64_t numel) {
+  if (base + 8 <= numel) return LAST ? ld_stream_v4(a + base) : __ldg(reinterpret_cast<const uint4*>(a + base));
+  uint32_t w[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const uint32_t lo = (base + 2 * j < numel) ? __bfloat16_as_ushort(a[base + 2 * j]) : 0u;
+    const uint32_t hi = (base + 2 * j + 1 < numel) ? __bfloat16_as_ushort(a[base + 2 * j + 1]) : 0u;
+    w[j] = lo | (hi << 16);
+  }
+  return make_uint4(w[0], w[1], w[2], w[3]);
+}
+
+// bit e set: element e of the chunk is kept (above the threshold and not zero: a zero is no entry of a sparse tensor)
+__device__ __forceinline__ uint32_t keep_mask8(const uint4& u, float thr) {
+  const uint32_t w[4] = {u.x, u.y, u.z, u.w};
   uint32_t mk = 0u;
 #pragma unroll
-  for (int e = 0; e < 16; ++e) {
-    float f = (e & 1) ? bf16hi_to_f32(w[e >> 1]) : bf16lo_to_f32(w[e >> 1]);
-    if (f > thr && f != 0.f && (base + e) < numel) mk |= 1u << e;
+  for (int j = 0; j < 4; ++j) {
+    const float lo = bf16lo_to_f32(w[j]), hi = bf16hi_to_f32(w[j]);
+    if (lo > thr && lo != 0.f) mk |= 1u << (2 * j);
+    if (hi > thr && hi != 0.f) mk |= 2u << (2 * j);
   }
   return mk;
 }
 
-__device__ __forceinline__ void load16(const __nv_bfloat16* a, int64_t base, int64_t numel, uint32_t (&w)[8]) {
-  if (base + 16 <= numel) {
-    uint4 u = ld_stream_v4(a + base), v = ld_stream_v4(a + base + 8);
-    w[0] = u.x; w[1] = u.y; w[2] = u.z; w[3] = u.w; w[4] = v.x; w[5] = v.y; w[6] = v.z; w[7] = v.w;
-  } else {
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      uint32_t lo = (base + 2 * j < numel) ? __bfloat16_as_ushort(a[base + 2 * j]) : 0u;
-      uint32_t hi = (base + 2 * j + 1 < numel) ? __bfloat16_as_ushort(a[base + 2 * j + 1]) : 0u;
-      w[j] = lo | (hi << 16);
-    }
-  }
-}
-
-__device__ __forceinline__ int block_excl_scan(int v, int& total) {
-  __shared__ int s_w[kTileThreads / 32];
-  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+__device__ __forceinline__ int warp_excl_scan(int v, int lane, int& total) {
   int incl = v;
 #pragma unroll
   for (int o = 1; o < 32; o <<= 1) {
-    int t = __shfl_up_sync(0xffffffffu, incl, o);
+    const int t = __shfl_up_sync(0xffffffffu, incl, o);
     if (lane >= o) incl += t;
   }
-  if (lane == 31) s_w[wid] = incl;
-  __syncthreads();
-  int wbase = 0, tot = 0;
-#pragma unroll
-  for (int i = 0; i < kTileThreads / 32; ++i) {
-    int c = s_w[i];
-    if (i < wid) wbase += c;
-    tot += c;
-  }
-  total = tot;
-  __syncthreads();
-  return wbase + incl - v;
+  total = __shfl_sync(0xffffffffu, incl, 31);
+  return incl - v;
 }
 
-__global__ void __launch_bounds__(kTileThreads)
+// (four loads in flight per lane and 32 registers: all 64 warp slots of an SM are taken, one wave for 9472 tiles)
+__global__ void __launch_bounds__(kTileThreads, 8)
 prune_count_kernel(const __nv_bfloat16* __restrict__ a, int64_t numel, float thr, int64_t n_tiles,
                    int64_t* __restrict__ ws) {
-  for (int64_t tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
-    const int64_t base = tile * kTileElems + 16 * (int64_t)threadIdx.x;
-    uint32_t w[8];
+  constexpr int CB = 4;
+  const int lane = threadIdx.x & 31;
+  const int64_t warp0 = (int64_t)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
+  for (int64_t tile = warp0; tile < n_tiles; tile += (int64_t)gridDim.x * kWarpsPerBlock) {
+    const int64_t t0 = tile * kTileElems + 8 * lane;
     int c = 0;
-    if (base < numel) { load16(a, base, numel, w); c = __popc(keep_mask16(w, thr, base, numel)); }
-    int total;
-    block_excl_scan(c, total);
-    if (threadIdx.x == 0) ws[1 + tile] = total;
+#pragma unroll
+    for (int b = 0; b < kTileElems / (256 * CB); ++b) {
+      uint4 u[CB];
+#pragma unroll
+      for (int j = 0; j < CB; ++j) {
+        const int64_t base = t0 + 256 * (b * CB + j);
+        u[j] = base < numel ? load_chunk<false>(a, base, numel) : make_uint4(0u, 0u, 0u, 0u);
+      }
+#pragma unroll
+      for (int j = 0; j < CB; ++j) c += __popc(keep_mask8(u[j], thr));
+    }
+    c = (int)__reduce_add_sync(0xffffffffu, (unsigned)c);
+    if (lane == 0) ws[1 + tile] = c;
   }
 }
 
-// single block: counts -> exclusive offsets, total into ws[0]
+// single block: counts -> exclusive offsets, total into ws[0].  The counts are taken 4096 at a time: every thread
+// fetches four of them (coalesced, all four loads in flight), then four block-wide scans chained by a carry.
 __global__ void __launch_bounds__(1024)
 prune_scan_kernel(int64_t* __restrict__ ws, int64_t n_tiles) {
-  __shared__ int64_t s_part[1024];
-  const int64_t per = (n_tiles + 1023) / 1024;
-  const int64_t b = threadIdx.x * per, e = (b + per < n_tiles) ? b + per : n_tiles;
-  int64_t sum = 0;
-  for (int64_t i = b; i < e; ++i) sum += ws[1 + i];
-  s_part[threadIdx.x] = sum;
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    int64_t run = 0;
-    for (int i = 0; i < 1024; ++i) { int64_t t = s_part[i]; s_part[i] = run; run += t; }
-    ws[0] = run;
+  constexpr int U = 4;
+  __shared__ int64_t s_off[U][32];      // per scan: inclusive warp totals, then the warps' exclusive offsets
+  __shared__ int64_t s_tot[U];
+  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+  int64_t carry = 0;
+  for (int64_t c0 = 0; c0 < n_tiles; c0 += 1024 * U) {
+    int64_t v[U], incl[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int64_t i = c0 + 1024 * u + threadIdx.x;
+      v[u] = i < n_tiles ? ws[1 + i] : 0;
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      int64_t x = v[u];
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int64_t t = __shfl_up_sync(0xffffffffu, x, o);
+        if (lane >= o) x += t;
+      }
+      incl[u] = x;
+      if (lane == 31) s_off[u][wid] = x;
+    }
+    __syncthreads();
+    if (wid < U) {
+      const int64_t t0 = s_off[wid][lane];
+      int64_t x = t0;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int64_t t = __shfl_up_sync(0xffffffffu, x, o);
+        if (lane >= o) x += t;
+      }
+      s_off[wid][lane] = x - t0;
+      if (lane == 31) s_tot[wid] = x;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int64_t i = c0 + 1024 * u + threadIdx.x;
+      if (i < n_tiles) ws[1 + i] = carry + s_off[u][wid] + incl[u] - v[u];
+      carry += s_tot[u];
+    }
+    __syncthreads();
   }
-  __syncthreads();
-  int64_t run = s_part[threadIdx.x];
-  for (int64_t i = b; i < e; ++i) { int64_t t = ws[1 + i]; ws[1 + i] = run; run += t; }
+  if (threadIdx.x == 0) ws[0] = carry;
 }
 
-__global__ void __launch_bounds__(kTileThreads)
+// Ordered fill.  The entries of four trips (1024 elements) are first packed into a per-warp staging area in list
+// order as (offset within the 1024 << 16 | value), then written out by consecutive lanes: a list entry is 8 + 2
+// bytes, and one store instruction per entry and lane would cost a 32-byte memory transaction for each of them.
+constexpr int kFillTrips = 4;
+
+__global__ void __launch_bounds__(kTileThreads, 4)
 prune_fill_kernel(const __nv_bfloat16* __restrict__ a, int64_t numel, float thr, int64_t n_tiles,
                   const int64_t* __restrict__ ws, int64_t* __restrict__ idx_out,
                   __nv_bfloat16* __restrict__ val_out, int64_t capacity) {
-  for (int64_t tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
-    const int64_t base = tile * kTileElems + 16 * (int64_t)threadIdx.x;
-    uint32_t w[8];
-    uint32_t mk = 0u;
-    if (base < numel) { load16(a, base, numel, w); mk = keep_mask16(w, thr, base, numel); }
-    int total;
-    int64_t pos = ws[1 + tile] + block_excl_scan(__popc(mk), total);
+  __shared__ uint32_t s_stage[kWarpsPerBlock][256 * kFillTrips];
+  const int lane = threadIdx.x & 31;
+  uint32_t* stage = s_stage[threadIdx.x >> 5];
+  const int64_t warp0 = (int64_t)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
+  for (int64_t tile = warp0; tile < n_tiles; tile += (int64_t)gridDim.x * kWarpsPerBlock) {
+    const int64_t t0 = tile * kTileElems + 8 * lane;
+    int64_t run = ws[1 + tile];            // list position of the tile's first entry
 #pragma unroll
-    for (int e = 0; e < 16; ++e) {
-      if (mk & (1u << e)) {
-        if (pos < capacity) {
-          idx_out[pos] = base + e;
-          const uint32_t ww = w[e >> 1];
-          val_out[pos] = __ushort_as_bfloat16((e & 1) ? (uint16_t)(ww >> 16) : (uint16_t)(ww & 0xffffu));
+    for (int b = 0; b < kTileElems / (256 * kBatch); ++b) {
+      uint4 u[kBatch];
+#pragma unroll
+      for (int j = 0; j < kBatch; ++j) {
+        const int64_t base = t0 + 256 * (b * kBatch + j);
+        u[j] = base < numel ? load_chunk<true>(a, base, numel) : make_uint4(0u, 0u, 0u, 0u);
+      }
+#pragma unroll
+      for (int g = 0; g < kBatch / kFillTrips; ++g) {
+        int n_staged = 0;
+#pragma unroll
+        for (int jj = 0; jj < kFillTrips; ++jj) {
+          // the entries of one trip (256 consecutive elements) are consecutive in the list: lanes in order
+          const int j = g * kFillTrips + jj;
+          const uint32_t mk = keep_mask8(u[j], thr);
+          int total;
+          int pos = n_staged + warp_excl_scan(__popc(mk), lane, total);
+          n_staged += total;
+          const uint32_t w[4] = {u[j].x, u[j].y, u[j].z, u[j].w};
+          const uint32_t off = (uint32_t)(256 * jj + 8 * lane) << 16;
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            if (mk & (1u << e)) {
+              const uint32_t v16 = (e & 1) ? (w[e >> 1] >> 16) : (w[e >> 1] & 0xffffu);
+              stage[pos++] = (off + ((uint32_t)e << 16)) | v16;
+            }
+          }
         }
-        ++pos;
+        __syncwarp();
+        const int64_t g0 = tile * kTileElems + 256 * (b * kBatch + g * kFillTrips);   // element index of offset 0
+        for (int i = lane; i < n_staged; i += 32) {
+          const int64_t p = run + i;
+          if (p < capacity) {
+            const uint32_t wv = stage[i];
+            idx_out[p] = g0 + (int64_t)(wv >> 16);
+            val_out[p] = __ushort_as_bfloat16((uint16_t)(wv & 0xffffu));
+          }
+        }
+        run += n_staged;
+        __syncwarp();
       }
     }
   }
@@ -139,8 +217,10 @@ prune_scatter_counted_kernel(const int64_t* __restrict__ idx, const __nv_bfloat1
 }
 
 static inline int64_t n_tiles_of(int64_t numel) { return (numel + kTileElems - 1) / kTileElems; }
+// one warp per tile, eight tiles per block; very large maps wrap around a grid of 32 blocks per SM
 static inline int tile_grid(int64_t n_tiles) {
-  int64_t g = n_tiles < (int64_t)kNumSMs * 8 ? n_tiles : (int64_t)kNumSMs * 8;
+  int64_t g = (n_tiles + kWarpsPerBlock - 1) / kWarpsPerBlock;
+  if (g > (int64_t)kNumSMs * 32) g = (int64_t)kNumSMs * 32;
   return (int)(g < 1 ? 1 : g);
 }
 // the comparison of the reference runs in bf16: the fp32 threshold is rounded to bf16 first

@@ -90,6 +90,22 @@ def test_softmax_prune_oracle(cf, shape):
     assert allk.values().numel() == int((a != 0).sum())
 
 
+@pytest.mark.parametrize("numel", [1, 7, 4095, 4097, 3 * 4096 + 5, 9 * 4096 + 8 * 31 + 3, 70001])
+def test_softmax_prune_ragged_sizes(cf, numel):
+    """Element counts that end inside a 16-byte chunk, inside a warp trip and inside a tile; dense and sparse keeps."""
+    g = torch.Generator().manual_seed(numel)
+    a = torch.rand(numel, generator=g).to(torch.bfloat16)
+    a[torch.rand(numel, generator=g) < 0.2] = 0
+    for thr in (0.9, 0.5, -1.0):
+        idx, val = oracle.ref_softmax_prune(a, torch.tensor(thr))
+        sp = cf.compression_softmax(a.to(DEV), thr)
+        assert torch.equal(sp.indices().reshape(-1).cpu(), idx) and torch.equal(sp.values().cpu(), val)
+        assert torch.equal(cf.decompression_softmax(sp).cpu(), oracle.ref_softmax_restore(idx, val, a.shape))
+        m = cf.compression_softmax_static(a.to(DEV), thr, capacity=numel)
+        n = int(m.nnz.item())
+        assert n == idx.numel() and torch.equal(m.idx[:n].cpu(), idx) and torch.equal(m.val[:n].cpu(), val)
+
+
 @pytest.mark.parametrize("q", QS)
 @pytest.mark.parametrize("shape", [(1, 1, 64, 64), (2, 2, 128, 128), (1, 2, 512, 512), (1, 1, 320, 320), (1, 1, 64, 2048),
                                    (1, 1, 13, 128), (1, 1, 5, 1024), (1, 3, 256, 256), (1, 1, 3, 4096)])
