@@ -2,6 +2,8 @@
 // threshold, and its dense restore.  The list is ordered by flattened index, so the
 // compaction is a two-phase stream compaction: per-tile counts, a scan of the counts,
 // then the ordered fill.  The workspace holds [0] = total, [1 + t] = exclusive offset of tile t.
+// Both passes over the map give a tile of 4096 elements to a warp (no block-wide barriers) and test two
+// elements per instruction with packed bf16 compares.
 #include "hyc_common.cuh"
 #include <string.h>
 
@@ -10,10 +12,9 @@ namespace hyc {
 constexpr int kTileThreads = 256;
 constexpr int kTileElems = 4096;                // elements (8 KiB) per tile: the unit of the offsets in the workspace
 constexpr int kWarpsPerBlock = kTileThreads / 32;
-constexpr int kBatch = 8;                       // 16-byte chunks a lane has in flight; a tile is two batches per lane
 
 // A WARP owns a tile.  Chunk c of the tile (8 elements, 16 bytes) is read by lane c % 32 in trip c / 32, so that every
-// load instruction of the warp covers 512 contiguous bytes and a lane has kBatch independent loads in flight.
+// load instruction of the warp covers 512 contiguous bytes and a lane has several independent loads in flight.
 
 // one chunk of 8 elements starting at element `base` (a multiple of 8); elements at or beyond numel read as zero.
 // LAST: the final read of the map (evict-first); the counting pass reads with the default policy so that a map
@@ -31,17 +32,27 @@ __device__ __forceinline__ uint4 load_chunk(const __nv_bfloat16* a, int64_t base
   return make_uint4(w[0], w[1], w[2], w[3]);
 }
 
-// bit e set: element e of the chunk is kept (above the threshold and not zero: a zero is no entry of a sparse tensor)
-__device__ __forceinline__ uint32_t keep_mask8(const uint4& u, float thr) {
-  const uint32_t w[4] = {u.x, u.y, u.z, u.w};
-  uint32_t mk = 0u;
-#pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    const float lo = bf16lo_to_f32(w[j]), hi = bf16hi_to_f32(w[j]);
-    if (lo > thr && lo != 0.f) mk |= 1u << (2 * j);
-    if (hi > thr && hi != 0.f) mk |= 2u << (2 * j);
-  }
-  return mk;
+// The keep test `x > thr && x != 0` (a zero is no entry of a sparse tensor) on packed bf16 pairs: one compare
+// instruction per two elements gives 0xffff per kept half.  For thr >= 0 the first condition implies the second
+// (NEG = false); a NaN is never kept, as in the fp32 comparison.
+template <bool NEG>
+__device__ __forceinline__ uint32_t pair_mask(uint32_t w, __nv_bfloat162 t2) {
+  const __nv_bfloat162 x = *reinterpret_cast<const __nv_bfloat162*>(&w);
+  uint32_t m = __hgt2_mask(x, t2);
+  if (NEG) m &= __hne2_mask(x, __float2bfloat162_rn(0.f));
+  return m;
+}
+// one bit per kept element of the chunk: element 2j at bit 2j, element 2j + 1 at bit 16 + 2j + 1
+template <bool NEG>
+__device__ __forceinline__ uint32_t keep_bits(const uint4& u, __nv_bfloat162 t2) {
+  return (pair_mask<NEG>(u.x, t2) & 0x00020001u) | (pair_mask<NEG>(u.y, t2) & 0x00080004u) |
+         (pair_mask<NEG>(u.z, t2) & 0x00200010u) | (pair_mask<NEG>(u.w, t2) & 0x00800040u);
+}
+// bit e set: element e of the chunk is kept
+template <bool NEG>
+__device__ __forceinline__ uint32_t keep_mask8(const uint4& u, __nv_bfloat162 t2) {
+  const uint32_t t = keep_bits<NEG>(u, t2);
+  return (t | (t >> 16)) & 0xffu;
 }
 
 __device__ __forceinline__ int warp_excl_scan(int v, int lane, int& total) {
@@ -56,10 +67,12 @@ __device__ __forceinline__ int warp_excl_scan(int v, int lane, int& total) {
 }
 
 // (four loads in flight per lane and 32 registers: all 64 warp slots of an SM are taken, one wave for 9472 tiles)
+template <bool NEG>
 __global__ void __launch_bounds__(kTileThreads, 8)
 prune_count_kernel(const __nv_bfloat16* __restrict__ a, int64_t numel, float thr, int64_t n_tiles,
                    int64_t* __restrict__ ws) {
   constexpr int CB = 4;
+  const __nv_bfloat162 t2 = __float2bfloat162_rn(thr);
   const int lane = threadIdx.x & 31;
   const int64_t warp0 = (int64_t)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
   for (int64_t tile = warp0; tile < n_tiles; tile += (int64_t)gridDim.x * kWarpsPerBlock) {
@@ -74,7 +87,7 @@ prune_count_kernel(const __nv_bfloat16* __restrict__ a, int64_t numel, float thr
         u[j] = base < numel ? load_chunk<false>(a, base, numel) : make_uint4(0u, 0u, 0u, 0u);
       }
 #pragma unroll
-      for (int j = 0; j < CB; ++j) c += __popc(keep_mask8(u[j], thr));
+      for (int j = 0; j < CB; ++j) c += __popc(keep_bits<NEG>(u[j], t2));
     }
     c = (int)__reduce_add_sync(0xffffffffu, (unsigned)c);
     if (lane == 0) ws[1 + tile] = c;
@@ -135,13 +148,18 @@ prune_scan_kernel(int64_t* __restrict__ ws, int64_t n_tiles) {
 // Ordered fill.  The entries of four trips (1024 elements) are first packed into a per-warp staging area in list
 // order as (offset within the 1024 << 16 | value), then written out by consecutive lanes: a list entry is 8 + 2
 // bytes, and one store instruction per entry and lane would cost a 32-byte memory transaction for each of them.
+// The work per trip does not depend on how the kept entries are spread over the lanes (in a causal map they
+// cluster: the first rows keep everything, the masked half keeps nothing); a trip without any entry is skipped.
+constexpr int kBatch = 8;                       // chunks a lane has in flight: a tile is two batches
 constexpr int kFillTrips = 4;
 
+template <bool NEG>
 __global__ void __launch_bounds__(kTileThreads, 4)
 prune_fill_kernel(const __nv_bfloat16* __restrict__ a, int64_t numel, float thr, int64_t n_tiles,
                   const int64_t* __restrict__ ws, int64_t* __restrict__ idx_out,
                   __nv_bfloat16* __restrict__ val_out, int64_t capacity) {
   __shared__ uint32_t s_stage[kWarpsPerBlock][256 * kFillTrips];
+  const __nv_bfloat162 t2 = __float2bfloat162_rn(thr);
   const int lane = threadIdx.x & 31;
   uint32_t* stage = s_stage[threadIdx.x >> 5];
   const int64_t warp0 = (int64_t)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
@@ -163,32 +181,33 @@ prune_fill_kernel(const __nv_bfloat16* __restrict__ a, int64_t numel, float thr,
         for (int jj = 0; jj < kFillTrips; ++jj) {
           // the entries of one trip (256 consecutive elements) are consecutive in the list: lanes in order
           const int j = g * kFillTrips + jj;
-          const uint32_t mk = keep_mask8(u[j], thr);
-          int total;
-          int pos = n_staged + warp_excl_scan(__popc(mk), lane, total);
-          n_staged += total;
-          const uint32_t w[4] = {u[j].x, u[j].y, u[j].z, u[j].w};
-          const uint32_t off = (uint32_t)(256 * jj + 8 * lane) << 16;
+          const uint32_t mk = keep_mask8<NEG>(u[j], t2);
+          if (__any_sync(0xffffffffu, mk != 0u)) {
+            int total;
+            int pos = n_staged + warp_excl_scan(__popc(mk), lane, total);
+            n_staged += total;
+            const uint32_t w[4] = {u[j].x, u[j].y, u[j].z, u[j].w};
+            const uint32_t off = (uint32_t)(256 * jj + 8 * lane);
 #pragma unroll
-          for (int e = 0; e < 8; ++e) {
-            if (mk & (1u << e)) {
-              const uint32_t v16 = (e & 1) ? (w[e >> 1] >> 16) : (w[e >> 1] & 0xffffu);
-              stage[pos++] = (off + ((uint32_t)e << 16)) | v16;
+            for (int e = 0; e < 8; ++e) {
+              if (mk & (1u << e)) stage[pos++] = __byte_perm(w[e >> 1], off + e, (e & 1) ? 0x5432 : 0x5410);
             }
           }
         }
-        __syncwarp();
-        const int64_t g0 = tile * kTileElems + 256 * (b * kBatch + g * kFillTrips);   // element index of offset 0
-        for (int i = lane; i < n_staged; i += 32) {
-          const int64_t p = run + i;
-          if (p < capacity) {
-            const uint32_t wv = stage[i];
-            idx_out[p] = g0 + (int64_t)(wv >> 16);
-            val_out[p] = __ushort_as_bfloat16((uint16_t)(wv & 0xffffu));
+        if (n_staged) {
+          __syncwarp();
+          const int64_t g0 = tile * kTileElems + 256 * (b * kBatch + g * kFillTrips);   // element index of offset 0
+          for (int i = lane; i < n_staged; i += 32) {
+            const int64_t p = run + i;
+            if (p < capacity) {
+              const uint32_t wv = stage[i];
+              idx_out[p] = g0 + (int64_t)(wv >> 16);
+              val_out[p] = __ushort_as_bfloat16((uint16_t)(wv & 0xffffu));
+            }
           }
+          run += n_staged;
+          __syncwarp();
         }
-        run += n_staged;
-        __syncwarp();
       }
     }
   }
@@ -232,6 +251,17 @@ static inline float thr_bf16(float t) {
   return r;
 }
 
+// thr is the bf16-rounded threshold; a negative one (or NaN) takes the kernels that also test for zero
+static inline void launch_count(const __nv_bfloat16* a, int64_t numel, float thr, int64_t nt, int64_t* ws, cudaStream_t st) {
+  if (thr >= 0.f) prune_count_kernel<false><<<tile_grid(nt), kTileThreads, 0, st>>>(a, numel, thr, nt, ws);
+  else prune_count_kernel<true><<<tile_grid(nt), kTileThreads, 0, st>>>(a, numel, thr, nt, ws);
+}
+static inline void launch_fill(const __nv_bfloat16* a, int64_t numel, float thr, int64_t nt, const int64_t* ws,
+                               int64_t* idx_out, __nv_bfloat16* val_out, int64_t capacity, cudaStream_t st) {
+  if (thr >= 0.f) prune_fill_kernel<false><<<tile_grid(nt), kTileThreads, 0, st>>>(a, numel, thr, nt, ws, idx_out, val_out, capacity);
+  else prune_fill_kernel<true><<<tile_grid(nt), kTileThreads, 0, st>>>(a, numel, thr, nt, ws, idx_out, val_out, capacity);
+}
+
 }  // namespace hyc
 
 using namespace hyc;
@@ -249,8 +279,7 @@ extern "C" HYC_API int hyc_softmax_prune_count(const void* a, int64_t numel, flo
   if (workspace_bytes < hyc_softmax_prune_workspace_bytes(numel)) return HYC_ERR_WORKSPACE;
   const int64_t nt = n_tiles_of(numel);
   cudaStream_t st = (cudaStream_t)stream;
-  prune_count_kernel<<<tile_grid(nt), kTileThreads, 0, st>>>((const __nv_bfloat16*)a, numel, thr_bf16(threshold), nt,
-                                                              (int64_t*)workspace);
+  launch_count((const __nv_bfloat16*)a, numel, thr_bf16(threshold), nt, (int64_t*)workspace, st);
   HYC_CHECK_LAUNCH();
   prune_scan_kernel<<<1, 1024, 0, st>>>((int64_t*)workspace, nt);
   HYC_CHECK_LAUNCH();
@@ -266,9 +295,8 @@ extern "C" HYC_API int hyc_softmax_prune_fill(const void* a, int64_t numel, floa
   if (!aligned(a, 16) || !aligned(workspace, 8)) return HYC_ERR_ALIGN;
   if (capacity == 0) return HYC_OK;
   const int64_t nt = n_tiles_of(numel);
-  prune_fill_kernel<<<tile_grid(nt), kTileThreads, 0, (cudaStream_t)stream>>>(
-      (const __nv_bfloat16*)a, numel, thr_bf16(threshold), nt, (const int64_t*)workspace, idx_out,
-      (__nv_bfloat16*)val_out, capacity);
+  launch_fill((const __nv_bfloat16*)a, numel, thr_bf16(threshold), nt, (const int64_t*)workspace, idx_out,
+              (__nv_bfloat16*)val_out, capacity, (cudaStream_t)stream);
   HYC_CHECK_LAUNCH();
   return HYC_OK;
 }
@@ -352,13 +380,12 @@ extern "C" HYC_API int hyc_softmax_prune_static(const void* a, int64_t numel, fl
   if (!ws) { hyc_set_last_cuda_error(err); return HYC_ERR_LAUNCH; }
   cudaStream_t st = (cudaStream_t)stream;
   const float thr = thr_bf16(threshold);
-  prune_count_kernel<<<tile_grid(nt), kTileThreads, 0, st>>>((const __nv_bfloat16*)a, numel, thr, nt, ws);
+  launch_count((const __nv_bfloat16*)a, numel, thr, nt, ws, st);
   HYC_CHECK_LAUNCH();
   prune_scan_kernel<<<1, 1024, 0, st>>>(ws, nt);
   HYC_CHECK_LAUNCH();
   if (capacity > 0) {
-    prune_fill_kernel<<<tile_grid(nt), kTileThreads, 0, st>>>((const __nv_bfloat16*)a, numel, thr, nt, ws, idx_out,
-                                                              (__nv_bfloat16*)val_out, capacity);
+    launch_fill((const __nv_bfloat16*)a, numel, thr, nt, ws, idx_out, (__nv_bfloat16*)val_out, capacity, st);
     HYC_CHECK_LAUNCH();
   }
   if (cudaMemcpyAsync(nnz_out, ws, sizeof(int64_t), cudaMemcpyDeviceToDevice, st) != cudaSuccess) {
