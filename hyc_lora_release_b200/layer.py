@@ -64,9 +64,14 @@ class FusedLayerFunction(torch.autograd.Function):
         ctx.hyc = None
         hook = module.on_lora_grads
         gm = mlp_backward(grad_y, sm, mw, status=st, on_lora_grads=hook)
+        saved_map = sa.get('a_saved')
         ga = attention_backward(gm['grad_x'], sa, aw, status=st, on_lora_grads=hook)
         if module.check_kernel_status:
             check_status(st, "fused layer")
+            # fixed-capacity prune buffers: more entries above the threshold than they hold would have been dropped
+            if hasattr(saved_map, "overflowed") and saved_map.overflowed():
+                raise RuntimeError("fused layer: the pruned probability map overflowed its buffers (%d entries); raise "
+                                   "AttnState.prune_capacity_margin" % saved_map.capacity)
         grads = [ga['grad_aq'], ga['grad_bq'], ga['grad_ak'], ga['grad_bk'], ga['grad_av'], ga['grad_bv'],
                  ga['grad_ao'], ga['grad_bo'], gm['grad_ag'], gm['grad_bg'], gm['grad_au'], gm['grad_bu'],
                  gm['grad_ad'], gm['grad_bd']]
