@@ -104,6 +104,7 @@ def test_softmax_prune_ragged_sizes(cf, numel):
         m = cf.compression_softmax_static(a.to(DEV), thr, capacity=numel)
         n = int(m.nnz.item())
         assert n == idx.numel() and torch.equal(m.idx[:n].cpu(), idx) and torch.equal(m.val[:n].cpu(), val)
+        assert torch.equal(m.to_dense().cpu(), oracle.ref_softmax_restore(idx, val, a.shape))   # tile-wise restore
 
 
 @pytest.mark.parametrize("q", QS)
