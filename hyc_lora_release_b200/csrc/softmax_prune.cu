@@ -94,11 +94,12 @@ prune_count_kernel(const __nv_bfloat16* __restrict__ a, int64_t numel, float thr
   }
 }
 
-// single block: counts -> exclusive offsets, total into ws[0].  The counts are taken 4096 at a time: every thread
-// fetches four of them (coalesced, all four loads in flight), then four block-wide scans chained by a carry.
+// single block: counts -> exclusive offsets, total into ws[0] (and into *total_out when given).  The counts are
+// taken 8192 at a time: every thread fetches eight of them (coalesced, all eight loads in flight), then eight
+// block-wide scans chained by a carry.
 __global__ void __launch_bounds__(1024)
-prune_scan_kernel(int64_t* __restrict__ ws, int64_t n_tiles) {
-  constexpr int U = 4;
+prune_scan_kernel(int64_t* __restrict__ ws, int64_t n_tiles, int64_t* __restrict__ total_out) {
+  constexpr int U = 8;
   __shared__ int64_t s_off[U][32];      // per scan: inclusive warp totals, then the warps' exclusive offsets
   __shared__ int64_t s_tot[U];
   const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
@@ -142,7 +143,10 @@ prune_scan_kernel(int64_t* __restrict__ ws, int64_t n_tiles) {
     }
     __syncthreads();
   }
-  if (threadIdx.x == 0) ws[0] = carry;
+  if (threadIdx.x == 0) {
+    ws[0] = carry;
+    if (total_out) *total_out = carry;
+  }
 }
 
 // Ordered fill.  The entries of four trips (1024 elements) are first packed into a per-warp staging area in list
@@ -281,7 +285,7 @@ extern "C" HYC_API int hyc_softmax_prune_count(const void* a, int64_t numel, flo
   cudaStream_t st = (cudaStream_t)stream;
   launch_count((const __nv_bfloat16*)a, numel, thr_bf16(threshold), nt, (int64_t*)workspace, st);
   HYC_CHECK_LAUNCH();
-  prune_scan_kernel<<<1, 1024, 0, st>>>((int64_t*)workspace, nt);
+  prune_scan_kernel<<<1, 1024, 0, st>>>((int64_t*)workspace, nt, nullptr);
   HYC_CHECK_LAUNCH();
   return HYC_OK;
 }
@@ -382,15 +386,11 @@ extern "C" HYC_API int hyc_softmax_prune_static(const void* a, int64_t numel, fl
   const float thr = thr_bf16(threshold);
   launch_count((const __nv_bfloat16*)a, numel, thr, nt, ws, st);
   HYC_CHECK_LAUNCH();
-  prune_scan_kernel<<<1, 1024, 0, st>>>(ws, nt);
+  prune_scan_kernel<<<1, 1024, 0, st>>>(ws, nt, nnz_out);
   HYC_CHECK_LAUNCH();
   if (capacity > 0) {
     launch_fill((const __nv_bfloat16*)a, numel, thr, nt, ws, idx_out, (__nv_bfloat16*)val_out, capacity, st);
     HYC_CHECK_LAUNCH();
-  }
-  if (cudaMemcpyAsync(nnz_out, ws, sizeof(int64_t), cudaMemcpyDeviceToDevice, st) != cudaSuccess) {
-    hyc_set_last_cuda_error((int)cudaGetLastError());
-    return HYC_ERR_LAUNCH;
   }
   return HYC_OK;
 }
