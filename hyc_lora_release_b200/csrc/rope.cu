@@ -8,7 +8,10 @@
 //   out[j]     = x[j] * c - x[j + h] * s
 //   out[j + h] = x[j + h] * c + x[j] * s            backward: the same with s negated
 //
-// Arithmetic: fp32 from the bf16 (or fp32) operands, one rounding to bf16 at the store.
+// Arithmetic: that of the reference's kernel, which computes in the dtype of the sine table
+// (operators/rope_kernels.py:73-78: `Q1 = tl.load(...).to(sin1.dtype)`): with bf16 tables every product and the
+// sum are bf16 operations (three roundings per output); with fp32 tables they are separate fp32 operations and the
+// store rounds to bf16.  No multiply-add contraction in either form.
 // One thread owns eight adjacent j of one head: two 16-byte loads and two 16-byte stores of x, 16 (bf16
 // tables) or 2 x 32 (fp32 tables) bytes of each table; the tables stay in L1/L2 (seq_len * head_dim values).
 #include "hyc_common.cuh"
@@ -33,8 +36,9 @@ rope_kernel(const __nv_bfloat16* __restrict__ x, int64_t ldx, __nv_bfloat16* __r
     const uint4 a = *reinterpret_cast<const uint4*>(xp);
     const uint4 b = *reinterpret_cast<const uint4*>(xp + half);
     const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, bw[4] = {b.x, b.y, b.z, b.w};
-    float c[8], s[8];
+    uint32_t o1[4], o2[4];
     if (TABLE_F32) {
+      float c[8], s[8];
       const float* cp = reinterpret_cast<const float*>(cos_t) + pos * ld_table + j0;
       const float* sp = reinterpret_cast<const float*>(sin_t) + pos * ld_table + j0;
 #pragma unroll
@@ -43,24 +47,32 @@ rope_kernel(const __nv_bfloat16* __restrict__ x, int64_t ldx, __nv_bfloat16* __r
         c[e] = cv.x; c[e + 1] = cv.y; c[e + 2] = cv.z; c[e + 3] = cv.w;
         s[e] = sv.x; s[e + 1] = sv.y; s[e + 2] = sv.z; s[e + 3] = sv.w;
       }
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float x1l = bf16lo_to_f32(aw[e]), x1h = bf16hi_to_f32(aw[e]);
+        const float x2l = bf16lo_to_f32(bw[e]), x2h = bf16hi_to_f32(bw[e]);
+        const float sl = s[2 * e] * sin_sign, sh = s[2 * e + 1] * sin_sign;
+        const float cl = c[2 * e], ch = c[2 * e + 1];
+        o1[e] = pack_bf16x2_rn(__fsub_rn(__fmul_rn(x1l, cl), __fmul_rn(x2l, sl)), __fsub_rn(__fmul_rn(x1h, ch), __fmul_rn(x2h, sh)));
+        o2[e] = pack_bf16x2_rn(__fadd_rn(__fmul_rn(x2l, cl), __fmul_rn(x1l, sl)), __fadd_rn(__fmul_rn(x2h, ch), __fmul_rn(x1h, sh)));
+      }
     } else {
       const uint4 cv = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(cos_t) + pos * ld_table + j0);
       const uint4 sv = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(sin_t) + pos * ld_table + j0);
       const uint32_t cw[4] = {cv.x, cv.y, cv.z, cv.w}, sw[4] = {sv.x, sv.y, sv.z, sv.w};
+      const uint32_t flip = sin_sign < 0.f ? 0x80008000u : 0u;     // backward: the sine negated (exact)
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
-        c[2 * e] = bf16lo_to_f32(cw[e]); c[2 * e + 1] = bf16hi_to_f32(cw[e]);
-        s[2 * e] = bf16lo_to_f32(sw[e]); s[2 * e + 1] = bf16hi_to_f32(sw[e]);
+        const uint32_t sn = sw[e] ^ flip;
+        const __nv_bfloat162 x1 = *reinterpret_cast<const __nv_bfloat162*>(&aw[e]);
+        const __nv_bfloat162 x2 = *reinterpret_cast<const __nv_bfloat162*>(&bw[e]);
+        const __nv_bfloat162 c2 = *reinterpret_cast<const __nv_bfloat162*>(&cw[e]);
+        const __nv_bfloat162 s2 = *reinterpret_cast<const __nv_bfloat162*>(&sn);
+        const __nv_bfloat162 r1 = __hsub2_rn(__hmul2_rn(x1, c2), __hmul2_rn(x2, s2));
+        const __nv_bfloat162 r2 = __hadd2_rn(__hmul2_rn(x2, c2), __hmul2_rn(x1, s2));
+        o1[e] = *reinterpret_cast<const uint32_t*>(&r1);
+        o2[e] = *reinterpret_cast<const uint32_t*>(&r2);
       }
-    }
-    uint32_t o1[4], o2[4];
-#pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      const float x1l = bf16lo_to_f32(aw[e]), x1h = bf16hi_to_f32(aw[e]);
-      const float x2l = bf16lo_to_f32(bw[e]), x2h = bf16hi_to_f32(bw[e]);
-      const float sl = s[2 * e] * sin_sign, sh = s[2 * e + 1] * sin_sign;
-      o1[e] = pack_bf16x2_rn(fmaf(x1l, c[2 * e], -(x2l * sl)), fmaf(x1h, c[2 * e + 1], -(x2h * sh)));
-      o2[e] = pack_bf16x2_rn(fmaf(x2l, c[2 * e], x1l * sl), fmaf(x2h, c[2 * e + 1], x1h * sh));
     }
     __nv_bfloat16* op = out + row * ldo + (int64_t)head * head_dim + j0;
     *reinterpret_cast<uint4*>(op) = make_uint4(o1[0], o1[1], o1[2], o1[3]);

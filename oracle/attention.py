@@ -4,8 +4,8 @@ docstring).  CPU restatement, with the reference's bf16 rounding points, of
 99-201) and ``.backward`` (:400-493) with plain bf16 frozen weights (NF4 de-quantization = identity).
 
 The rotary embedding follows the rotate-half formula the reference's kernel implements
-(operators/rope_kernels.py:38-78); here the arithmetic is fp32 with one rounding to bf16, which is also what
-the CUDA kernel does (the reference computes in the dtype of the sine table).  Two map modes: ``prune`` is the
+(operators/rope_kernels.py:38-78), in the dtype of the sine table like the reference (pinned by the golden
+vectors of that kernel).  Two map modes: ``prune`` is the
 reference's global-threshold prune, ``topk`` the per-row top-k + grouped remainder defined in
 ``oracle/softmax_map.py``.
 """
@@ -29,14 +29,17 @@ BF16 = torch.bfloat16
 def ref_rope(x, cos, sin, backward=False):
     """``rope_forward`` / ``rope_backward`` (operators/rope_kernels.py:81-131) on x [B, M, heads, d]; cos, sin
     [>= M, d] tables whose first d/2 columns are used (:55-58).  out1 = x1*cos - x2*sin, out2 = x2*cos + x1*sin
-    (:77-78), sine negated in the backward pass (:62-63)."""
+    (:77-78), sine negated in the backward pass (:62-63).  The kernel computes in the dtype of the sine table
+    (:73-74): with bf16 tables the two products and the sum are three bf16 operations, with fp32 tables three
+    fp32 operations and the store rounds."""
     b, m, h, d = x.shape
     half = d // 2
-    c = cos.squeeze()[:m, :half].float().reshape(1, m, 1, half)
-    s = sin.squeeze()[:m, :half].float().reshape(1, m, 1, half)
+    dt = torch.float32 if sin.dtype == torch.float32 else BF16
+    c = cos.squeeze()[:m, :half].to(dt).reshape(1, m, 1, half)
+    s = sin.squeeze()[:m, :half].to(dt).reshape(1, m, 1, half)
     if backward:
         s = -s
-    x1, x2 = x[..., :half].float(), x[..., half:].float()
+    x1, x2 = x[..., :half].to(dt), x[..., half:].to(dt)
     return torch.cat([x1 * c - x2 * s, x2 * c + x1 * s], dim=-1).to(BF16)
 
 

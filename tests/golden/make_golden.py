@@ -8,15 +8,20 @@ so the test-suite itself never needs the checkout):
 What runs:
   * the reference's pure-PyTorch functions of operators/compress_function.py, imported
     unchanged (statistics, softmax prune / to_dense, update_dict);
-  * the reference's Triton kernels (operators/compress_function_kernel.py and the two
-    triton_fuse_lora_silu_hadamard_*_kernels.py files), unchanged, through the Triton CPU
+  * the reference's Triton kernels (operators/compress_function_kernel.py, the two
+    triton_fuse_lora_silu_hadamard_*_kernels.py files, the RMSNorm forward / backward kernels of
+    operators/rmsnorm_kernels.py, the softmax backward kernel of operators/softmax_kernels.py and
+    the rotary kernel of operators/rope_kernels.py), unchanged, through the Triton CPU
     interpreter.  The kernels are launched through ``.fn`` (the autotuner needs a GPU
     driver) with the tile sizes of their autotune configs.  Two interpreter repairs are
     applied, neither touches kernel source: (1) the interpreter keeps bf16 as raw uint16
     and would do arithmetic on the bits and truncate on down-casts, so bf16 binary ops,
     dots and float conversions are replaced by correct round-to-nearest-even versions;
     (2) the three libdevice calls the kernels use (round, float2uint_rn, uint2float_rn)
-    are given their C semantics (roundf = halves away from zero).
+    are given their C semantics (roundf = halves away from zero); (3) ``tl.sum`` of a bf16
+    tensor accumulates in fp32 and returns fp32, as in the Triton release the reference pins
+    (triton==2.3.0, requirements.txt:12: ``sum`` promotes its input with
+    ``_promote_reduction_input``); the installed interpreter would add up the raw bit patterns.
 """
 import os, sys
 os.environ['TRITON_INTERPRET'] = '1'
@@ -69,6 +74,13 @@ def create_dot(self, a, b, d, input_precision, max_num_imprecise_acc):
 ti.InterpreterBuilder.create_dot = create_dot
 ti.InterpreterBuilder.get_bf16 = lambda self, v: ti.TensorHandle(_f32_to_bf16bits(np.array([v], dtype=np.float32)), tl.bfloat16)
 
+def _sum_bf16_as_f32(self, input):
+    if input.dtype.scalar == tl.bfloat16:
+        v = _bits_to_f32(np.asarray(input.handle.data).view(np.uint16))
+        return self.to_tensor(np.sum(v, axis=self.axis, keepdims=self.keep_dims, dtype=np.float32), tl.float32)
+    return self.to_tensor(np.sum(input.handle.data, axis=self.axis, keepdims=self.keep_dims), input.dtype)
+ti.ReduceOps.sum = _sum_bf16_as_f32
+
 class LibdeviceShim:   # semantics of the three libdevice calls the kernels use
     @staticmethod
     def round(x):      # C roundf: halves away from zero; frac is exact in fp32
@@ -82,6 +94,9 @@ import operators.compress_function_kernel as ck
 import operators.compress_function as cf
 import operators.triton_fuse_lora_silu_hadamard_forward_kernels as fk
 import operators.triton_fuse_lora_silu_hadamard_backward_kernels as bk
+import operators.rmsnorm_kernels as rk
+import operators.softmax_kernels as sk
+import operators.rope_kernels as pk
 for m in (ck, fk, bk):
     m.tl_math = LibdeviceShim
 
@@ -128,6 +143,46 @@ def ref_fused_bwd(xa1, b1, q1, s1, xa2, b2, q2, s2, g, q):
         *xa1.stride(), *b1.stride(), *g.stride(), *q1.stride(), s1.stride(1), q, epp,
         BLOCK_SIZE_M=32, BLOCK_SIZE_N=32, BLOCK_SIZE_K=R, GROUP_SIZE_M=4)
     return o, gg, gu
+
+
+def ref_rmsnorm_fwd(x, w, eps):
+    """The launch of ``rmsnorm_forward`` (operators/rmsnorm_kernels.py:116-150) on CPU tensors (the wrapper itself
+    allocates on "cuda")."""
+    x = x.contiguous(); y = torch.empty_like(x)
+    x_arg = x.reshape(-1, x.shape[-1]); M, N = x_arg.shape
+    mean = torch.zeros((M,), dtype=torch.float32); rstd = torch.empty((M,), dtype=torch.float32)
+    BLOCK = min(65536 // x.element_size(), triton.next_power_of_2(N))
+    rk._rms_norm_fwd_fused[(M,)](x_arg, y, w, mean, rstd, x_arg.stride(0), N, eps, BLOCK_SIZE=BLOCK)
+    return y, rstd, BLOCK
+
+def ref_rmsnorm_bwd(dy, x, w, rstd, eps, BLOCK):
+    """The launch of ``rmsnorm_backward`` (:153-185).  The interpreter runs the programs one after the other, so the
+    lock the kernel spins on (:103-113) is always free."""
+    N = w.shape[0]
+    G = 64
+    if N <= 8192: G = 96
+    if N <= 4096: G = 128
+    if N <= 1024: G = 256
+    locks = torch.zeros(2 * G, dtype=torch.int32); dw = torch.zeros((G, N), dtype=x.dtype)
+    dx = torch.empty_like(dy)
+    x_arg = x.reshape(-1, x.shape[-1]); M, N = x_arg.shape
+    mean = torch.zeros((M,), dtype=torch.float32)
+    rk._rms_norm_bwd_dx_fused[(M,)](dx, dy, dw, x, w, mean, rstd, locks, x_arg.stride(0), N, eps,
+                                    BLOCK_SIZE_N=BLOCK, GROUP_SIZE_M=G)
+    return dx
+
+def ref_softmax_bwd(y, g):
+    """``softmax_backward`` (operators/softmax_kernels.py:41-56) is plain host code: called as it is."""
+    return sk.softmax_backward(y, g)
+
+def ref_rope(x, cos, sin, backward):
+    """``rope_forward`` / ``rope_backward`` (operators/rope_kernels.py:81-131), called as they are."""
+    if not backward:
+        return pk.rope_forward(x.clone(), cos, sin)
+    B, M, n, d = x.shape
+    BLOCK, warps = pk.calculate_settings(d // 2)
+    div, mod = divmod(n, pk.ROPE_GROUP_SIZE)
+    return pk.rope_backward(x.clone(), cos, sin, div + (mod != 0), BLOCK, warps)
 
 
 def main():
@@ -193,6 +248,30 @@ def main():
     out['softmax'] = dict(a=a, ratio=0.05, thr=thr, idx=sp.coalesce().indices().clone(), val=sp.coalesce().values().clone(),
                           dense=cf.decompression_softmax(sp).reshape(a.shape),
                           thr2=thr_mean, idx2=sp2.coalesce().indices().clone(), val2=sp2.coalesce().values().clone())
+    # a-14: RMSNorm forward / backward (operators/rmsnorm_kernels.py:10-54, 58-113)
+    xs = randn(3, 40, 192); xs[:, :, 7] *= 25
+    xs = xs.to(torch.bfloat16)
+    wn = (1 + 0.1 * randn(192)).to(torch.bfloat16)
+    yn, rstd, BLOCK = ref_rmsnorm_fwd(xs, wn, 1e-5)
+    dyn = randn(3, 40, 192).to(torch.bfloat16)
+    dxn = ref_rmsnorm_bwd(dyn, xs, wn, rstd, 1e-5, BLOCK)
+    out['rmsnorm'] = dict(x=xs, w=wn, eps=1e-5, y=yn, rstd=rstd, dy=dyn, dx=dxn)
+    # a-15: softmax backward (operators/softmax_kernels.py:7-38) on a causal map
+    ys = a[:, :2].contiguous()
+    gs = randn(*ys.shape).to(torch.bfloat16)
+    out['softmax_bwd'] = dict(y=ys, g=gs, o=ref_softmax_bwd(ys, gs))
+    # rotary embedding (operators/rope_kernels.py:38-78), bf16 and fp32 tables
+    pos = torch.arange(24, dtype=torch.float32)
+    inv = 1.0 / (10000.0 ** (torch.arange(0, 64, 2, dtype=torch.float32) / 64))
+    emb = torch.cat([torch.outer(pos, inv)] * 2, dim=-1)
+    xr_ = randn(2, 20, 6, 64).to(torch.bfloat16)
+    rp = dict(x=xr_)
+    for nm, dt in (('bf16', torch.bfloat16), ('f32', torch.float32)):
+        c, s_ = emb.cos().to(dt), emb.sin().to(dt)
+        rp['cos_' + nm] = c; rp['sin_' + nm] = s_
+        rp['fwd_' + nm] = ref_rope(xr_, c, s_, False)
+        rp['bwd_' + nm] = ref_rope(xr_, c, s_, True)
+    out['rope'] = rp
     # a-10: update_dict running mean (compress_function.py:15-27)
     old = {'outlier_channel_index': None, 'scale': None}
     hist = []

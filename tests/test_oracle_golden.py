@@ -65,6 +65,39 @@ def test_softmax_prune(golden):
     assert torch.equal(oracle.ref_softmax_restore(idx, val, d["a"].shape), d["dense"])
 
 
+def test_rmsnorm_golden(golden):
+    """operators/rmsnorm_kernels.py:10-54, 58-113 run through the interpreter.  The mean of squares is an fp32
+    sum whose order differs (the kernel reduces a block, torch sums pairwise): rstd within two fp32 ulps, the
+    bf16 outputs equal."""
+    d = golden["rmsnorm"]
+    y, rstd = oracle.ref_rmsnorm_forward(d["x"], d["w"], d["eps"])
+    assert torch.equal(y, d["y"])
+    assert ((rstd - d["rstd"]).abs() <= d["rstd"].abs() * 2 ** -22).all()
+    assert torch.equal(oracle.ref_rmsnorm_backward(d["dy"], d["x"], d["w"], d["rstd"]), d["dx"])
+    # the LayerNorm-style mean term of the reference's backward (:96-98) is part of the pinned result
+    n = d["x"].shape[-1]
+    xhat = d["x"].float() * d["rstd"].reshape(3, 40, 1)
+    wdy = d["w"].float() * d["dy"].float()
+    no_c2 = ((wdy - xhat * (xhat * wdy).sum(-1, keepdim=True) / n) * d["rstd"].reshape(3, 40, 1)).bfloat16()
+    assert not torch.equal(no_c2, d["dx"])
+
+
+def test_softmax_backward_golden(golden):
+    """operators/softmax_kernels.py:7-38 through the interpreter (bf16 product, fp32 row sum as in the pinned
+    Triton release)."""
+    d = golden["softmax_bwd"]
+    assert torch.equal(oracle.ref_softmax_backward(d["y"], d["g"]), d["o"])
+
+
+def test_rope_golden(golden):
+    """operators/rope_kernels.py:38-131 through the interpreter, bf16 and fp32 tables, both directions."""
+    from oracle.attention import ref_rope
+    d = golden["rope"]
+    for nm in ("bf16", "f32"):
+        assert torch.equal(ref_rope(d["x"], d["cos_" + nm], d["sin_" + nm]), d["fwd_" + nm])
+        assert torch.equal(ref_rope(d["x"], d["cos_" + nm], d["sin_" + nm], backward=True), d["bwd_" + nm])
+
+
 def test_roundf_half_away():
     r = torch.tensor([0.5, -0.5, 1.5, -1.5, 2.5, 0.49999997, -0.49999997, 7.5, -8.5, 0.0, 1e9, float("inf")])
     want = torch.tensor([1.0, -1.0, 2.0, -2.0, 3.0, 0.0, -0.0, 8.0, -9.0, 0.0, 1e9, float("inf")])
