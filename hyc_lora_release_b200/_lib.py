@@ -1,6 +1,7 @@
 """ctypes binding of libhyc.so.  One entry per declaration of include/hyc.h."""
 import ctypes
 import os
+import threading
 
 import torch
 
@@ -12,7 +13,7 @@ if not os.path.exists(LIB_PATH):
         "libhyc.so is not built (%s). Build it with `python hyc_lora_release_b200/build.py`; "
         "there is no fallback implementation." % LIB_PATH)
 
-lib = ctypes.CDLL(LIB_PATH)
+_cdll = ctypes.CDLL(LIB_PATH)
 
 _p, _i, _l, _f, _z = ctypes.c_void_p, ctypes.c_int, ctypes.c_int64, ctypes.c_float, ctypes.c_size_t
 
@@ -32,6 +33,9 @@ SIGNATURES = {
     "hyc_softmax_prune_restore": (_i, [_p, _p, _l, _p, _l, _p]),
     "hyc_softmax_prune_restore_counted": (_i, [_p, _p, _p, _l, _p, _l, _p]),
     "hyc_softmax_prune_static": (_i, [_p, _l, _f, _p, _p, _l, _p, _p]),
+    "hyc_softmax_prune_tiled_directory_bytes": (_z, [_l]),
+    "hyc_softmax_prune_tiled": (_i, [_p, _l, _f, _p, _l, _p, _p, _p]),
+    "hyc_softmax_prune_tiled_restore": (_i, [_p, _l, _p, _p, _l, _p]),
     "hyc_softmax_topk_compress": (_i, [_p, _l, _i, _i, _p, _p, _p, _p, _p, _i, _p]),
     "hyc_softmax_topk_restore": (_i, [_p, _p, _i, _p, _p, _p, _l, _i, _p, _i, _p]),
     "hyc_softmax_topk_restore_bwd": (_i, [_p, _p, _i, _p, _p, _p, _l, _i, _p, _p, _i, _f, _p]),
@@ -57,9 +61,33 @@ SIGNATURES = {
 }
 
 for _name, (_res, _args) in SIGNATURES.items():
-    _fn = getattr(lib, _name)
+    _fn = getattr(_cdll, _name)
     _fn.restype = _res
     _fn.argtypes = _args
+
+_pending = threading.local()
+
+
+class _DeviceGuardedLibrary:
+    """The library's entry points launch on the CURRENT device.  Every call site passes ``stream_of(t)``, which
+    notes the device of ``t``; the call then runs with that device current, so a tensor on cuda:1 is never paired
+    with a launch (or the built-in scratch) of cuda:0."""
+
+    def __getattr__(self, name):
+        fn = getattr(_cdll, name)
+
+        def call(*args):
+            dev = getattr(_pending, "device", None)      # kept: a stream handle may serve several calls in a row
+            if dev is not None and dev != torch.cuda.current_device():
+                with torch.cuda.device(dev):
+                    return fn(*args)
+            return fn(*args)
+        call.__name__ = name
+        setattr(self, name, call)
+        return call
+
+
+lib = _DeviceGuardedLibrary()
 
 
 class HycError(RuntimeError):
@@ -83,10 +111,20 @@ def ptr(t):
 
 
 def stream_of(t):
+    """torch's current stream on the device of ``t``; also notes that device for the call that follows."""
+    _pending.device = t.device.index
     return ctypes.c_void_p(torch.cuda.current_stream(t.device).cuda_stream)
 
 
 def require_cuda(*tensors):
+    """All given tensors (None entries skipped) must be CUDA tensors on ONE device."""
+    dev = None
     for t in tensors:
-        if t is not None and not t.is_cuda:
+        if t is None:
+            continue
+        if not t.is_cuda:
             raise RuntimeError("this operator runs only on CUDA tensors (sm_100a kernels); there is no CPU path")
+        if dev is None:
+            dev = t.device
+        elif t.device != dev:
+            raise RuntimeError("the tensors of one call live on different devices (%s and %s)" % (dev, t.device))

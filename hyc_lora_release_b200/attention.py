@@ -261,7 +261,7 @@ def attention_backward(grad_medium, saved, w: AttnWeights, status=None, on_lora_
     if saved['map_mode'] == "topk":
         a = m.to_dense()
     else:
-        a = m.to_dense().reshape(saved['a_shape']) if isinstance(m, cf.PrunedMap) else \
+        a = m.to_dense().reshape(saved['a_shape']) if isinstance(m, (cf.PrunedMap, cf.TiledPrunedMap)) else \
             cf.decompression_softmax(m).reshape(saved['a_shape'])
     v2 = _rebuild(saved['v_q'], saved['v_scale'], saved['v_xa'], w.bv, q)
     vh = _repeat_kv(_heads(v2, B, M, nkv), n_rep)

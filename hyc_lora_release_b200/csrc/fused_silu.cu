@@ -556,7 +556,7 @@ static inline dim3 fused_wide_grid(K kern, int64_t rows, int N) {
   const int64_t tiles = (rows + 15) / 16;
   int per_sm = 0;
   if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, 256, 0) != cudaSuccess || per_sm < 1) per_sm = 2;
-  int64_t slots = ((int64_t)kNumSMs * per_sm) / cgroups;
+  int64_t slots = ((int64_t)num_sms() * per_sm) / cgroups;
   if (slots > tiles) slots = tiles;
   if (slots < 1) slots = 1;
   if (slots > 65535) slots = 65535;
@@ -566,7 +566,7 @@ static inline dim3 fused_wide_grid(K kern, int64_t rows, int N) {
 static inline dim3 fused_grid(int64_t rows, int N) {
   const int cgroups = (N / 32 + 7) / 8;
   const int64_t tiles = (rows + 15) / 16;
-  int64_t slots = ((int64_t)kNumSMs * 6 + cgroups - 1) / cgroups;
+  int64_t slots = ((int64_t)num_sms() * 6 + cgroups - 1) / cgroups;
   if (slots > tiles) slots = tiles;
   if (slots < 1) slots = 1;
   if (slots > 65535) slots = 65535;

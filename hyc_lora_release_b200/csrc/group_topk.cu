@@ -462,7 +462,7 @@ topk_restore_kernel(const __nv_bfloat16* __restrict__ val, const uint16_t* __res
 
 static inline int warp_grid(int64_t items) {
   int64_t blocks = (items + 7) / 8;
-  int64_t cap = (int64_t)kNumSMs * 8;
+  int64_t cap = (int64_t)num_sms() * 8;
   if (blocks > cap) blocks = cap;
   if (blocks < 1) blocks = 1;
   return (int)blocks;

@@ -16,7 +16,25 @@ extern "C" HYC_API void hyc_set_last_cuda_error(int e);
 
 namespace hyc {
 
-constexpr int kNumSMs = 148;
+// Multiprocessor count of the current device (launch geometry), asked once per device.  The cache is written
+// without a lock: concurrent callers store the same value.
+inline int num_sms() {
+  static int cached[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  if (cached[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n < 1) n = 148;
+    cached[dev] = n;
+  }
+  return cached[dev];
+}
+// index of the current device for per-device one-time set-up (-1: no device)
+inline int current_device_slot() {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return -1;
+  return dev;
+}
 
 __host__ __device__ inline bool aligned(const void* p, size_t a) {
   return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0;

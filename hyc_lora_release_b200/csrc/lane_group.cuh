@@ -190,9 +190,9 @@ inline void lane_launch_shape(K kern, int64_t rows, int rows_per_warp, int& grid
   for (int w = 8; w >= 5; --w) {
     int per_sm = 0;
     if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, 32 * w, 0) != cudaSuccess || per_sm < 1) per_sm = 1;
-    const int64_t resident = (int64_t)kNumSMs * per_sm * w;
+    const int64_t resident = (int64_t)num_sms() * per_sm * w;
     int64_t blocks = (items + w - 1) / w;
-    if (blocks > (int64_t)kNumSMs * per_sm) blocks = (int64_t)kNumSMs * per_sm;
+    if (blocks > (int64_t)num_sms() * per_sm) blocks = (int64_t)num_sms() * per_sm;
     const int64_t rounds = (items + resident - 1) / resident;
     const double eff = items <= resident ? 1.0 + 1e-3 * w : (double)items / (double)(rounds * resident);
     if (eff > best + 1e-9) { best = eff; grid = (int)(blocks < 1 ? 1 : blocks); threads = 32 * w; }

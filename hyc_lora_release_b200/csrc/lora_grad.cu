@@ -191,7 +191,7 @@ extern "C" HYC_API int hyc_lora_grad_a_dequant(const void* q, const void* scale,
   HYC_CHECK_LAUNCH();
   const int64_t n = (int64_t)R2 * H;
   int64_t rb = (n + 255) / 256;
-  if (rb > kNumSMs * 8) rb = kNumSMs * 8;
+  if (rb > num_sms() * 8) rb = num_sms() * 8;
   lora_grad_a_reduce_kernel<<<(int)rb, 256, 0, st>>>((const float*)workspace, splits, n, (__nv_bfloat16*)out);
   HYC_CHECK_LAUNCH();
   return HYC_OK;

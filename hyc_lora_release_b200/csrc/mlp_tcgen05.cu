@@ -821,17 +821,19 @@ template <int EPI, int QBIT, bool B_MN>
 static int launch(const CUtensorMap& a1, const CUtensorMap& b1, const CUtensorMap& a2, const CUtensorMap& b2,
                   const CUtensorMap& a3, const CUtensorMap& b3, const Params& p, cudaStream_t st) {
   auto kern = mlp_gemm_kernel<EPI, QBIT, B_MN>;
-  static bool attr = false;
-  if (!attr) {
+  // the attribute belongs to a (function, device) pair: set once per device (unknown device: every time)
+  static bool attr[64] = {false};
+  const int slot = current_device_slot();
+  if (slot < 0 || !attr[slot]) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess) {
       hyc_set_last_cuda_error((int)cudaGetLastError());
       return HYC_ERR_LAUNCH;
     }
-    attr = true;
+    if (slot >= 0) attr[slot] = true;
   }
   constexpr int TILE_N = (EPI == EPI_GATEUP) ? BN / 2 : BN;
   const int tiles = ((p.M + BM - 1) / BM) * (p.N / TILE_N);
-  const int grid = tiles < kNumSMs ? tiles : kNumSMs;
+  const int grid = tiles < num_sms() ? tiles : num_sms();
 #ifdef HYC_TC_PROF
   Params pp = p;
   pp.prof = g_tc_prof;

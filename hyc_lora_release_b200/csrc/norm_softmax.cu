@@ -491,7 +491,7 @@ extern "C" HYC_API int hyc_rmsnorm_fwd(const void* x, const void* w, float eps, 
   if (rows < 0 || N <= 0 || N % 8 != 0 || N > kNormThreads * 8 * kNormMaxVec) return HYC_ERR_SHAPE;
   if (!aligned(x, 16) || !aligned(w, 16) || !aligned(y, 16)) return HYC_ERR_ALIGN;
   if (rows == 0) return HYC_OK;
-  int64_t grid = rows < (int64_t)kNumSMs * 8 ? rows : (int64_t)kNumSMs * 8;
+  int64_t grid = rows < (int64_t)num_sms() * 8 ? rows : (int64_t)num_sms() * 8;
   if (N <= 2 * kNormThreads * 8)
     rmsnorm_fwd_kernel<2><<<(int)grid, kNormThreads, 0, (cudaStream_t)stream>>>(
         (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, eps, (__nv_bfloat16*)y, rstd, rows, N);
@@ -516,7 +516,7 @@ extern "C" HYC_API int hyc_rmsnorm_fwd_save(const void* x, const void* w, float 
   if (rows == 0) return HYC_OK;
   // resident blocks only: a block computes its per-column constants and the outlier-column map once, then walks
   // rows with the next row's loads in flight
-  const int64_t cap = (int64_t)kNumSMs * (N <= 2 * kNormThreads * 8 ? 3 : 1);
+  const int64_t cap = (int64_t)num_sms() * (N <= 2 * kNormThreads * 8 ? 3 : 1);
   const int64_t grid = rows < cap ? rows : cap;
   const size_t smem = k > 0 ? (size_t)N * 2 : 0;
 #define FS(QB) if (N <= 2 * kNormThreads * 8) FSV(QB, 2); else FSV(QB, kNormMaxVec)
@@ -542,7 +542,7 @@ extern "C" HYC_API int hyc_rmsnorm_bwd_packed(const void* dy, const void* qx, co
       (residual_grad && !aligned(residual_grad, 16))) return HYC_ERR_ALIGN;
   if (rows == 0) return HYC_OK;
   // resident blocks only (each block builds the outlier-column map once and then walks rows)
-  const int64_t cap = (int64_t)kNumSMs * (N <= 2 * kNormThreads * 8 ? 4 : 1);
+  const int64_t cap = (int64_t)num_sms() * (N <= 2 * kNormThreads * 8 ? 4 : 1);
   const int64_t grid = rows < cap ? rows : cap;
   const size_t smem = k > 0 ? (size_t)N * 2 : 0;
 #define BPN(QB, NV) rmsnorm_bwd_packed_kernel<QB, NV><<<(int)grid, kNormThreads, smem, (cudaStream_t)stream>>>(      \
@@ -563,7 +563,7 @@ extern "C" HYC_API int hyc_rmsnorm_bwd(const void* dy, const void* x, const void
   if (rows < 0 || N <= 0 || N % 8 != 0 || N > kNormThreads * 8 * kNormMaxVec) return HYC_ERR_SHAPE;
   if (!aligned(x, 16) || !aligned(w, 16) || !aligned(dy, 16) || !aligned(dx, 16)) return HYC_ERR_ALIGN;
   if (rows == 0) return HYC_OK;
-  int64_t grid = rows < (int64_t)kNumSMs * 8 ? rows : (int64_t)kNumSMs * 8;
+  int64_t grid = rows < (int64_t)num_sms() * 8 ? rows : (int64_t)num_sms() * 8;
   if (N <= 2 * kNormThreads * 8)
     rmsnorm_bwd_kernel<2><<<(int)grid, kNormThreads, 0, (cudaStream_t)stream>>>(
         (const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, rstd, (__nv_bfloat16*)dx, rows, N);
@@ -584,7 +584,7 @@ extern "C" HYC_API int hyc_softmax_bwd(const void* y, const void* g, void* o, in
     return HYC_OK;
   }
   int64_t grid = (rows + 7) / 8;
-  if (grid > (int64_t)kNumSMs * 8) grid = (int64_t)kNumSMs * 8;
+  if (grid > (int64_t)num_sms() * 8) grid = (int64_t)num_sms() * 8;
   softmax_bwd_kernel<<<(int)grid, 256, 0, (cudaStream_t)stream>>>(
       (const __nv_bfloat16*)y, (const __nv_bfloat16*)g, (__nv_bfloat16*)o, rows, S, out_scale);
   HYC_CHECK_LAUNCH();
@@ -600,7 +600,7 @@ extern "C" HYC_API int hyc_softmax_fwd_scale_mask(const void* scores, float scal
   if (mask_or_null && (!aligned(mask_or_null, 16) || (mask_stride_b & 7) || (mask_stride_h & 7) || (mask_stride_row & 7))) return HYC_ERR_ALIGN;
   if (rows == 0) return HYC_OK;
   int64_t grid = (rows + 7) / 8;
-  if (grid > (int64_t)kNumSMs * 8) grid = (int64_t)kNumSMs * 8;
+  if (grid > (int64_t)num_sms() * 8) grid = (int64_t)num_sms() * 8;
 #define SF(NV) softmax_fwd_kernel<NV><<<(int)grid, 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)scores, scale, \
       (const __nv_bfloat16*)mask_or_null, mask_stride_b, mask_stride_h, mask_stride_row, heads, M, (__nv_bfloat16*)a, rows, S)
   if (S <= 512) SF(2); else if (S <= 1024) SF(4); else if (S <= 2048) SF(8); else SF(16);

@@ -474,7 +474,7 @@ static inline dim3 stream_grid(Kernel kern, int threads, size_t smem, int64_t ro
   const int64_t groups = (rows + unroll - 1) / unroll;
   int per_sm = 0;
   if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, threads, smem) != cudaSuccess || per_sm < 1) per_sm = 2;
-  int64_t slots = ((int64_t)kNumSMs * per_sm) / col_tiles;
+  int64_t slots = ((int64_t)num_sms() * per_sm) / col_tiles;
   if (slots > groups) slots = groups;
   if (slots < 1) slots = 1;
   if (slots > 65535) slots = 65535;

@@ -95,7 +95,7 @@ extern "C" HYC_API int hyc_rope(const void* x, int64_t ldx, void* out, int64_t l
   if (rows == 0) return HYC_OK;
   const int64_t total = rows * n_heads * (head_dim / 16);
   int64_t blocks = (total + 255) / 256;
-  const int64_t cap = (int64_t)kNumSMs * 8;
+  const int64_t cap = (int64_t)num_sms() * 8;
   if (blocks > cap) blocks = cap;
   const float sgn = backward ? -1.f : 1.f;
   if (table_is_f32)

@@ -239,11 +239,146 @@ prune_scatter_counted_kernel(const int64_t* __restrict__ idx, const __nv_bfloat1
   }
 }
 
+// One-pass, tiled form for callers that only ever restore the map (the fused layer in steady state): the map is
+// read once, there is no offset array and no second launch, and an entry costs 4 bytes instead of 10.
+// A BATCH is 2048 consecutive elements (half a tile).  A warp stages the entries of a batch in shared memory as
+// (offset within the batch << 16 | bf16 value) words, reserves a span of the word list with ONE atomic add on the
+// device-side count, writes the span with consecutive lanes and records {span start, entries} in the batch's
+// directory slot.  Which span a batch gets depends on the order in which the warps arrive; inside a span the
+// entries of a lane are adjacent (the order is fixed, but not ascending).  The count keeps growing past `capacity` (the caller sees the overflow);
+// words beyond it are dropped.
+constexpr int kBatchElems = 256 * kBatch;       // 2048
+
+template <bool NEG>
+__global__ void __launch_bounds__(kTileThreads, 4)
+prune_tiled_kernel(const __nv_bfloat16* __restrict__ a, int64_t numel, float thr, int64_t n_tiles,
+                   uint32_t* __restrict__ words, uint32_t capacity, uint2* __restrict__ dir,
+                   unsigned long long* __restrict__ count) {
+  __shared__ uint32_t s_stage[kWarpsPerBlock][256 * kFillTrips];
+  const __nv_bfloat162 t2 = __float2bfloat162_rn(thr);
+  const int lane = threadIdx.x & 31;
+  uint32_t* stage = s_stage[threadIdx.x >> 5];
+  const int64_t n_batches = (numel + kBatchElems - 1) / kBatchElems;
+  const int64_t warp0 = (int64_t)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
+  for (int64_t tile = warp0; tile < n_tiles; tile += (int64_t)gridDim.x * kWarpsPerBlock) {
+    const int64_t t0 = tile * kTileElems + 8 * lane;
+#pragma unroll 1
+    for (int b = 0; b < kTileElems / kBatchElems; ++b) {
+      const int64_t batch = tile * (kTileElems / kBatchElems) + b;
+      if (batch >= n_batches) break;
+      uint4 u[kBatch];
+#pragma unroll
+      for (int j = 0; j < kBatch; ++j) {
+        const int64_t base = t0 + 256 * (b * kBatch + j);
+        u[j] = base < numel ? load_chunk<true>(a, base, numel) : make_uint4(0u, 0u, 0u, 0u);
+      }
+      uint32_t mk[kBatch / kFillTrips];      // the keep masks of a group's four trips, one byte each
+      int cg[kBatch / kFillTrips];
+#pragma unroll
+      for (int g = 0; g < kBatch / kFillTrips; ++g) {
+        mk[g] = 0u;
+#pragma unroll
+        for (int jj = 0; jj < kFillTrips; ++jj) mk[g] |= keep_mask8<NEG>(u[g * kFillTrips + jj], t2) << (8 * jj);
+        cg[g] = __popc(mk[g]);
+      }
+      // both group totals in one reduction (a group holds at most 1024 entries)
+      const unsigned packed = __reduce_add_sync(0xffffffffu, (unsigned)cg[0] | ((unsigned)cg[1] << 16));
+      const unsigned n_batch = (packed & 0xffffu) + (packed >> 16);
+      unsigned long long span = 0;
+      if (lane == 0) {
+        if (n_batch) span = atomicAdd(count, (unsigned long long)n_batch);
+        // a span that starts beyond 2^32 words cannot be addressed (and is far beyond any capacity): recorded as empty
+        dir[batch] = span <= 0xffffffffull ? make_uint2((uint32_t)span, n_batch) : make_uint2(0u, 0u);
+      }
+      if (n_batch == 0) continue;
+      unsigned long long run = __shfl_sync(0xffffffffu, span, 0);
+#pragma unroll
+      for (int g = 0; g < kBatch / kFillTrips; ++g) {
+        const int n_staged = g == 0 ? (int)(packed & 0xffffu) : (int)(packed >> 16);
+        if (n_staged == 0) continue;
+        int total;
+        int pos = warp_excl_scan(cg[g], lane, total);
+#pragma unroll
+        for (int jj = 0; jj < kFillTrips; ++jj) {
+          const int j = g * kFillTrips + jj;
+          const uint32_t w[4] = {u[j].x, u[j].y, u[j].z, u[j].w};
+          const uint32_t off = (uint32_t)(256 * j + 8 * lane);        // offset inside the batch
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            if (mk[g] & (1u << (8 * jj + e))) stage[pos++] = __byte_perm(w[e >> 1], off + e, (e & 1) ? 0x5432 : 0x5410);
+          }
+        }
+        __syncwarp();
+        for (int i = lane; i < n_staged; i += 32) {
+          const unsigned long long p = run + i;
+          if (p < capacity) words[p] = stage[i];
+        }
+        run += n_staged;
+        __syncwarp();
+      }
+    }
+  }
+}
+
+// Restore of the tiled form in one pass: a warp builds a batch's 4 KB of the dense map in shared memory (zeros, then
+// the batch's entries from its span) and writes it with 16-byte stores.  One directory read and one dependent
+// round of list reads per batch; every output byte is written exactly once.
+__global__ void __launch_bounds__(kTileThreads, 4)
+prune_tiled_restore_kernel(const uint32_t* __restrict__ words, uint32_t capacity, const uint2* __restrict__ dir,
+                           __nv_bfloat16* __restrict__ out, int64_t numel, int64_t n_batches) {
+  __shared__ __align__(16) uint16_t s_tile[kWarpsPerBlock][kBatchElems];
+  const int lane = threadIdx.x & 31;
+  uint16_t* tile = s_tile[threadIdx.x >> 5];
+  uint4* tile4 = reinterpret_cast<uint4*>(tile);
+  const int64_t warp0 = (int64_t)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
+  const int64_t stride = (int64_t)gridDim.x * kWarpsPerBlock;
+  uint2 d = warp0 < n_batches ? __ldg(dir + warp0) : make_uint2(0u, 0u);
+  for (int64_t batch = warp0; batch < n_batches; batch += stride) {
+    const uint2 cur = d;
+    if (batch + stride < n_batches) d = __ldg(dir + batch + stride);     // the next batch's slot, one round ahead
+    // entries first (the loads are in flight while the tile is cleared)
+    uint32_t n = cur.y;
+    if (cur.x >= capacity) n = 0u;
+    else if (n > capacity - cur.x) n = capacity - cur.x;
+    constexpr int PRE = 4;
+    uint32_t w[PRE];
+#pragma unroll
+    for (int i = 0; i < PRE; ++i) {
+      const uint32_t j = lane + 32u * i;
+      w[i] = j < n ? __ldg(words + cur.x + j) : 0xffffffffu;
+    }
+#pragma unroll
+    for (int c = 0; c < kBatchElems / (8 * 32); ++c) tile4[c * 32 + lane] = make_uint4(0u, 0u, 0u, 0u);
+    __syncwarp();
+#pragma unroll
+    for (int i = 0; i < PRE; ++i) {
+      const uint32_t j = lane + 32u * i;
+      if (j < n) tile[(w[i] >> 16) & (kBatchElems - 1)] = (uint16_t)(w[i] & 0xffffu);
+    }
+    for (uint32_t j = lane + 32u * PRE; j < n; j += 32u) {
+      const uint32_t wv = __ldg(words + cur.x + j);
+      tile[(wv >> 16) & (kBatchElems - 1)] = (uint16_t)(wv & 0xffffu);
+    }
+    __syncwarp();
+    const int64_t e0 = batch * kBatchElems;
+#pragma unroll
+    for (int c = 0; c < kBatchElems / (8 * 32); ++c) {
+      const int64_t e = e0 + 8 * (c * 32 + lane);
+      if (e + 8 <= numel) {
+        st_stream_v4(out + e, tile4[c * 32 + lane]);
+      } else {
+        for (int t = 0; t < 8 && e + t < numel; ++t) out[e + t] = __ushort_as_bfloat16(tile[8 * (c * 32 + lane) + t]);
+      }
+    }
+    __syncwarp();
+  }
+}
+
 static inline int64_t n_tiles_of(int64_t numel) { return (numel + kTileElems - 1) / kTileElems; }
 // one warp per tile, eight tiles per block; very large maps wrap around a grid of 32 blocks per SM
 static inline int tile_grid(int64_t n_tiles) {
   int64_t g = (n_tiles + kWarpsPerBlock - 1) / kWarpsPerBlock;
-  if (g > (int64_t)kNumSMs * 32) g = (int64_t)kNumSMs * 32;
+  if (g > (int64_t)num_sms() * 32) g = (int64_t)num_sms() * 32;
   return (int)(g < 1 ? 1 : g);
 }
 // the comparison of the reference runs in bf16: the fp32 threshold is rounded to bf16 first
@@ -313,7 +448,7 @@ extern "C" HYC_API int hyc_softmax_prune_restore(const int64_t* idx, const void*
   if (cudaMemsetAsync(a_out, 0, (size_t)numel * 2, st) != cudaSuccess) { hyc_set_last_cuda_error((int)cudaGetLastError()); return HYC_ERR_LAUNCH; }
   if (nnz > 0) {
     int64_t g = (nnz + 255) / 256;
-    if (g > (int64_t)kNumSMs * 16) g = (int64_t)kNumSMs * 16;
+    if (g > (int64_t)num_sms() * 16) g = (int64_t)num_sms() * 16;
     prune_scatter_kernel<<<(int)g, 256, 0, st>>>(idx, (const __nv_bfloat16*)val, nnz, (__nv_bfloat16*)a_out, numel);
     HYC_CHECK_LAUNCH();
   }
@@ -328,11 +463,54 @@ extern "C" HYC_API int hyc_softmax_prune_restore_counted(const int64_t* idx, con
   if (cudaMemsetAsync(a_out, 0, (size_t)numel * 2, st) != cudaSuccess) { hyc_set_last_cuda_error((int)cudaGetLastError()); return HYC_ERR_LAUNCH; }
   if (capacity > 0) {
     int64_t g = (capacity + 255) / 256;
-    if (g > (int64_t)kNumSMs * 16) g = (int64_t)kNumSMs * 16;
+    if (g > (int64_t)num_sms() * 16) g = (int64_t)num_sms() * 16;
     prune_scatter_counted_kernel<<<(int)g, 256, 0, st>>>(idx, (const __nv_bfloat16*)val, nnz_dev, capacity,
                                                          (__nv_bfloat16*)a_out, numel);
     HYC_CHECK_LAUNCH();
   }
+  return HYC_OK;
+}
+
+extern "C" HYC_API size_t hyc_softmax_prune_tiled_directory_bytes(int64_t numel) {
+  if (numel < 0) return 0;
+  return (size_t)((numel + kBatchElems - 1) / kBatchElems) * sizeof(uint2);
+}
+
+extern "C" HYC_API int hyc_softmax_prune_tiled(const void* a, int64_t numel, float threshold,
+                                               uint32_t* words_out, int64_t capacity, void* directory_out,
+                                               int64_t* nnz_out, void* stream) {
+  if (!a || !nnz_out || !directory_out) return HYC_ERR_NULL;
+  if (capacity > 0 && !words_out) return HYC_ERR_NULL;
+  if (numel <= 0 || capacity < 0 || capacity > 0xffffffffll) return HYC_ERR_SHAPE;
+  if (!aligned(a, 16) || !aligned(nnz_out, 8) || !aligned(directory_out, 8) || !aligned(words_out, 4)) return HYC_ERR_ALIGN;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (cudaMemsetAsync(nnz_out, 0, sizeof(int64_t), st) != cudaSuccess) { hyc_set_last_cuda_error((int)cudaGetLastError()); return HYC_ERR_LAUNCH; }
+  const int64_t nt = n_tiles_of(numel);
+  const float thr = thr_bf16(threshold);
+  // four resident blocks of eight warps per multiprocessor; larger maps wrap around
+  int64_t g = (nt + kWarpsPerBlock - 1) / kWarpsPerBlock;
+  if (g > (int64_t)num_sms() * 4) g = (int64_t)num_sms() * 4;
+  if (thr >= 0.f)
+    prune_tiled_kernel<false><<<(int)g, kTileThreads, 0, st>>>((const __nv_bfloat16*)a, numel, thr, nt, words_out, (uint32_t)capacity,
+                                                            (uint2*)directory_out, (unsigned long long*)nnz_out);
+  else
+    prune_tiled_kernel<true><<<(int)g, kTileThreads, 0, st>>>((const __nv_bfloat16*)a, numel, thr, nt, words_out, (uint32_t)capacity,
+                                                           (uint2*)directory_out, (unsigned long long*)nnz_out);
+  HYC_CHECK_LAUNCH();
+  return HYC_OK;
+}
+
+extern "C" HYC_API int hyc_softmax_prune_tiled_restore(const uint32_t* words, int64_t capacity, const void* directory,
+                                                       void* a_out, int64_t numel, void* stream) {
+  if (!a_out || !directory || (capacity > 0 && !words)) return HYC_ERR_NULL;
+  if (numel <= 0 || capacity < 0 || capacity > 0xffffffffll) return HYC_ERR_SHAPE;
+  if (!aligned(a_out, 16) || !aligned(directory, 8)) return HYC_ERR_ALIGN;
+  const int64_t nb = (numel + kBatchElems - 1) / kBatchElems;
+  int64_t g = (nb + kWarpsPerBlock - 1) / kWarpsPerBlock;
+  if (g > (int64_t)num_sms() * 4) g = (int64_t)num_sms() * 4;
+  prune_tiled_restore_kernel<<<(int)g, kTileThreads, 0, (cudaStream_t)stream>>>(words, (uint32_t)capacity, (const uint2*)directory,
+                                                                             (__nv_bfloat16*)a_out, numel, nb);
+  HYC_CHECK_LAUNCH();
   return HYC_OK;
 }
 
@@ -356,6 +534,8 @@ constexpr int64_t kStaticMaxTiles = 65536;
 static __device__ __align__(256) int64_t g_prune_offsets[1 + kStaticMaxTiles];
 
 static int64_t* static_offsets_for_current_device(int* err) {
+  // one slot per device, filled on that device's first call.  Written without a lock: the documented use is one
+  // host thread per GPU, and two threads racing on a slot would store the same address.
   static int64_t* cached[64] = {nullptr};
   int dev = -1;
   cudaError_t e = cudaGetDevice(&dev);
@@ -379,6 +559,15 @@ extern "C" HYC_API int hyc_softmax_prune_static(const void* a, int64_t numel, fl
   if (!aligned(a, 16) || !aligned(nnz_out, 8)) return HYC_ERR_ALIGN;
   const int64_t nt = n_tiles_of(numel);
   if (nt > kStaticMaxTiles) return HYC_ERR_CAPACITY;   // map too large for the built-in scratch
+  // the built-in scratch is the CURRENT device's copy: a map that lives on another GPU is refused before any launch
+  {
+    cudaPointerAttributes pa;
+    int cur = -1;
+    if (cudaPointerGetAttributes(&pa, a) == cudaSuccess && pa.type == cudaMemoryTypeDevice &&
+        cudaGetDevice(&cur) == cudaSuccess && pa.device != cur)
+      return HYC_ERR_UNSUPPORTED;
+    (void)cudaGetLastError();      // an unregistered (host test) pointer leaves an error state behind: clear it
+  }
   int err = 0;
   int64_t* ws = static_offsets_for_current_device(&err);
   if (!ws) { hyc_set_last_cuda_error(err); return HYC_ERR_LAUNCH; }

@@ -157,10 +157,14 @@ extern "C" HYC_API int hyc_channel_norm_topk(const void* x0, int M, int N, int64
     int n_pow2 = 2;
     while (n_pow2 < N) n_pow2 <<= 1;
     size_t smem = (size_t)n_pow2 * sizeof(uint32_t);
-    static bool attr_set = false;
-    if (smem > 48 * 1024 && !attr_set) {
-      cudaFuncSetAttribute(channel_topk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 128 * 1024);
-      attr_set = true;
+    static bool attr_set[64] = {false};      // per device
+    const int slot = current_device_slot();
+    if (smem > 48 * 1024 && (slot < 0 || !attr_set[slot])) {
+      if (cudaFuncSetAttribute(channel_topk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 128 * 1024) != cudaSuccess) {
+        hyc_set_last_cuda_error((int)cudaGetLastError());
+        return HYC_ERR_LAUNCH;
+      }
+      if (slot >= 0) attr_set[slot] = true;
     }
     channel_topk_kernel<<<1, 1024, smem, st>>>((const __nv_bfloat16*)norm_out, N, n_pow2, k, idx_out);
     HYC_CHECK_LAUNCH();

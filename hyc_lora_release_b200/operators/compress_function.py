@@ -322,14 +322,68 @@ class PrunedMap:
         return out
 
 
-def compression_softmax_static(x: torch.Tensor, outlier, capacity=None, margin=1.5, ratio=None):
+class TiledPrunedMap:
+    """The threshold-pruned map in the tiled form of ``hyc_softmax_prune_tiled``: 4-byte words (offset inside a
+    2048-element batch << 16 | bf16 bits) in per-batch spans, a directory of {span start, entries} per batch and the
+    device-side count.  ``to_dense()`` rebuilds the map in one pass; nothing synchronises with the host."""
+
+    BATCH = 2048
+
+    def __init__(self, words, directory, nnz, shape):
+        self.words, self.directory, self.nnz, self.shape = words, directory, nnz, tuple(shape)
+
+    @property
+    def capacity(self):
+        return self.words.numel()
+
+    def nbytes(self):
+        return self.words.numel() * 4 + self.directory.numel() * 4 + 8
+
+    def overflowed(self):
+        """True if more entries passed the threshold than the buffers hold (synchronises)."""
+        return int(self.nnz.item()) > self.capacity
+
+    def to_dense(self, out=None):
+        numel = 1
+        for d in self.shape:
+            numel *= d
+        if out is None:
+            out = torch.empty(self.shape, dtype=BF16, device=self.words.device)
+        elif out.numel() != numel or out.dtype != BF16 or not out.is_contiguous():
+            raise ValueError("`out` must be a contiguous bf16 tensor with the map's number of elements")
+        check(lib.hyc_softmax_prune_tiled_restore(ptr(self.words), self.capacity, ptr(self.directory), ptr(out), numel,
+                                                  stream_of(self.words)), "hyc_softmax_prune_tiled_restore")
+        return out
+
+    def entries(self):
+        """(flattened index int64, value bf16) of the stored entries in ascending index order, decoded with torch
+        operations (for inspection and tests; synchronises)."""
+        d = self.directory.view(-1, 2).to(torch.int64)
+        start, cnt = d[:, 0], d[:, 1]
+        cnt = torch.minimum(cnt, (self.capacity - start).clamp(min=0))
+        batch = torch.repeat_interleave(torch.arange(d.shape[0], device=d.device), cnt)
+        first = torch.repeat_interleave(start, cnt)
+        ofs = torch.arange(batch.numel(), device=d.device) - torch.repeat_interleave(torch.cumsum(cnt, 0) - cnt, cnt)
+        w = self.words[first + ofs].to(torch.int64)
+        idx = batch * self.BATCH + (w >> 16)
+        val = (w & 0xffff).to(torch.int16).view(BF16) if w.numel() else torch.empty(0, dtype=BF16, device=d.device)
+        order = torch.argsort(idx)
+        return idx[order], val[order]
+
+
+def compression_softmax_static(x: torch.Tensor, outlier, capacity=None, margin=1.5, ratio=None, ordered=False):
     """``compression_softmax`` (compress_function.py:309-313) without the device-to-host read of the count: the
     kept entries go into buffers of a fixed ``capacity`` (default: ``margin`` x ``ratio`` x numel + 1024, for a
     threshold calibrated to keep ``ratio`` of the entries) and the count stays on the device.  Entries beyond the
     capacity are dropped; ``PrunedMap.overflowed()`` tells.  ``outlier``: a Python float or a tensor (one
     synchronisation if it lives on the device: pass the calibrated threshold as a float in steady state).
-    Maps of up to 268,435,456 elements; calls on one GPU must not overlap (they share scratch inside the library);
-    the first call on a device must be made outside of stream capture."""
+
+    ``ordered=False`` (default) -> ``TiledPrunedMap``: one pass over the map, the same (index, value) pairs as the
+    reference's sparse tensor kept as 4-byte words in per-batch spans (their order depends on the run --
+    ``to_dense()`` does not care), restored in one pass.  -> ``PrunedMap`` otherwise:
+    ``ordered=True``: ascending flattened index like ``to_sparse``, through the count + scan + fill kernels with the
+    library's built-in scratch: maps of up to 268,435,456 elements, calls on one GPU must not overlap (they share
+    that scratch), and the first call on a device must be made outside of stream capture."""
     require_cuda(x)
     xf = x.to(BF16).contiguous()
     numel = xf.numel()
@@ -338,9 +392,15 @@ def compression_softmax_static(x: torch.Tensor, outlier, capacity=None, margin=1
             raise ValueError("give `capacity` or the calibrated `ratio`")
         capacity = int(numel * ratio * margin) + 1024
     capacity = min(int(capacity), numel)
+    nnz = torch.empty(1, dtype=torch.int64, device=x.device)
+    if not ordered:
+        words = torch.empty(capacity, dtype=torch.int32, device=x.device)
+        directory = torch.empty(lib.hyc_softmax_prune_tiled_directory_bytes(numel) // 4, dtype=torch.int32, device=x.device)
+        check(lib.hyc_softmax_prune_tiled(ptr(xf), numel, float(outlier), ptr(words), capacity, ptr(directory), ptr(nnz),
+                                          stream_of(x)), "hyc_softmax_prune_tiled")
+        return TiledPrunedMap(words, directory, nnz, x.shape)
     idx = torch.empty(capacity, dtype=torch.int64, device=x.device)
     val = torch.empty(capacity, dtype=BF16, device=x.device)
-    nnz = torch.empty(1, dtype=torch.int64, device=x.device)
     check(lib.hyc_softmax_prune_static(ptr(xf), numel, float(outlier), ptr(idx), ptr(val), capacity, ptr(nnz),
                                        stream_of(x)), "hyc_softmax_prune_static")
     return PrunedMap(idx, val, nnz, x.shape)

@@ -117,6 +117,24 @@ int hyc_softmax_prune_restore(const int64_t* idx, const void* val, int64_t nnz,
 int hyc_softmax_prune_restore_counted(const int64_t* idx, const void* val, const int64_t* nnz_dev, int64_t capacity,
                                       void* a_out, int64_t numel, void* stream);
 
+/* The same threshold prune in ONE pass over the map, in a tiled form, for callers that only ever restore the map
+ * (the restore of the layers is to_dense, compress_function.py:316-317; nothing reads the COO list itself): no
+ * workspace, no second launch, 4 bytes per kept entry instead of 10.  The map is cut into batches of 2048
+ * consecutive elements; the entries of a batch go into a span of words_out as (offset in the batch << 16 | bf16
+ * bits), in no particular order inside the span, and directory_out[batch] = {first word of the span, entries} (two uint32;
+ * hyc_softmax_prune_tiled_directory_bytes(numel) bytes).  Spans are handed out by one atomic add per batch on
+ * *nnz_out, so their order depends on the run; the set of (index, value) pairs is that of compression_softmax
+ * (compress_function.py:309-313).  nnz_out (device int64, zeroed by this call) ends up as the number of kept
+ * entries, which may exceed `capacity` (<= 2^32 - 1; the excess is dropped: compare the two). */
+size_t hyc_softmax_prune_tiled_directory_bytes(int64_t numel);
+int hyc_softmax_prune_tiled(const void* a, int64_t numel, float threshold,
+                            uint32_t* words_out, int64_t capacity, void* directory_out,
+                            int64_t* nnz_out, void* stream);
+/* to_dense for the tiled form, one pass: every batch's 4 KB are built on chip and written once (no zero-fill pass,
+ * no scattered 2-byte stores). */
+int hyc_softmax_prune_tiled_restore(const uint32_t* words, int64_t capacity, const void* directory,
+                                    void* a_out, int64_t numel, void* stream);
+
 /* No counterpart in the reference.  The same threshold prune for callers that must not allocate
  * device memory at call time (a fixed up-front memory plan, or a host that forbids allocation inside
  * operator callbacks) and so have no workspace to pass: the tile offsets live in a 512 KiB array built
@@ -124,7 +142,8 @@ int hyc_softmax_prune_restore_counted(const int64_t* idx, const void* val, const
  * and nothing is allocated.  nnz_out (device int64) receives the number of kept entries; entries
  * beyond `capacity` are dropped, so compare the two.  Limit: numel <= 268,435,456 (else
  * HYC_ERR_CAPACITY).  The first call on each device resolves the array's address and should be made
- * outside of stream capture.  Calls share the array: do not let two of them overlap on one GPU. */
+ * outside of stream capture.  Calls share the array: do not let two of them overlap on one GPU.  A map that
+ * lives on another GPU than the current one is refused (HYC_ERR_UNSUPPORTED): the scratch is per device. */
 int hyc_softmax_prune_static(const void* a, int64_t numel, float threshold,
                              int64_t* idx_out, void* val_out, int64_t capacity,
                              int64_t* nnz_out, void* stream);

@@ -101,10 +101,12 @@ def test_softmax_prune_ragged_sizes(cf, numel):
         sp = cf.compression_softmax(a.to(DEV), thr)
         assert torch.equal(sp.indices().reshape(-1).cpu(), idx) and torch.equal(sp.values().cpu(), val)
         assert torch.equal(cf.decompression_softmax(sp).cpu(), oracle.ref_softmax_restore(idx, val, a.shape))
-        m = cf.compression_softmax_static(a.to(DEV), thr, capacity=numel)
-        n = int(m.nnz.item())
-        assert n == idx.numel() and torch.equal(m.idx[:n].cpu(), idx) and torch.equal(m.val[:n].cpu(), val)
-        assert torch.equal(m.to_dense().cpu(), oracle.ref_softmax_restore(idx, val, a.shape))   # tile-wise restore
+        for ordered in (True, False):
+            m = cf.compression_softmax_static(a.to(DEV), thr, capacity=numel, ordered=ordered)
+            n = int(m.nnz.item())
+            mi, mv = (m.idx[:n], m.val[:n]) if ordered else m.entries()
+            assert n == idx.numel() and torch.equal(mi.cpu(), idx) and torch.equal(mv.cpu(), val)
+            assert torch.equal(m.to_dense().cpu(), oracle.ref_softmax_restore(idx, val, a.shape))
 
 
 @pytest.mark.parametrize("q", QS)
@@ -233,22 +235,54 @@ def test_topk_config1_full_size_properties(cf):
     assert m.nbytes() < 0.45 * a.numel() * 2
 
 
-def test_softmax_prune_with_the_count_left_on_the_device(cf):
-    """``compression_softmax_static`` -> ``PrunedMap``: the same entries as the sparse-tensor form, restored without
-    a host synchronisation; a capacity that is too small drops the tail and says so."""
+@pytest.mark.parametrize("ordered", [True, False])
+def test_softmax_prune_with_the_count_left_on_the_device(cf, ordered):
+    """``compression_softmax_static`` -> ``PrunedMap`` / ``TiledPrunedMap``: the same entries as the sparse-tensor form, restored without
+    a host synchronisation; a capacity that is too small drops the tail and says so.  ordered=False is the one-pass
+    kernel: the same SET of (index, value) pairs, dense restore bit-identical."""
     a = _softmax_map(2, 3, 256, seed=9).to(DEV)
     thr = float(cf.get_statistics_softmax(a, 0.05))
     sp = cf.compression_softmax(a, thr)
     nnz = sp.values().numel()
-    m = cf.compression_softmax_static(a, thr, ratio=0.05)
+    m = cf.compression_softmax_static(a, thr, ratio=0.05, ordered=ordered)
     assert m.capacity >= nnz and int(m.nnz.item()) == nnz and not m.overflowed()
-    assert torch.equal(m.idx[:nnz], sp.indices().reshape(-1)) and torch.equal(m.val[:nnz], sp.values())
+    if ordered:
+        assert torch.equal(m.idx[:nnz], sp.indices().reshape(-1)) and torch.equal(m.val[:nnz], sp.values())
+    else:
+        mi, mv = m.entries()
+        assert torch.equal(mi, sp.indices().reshape(-1)) and torch.equal(mv, sp.values())
+        # 4-byte words (+ 8 bytes per 2048 elements) against int64 index + bf16 value, same capacity
+        assert m.nbytes() < 0.5 * cf.compression_softmax_static(a, thr, ratio=0.05, ordered=True).nbytes()
     dense = cf.decompression_softmax(sp).reshape(a.shape)
     assert torch.equal(m.to_dense(), dense)
     buf = torch.full(a.shape, 3.0, dtype=torch.bfloat16, device=DEV)
     assert m.to_dense(out=buf) is buf and torch.equal(buf, dense)
-    small = cf.compression_softmax_static(a, thr, capacity=nnz // 2)
+    small = cf.compression_softmax_static(a, thr, capacity=nnz // 2, ordered=ordered)
     assert small.overflowed() and int(small.nnz.item()) == nnz
-    part = torch.zeros(a.numel(), dtype=torch.bfloat16, device=DEV)
-    part[sp.indices().reshape(-1)[: nnz // 2]] = sp.values()[: nnz // 2]
-    assert torch.equal(small.to_dense().reshape(-1), part)
+    got = small.to_dense().reshape(-1)
+    if ordered:
+        part = torch.zeros(a.numel(), dtype=torch.bfloat16, device=DEV)
+        part[sp.indices().reshape(-1)[: nnz // 2]] = sp.values()[: nnz // 2]
+        assert torch.equal(got, part)
+    else:       # some half of the entries, each with its own value, nothing else
+        kept = got != 0
+        assert int(kept.sum()) == nnz // 2 and torch.equal(got[kept], dense.reshape(-1)[kept])
+
+
+@pytest.mark.parametrize("numel,thr", [(99 * 99, 0.02), (4096 * 3 + 5, -1.0), (8, 0.5), (2048 * 37, 0.0)])
+def test_softmax_prune_tiled_ragged_and_negative_threshold(cf, numel, thr):
+    """Sizes that end inside a chunk, a negative threshold on a tensor with exact zeros (zeros are no entries), a
+    zero threshold: the tiled form holds exactly the entries of the two-phase list, run after run."""
+    g = torch.Generator().manual_seed(numel)
+    x = torch.randn(numel, generator=g)
+    x[torch.rand(numel, generator=g) < 0.3] = 0.0
+    x = x.to(torch.bfloat16).to(DEV).reshape(1, 1, 1, numel)
+    sp = cf.compression_softmax(x, thr)
+    want_idx, want_val = sp.indices().reshape(-1), sp.values()
+    for _ in range(2):
+        m = cf.compression_softmax_static(x, thr, capacity=numel)
+        n = int(m.nnz.item())
+        assert n == want_idx.numel()
+        mi, mv = m.entries()
+        assert torch.equal(mi, want_idx) and torch.equal(mv, want_val)
+        assert torch.equal(m.to_dense().reshape(-1), cf.decompression_softmax(sp).reshape(-1))

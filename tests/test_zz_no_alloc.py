@@ -54,3 +54,30 @@ def test_static_prune_limits():
     # capacity 0: count only
     assert lib.hyc_softmax_prune_static(ptr(a), a.numel(), ctypes.c_float(0.0), None, None, 0, ptr(nnz), stream_of(a)) == 0
     assert int(nnz.item()) == int((a != 0).sum())
+
+
+def test_static_prune_tail_negative_threshold_and_short_capacity():
+    """The branches a regression would land in: a map whose size ends inside a 16-byte chunk, a negative threshold
+    on a map with exact zeros (a zero is no entry), and buffers shorter than the list (the full count is still
+    reported, the first `capacity` entries are the two-phase list's, nothing is written past the end)."""
+    from hyc_lora_release_b200._lib import check, lib, ptr, stream_of
+    from hyc_lora_release_b200.operators import compress_function as cf
+    g = torch.Generator().manual_seed(11)
+    for shape, thr in (((1, 1, 99, 99), 0.02), ((1, 1, 99, 99), -1.0)):
+        x = torch.randn(*shape, generator=g)
+        x[torch.rand(*shape, generator=g) < 0.25] = 0.0
+        a = x.to(torch.bfloat16).to(DEV)
+        sp = cf.compression_softmax(a, thr)
+        ridx, rval = sp.indices().reshape(-1), sp.values()
+        n = ridx.numel()
+        assert n > 16
+        for cap in (n + 8, n - 5):
+            idx = torch.full((n + 8,), -1, dtype=torch.int64, device=DEV)
+            val = torch.zeros(n + 8, dtype=torch.bfloat16, device=DEV)
+            nnz = torch.zeros(1, dtype=torch.int64, device=DEV)
+            check(lib.hyc_softmax_prune_static(ptr(a), a.numel(), ctypes.c_float(thr), ptr(idx), ptr(val), cap, ptr(nnz),
+                                               stream_of(a)), "hyc_softmax_prune_static")
+            kept = min(cap, n)
+            assert int(nnz.item()) == n
+            assert torch.equal(idx[:kept], ridx[:kept]) and torch.equal(val[:kept], rval[:kept])
+            assert bool((idx[kept:] == -1).all())
