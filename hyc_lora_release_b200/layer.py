@@ -55,6 +55,8 @@ class FusedLayerFunction(torch.autograd.Function):
         y, sm = mlp_forward(x_medium, mw, module.mlp_state, status=st)
         if module.track_saved_bytes:
             module.last_saved_bytes = saved_nbytes(sa) + saved_nbytes(sm)
+        if module.keep_saved:
+            module.last_saved = (sa, sm)
         ctx.hyc = (sa, sm, aw, mw, st, module, x.dtype)
         return y.to(x.dtype)
 
@@ -112,6 +114,8 @@ class FusedLlamaLayerIntraInterFullFuse(torch.nn.Module):
         self.check_kernel_status = False   # True: read the bounded-wait status word back after every backward pass
         self.track_saved_bytes = False     # True: forward records the bytes kept for backward in last_saved_bytes
         self.last_saved_bytes = None
+        self.keep_saved = False            # True: forward also leaves its two saved dictionaries in last_saved (inspection)
+        self.last_saved = None
         self._weights = None
 
     # ---- the reference's attributes

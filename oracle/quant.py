@@ -123,7 +123,7 @@ def ref_pack(codes: torch.Tensor, q_bit: int) -> torch.Tensor:
     *lead, n = codes.shape
     assert n % 32 == 0
     cb = codes.reshape(*lead, n // 32, epp, 32 // epp).to(torch.int32)
-    out = torch.zeros(*lead, n // 32, 32 // epp, dtype=torch.int32)
+    out = torch.zeros(*lead, n // 32, 32 // epp, dtype=torch.int32, device=codes.device)
     for i in range(epp):
         out |= cb[..., i, :] << (q_bit * i)
     return out.to(torch.uint8).reshape(*lead, n // epp)

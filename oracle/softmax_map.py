@@ -35,7 +35,7 @@ def ref_softmax_prune(x: torch.Tensor, thr):
 def ref_softmax_restore(idx, val, shape) -> torch.Tensor:
     """``to_dense().reshape(shape)``
     (fused_llama_layer_intra_inter_full_fuse.py:414-415)."""
-    out = torch.zeros(int(torch.tensor(shape).prod()), dtype=BF16)
+    out = torch.zeros(int(torch.tensor(shape).prod()), dtype=BF16, device=val.device)
     out[idx] = val
     return out.reshape(shape)
 

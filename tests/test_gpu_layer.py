@@ -105,6 +105,40 @@ def _attn_static(sv):
 ATTN_ARGS = ("wq", "wk", "wv", "wo", "aq", "bq", "ak", "bk", "av", "bv", "ao", "bo")
 
 
+def _flipped_codes(a, b, q):
+    """Fraction of q-bit codes that differ between two packed tensors."""
+    x = (a.cpu() ^ b.cpu()).to(torch.int32)
+    n = 0
+    for i in range(8 // q):
+        n += int((((x >> (q * i)) & ((1 << q) - 1)) != 0).sum())
+    return n / (a.numel() * (8 // q))
+
+
+def _attn_saved_for_oracle(saved):
+    """The device's saved tensors of the attention half in the form the oracle's backward reads (CPU)."""
+    from hyc_lora_release_b200.operators import compress_function as cf
+    B, M, H = saved["shape"]
+    out = dict(a_shape=saved["a_shape"], map_q_bit=4)
+    for k in ("rstd", "x_o", "x_scale", "x_idx", "xn_scale", "q_scale", "k_scale", "v_scale", "o_scale"):
+        out[k] = saved[k].cpu()
+    for k in ("x_q", "xn_q", "q_q", "k_q", "v_q", "o_q", "q_xa", "k_xa", "v_xa", "o_xa"):
+        out[k] = saved[k].cpu().reshape(B, M, -1)
+    m = saved["a_saved"]
+    if isinstance(m, cf.TopkMap):
+        out["map_q_bit"] = m.q_bit
+        out["a_saved"] = ("topk", m.val.cpu(), m.col.cpu().to(torch.int64), m.q.cpu(), m.scale.cpu(), m.zp.cpu())
+    elif isinstance(m, cf.TiledPrunedMap):
+        idx, val = m.entries()
+        out["a_saved"] = ("prune", idx.cpu(), val.cpu(), None)
+    elif isinstance(m, cf.PrunedMap):
+        n = int(m.nnz.item())
+        out["a_saved"] = ("prune", m.idx[:n].cpu(), m.val[:n].cpu(), None)
+    else:
+        mc = m.coalesce()
+        out["a_saved"] = ("prune", mc.indices().reshape(-1).cpu(), mc.values().cpu(), None)
+    return out
+
+
 @pytest.mark.parametrize("q,heads,kv,map_mode", [(4, 4, 4, "topk"), (8, 4, 2, "topk"), (4, 4, 4, "prune"), (2, 4, 2, "prune")])
 def test_attention_block_forward_backward(q, heads, kv, map_mode):
     from hyc_lora_release_b200 import attention as at
@@ -120,25 +154,29 @@ def test_attention_block_forward_backward(q, heads, kv, map_mode):
     gout = (torch.randn(B, M, H, generator=g)).to(BF16)
     xd, cosd, sind, maskd, goutd = x.to(DEV), cos.to(DEV), sin.to(DEV), mask.to(DEV), gout.to(DEV)
     static = None
-    # 2-bit codes of COMPUTED tensors (q/k/v main branches, o) flip where the device and the CPU sums differ in the
-    # last bit, and one flip is a third of the range: looser bounds for q = 2
-    ra, ca, rl, cl = (2e-2, 0.998, 3e-2, 0.995) if q > 2 else (6e-2, 0.99, 1.5e-1, 0.98)
     for it in range(7):      # 5 calibration iterations, then the steady-state branch
         if it >= 5:
             static = _attn_static(state.static_value)
         ref_out, ref_saved = ref_attention_block_forward(x, p["norm_w1"], cos, sin, *ow, mask, heads, d, kv, q, 0.01, 0.05,
                                                          map_mode=map_mode, static=static)
-        ref_g = ref_attention_block_backward(gout, ref_saved, p["norm_w1"], cos, sin, *ow, heads, d, kv, q)
         out, saved = at.attention_forward(xd, W, state, cosd, sind, maskd, heads, d, kv, status=st)
         grads = at.attention_backward(goutd, saved, W, status=st)
         check_status(st, "attention")
         assert close(out, ref_out), it
         assert torch.equal(saved["x_q"].cpu(), ref_saved["x_q"]) and torch.equal(saved["x_o"].cpu(), ref_saved["x_o"])
-        assert close(grads["grad_x"], ref_g["grad_x"], rel=ra, cos=ca), it
+        # codes of COMPUTED tensors (x_norm, the q/k/v main branches, o) are pinned by the operator tests (bit-exact
+        # against the oracle quantizer on the emitted tensor); against the oracle's own forward a code flips where the
+        # tensor-core sum and the CPU sum round differently: counted and bounded
+        for name in ("xn_q", "q_q", "k_q", "v_q", "o_q"):
+            flips = _flipped_codes(saved[name].reshape(B, M, -1), ref_saved[name], q)
+            assert flips < 0.02, (it, name, flips)
+        # the backward is checked on the DEVICE's saved tensors, so every gradient is held to the path's tolerance
+        ref_g = ref_attention_block_backward(gout, _attn_saved_for_oracle(saved), p["norm_w1"], cos, sin, *ow, heads, d, kv, q)
+        assert close(grads["grad_x"], ref_g["grad_x"]), it
         for name in ("q", "k", "v"):
-            assert close(grads["grad_" + name], ref_g["grad_" + name], rel=ra, cos=ca), (it, name)
+            assert close(grads["grad_" + name], ref_g["grad_" + name]), (it, name)
         for name in ("aq", "bq", "ak", "bk", "av", "bv", "ao", "bo"):   # oracle [in, r] / [r, out] -> weight layout
-            assert close(grads["grad_" + name], ref_g["grad_" + name].t(), rel=rl, cos=cl), (it, name)
+            assert close(grads["grad_" + name], ref_g["grad_" + name].t()), (it, name)
     assert state.iteration == 7
 
 
@@ -175,6 +213,7 @@ def test_layer_module_through_autograd(heads, kv, map_mode):
                                 layernorm_outlier_ratio=0.01, q_bit=q, softmax_map_mode=map_mode)
     layer.set_hyclora_config(cfg)
     layer.check_kernel_status = True
+    layer.keep_saved = True
     n1 = torch.nn.Parameter(p["norm_w1"].to(DEV), requires_grad=False)
     n2 = torch.nn.Parameter(p["norm_w2"].to(DEV), requires_grad=False)
     gy = torch.randn(B, M, H, generator=g).to(BF16)
@@ -205,17 +244,20 @@ def test_layer_module_through_autograd(heads, kv, map_mode):
                            gate_scale=sv["gate"]["scale"].cpu().to(BF16), up_scale=sv["up"]["scale"].cpu().to(BF16),
                            x_norm_2_scale=sv["x_norm_2"]["scale"].cpu().to(BF16)))
     ref_y, ref_saved = ref_layer_forward(x, p, cos, sin, mask, heads, d, kv, q, 0.01, 0.05, map_mode=map_mode, static=static)
-    ref_g = ref_layer_backward(gy, ref_saved, p, cos, sin, heads, d, kv, q)
     assert close(y, ref_y)
-    # the saved tensors downstream of the first GEMM are codes of COMPUTED activations, so a few 4-bit codes differ
-    # between the device and the CPU sums (one step = 1/15 of a channel's range): the cosine stays tight, the
-    # largest single deviation does not
-    assert close(xin.grad, ref_g["grad_x"], rel=6e-2, cos=0.998)
+    # backward: the oracle's backward on the tensors the DEVICE saved in this iteration (codes of computed tensors
+    # may differ from the oracle's own forward in a few places, which the block tests count), path tolerance
+    from test_gpu_mlp import _saved_for_oracle
+    sa, sm = layer.last_saved
+    ref_g = ref_layer_backward(gy, (_attn_saved_for_oracle(sa), _saved_for_oracle(sm)), p, cos, sin, heads, d, kv, q)
+    # grad_x is the end of the longest chain of bf16 roundings (MLP backward, then attention backward): a large
+    # element may land two bf16 steps (2 x 2^-7 of its value) from the oracle's; the LoRA gradients are held to 1e-2
+    assert close(xin.grad, ref_g["grad_x"], rel=2 ** -6)
     for n in ("q", "k", "v", "o", "gate", "up", "down"):
         ga, gb = mods[n][1].default.weight.grad, mods[n][2].default.weight.grad
         assert ga is not None and gb is not None, n
-        assert close(ga, ref_g["grad_a" + n].t(), rel=1e-1, cos=0.995), n
-        assert close(gb, ref_g["grad_b" + n].t(), rel=1e-1, cos=0.995), n
+        assert close(ga, ref_g["grad_a" + n].t()), n
+        assert close(gb, ref_g["grad_b" + n].t()), n
     # a 4-bit quant_state or a bias is refused, not silently ignored
     bad = _base(p["wq"].t().to(DEV))
     bad.weight.quant_state = object()

@@ -15,10 +15,13 @@ BF16 = torch.bfloat16
 
 
 def close(a, b, rel=1e-2, cos=0.999):
-    a, b = a.float().cpu().flatten(), b.float().cpu().flatten()
+    a, b = a.double().cpu().flatten(), b.double().cpu().flatten()
     scale = b.abs().max().clamp(min=1e-30)
     c = torch.nn.functional.cosine_similarity(a, b, dim=0)
-    return bool((a - b).abs().max() <= rel * scale) and bool(c > cos)
+    ok = bool((a - b).abs().max() <= rel * scale) and bool(c > cos)
+    if not ok:
+        print("max rel err %.4g (bound %g), cosine %.6f (bound %g)" % (float((a - b).abs().max() / scale), rel, float(c), cos))
+    return ok
 
 
 @pytest.fixture(scope="module")
@@ -183,8 +186,37 @@ def test_linear_lora_save_epilogue(mlp, q):
     assert close(y, main_ref + (x.float() @ a.float().t()) @ b.float().t())
 
 
+def _saved_for_oracle(saved, dev=None):
+    """The device's saved tensors in the shapes the oracle's backward expects (on `dev`, default CPU)."""
+    B, M, H = saved["shape"]
+    to = (lambda t: t.cpu()) if dev is None else (lambda t: t.to(dev))
+    out = {}
+    for k in ("rstd", "xm_o", "xm_q", "xm_scale", "xm_idx", "xn_q", "xn_scale", "gate_q", "gate_scale", "up_q", "up_scale"):
+        out[k] = to(saved[k])
+    for k in ("xm_q", "xn_q", "gate_q", "up_q"):
+        out[k] = out[k].reshape(B, M, -1)
+    for k in ("gate_xa", "up_xa", "down_xa"):
+        out[k] = to(saved[k]).reshape(B, M, -1)
+    return out
+
+
+def _flipped_codes(a, b, q):
+    """Fraction of q-bit codes that differ between two packed tensors."""
+    x = (a.cpu() ^ b.cpu()).to(torch.int32)
+    n = 0
+    for i in range(8 // q):
+        n += int((((x >> (q * i)) & ((1 << q) - 1)) != 0).sum())
+    return n / (a.numel() * (8 // q))
+
+
 @pytest.mark.parametrize("q", (2, 4, 8))
 def test_mlp_block_forward_backward(mlp, q):
+    """Whole MLP half against the oracle, 5 calibration iterations and 2 steady-state ones.  Forward: output and the
+    saved form of the INPUT (codes + outlier slab) against the oracle's forward.  The codes of COMPUTED tensors
+    (x_norm, the gate/up main branches) are pinned elsewhere (operator tests: bit-exact against the oracle quantizer
+    on the emitted tensor); here they may differ from the oracle's in the few places where the tensor-core sum and
+    the CPU sum round differently -- the fraction is counted and bounded.  Backward: the oracle's backward is given
+    the DEVICE's saved tensors, so that every gradient is compared at the path's tolerance (1e-2, cosine 0.999)."""
     g = torch.Generator().manual_seed(7 + q)
     B, M, H, I = 2, 128, 512, 1024
     x, w = _mlp_problem(g, B, M, H, I)
@@ -196,7 +228,6 @@ def test_mlp_block_forward_backward(mlp, q):
           w["ad"].t(), w["bd"].t())
     ref_out, ref_saved = oracle.ref_mlp_block_forward(x, *ow, q, 0.01)
     gout = _randn(g, B, M, H)
-    ref_g = oracle.ref_mlp_block_backward(gout, ref_saved, *ow, q)
     for it in range(7):     # 5 calibration iterations, then the steady-state branch
         if it == 5:
             # steady state: the oracle takes the same calibrated statistics (running means) as the device
@@ -206,16 +237,101 @@ def test_mlp_block_forward_backward(mlp, q):
                           gate_scale=sv["gate"]["scale"].cpu().to(BF16), up_scale=sv["up"]["scale"].cpu().to(BF16),
                           x_norm_2_scale=sv["x_norm_2"]["scale"].cpu().to(BF16))
             ref_out, ref_saved = oracle.ref_mlp_block_forward(x, *ow, q, 0.01, static=static)
-            ref_g = oracle.ref_mlp_block_backward(gout, ref_saved, *ow, q)
         out, saved = mlp.mlp_forward(x.to(DEV), W, state, status=st)
         grads = mlp.mlp_backward(gout.to(DEV), saved, W, status=st)
         mlp.check_status(st, "mlp")
         assert close(out, ref_out), it
         assert torch.equal(saved["xm_q"].cpu(), ref_saved["xm_q"])
         assert torch.equal(saved["xm_o"].cpu(), ref_saved["xm_o"])
+        for name in ("xn_q", "gate_q", "up_q"):
+            flips = _flipped_codes(saved[name].reshape(B, M, -1), ref_saved[name], q)
+            assert flips < 0.01, (it, name, flips)
+        ref_g = oracle.ref_mlp_block_backward(gout, _saved_for_oracle(saved), *ow, q)
         assert close(grads["grad_x"], ref_g["grad_x"]), it
-        for name in ("ag", "au", "ad"):     # oracle layout [in, r] -> weight layout [r, in]
-            assert close(grads["grad_" + name], ref_g["grad_" + name].t(), rel=2e-2), (it, name)
-        for name in ("bg", "bu", "bd"):     # oracle layout [r, out] -> weight layout [out, r]
-            assert close(grads["grad_" + name], ref_g["grad_" + name].t(), rel=2e-2), (it, name)
+        for name in ("ag", "au", "ad", "bg", "bu", "bd"):     # oracle layout [in, r] / [r, out] -> the weight's layout
+            assert close(grads["grad_" + name], ref_g["grad_" + name].t()), (it, name)
     assert state.iteration == 7
+
+
+def _fp32_product_rows(a, b_t, rows):
+    """fp32 statement of (a @ b_t^T)[rows] on the device (a checker: plain torch, TF32 off)."""
+    prev = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = False
+    try:
+        return a[rows].float() @ b_t.float().t()
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = prev
+
+
+@pytest.mark.parametrize("shape,q", [("llama", 4), ("mistral", 2), ("mistral", 4), ("mistral", 8)])
+def test_mlp_block_full_size(mlp, shape, q):
+    """The MLP half at the full sizes of the benchmark configurations (Llama-2-7B: 2048 tokens x 4096 x 11008, q 4;
+    Mistral-7B: 8192 tokens x 4096 x 14336, q 2/4/8): multi-wave persistence of the tcgen05 kernels, 43 / 56 column
+    tiles, 172 / 224 K blocks.  The checkers run on the GPU (plain torch in fp32 for the products, the oracle's own
+    functions on CUDA tensors for the element-wise chains): emitted main branches against an fp32 product on row
+    slices, codes bit-exact against the oracle quantizer on the emitted tensors, the backward against the oracle's
+    backward on the device's saved tensors at 1e-2 / cosine 0.999."""
+    from hyc_lora_release_b200._lib import check, lib, ptr, stream_of
+    from hyc_lora_release_b200.operators import compress_function as cf
+    B, M, H, I, n_out, amp, ratio = (4, 512, 4096, 11008, 20, 30, 0.005) if shape == "llama" else (1, 8192, 4096, 14336, 41, 20, 0.01)
+    T, R = B * M, 16
+    g = torch.Generator(device=DEV).manual_seed(100 + q + I)
+    rn = lambda *sh, sc=1.0: (torch.randn(*sh, generator=g, device=DEV) * sc).to(BF16)
+    x = torch.randn(B, M, H, generator=g, device=DEV)
+    x[:, :, torch.randperm(H, generator=g, device=DEV)[:n_out]] *= amp
+    x = x.to(BF16)
+    w = dict(norm_w=(1 + 0.1 * torch.randn(H, generator=g, device=DEV)).to(BF16), wg=rn(I, H, sc=.02), wu=rn(I, H, sc=.02),
+             wd=rn(H, I, sc=.02), ag=rn(R, H, sc=.02), bg=rn(I, R, sc=.02), au=rn(R, H, sc=.02), bu=rn(I, R, sc=.02),
+             ad=rn(R, I, sc=.02), bd=rn(H, R, sc=.02))
+    W = mlp.MLPWeights(**w)
+    state = mlp.MLPState(q_bit=q, layernorm_outlier_ratio=ratio)
+    st = torch.zeros(1, dtype=torch.int32, device=DEV)
+    gout = rn(B, M, H)
+    for it in range(6):          # 5 calibration iterations, then the single-pass steady state
+        out, saved = mlp.mlp_forward(x, W, state, status=st)
+        grads = mlp.mlp_backward(gout, saved, W, status=st)
+    mlp.check_status(st, "mlp full size")
+    sv = state.static_value
+    ow = (w["norm_w"], w["wg"].t(), w["wu"].t(), w["wd"].t(), w["ag"].t(), w["bg"].t(), w["au"].t(), w["bu"].t(),
+          w["ad"].t(), w["bd"].t())
+    # ---- forward: the main branches of the steady-state kernel, re-emitted with the calibrated scales
+    from hyc_lora_release_b200.operators.rmsnorm_kernels import rmsnorm_forward
+    x_norm = rmsnorm_forward(x, w["norm_w"], 1e-5)[0]
+    assert close(x_norm, oracle.ref_rmsnorm_forward(x, w["norm_w"], 1e-5)[0], rel=4e-3)
+    xn2 = x_norm.reshape(T, H)
+    gs, us = saved["gate_scale"], saved["up_scale"]
+    epp = 8 // q
+    q1 = torch.empty(T, I // epp, dtype=torch.uint8, device=DEV); q2 = torch.empty_like(q1)
+    had = torch.empty(T, I, dtype=BF16, device=DEV); m1 = torch.empty_like(had); m2 = torch.empty_like(had)
+    check(lib.hyc_mlp_gateup_fwd_tcgen05(ptr(xn2), ptr(w["wg"]), ptr(w["wu"]), T, H, I, ptr(saved["gate_xa"]), ptr(w["bg"]), 16, 1,
+                                         ptr(saved["up_xa"]), ptr(w["bu"]), 16, 1, ptr(gs), ptr(us), ptr(q1), ptr(q2), ptr(had),
+                                         ptr(m1), ptr(m2), q, ptr(st), stream_of(x)), "gateup")
+    mlp.check_status(st, "gateup full size")
+    assert torch.equal(q1.reshape(B, M, -1), saved["gate_q"]) and torch.equal(q2.reshape(B, M, -1), saved["up_q"])
+    rows = torch.cat([torch.arange(0, 256), torch.arange(T // 2 - 64, T // 2 + 64), torch.arange(T - 256, T)]).to(DEV)
+    assert close(m1[rows], _fp32_product_rows(xn2, w["wg"], rows), rel=4e-3)
+    assert close(m2[rows], _fp32_product_rows(xn2, w["wu"], rows), rel=4e-3)
+    # codes: the device quantizer operator on the emitted tensor (itself bit-exact against the reference's kernel) on
+    # everything, the CPU oracle on a slice of rows
+    assert torch.equal(q1, cf.compression_quantization(m1[None], gs, q)[0])
+    assert torch.equal(q2, cf.compression_quantization(m2[None], us, q)[0])
+    sl = slice(T // 3, T // 3 + 64)
+    assert torch.equal(q1[sl].cpu(), oracle.ref_compress(m1[sl].cpu()[None], gs.cpu()[None], q)[0])
+    oq1, oq2, ohad = oracle.ref_fused_silu_forward(saved["gate_xa"][None], w["bg"].t(), m1[None], gs[None],
+                                                   saved["up_xa"][None], w["bu"].t(), m2[None], us[None], q)
+    assert torch.equal(oq1[0], q1) and torch.equal(oq2[0], q2) and close(had, ohad[0])
+    # ---- the input's saved form and the output
+    xm_o, xm_q = oracle.ref_compress_channel_base(x, sv["x_medium"]["scale"].to(BF16), sv["x_medium"]["outlier_channel_index"], q)
+    assert torch.equal(saved["xm_q"], xm_q) and torch.equal(saved["xm_o"], xm_o)
+    down = _fp32_product_rows(had, w["wd"], rows) + (saved["down_xa"][rows].float() @ w["bd"].float().t())
+    assert close(out.reshape(T, H)[rows], x.reshape(T, H)[rows].float() + down)
+    # ---- backward against the oracle's backward on the device's saved tensors (all on the GPU)
+    ref_g = oracle.ref_mlp_block_backward(gout, _saved_for_oracle(saved, DEV), *ow, q)
+    # the three element-wise intermediates (22 M / 117 M bf16 values each) and grad_x (8 M / 33 M) are the ends of
+    # chains of bf16 roundings that start from GEMM results: somewhere a large element ends two bf16 steps
+    # (2 x 2^-7 of its value) from the oracle's, so their bound is 2^-6; the LoRA gradients are held to 1e-2
+    assert close(grads["hadamard"], ref_g["hadamard"], rel=2 ** -6) and close(grads["g_gate"], ref_g["g_gate"], rel=2 ** -6)
+    assert close(grads["g_up"], ref_g["g_up"], rel=2 ** -6)
+    assert close(grads["grad_x"], ref_g["grad_x"], rel=2 ** -6), "grad_x"
+    for name in ("ag", "au", "ad", "bg", "bu", "bd"):
+        assert close(grads["grad_" + name], ref_g["grad_" + name].t()), name
