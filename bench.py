@@ -4,8 +4,8 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
 
 Headline workload (N = 1): the attention-map save/restore of a [4,32,512,512] bf16 causal
-softmax map, per-row top-k (ratio 0.05) + 4-bit 64-wide groups; one step = compress +
-decompress of one map.  Prints ONE JSON line.
+softmax map, per-row top-k (ratio 0.05) + 4-bit 64-wide groups; one step = ROUND_TRIPS compress +
+decompress round trips over a ring of maps.  Prints ONE JSON line.
 Under torchrun every rank works on its own shard of maps (weak scaling, no data-path
 collective); the time is the maximum over ranks.
 """
@@ -26,10 +26,12 @@ sys.path.insert(0, ROOT)
 MAP_SHAPE = (4, 32, 512, 512)
 RATIO = 0.05
 QBIT = 4
-NBUF = 4          # distinct input/output sets rotated between steps (4 x 64 MiB in, > L2)
-# dram__bytes_read.sum + dram__bytes_write.sum of ONE launch on this workload, from the ncu capture that
-# profiles/topk_lane_attention_map_4x32x512x512_q4.md summarises (bytes)
-NCU_TRAFFIC = {"hyc::topk_lane_compress_kernel<4,8>": 70.0e6, "hyc::topk_lane_restore_kernel<4,8,false>": 35.9e6}
+NBUF = 4          # distinct input/output sets rotated between round trips (4 x 64 MiB in, > L2)
+ROUND_TRIPS = 64  # compress + decompress round trips that make one step (a step is about 4 ms of device time)
+SAMPLE_SHAPE = (1, 8, 512, 512)     # the slice of the map one step of the CPU arms works on (1/16 of the map)
+# dram__bytes_read.sum + dram__bytes_write.sum of ONE launch on this workload (bytes), taken from an ncu capture of the
+# kernels as they are built now; None when no capture of the current build exists
+NCU_TRAFFIC = {"hyc::topk_lane_compress_kernel<4,8>": None, "hyc::topk_lane_restore_kernel<4,8,false>": None}
 
 
 def peaks():
@@ -118,57 +120,107 @@ class ClockSampler:
                 "samples": len(sm), "reasons": sorted(reasons)}
 
 
-def cpu_port_sample(target_s=12.0):
-    """The CPU restatement (oracle) of the same compress + decompress on a bounded sample:
-    maps of shape [1,8,512,512] until about `target_s` seconds have passed."""
-    import oracle
-    cores = os.cpu_count() or 1
-    torch.set_num_threads(cores)
-    shape = (1, 8, 512, 512)
-    a = make_map(99, "cpu", shape)
-    nbytes = 2 * algo_bytes(shape, QBIT, RATIO)
-    oracle.topk_decompress(*oracle.topk_compress(a, RATIO, QBIT), QBIT, a.shape)   # warm-up
+def find_reference():
+    """Folder that holds the reference's ``operators/compress_function.py``: $HYC_REFERENCE, a checkout at
+    /root/reference, or the copy staged by oracle/stage_reference.py (oracle/_ref).  None when there is none."""
+    for cand in (os.environ.get("HYC_REFERENCE"), "/root/reference", os.path.join(ROOT, "oracle", "_ref")):
+        if cand and os.path.isfile(os.path.join(cand, "operators", "compress_function.py")):
+            return cand
+    return None
+
+
+def load_reference_compress(ref):
+    """The reference's operators/compress_function.py imported UNCHANGED (as a sub-module of a synthetic package,
+    so that its relative import of the kernel module resolves inside the same folder)."""
+    import importlib
+    import types
+    name = "hyc_reference_operators"
+    if name not in sys.modules:
+        pkg = types.ModuleType(name)
+        pkg.__path__ = [os.path.join(ref, "operators")]
+        sys.modules[name] = pkg
+    return importlib.import_module(name + ".compress_function")
+
+
+class CpuArm:
+    """The CPU implementation of the attention-map save/restore on the host cores, on a [1,8,512,512] slice of the
+    map per step.  kind "reference": the reference's own pure-PyTorch path imported unchanged -- calibration with
+    get_statistics_softmax once (compress_function.py:30-32), then per step compression_softmax (mask multiply +
+    to_sparse, :309-313) and decompression_softmax (to_dense, :316-317), which is what the reference's layer runs in
+    steady state for this tensor.  kind "port": the CPU oracle's restatement of this repository's top-k form, only
+    when no copy of the reference is reachable.  Throughput is counted in the SAME unit as the GPU arm: algorithmic
+    bytes of the top-k round trip per map element, so the two values compare as maps per second."""
+
+    def __init__(self):
+        self.cores = os.cpu_count() or 1
+        torch.set_num_threads(self.cores)
+        self.a = make_map(99, "cpu", SAMPLE_SHAPE)
+        self.nbytes = 2 * algo_bytes(SAMPLE_SHAPE, QBIT, RATIO)
+        ref = find_reference()
+        self.kind, self.why = "port", "no copy of the reference reachable (HYC_REFERENCE, /root/reference, oracle/_ref)"
+        if ref is not None:
+            try:
+                cf = load_reference_compress(ref)
+                thr = cf.get_statistics_softmax(self.a, RATIO)
+                self._step = lambda: cf.decompression_softmax(cf.compression_softmax(self.a, thr))
+                self.kind, self.why = "reference", ref
+            except Exception as e:       # an import that fails (a Triton too old or too new for the kernel module)
+                self.why = "reference at %s not importable: %s" % (ref, repr(e)[:200])
+        if self.kind == "port":
+            import oracle
+            self._step = lambda: oracle.topk_decompress(*oracle.topk_compress(self.a, RATIO, QBIT), QBIT, self.a.shape)
+
+    def step(self):
+        self._step()
+
+    def describe(self, steps, secs):
+        what = ("get_statistics_softmax once, then compression_softmax + decompression_softmax of the reference "
+                "(operators/compress_function.py, imported unchanged)") if self.kind == "reference" else \
+            "oracle.topk_compress + oracle.topk_decompress (CPU restatement; %s)" % self.why
+        return "%d steps of %s on a %s slice of the map (1/16 of it), %.1f s" % (steps, what, list(SAMPLE_SHAPE), secs)
+
+
+def cpu_baseline_sample(target_s=10.0):
+    """About `target_s` seconds of the CPU arm (rank 0, N = 1 only)."""
+    arm = CpuArm()
+    arm.step()
     t0 = time.perf_counter()
     reps = 0
     while True:
-        c = oracle.topk_compress(a, RATIO, QBIT)
-        oracle.topk_decompress(*c, QBIT, a.shape)
+        arm.step()
         reps += 1
         el = time.perf_counter() - t0
-        if el >= target_s or reps >= 4096:
+        if el >= target_s or reps >= 1000000:
             break
-    return {"value": reps * nbytes / el / 1e9, "unit": "GB/s", "cores": cores, "kind": "port",
-            "sample": "%d x compress+decompress of a [1,8,512,512] map (%.1f s)" % (reps, el)}, el / reps, nbytes
+    return {"value": reps * arm.nbytes / el / 1e9, "unit": "GB/s", "cores": arm.cores, "kind": arm.kind,
+            "sample": arm.describe(reps, el)}
 
 
 def run_reference(args):
-    """Reference arm: the CPU implementation of the path (the oracle port: the reference itself has
-    no CPU quantize kernel and no top-k mode) on the host cores, same metric and config."""
+    """Reference arm: the reference's CPU implementation of the headline path on the host cores (all threads), same
+    metric, unit and config as the GPU arm, exactly --steps timed steps after --warmup untimed ones; one step works on a
+    [1,8,512,512] slice of the map (stated in config.sample).  Under torchrun rank 0 alone runs it."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    import oracle
-    cores = os.cpu_count() or 1
-    torch.set_num_threads(cores)
-    shape = (1, 8, 512, 512)
-    a = make_map(99, "cpu", shape)
-    nbytes = 2 * algo_bytes(shape, QBIT, RATIO)
-    steps = max(1, min(args.steps, 8))
-    warm = max(1, min(args.warmup, 2))
-    for _ in range(warm):
-        oracle.topk_decompress(*oracle.topk_compress(a, RATIO, QBIT), QBIT, a.shape)
+    arm = CpuArm()
+    for _ in range(args.warmup):
+        arm.step()
     t0 = time.perf_counter()
-    for _ in range(steps):
-        oracle.topk_decompress(*oracle.topk_compress(a, RATIO, QBIT), QBIT, a.shape)
+    for _ in range(args.steps):
+        arm.step()
     el = time.perf_counter() - t0
-    v = steps * nbytes / el / 1e9
-    sample = "%d steps, each compress+decompress of a [1,8,512,512] map (1/16 of the workload's map)" % steps
+    v = args.steps * arm.nbytes / el / 1e9
+    cfg = config_dict()
+    cfg["sample"] = "one step = one save/restore of a %s slice (1/16 of the map, %d of its rows)" % (
+        list(SAMPLE_SHAPE), SAMPLE_SHAPE[0] * SAMPLE_SHAPE[1] * SAMPLE_SHAPE[2])
     print(json.dumps({
         "impl": "reference", "metric": "activation compress+decompress GB/s", "value": v, "unit": "GB/s",
-        "n_gpus": args.gpus, "steps": steps, "warmup": warm, "ms_per_step": el / steps * 1e3,
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": el / args.steps * 1e3,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16->u8", "data": "synthetic",
-        "config": config_dict(),
-        "cpu_baseline": {"value": v, "unit": "GB/s", "cores": cores, "kind": "port", "sample": sample},
+        "config": cfg,
+        "cpu_baseline": {"value": v, "unit": "GB/s", "cores": arm.cores, "kind": arm.kind,
+                         "sample": arm.describe(args.steps, el)},
         "e2e": {"value": v, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }))
 
@@ -177,6 +229,7 @@ def config_dict():
     return {"workload": "attention-map save/restore, softmax [4,32,512,512] bf16 causal, top-k per row "
                         "ratio 0.05 + q_bit 4 groups of 64 (BASELINE configs[1])",
             "q_bit": QBIT, "outlier_ratio": RATIO, "rows_per_gpu": MAP_SHAPE[0] * MAP_SHAPE[1] * MAP_SHAPE[2],
+            "round_trips_per_step": ROUND_TRIPS,
             "l2": "inputs and outputs rotated over %d distinct buffer sets (%d MiB dense) > 126 MB L2" % (
                 NBUF, NBUF * 64)}
 
@@ -242,6 +295,92 @@ def extra_workloads(dev, hbm):
     out.append(fused_elementwise_workload(dev, hbm))
     out.append(attention_backward_workload(dev, hbm))
     out.append(prune_workload(dev, hbm))
+    out.extend(reference_triton_lines(dev, hbm))
+    return out
+
+
+def reference_triton_lines(dev, hbm):
+    """The reference's own Triton kernels, compiled by the installed Triton for THIS GPU and timed with CUDA events on
+    the tensors of the lines above: the quantize / de-quantize pair (compress_function_kernel.py:47-112, 150-206), the
+    channel-base and the softmax-prune round trips through the reference's API, and the two fused LoRA-SiLU-Hadamard
+    kernels.  A reported comparison; an error message stands in where Triton refuses a kernel."""
+    ref = find_reference()
+    if ref is None:
+        return [{"workload": "reference Triton kernels on this GPU", "unavailable": "no copy of the reference reachable"}]
+    out = []
+    try:
+        import importlib
+        cf = load_reference_compress(ref)
+        fwd = importlib.import_module("hyc_reference_operators.triton_fuse_lora_silu_hadamard_forward_kernels")
+        bwd = importlib.import_module("hyc_reference_operators.triton_fuse_lora_silu_hadamard_backward_kernels")
+        import triton
+        ver = triton.__version__
+    except Exception as e:
+        return [{"workload": "reference Triton kernels on this GPU", "unavailable": repr(e)[:300]}]
+    g = torch.Generator().manual_seed(1234)
+
+    def timed(fn, n=10):
+        return time_loop(lambda i: fn(), n, 3) / n
+
+    def guarded(name, fn):
+        try:
+            line = fn()
+        except Exception as e:
+            line = {"unavailable": repr(e)[:300]}
+        line["workload"] = "reference Triton on this GPU (triton %s): %s" % (ver, name)
+        out.append(line)
+    for shape, n_out, mult, ratio, qs in (((4, 512, 4096), 20, 30.0, 0.005, (4,)), ((1, 8192, 14336), 143, 20.0, 0.01, (2, 4, 8))):
+        x = torch.randn(*shape, generator=g)
+        x[:, :, torch.randperm(shape[-1], generator=g)[:n_out]] *= mult
+        x = x.to(torch.bfloat16).to(dev)
+        for q in qs:
+            def pair(q=q, x=x):
+                s_ = cf.get_statistics_only_quant(x, q, "per-channel")
+                s_ = (s_ + (s_ == 0) * 1e-3).to(torch.bfloat16)
+                qq = cf.compression_quantization(x, s_, q)
+                tc, td = timed(lambda: cf.compression_quantization(x, s_, q)), timed(lambda: cf.decompression_dequantization(qq, s_, q))
+                nb = x.numel() * (4 + q / 4.0)
+                return {"q_bit": q, "value": nb / (tc + td) / 1e9, "unit": "GB/s", "frac_of_hbm": nb / (tc + td) / 1e9 / hbm,
+                        "kernel_ms": {"compress": tc * 1e3, "decompress": td * 1e3}}
+            guarded("compression_quantization + decompression_dequantization %s" % list(shape), pair)
+        if shape[-1] == 4096:
+            def chan(x=x, ratio=ratio):
+                idx, sc = cf.get_statistics_channel_base(x, ratio, 4, "per-channel")
+                st = {"outlier_channel_index": idx, "scale": sc}
+
+                def rt():
+                    xo, qq, i2, s2 = cf.compression_pack_channel_base(x.clone(), ratio, 4, "per-channel", 9, 5, st)
+                    return cf.outlier_addition_fuse_decompression_dequantization(qq, s2, xo, i2, 4)
+                t = timed(rt)
+                nb = x.numel() * 5.0
+                return {"q_bit": 4, "value": nb / t / 1e9, "unit": "GB/s", "frac_of_hbm": nb / t / 1e9 / hbm, "ms_per_step": t * 1e3,
+                        "note": "as the layer calls it: clone + index gather + zeroing + quant kernel, then dequant kernel + scatter"}
+            guarded("channel-base round trip %s" % list(shape), chan)
+        del x
+
+    def prune():
+        a = make_map(2000, dev)
+        thr = cf.get_statistics_softmax(a, RATIO)
+        t = timed(lambda: cf.decompression_softmax(cf.compression_softmax(a, thr)), 5)
+        nnz = int(cf.compression_softmax(a, thr).values().numel())
+        nb = a.numel() * 4 + 20 * nnz
+        return {"value": nb / t / 1e9, "unit": "GB/s", "frac_of_hbm": nb / t / 1e9 / hbm, "ms_per_step": t * 1e3}
+    guarded("compression_softmax + to_dense [4,32,512,512]", prune)
+
+    def fused():
+        T, N, R, q = 8192, 14336, 16, 4
+        rn = lambda *sh, sc=1.0: (torch.randn(*sh, generator=g) * sc).to(torch.bfloat16).to(dev)
+        xa1, xa2, b1, b2 = rn(1, T, R), rn(1, T, R), rn(R, N, sc=.05), rn(R, N, sc=.05)
+        x1, x2, go = rn(1, T, N), rn(1, T, N), rn(1, T, N)
+        s1, s2 = cf.get_statistics_only_quant(x1, q, "per-channel"), cf.get_statistics_only_quant(x2, q, "per-channel")
+        q1, q2, _ = fwd.triton_fuse_silu_forward(xa1, b1, x1, s1, xa2, b2, x2, s2, q)
+        tf = timed(lambda: fwd.triton_fuse_silu_forward(xa1, b1, x1, s1, xa2, b2, x2, s2, q), 6)
+        tb = timed(lambda: bwd.triton_fuse_silu_backward(xa1, b1, q1, s1, xa2, b2, q2, s2, go, q), 6)
+        nel = T * N
+        bf_, bb = nel * (4 + 2 + 2 * q / 8), nel * (2 * q / 8 + 2 + 6)
+        return {"q_bit": q, "value": (bf_ + bb) / (tf + tb) / 1e9, "unit": "GB/s", "frac_of_hbm": (bf_ + bb) / (tf + tb) / 1e9 / hbm,
+                "forward": {"ms": tf * 1e3, "GBps": bf_ / tf / 1e9}, "backward": {"ms": tb * 1e3, "GBps": bb / tb / 1e9}}
+    guarded("triton_fuse_silu_forward + triton_fuse_silu_backward [1,8192,14336]", fused)
     return out
 
 
@@ -385,14 +524,56 @@ def run_profile(args):
                       "GBps": args.steps * nbytes / t / 1e9}))
 
 
-def mlp_workload(dev, dist=None, steps=20, warmup=4, shape="llama", q_bit=4):
+def ranks_hold_identical(reducer, dist):
+    """True when every rank's averaged gradient buffer has the same fingerprint (None on a single rank)."""
+    if dist is None:
+        return None
+    mine = reducer.checksum()
+    all_sums = [None] * dist.get_world_size()
+    dist.all_gather_object(all_sums, mine)
+    return all(v == all_sums[0] for v in all_sums)
+
+
+def mlp_eager_baseline(dev, B, M, H, I, R, steps=10, warmup=3):
+    """The same MLP block in plain PyTorch on the same GPU: library (cuBLAS) matmuls, torch element-wise kernels and
+    autograd, LoRA rank R on gate/up/down, frozen bf16 weights, NOTHING compressed (every activation saved in bf16).
+    Reported beside the fused path; not part of it."""
+    g = torch.Generator().manual_seed(4321)
+    rn = lambda *sh, sc=1.0: (torch.randn(*sh, generator=g) * sc).to(torch.bfloat16).to(dev)
+    x = rn(B, M, H).requires_grad_(True)
+    wg, wu, wd = rn(I, H, sc=.02), rn(I, H, sc=.02), rn(H, I, sc=.02)
+    lora = [rn(R, H, sc=.02), rn(I, R, sc=.02), rn(R, H, sc=.02), rn(I, R, sc=.02), rn(R, I, sc=.02), rn(H, R, sc=.02)]
+    for t in lora:
+        t.requires_grad_(True)
+    ag, bg, au, bu, ad, bd = lora
+    nw = torch.ones(H, dtype=torch.bfloat16, device=dev)
+    gout = rn(B, M, H)
+
+    def step(i):
+        xn = torch.nn.functional.rms_norm(x, (H,), nw, 1e-5)
+        gate = xn @ wg.t() + (xn @ ag.t()) @ bg.t()
+        up = xn @ wu.t() + (xn @ au.t()) @ bu.t()
+        had = torch.nn.functional.silu(gate) * up
+        y = x + had @ wd.t() + (had @ ad.t()) @ bd.t()
+        torch.autograd.grad(y, [x] + lora, gout)
+    t = time_loop(step, steps, warmup)
+    return {"tokens_per_s": B * M * steps / t, "ms_per_step": t / steps * 1e3,
+            "what": "plain PyTorch on the same GPU: cuBLAS matmuls + torch element-wise kernels + autograd, bf16 "
+                    "activations kept uncompressed"}
+
+
+def mlp_workload(dev, dist=None, steps=20, warmup=4, shape="llama", q_bit=4, eager=False):
     """Fused LoRA-SiLU-Hadamard MLP forward + backward.  shape "llama" = BASELINE configs[2]: x [4,512,4096] per
     GPU, intermediate 11008, 0.5 % outlier channels x30; shape "mistral" = BASELINE configs[3]: 8192 tokens per GPU,
     intermediate 14336, 1 % outlier channels x20.  Frozen W ~ N(0, .02), LoRA rank 16, saved activations q_bit
-    wide; calibration (5 iterations) happens before the timed region.  With several ranks every rank runs its
-    own token shard and the LoRA gradients are all-reduced inside the timed step."""
+    wide; calibration (5 iterations, statistics synchronised across ranks) happens before the timed region.  With
+    several ranks every rank runs its OWN token shard (inputs seeded per rank, weights shared) and the six LoRA
+    gradients are averaged over the ranks inside the timed step (one bucketed all-reduce started from the
+    backward's hook); after the timed region the ranks' averaged gradients are compared."""
     from hyc_lora_release_b200 import mlp, parallel
+    rank = dist.get_rank() if dist is not None else 0
     g = torch.Generator().manual_seed(4321)
+    gr = torch.Generator().manual_seed(9000 + rank)          # this rank's token shard
     if shape == "llama":
         B, M, H, I, R, n_out, amp, ratio = 4, 512, 4096, 11008, 16, 20, 30, 0.005
         name = "Llama-2-7B shapes, x [4,512,4096] per GPU, q_bit %d (BASELINE configs[2])" % q_bit
@@ -401,25 +582,28 @@ def mlp_workload(dev, dist=None, steps=20, warmup=4, shape="llama", q_bit=4):
         name = "Mistral-7B shapes, x [1,8192,4096] per GPU, q_bit %d (BASELINE configs[3])" % q_bit
     T = B * M
     rn = lambda *sh, sc=1.0: (torch.randn(*sh, generator=g) * sc).to(torch.bfloat16).to(dev)
-    x = torch.randn(B, M, H, generator=g)
-    x[:, :, torch.randperm(H, generator=g)[:n_out]] *= amp
-    x = x.to(torch.bfloat16).to(dev)
+    outlier_channels = torch.randperm(H, generator=g)[:n_out]
     ku = lambda out, inp: ((torch.rand(out, inp, generator=g) * 2 - 1) * (1.0 / inp) ** 0.5).to(torch.bfloat16).to(dev)
     W = mlp.MLPWeights(norm_w=torch.ones(H, dtype=torch.bfloat16, device=dev),
                        wg=rn(I, H, sc=.02), wu=rn(I, H, sc=.02), wd=rn(H, I, sc=.02),
                        ag=ku(R, H), bg=rn(I, R, sc=.02), au=ku(R, H), bu=rn(I, R, sc=.02), ad=ku(R, I), bd=rn(H, R, sc=.02))
+    x = torch.randn(B, M, H, generator=gr)
+    x[:, :, outlier_channels] *= amp
+    x = x.to(torch.bfloat16).to(dev)
+    gout = (torch.randn(B, M, H, generator=gr)).to(torch.bfloat16).to(dev)
     state = mlp.MLPState(q_bit=q_bit, layernorm_outlier_ratio=ratio)
     st = torch.zeros(1, dtype=torch.int32, device=dev)
-    gout = rn(B, M, H)
+    reducer = parallel.LoraGradReducer()
 
     def step(i):
         out, saved = mlp.mlp_forward(x, W, state, status=st)
-        pending = []
-        # the LoRA-gradient all-reduce starts inside the backward pass and overlaps its last two kernels
-        mlp.mlp_backward(gout, saved, W, status=st, on_lora_grads=lambda g_: pending.append(parallel.allreduce_lora_grads_async(g_)))
-        pending[0].wait()
+        # the LoRA-gradient exchange starts inside the backward pass and overlaps its last two kernels
+        mlp.mlp_backward(gout, saved, W, status=st, on_lora_grads=lambda g_: reducer.add("mlp", g_))
+        reducer.finish()
     for i in range(6):          # calibration iterations
         step(i)
+        if i < state.iteration_threshold:
+            parallel.sync_calibration(state.static_value)
     mlp.check_status(st, "mlp")
     t = time_loop(step, steps, warmup)
     mlp.check_status(st, "mlp")
@@ -432,13 +616,23 @@ def mlp_workload(dev, dist=None, steps=20, warmup=4, shape="llama", q_bit=4):
     flop_per_token = 12 * H * I + R * (18 * H + 22 * I)
     burst, sustained, src = tensor_peaks()
     tf = T * flop_per_token * steps / t / 1e12
-    return {"workload": "fused LoRA-SiLU-Hadamard MLP fwd+bwd, " + name, "q_bit": q_bit,
+    line = {"workload": "fused LoRA-SiLU-Hadamard MLP fwd+bwd, " + name, "q_bit": q_bit,
             "metric": "tokens/s", "value": world * T * steps / t, "unit": "tokens/s", "ms_per_step": t / steps * 1e3,
             "tokens_per_gpu": T, "flop_per_token": flop_per_token,
-            "roofline": {"bound": "tensor", "achieved": tf, "peak": sustained, "unit": "TFLOP/s", "frac": tf / sustained,
-                         "peak_source": src + " (sustained; burst %.0f -> frac %.3f)" % (burst, tf / burst)},
-            "gpu_launches_per_step": 4, "note": "4 tcgen05 GEMM launches + streaming kernels per step; "
-            "LoRA-gradient all-reduce inside the step when n_gpus > 1"}
+            "roofline": {"bound": "tensor", "kernel": "tc::mlp_gemm_kernel (gate+up forward, down forward, grad_down, grad_x: "
+                                                      "four launches per step)",
+                         "achieved": tf, "peak": sustained, "unit": "TFLOP/s", "frac": tf / sustained,
+                         "frac_of_burst_peak": tf / burst, "algorithmic_flop_per_step": T * flop_per_token,
+                         "traffic": None,
+                         "peak_source": src + " (sustained %.0f, burst %.0f TFLOP/s)" % (sustained, burst)},
+            "gpu_launches_per_step": 4, "identical_grads_on_all_ranks": ranks_hold_identical(reducer, dist),
+            "note": "4 tcgen05 GEMM launches + streaming kernels per step; with n_gpus > 1 every rank has its own token "
+                    "shard and the LoRA gradients are averaged by one all-reduce inside the step"}
+    if eager:
+        del W, x, gout
+        torch.cuda.empty_cache()
+        line["pytorch_eager_same_gpu"] = mlp_eager_baseline(dev, B, M, H, I, R)
+    return line
 
 
 def layer_workload(dev, dist=None, steps=10, warmup=3, graph=True):
@@ -450,7 +644,9 @@ def layer_workload(dev, dist=None, steps=10, warmup=3, graph=True):
     import types
     from hyc_lora_release_b200 import mlp, parallel
     from hyc_lora_release_b200.layer import FusedLlamaLayerIntraInterFullFuse
+    rank = dist.get_rank() if dist is not None else 0
     g = torch.Generator().manual_seed(777)
+    gr = torch.Generator().manual_seed(7000 + rank)          # this rank's sequence
     B, M, H, heads, d, I, R = 1, 2048, 4096, 32, 128, 11008, 16
     bf = torch.bfloat16
 
@@ -470,8 +666,9 @@ def layer_workload(dev, dist=None, steps=10, warmup=3, graph=True):
         return a, b
     dims = dict(q=(H, H), k=(H, H), v=(H, H), o=(H, H), gate=(I, H), up=(I, H), down=(H, I))
     mods = {n: (lin(o_, i_, sc=.02),) + adapter(o_, i_) for n, (o_, i_) in dims.items()}
-    x = torch.randn(B, M, H, generator=g)
-    x[:, :, torch.randperm(H, generator=g)[:20]] *= 30
+    outlier_channels = torch.randperm(H, generator=g)[:20]
+    x = torch.randn(B, M, H, generator=gr)
+    x[:, :, outlier_channels] *= 30
     x = x.to(bf).to(dev)
     pos = torch.arange(M, dtype=torch.float32)
     inv = 1.0 / (10000.0 ** (torch.arange(0, d, 2, dtype=torch.float32) / d))
@@ -480,12 +677,12 @@ def layer_workload(dev, dist=None, steps=10, warmup=3, graph=True):
     mask = torch.full((M, M), torch.finfo(bf).min).triu(1).to(bf).reshape(1, 1, M, M).to(dev)
     n1 = torch.ones(H, dtype=bf, device=dev)
     n2 = torch.ones(H, dtype=bf, device=dev)
-    gy = (torch.randn(B, M, H, generator=g)).to(bf).to(dev)
+    gy = (torch.randn(B, M, H, generator=gr)).to(bf).to(dev)
     layer = FusedLlamaLayerIntraInterFullFuse()
     layer.set_hyclora_config(types.SimpleNamespace(use_hyclora=True, iteration_threshold=5, softmax_outlier_ratio=0.05,
                                                    layernorm_outlier_ratio=0.005, q_bit=4, softmax_map_mode="topk"))
-    pending = []
-    layer.on_lora_grads = lambda gr: pending.append(parallel.allreduce_lora_grads_async(gr))
+    reducer = parallel.LoraGradReducer()
+    reducer.attach_layer(0, layer)
     args = [None, n1, None, cos, sin]
     for n in ("q", "k", "v", "o"):
         args += list(mods[n])
@@ -498,15 +695,15 @@ def layer_workload(dev, dist=None, steps=10, warmup=3, graph=True):
         xin = x.detach().requires_grad_(True)
         args[0] = xin
         y = layer(*args)
-        y.backward(gy)
-        for p_ in pending:
-            p_.wait()
-        pending.clear()
-        for m3 in mods.values():
-            m3[1].default.weight.grad = None
-            m3[2].default.weight.grad = None
+        # autograd hands the layer's LOCAL adapter gradients back; the averaged ones are what finish() leaves in .grad
+        torch.autograd.grad(y, [xin] + lora_weights, gy)
+        reducer.finish()
+    lora_weights = [m3[j].default.weight for m3 in mods.values() for j in (1, 2)]
     for i in range(6):
         step(i)
+        if i < 5:
+            parallel.sync_calibration(layer.attn_state.static_value)
+            parallel.sync_calibration(layer.mlp_state.static_value)
     layer.check_kernel_status = True
     layer.track_saved_bytes = True
     step(6)
@@ -553,6 +750,7 @@ def layer_workload(dev, dist=None, steps=10, warmup=3, graph=True):
             "metric": "tokens/s", "value": world * T * steps / t, "unit": "tokens/s (one layer)", "ms_per_step": t / steps * 1e3,
             "tokens_per_gpu": T, "flop_per_token": flop_per_token, "cuda_graph_replay_ms_per_step": graph_ms,
             "saved_for_backward_bytes": saved_bytes, "same_tensors_in_bf16_bytes": dense_bytes,
+            "identical_grads_on_all_ranks": ranks_hold_identical(reducer, dist),
             "roofline": {"bound": "tensor", "achieved": tf, "peak": sustained, "unit": "TFLOP/s", "frac": tf / sustained,
                          "peak_source": src + " (sustained)"},
             "note": "the two attention products per direction are library batched GEMMs and, like every pass over the "
@@ -597,13 +795,17 @@ def model_workload(dev, dist=None, steps=4, warmup=3, n_layers=32, graph=True):
     mask = torch.full((M, M), torch.finfo(bf).min).triu(1).to(bf).reshape(1, 1, M, M).to(dev)
     cfg = types.SimpleNamespace(use_hyclora=True, iteration_threshold=5, softmax_outlier_ratio=0.05,
                                 layernorm_outlier_ratio=0.005, q_bit=4, softmax_map_mode="topk")
-    pending = []
+    # every layer's LoRA gradients go into one flat buffer; an all-reduce starts for every 10 MB of it that is complete
+    reducer = parallel.LoraGradReducer(bucket_bytes=10 << 20)
     layers, adapters = [], []
-    for _ in range(n_layers):
+    gw = torch.Generator(device=dev).manual_seed(4242)       # weights: the same on every rank
+    g_rank = g
+    g = gw
+    for li in range(n_layers):
         mods = {n: (lin(o_, i_, sc=.02),) + adapter(o_, i_) for n, (o_, i_) in dims.items()}
         layer = FusedLlamaLayerIntraInterFullFuse()
         layer.set_hyclora_config(cfg)
-        layer.on_lora_grads = lambda gr: pending.append(parallel.allreduce_lora_grads_async(gr))
+        reducer.attach_layer(li, layer)
         args = [None, torch.ones(H, dtype=bf, device=dev), None, cos, sin]
         for n in ("q", "k", "v", "o"):
             args += list(mods[n])
@@ -639,6 +841,7 @@ def model_workload(dev, dist=None, steps=4, warmup=3, n_layers=32, graph=True):
             return dx.reshape(shape)
 
     n_ids = 4
+    g = g_rank                                                # token ids and labels: this rank's own batch
     ids = [torch.randint(0, V, (B, M), generator=g, device=dev) for _ in range(n_ids)]
     labels = [torch.randint(0, V, (B * M,), generator=g, device=dev) for _ in range(n_ids)]
     loss_box, grads_box = [None], [None]
@@ -649,10 +852,8 @@ def model_workload(dev, dist=None, steps=4, warmup=3, n_layers=32, graph=True):
             x = layer(x, *args[1:])       # (no reference to x is kept: a stale autograd graph would outlive the step)
         logits = NormHead.apply(x)
         loss = torch.nn.functional.cross_entropy(logits.float(), labels[i % n_ids])
-        grads_box[0] = torch.autograd.grad(loss, adapters)      # the 14 x n_layers adapter gradients of this rank
-        for p_ in pending:
-            p_.wait()
-        pending.clear()
+        grads_box[0] = torch.autograd.grad(loss, adapters)      # the 14 x n_layers adapter gradients of this rank ...
+        reducer.finish()                                        # ... and their average over the ranks, left in .grad
         loss_box[0] = loss.detach()
 
     def step(i):
@@ -660,6 +861,10 @@ def model_workload(dev, dist=None, steps=4, warmup=3, n_layers=32, graph=True):
         return float(loss_box[0].item())      # the device-to-host read of the step's result
     for i in range(6):                         # calibration iterations of every layer
         step(i)
+        if i < 5 and dist is not None:
+            for layer, _ in layers:
+                parallel.sync_calibration(layer.attn_state.static_value)
+                parallel.sync_calibration(layer.mlp_state.static_value)
     mlp.check_status(status, "model step")
     torch.cuda.reset_peak_memory_stats(dev)
     t = time_loop(step, steps, warmup)
@@ -703,6 +908,9 @@ def model_workload(dev, dist=None, steps=4, warmup=3, n_layers=32, graph=True):
            "metric": "tokens/s", "value": world * T * steps / t, "unit": "tokens/s", "ms_per_step": t / steps * 1e3,
            "tokens_per_gpu": T, "flop_per_token": flop_per_token, "cuda_graph_replay_ms_per_step": graph_ms,
            "loss": loss_value, "peak_memory_bytes": peak_mem,
+           "identical_grads_on_all_ranks": ranks_hold_identical(reducer, dist),
+           "lora_grad_exchange": {"buffer_bytes": 0 if reducer.flat is None else reducer.flat.numel() * 4,
+                                  "all_reduces_per_step": len(reducer._bucket_range)},
            "roofline": {"bound": "tensor", "achieved": tf, "peak": sustained, "unit": "TFLOP/s", "frac": tf / sustained,
                         "peak_source": src + " (sustained)"},
            "note": "embedding lookup and the cross-entropy are torch glue; every other launch is a kernel of this library "
@@ -713,8 +921,8 @@ def model_workload(dev, dist=None, steps=4, warmup=3, n_layers=32, graph=True):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=200)
-    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=300)
+    ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-extras", action="store_true", help="skip the secondary workloads and the CPU sample")
     ap.add_argument("--profile", default=None, choices=["attn_topk", "channel_q4", "channel_q2", "channel_q8", "mlp", "fused", "layer", "model", "prune"],
@@ -753,9 +961,11 @@ def main():
         dense[j] = handles[j].to_dense()
 
     def step(i):
-        j = i % NBUF
-        cf.compression_softmax_topk(maps[j], RATIO, QBIT, out=handles[j])
-        handles[j].to_dense(out=dense[j])
+        # one step = ROUND_TRIPS save/restore round trips over the ring of maps (a step is milliseconds, not microseconds)
+        for r in range(ROUND_TRIPS):
+            j = (i * ROUND_TRIPS + r) % NBUF
+            cf.compression_softmax_topk(maps[j], RATIO, QBIT, out=handles[j])
+            handles[j].to_dense(out=dense[j])
 
     def barrier():
         torch.cuda.synchronize()
@@ -781,7 +991,7 @@ def main():
         t = torch.tensor([secs], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         secs = float(t.item())
-    value = world * args.steps * 2 * one_way / secs / 1e9
+    value = world * args.steps * ROUND_TRIPS * 2 * one_way / secs / 1e9
 
     # per-kernel durations of the two kernels (CUDA events on the launching stream)
     # (one pass over the NBUF buffer sets captured in a CUDA graph, so that the average is the kernel's and
@@ -791,7 +1001,7 @@ def main():
         with torch.cuda.graph(g):
             for j in range(NBUF):
                 fn(j)
-        n_rep = max(5, min(args.steps, 100) // NBUF)
+        n_rep = 25
         return time_loop(lambda i: g.replay(), n_rep, 3) / (n_rep * NBUF)
     t_c = graph_avg(lambda j: cf.compression_softmax_topk(maps[j], RATIO, QBIT, out=handles[j]))
     t_d = graph_avg(lambda j: handles[j].to_dense(out=dense[j]))
@@ -836,7 +1046,7 @@ def main():
         b.record(cur)
         torch.cuda.synchronize()
         return a.elapsed_time(b) / 1e3
-    n_e = max(6, min(args.steps, 20))
+    n_e = max(8, min(args.steps, 32))        # one map per end-to-end step (PCIe-bound: about 1.5 ms each)
     barrier()
     t_e = e2e_loop(n_e, 4)
     if dist is not None:
@@ -848,6 +1058,7 @@ def main():
     dense_bytes = maps[0].numel() * 2
     e2e = {"value": world * n_e * 2 * one_way / t_e / 1e9, "unit": "GB/s",
            "h2d_bytes_per_step": dense_bytes, "d2h_bytes_per_step": dense_bytes, "steps": n_e,
+           "round_trips_per_step": 1,
            "api": "compress_function.compression_softmax_topk + TopkMap.to_dense on pinned host maps, four streams "
                   "(the read-back of one step overlaps the upload of the next)"}
 
@@ -855,7 +1066,7 @@ def main():
     sweep_lines = []
     if not args.no_extras:
         barrier()
-        mlp_line = mlp_workload(dev, dist)      # every rank takes part (all-reduce inside)
+        mlp_line = mlp_workload(dev, dist, eager=(world == 1))      # every rank takes part (all-reduce inside)
         sweep_lines = []
         for qb in (2, 4, 8):
             barrier()
@@ -868,7 +1079,7 @@ def main():
         also, cpu = [], None
         if not args.no_extras and world == 1:
             also = extra_workloads(dev, hbm)
-            cpu, _, _ = cpu_port_sample()
+            cpu = cpu_baseline_sample()
         if mlp_line is not None:
             also.append(mlp_line)
         also.extend(sweep_lines)
@@ -881,14 +1092,14 @@ def main():
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": secs / args.steps * 1e3,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16->u8",
             "data": "synthetic", "config": config_dict(), "clocks": clocks, "e2e": e2e,
-            "gpu_launches": 2 * args.steps,
+            "gpu_launches": 2 * ROUND_TRIPS * args.steps,
             "frac_of_hbm_peak": value / world / hbm,
             "roofline": {"bound": "hbm", "kernel": dom, "achieved": achieved, "peak": hbm, "unit": "GB/s",
                          "frac": achieved / hbm, "peak_source": peak_src,
                          "traffic": NCU_TRAFFIC.get(dom),
                          "algorithmic_bytes_per_launch": one_way,
                          "kernel_ms": {"compress": t_c * 1e3, "decompress": t_d * 1e3}},
-            "cpu_baseline": cpu, "also": also,
+            "cpu_baseline": cpu, "mlp": mlp_line, "also": also,
         }
         print(json.dumps(line))
     if dist is not None:

@@ -165,6 +165,14 @@ class FusedLlamaLayerIntraInterFullFuse(torch.nn.Module):
             self._weights = (key, aw, mw, lora)
         return self._weights[1:]
 
+    def named_lora_weights(self):
+        """{"grad_aq": q lora_A weight, "grad_bq": q lora_B weight, ...}: the 14 adapter weights of the last forward
+        call under the names their gradients carry in the ``on_lora_grads`` dictionaries."""
+        if self._weights is None:
+            return {}
+        names = ("aq", "bq", "ak", "bk", "av", "bv", "ao", "bo", "ag", "bg", "au", "bu", "ad", "bd")
+        return {"grad_" + n: w for n, w in zip(names, self._weights[3])}
+
     def forward(self, input, norm_weight_1, norm_bias_1, cos, sin,
                 q_proj_base, q_proj_lora_a, q_proj_lora_b, k_proj_base, k_proj_lora_a, k_proj_lora_b,
                 v_proj_base, v_proj_lora_a, v_proj_lora_b, o_proj_base, o_proj_lora_a, o_proj_lora_b,

@@ -81,19 +81,167 @@ def allreduce_lora_grads_async(grads: Dict[str, torch.Tensor], group=None, avera
 
 
 def sync_calibration(static_value: dict, group=None) -> dict:
-    """Make calibration statistics identical on all ranks: floating-point entries are averaged,
-    the outlier channel index of rank 0 wins."""
+    """Make calibration statistics identical on all ranks.  Entries without an outlier index (plain per-channel
+    scales, the map threshold) are averaged.  A channel-base entry (outlier index + scale) takes rank 0's index and
+    the MAXIMUM of the ranks' scales: every rank computed its scale with its OWN outlier channels zeroed (guard
+    value 1e-3 there), so a channel that is an outlier on some rank but not in the agreed list still gets the scale
+    of a rank that measured it, instead of a mean dragged down by guard values (which would clip it everywhere)."""
     if not dist.is_initialized() or dist.get_world_size(group) == 1:
         return static_value
     world = dist.get_world_size(group)
     for entry in static_value.values():
+        channel_base = entry.get('outlier_channel_index') is not None
         for name, t in entry.items():
             if t is None:
                 continue
             if name == 'outlier_channel_index':
                 dist.broadcast(t, src=0, group=group)
+            elif channel_base:
+                buf = t.float()
+                dist.all_reduce(buf, op=dist.ReduceOp.MAX, group=group)
+                entry[name] = buf.to(t.dtype)
             else:
                 buf = t.float()
                 dist.all_reduce(buf, op=dist.ReduceOp.SUM, group=group)
                 entry[name] = (buf / world).to(t.dtype)
     return static_value
+
+
+_MLP_GRAD_NAMES = frozenset(("grad_ag", "grad_bg", "grad_au", "grad_bu", "grad_ad", "grad_bd"))
+
+
+class LoraGradReducer:
+    """The data-parallel exchange of a model's LoRA gradients: ONE persistent flat fp32 buffer, a few bucketed
+    asynchronous all-reduces per step, averaged values left in ``.grad``.
+
+    Use: ``reducer.add(key, grads)`` from the layers' ``on_lora_grads`` hooks (``key`` identifies the caller, e.g.
+    ``(layer_index, "mlp")``; ``grads`` is the hook's dictionary); ``reducer.finish()`` once the backward pass is
+    over.  The first step records the order in which the gradients arrive and gives every tensor a slice of the
+    buffer in that order; from then on each ``add`` is one multi-tensor copy into the slices, and a bucket's
+    all-reduce starts as soon as its last slice is filled (``bucket_bytes`` of consecutive arrivals), so the
+    exchange overlaps the rest of the backward pass.  ``bind(key, name, param)`` attaches the parameter whose
+    ``.grad`` receives the averaged gradient in ``finish()``.  Without an initialised process group (or with one
+    rank) nothing is exchanged and ``finish()`` only fills ``.grad``."""
+
+    def __init__(self, group=None, bucket_bytes=16 << 20, dtype=torch.float32):
+        self.group, self.bucket_bytes, self.dtype = group, int(bucket_bytes), dtype
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self._slots = {}            # (key, name) -> (offset, numel, shape)
+        self._order = []            # keys in arrival order
+        self._names = {}            # key -> sorted names
+        self._params = {}           # (key, name) -> parameter
+        self._frozen = False
+        self._first = {}            # first step: key -> dict of gradients (kept until the layout is frozen)
+        self.flat = None
+        self._views = {}            # key -> list of fp32 views (order of self._names[key])
+        self._bucket_of = {}        # key -> bucket index
+        self._bucket_range = []     # bucket -> (begin, end) in elements
+        self._bucket_left = []      # bucket -> keys still missing in this step
+        self._bucket_size = []
+        self._works = []
+        self._layers = []
+
+    def bind(self, key, name, param):
+        self._params[(key, name)] = param
+
+    def attach_layer(self, index, layer):
+        """Wire a fused decoder layer module: its ``on_lora_grads`` hook feeds this reducer (the attention half and the
+        MLP half arrive separately, keys ``(index, "attn")`` and ``(index, "mlp")``), and the 14 adapter weights it is
+        driven with get the averaged gradients in ``.grad`` (bound after the first step, when the layer has seen them)."""
+        self._layers.append((index, layer))
+        layer.on_lora_grads = lambda grads, _i=index: self.add((_i, "mlp" if "grad_ag" in grads else "attn"), grads)
+
+    def _bind_layers(self):
+        for index, layer in self._layers:
+            names = layer.named_lora_weights()
+            for name, p in names.items():
+                self.bind((index, "mlp" if name in _MLP_GRAD_NAMES else "attn"), name, p)
+
+    # ---- layout (end of the first step)
+    def _freeze(self, device):
+        off = 0
+        for key in self._order:
+            for name in self._names[key]:
+                g = self._first[key][name]
+                self._slots[(key, name)] = (off, g.numel(), g.shape)
+                off += g.numel()
+        self.flat = torch.zeros(off, dtype=self.dtype, device=device)
+        esize = self.flat.element_size()
+        begin, cur = 0, 0
+        for key in self._order:
+            views = []
+            for name in self._names[key]:
+                o, n, shape = self._slots[(key, name)]
+                views.append(self.flat[o:o + n].view(shape))
+                cur = o + n
+            self._views[key] = views
+            self._bucket_of[key] = len(self._bucket_range)
+            if (cur - begin) * esize >= self.bucket_bytes:
+                self._bucket_range.append((begin, cur))
+                begin = cur
+        if cur > begin or not self._bucket_range:
+            self._bucket_range.append((begin, cur))
+        self._bucket_size = [0] * len(self._bucket_range)
+        for key in self._order:
+            self._bucket_size[self._bucket_of[key]] += 1
+        self._frozen = True
+
+    def _launch(self, b):
+        lo, hi = self._bucket_range[b]
+        if self.world > 1 and hi > lo:
+            op = dist.ReduceOp.AVG if dist.get_backend(self.group) == "nccl" else dist.ReduceOp.SUM
+            self._works.append((dist.all_reduce(self.flat[lo:hi], op=op, group=self.group, async_op=True), op, lo, hi))
+
+    def add(self, key, grads):
+        if not self._frozen:
+            if key in self._first:
+                raise RuntimeError("LoraGradReducer: %r delivered twice in one step" % (key,))
+            self._order.append(key)
+            self._names[key] = sorted(grads)
+            self._first[key] = dict(grads)
+            return
+        if key not in self._views:
+            raise RuntimeError("LoraGradReducer: %r was not part of the first step" % (key,))
+        torch._foreach_copy_(self._views[key], [grads[n] for n in self._names[key]])
+        b = self._bucket_of[key]
+        self._bucket_left[b] -= 1
+        if self._bucket_left[b] == 0:
+            self._launch(b)
+
+    def finish(self):
+        """Wait for the exchange, write the averaged gradients into the bound parameters' ``.grad`` and return the
+        flat buffer (fp32, averaged)."""
+        if not self._frozen:
+            if not self._first:
+                return None
+            dev = next(iter(next(iter(self._first.values())).values())).device
+            self._freeze(dev)
+            self._bind_layers()
+            self._bucket_left = list(self._bucket_size)
+            first, self._first = self._first, {}
+            for key in self._order:            # replay the first step through the frozen layout
+                self.add(key, first[key])
+        for work, op, lo, hi in self._works:
+            work.wait()
+            if op == dist.ReduceOp.SUM:
+                self.flat[lo:hi].div_(self.world)
+        self._works = []
+        dst, src = [], []
+        for (key, name), p in self._params.items():
+            o, n, shape = self._slots[(key, name)]
+            if p.grad is None:
+                p.grad = torch.empty_like(p)
+            dst.append(p.grad)
+            src.append(self.flat[o:o + n].view(shape))
+        if dst:
+            torch._foreach_copy_(dst, src)
+        self._bucket_left = list(self._bucket_size)
+        return self.flat
+
+    def checksum(self):
+        """A 64-bit fingerprint of the averaged buffer (for checking that all ranks hold identical gradients)."""
+        if self.flat is None:
+            return 0
+        bits = self.flat.view(torch.int32).to(torch.int64)
+        w = torch.arange(1, bits.numel() + 1, device=bits.device, dtype=torch.int64) % 1000003
+        return int((bits * w).sum().item())

@@ -28,7 +28,7 @@ import torch
 from .quant import ref_pack, ref_unpack
 
 __all__ = ["GROUP", "group_stats", "group_quant_codes", "group_compress",
-           "group_decompress", "fma32"]
+           "group_decompress", "fma32", "group_compress_divide_roundf", "group_decompress_divide_roundf"]
 
 GROUP = 64
 BF16 = torch.bfloat16
@@ -108,3 +108,35 @@ def group_decompress(packed, s, z, q_bit: int) -> torch.Tensor:
     half = 2 ** (q_bit - 1)
     v = (codes.float() - half).reshape(*lead, n // GROUP, GROUP) - z.float().unsqueeze(-1)
     return (v * s.float().unsqueeze(-1)).to(BF16).reshape(*lead, n)
+
+
+# ---- the same mode stated with the reference's zero-point arithmetic (comparison only) ----
+# Applying compress_function.py:62-77 and compress_function_kernel.py:279-299, 376-387 literally to a 64-wide
+# group gives: an fp32 IEEE divide, C roundf (halves away from zero), bf16 rounding after every step of the
+# de-quantizer.  The specification above replaced the divide by a reciprocal multiply, roundf by round-half-
+# to-even and the clamp by a saturating fma (two FMA-pipe instructions per element on the GPU instead of a
+# division, two min/max and a conversion).  These two functions keep the literal form so that the difference
+# between the two definitions can be measured (tests/test_oracle_golden.py).
+
+def group_compress_divide_roundf(x, q_bit: int):
+    from .quant import roundf_half_away
+    *lead, n = x.shape
+    xg = x.to(BF16).reshape(*lead, n // GROUP, GROUP)
+    mx = xg.max(dim=-1).values
+    mn = xg.min(dim=-1).values
+    s = ((mx - mn).to(BF16).float() / float(2 ** q_bit - 1)).to(BF16)
+    s = torch.where(s == 0, torch.tensor(1e-3, dtype=BF16), s)
+    half = 2 ** (q_bit - 1)
+    z = (-roundf_half_away(mn.float() / s.float()) - half).clamp(-128, 127)
+    r = xg.float() / s.float().unsqueeze(-1) + z.unsqueeze(-1)
+    c = (roundf_half_away(r).clamp(-half, half - 1) + half).to(torch.uint8).reshape(*lead, n)
+    return ref_pack(c, q_bit), s, z.to(torch.int8)
+
+
+def group_decompress_divide_roundf(packed, s, z, q_bit: int):
+    codes = ref_unpack(packed, q_bit)
+    *lead, n = codes.shape
+    half = 2 ** (q_bit - 1)
+    v = (codes.float().to(BF16) - half).to(BF16).reshape(*lead, n // GROUP, GROUP)
+    v = (v - z.to(BF16).unsqueeze(-1)).to(BF16)
+    return (v * s.to(BF16).unsqueeze(-1)).to(BF16).reshape(*lead, n)

@@ -42,6 +42,22 @@ def test_golden_zero_point(cf, golden, q):
 
 
 @pytest.mark.parametrize("q", QS)
+def test_pack_quant_zp_base_calibration_and_static(cf, golden, q):
+    """``compression_pack_quant_zp_base`` (compress_function.py:364-370): statistics while calibrating, the stored
+    ones afterwards; both branches against the golden vectors of the zero-point kernels."""
+    d = golden[f"q{q}"]
+    xz = d["xz"].to(DEV)
+    pk, s, z = cf.compression_pack_quant_zp_base(xz, q, "per-channel", 0, 5, None)
+    assert torch.equal(s.cpu(), d["zp_scale"]) and torch.equal(z.cpu(), d["zp"]) and torch.equal(pk.cpu(), d["zp_packed"])
+    static = {"scale": d["zp_scale"].to(DEV), "zero_point": d["zp"].to(DEV)}
+    other = (xz.float() * 0.5).to(torch.bfloat16)         # its own statistics would differ: the stored ones must be used
+    pk2, s2, z2 = cf.compression_pack_quant_zp_base(other, q, "per-channel", 7, 5, static)
+    assert s2 is static["scale"] and z2 is static["zero_point"]
+    assert torch.equal(pk2.cpu(), oracle.ref_compress(other.cpu(), d["zp_scale"], q, d["zp"]))
+    assert torch.equal(cf.decompression_dequantization_with_zero_point(pk, s, z, q).cpu(), d["zp_dequant"])
+
+
+@pytest.mark.parametrize("q", QS)
 def test_golden_channel_base(cf, golden, q):
     d = golden[f"q{q}"]
     x = d["x"].to(DEV)
