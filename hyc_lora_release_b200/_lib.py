@@ -37,6 +37,7 @@ SIGNATURES = {
     "hyc_softmax_prune_tiled": (_i, [_p, _l, _f, _p, _l, _p, _p, _p]),
     "hyc_softmax_prune_tiled_restore": (_i, [_p, _l, _p, _p, _l, _p]),
     "hyc_softmax_topk_compress": (_i, [_p, _l, _i, _i, _p, _p, _p, _p, _p, _i, _p]),
+    "hyc_softmax_fwd_topk_save": (_i, [_p, _f, _p, _l, _l, _l, _i, _i, _l, _i, _i, _p, _p, _p, _p, _p, _p, _i, _p]),
     "hyc_softmax_topk_restore": (_i, [_p, _p, _i, _p, _p, _p, _l, _i, _p, _i, _p]),
     "hyc_softmax_topk_restore_bwd": (_i, [_p, _p, _i, _p, _p, _p, _l, _i, _p, _p, _i, _f, _p]),
     "hyc_fused_lora_silu_hadamard_fwd": (_i, [_p] * 11 + [_l, _i, _i, _i, _p]),

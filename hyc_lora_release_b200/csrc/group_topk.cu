@@ -535,6 +535,23 @@ extern "C" HYC_API int hyc_group_unpack_dequant(const void* q, int64_t rows, int
   return HYC_OK;
 }
 
+extern "C" HYC_API int hyc_softmax_fwd_topk_save(const void* scores, float scale, const void* mask_or_null, int64_t mask_stride_b,
+                                                 int64_t mask_stride_h, int64_t mask_stride_row, int heads, int M,
+                                                 int64_t rows, int S, int k, void* a_out, void* val_out, uint16_t* col_out,
+                                                 void* q_out, void* scale_out, int8_t* zp_out, int q_bit, void* stream) {
+  if (!scores || !a_out || !q_out || !scale_out || !zp_out) return HYC_ERR_NULL;
+  if (k > 0 && (!val_out || !col_out)) return HYC_ERR_NULL;
+  if (q_bit != 2 && q_bit != 4 && q_bit != 8) return HYC_ERR_QBIT;
+  if (rows < 0 || S <= 0 || S % 64 != 0 || k < 0 || k > S || heads < 1 || M < 1 || rows % M != 0) return HYC_ERR_SHAPE;
+  if (rows == 0) return HYC_OK;
+  const int rc = topk_lane_softmax_compress(scores, scale, mask_or_null, mask_stride_b, mask_stride_h, mask_stride_row, heads, M,
+                                            rows, S, k, a_out, val_out, col_out, q_out, scale_out, zp_out, q_bit,
+                                            (cudaStream_t)stream);
+  if (rc) return rc;
+  HYC_CHECK_LAUNCH();
+  return HYC_OK;
+}
+
 extern "C" HYC_API int hyc_softmax_topk_compress(const void* a, int64_t rows, int S, int k,
                                          void* val_out, uint16_t* col_out,
                                          void* q_out, void* scale_out, int8_t* zp_out, int q_bit, void* stream) {

@@ -51,12 +51,24 @@ __device__ __forceinline__ uint32_t keep_lowest_bits(uint32_t w, int n) {
   return w ^ r;
 }
 
+// What the SOFTMAX form of the compress kernel needs besides the map itself: the raw scores are read from `a`, turned
+// into probabilities (scale, additive mask, softmax with the rounding points of softmax_fwd_kernel in
+// norm_softmax.cu), written to `dense` for the P.V product, and saved in the same pass.
+struct SoftmaxPrologue {
+  float scale;
+  const __nv_bfloat16* mask;     // additive mask or NULL; row m of (batch b, head h) at mask + b * mb + h * mh + m * S
+  int64_t mb, mh;
+  int heads, M;                  // rows = batch * heads * M, M a multiple of the rows a warp takes
+  __nv_bfloat16* dense;          // [rows, S] probabilities (may be the scores buffer itself)
+};
+
 // ---------------------------------------------------------------- compress
-template <int QBIT, int LPR>
+template <int QBIT, int LPR, bool SOFTMAX>
 __global__ void __launch_bounds__(256, HYC_LANE_MINB)
 topk_lane_compress_kernel(const __nv_bfloat16* __restrict__ a, int64_t rows, int k,
                           __nv_bfloat16* __restrict__ val_out, uint16_t* __restrict__ col_out,
-                          uint8_t* __restrict__ q, __nv_bfloat16* __restrict__ scale, int8_t* __restrict__ zp) {
+                          uint8_t* __restrict__ q, __nv_bfloat16* __restrict__ scale, int8_t* __restrict__ zp,
+                          SoftmaxPrologue sp) {
   constexpr int RPW = 32 / LPR;          // rows per warp
   constexpr int S = 64 * LPR;
   constexpr int64_t QLD = (int64_t)S * QBIT / 8;
@@ -77,6 +89,57 @@ topk_lane_compress_kernel(const __nv_bfloat16* __restrict__ a, int64_t rows, int
     __syncwarp();
     uint32_t xw[32];
     lane_slot_load(sx, lane, xw);
+
+    if (SOFTMAX) {
+      // ---- scores -> probabilities.  u = bf16(bf16(s * scale) + mask) replaces the raw scores in xw; the row maximum,
+      // the exponentials and their sum are fp32; p = bf16(e / sum).  The exponentials are evaluated twice (once for
+      // the sum, once for the result) instead of keeping 64 fp32 values per lane alive.
+      constexpr float kLog2e = 1.4426950408889634f;
+      __syncwarp();
+      if (sp.mask != nullptr) {
+        const int64_t bh = row0 / sp.M;
+        const int m0 = (int)(row0 - bh * sp.M);
+        lane_run_to_shared(sp.mask + (bh / sp.heads) * sp.mb + (bh % sp.heads) * sp.mh + (int64_t)m0 * S, n_rows * (S / 16),
+                           s_x[warp], lane);
+        __syncwarp();
+      }
+      __nv_bfloat162 hmx = __float2bfloat162_rn(-INFINITY);
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        uint4 mk = make_uint4(0u, 0u, 0u, 0u);
+        if (sp.mask != nullptr) mk = *reinterpret_cast<const uint4*>(sx + park_chunk(c, lane));
+        const uint32_t mw[4] = {mk.x, mk.y, mk.z, mk.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          uint32_t t = pack_bf16x2_rn(bf16lo_to_f32(xw[4 * c + j]) * sp.scale, bf16hi_to_f32(xw[4 * c + j]) * sp.scale);
+          if (sp.mask != nullptr)
+            t = pack_bf16x2_rn(bf16lo_to_f32(t) + bf16lo_to_f32(mw[j]), bf16hi_to_f32(t) + bf16hi_to_f32(mw[j]));
+          xw[4 * c + j] = t;
+          hmx = __hmax2(hmx, *reinterpret_cast<const __nv_bfloat162*>(&t));
+        }
+      }
+      float mx = fmaxf(__bfloat162float(hmx.x), __bfloat162float(hmx.y));
+#pragma unroll
+      for (int o = 1; o < LPR; o <<= 1) mx = fmaxf(mx, __shfl_xor_sync(kFull, mx, o));
+      const float mxl = mx * kLog2e;
+      float sum = 0.f;
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        sum += exp2f(fmaf(bf16lo_to_f32(xw[j]), kLog2e, -mxl)) + exp2f(fmaf(bf16hi_to_f32(xw[j]), kLog2e, -mxl));
+#pragma unroll
+      for (int o = 1; o < LPR; o <<= 1) sum += __shfl_xor_sync(kFull, sum, o);
+      const float inv = 1.0f / sum;
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        xw[j] = pack_bf16x2_rn(exp2f(fmaf(bf16lo_to_f32(xw[j]), kLog2e, -mxl)) * inv,
+                               exp2f(fmaf(bf16hi_to_f32(xw[j]), kLog2e, -mxl)) * inv);
+      // the probabilities go to the parked copy (the emission below picks its entries there) and out as the dense map
+      __syncwarp();
+      lane_slot_store(sx, lane, xw);
+      __syncwarp();
+      lane_shared_to_run(s_x[warp], sp.dense + row0 * S, n_rows * (S / 16), lane);
+      __syncwarp();
+    }
 
     if (k > 0) {
       // ---- values paired (column c, column c + 16) so that the transposed planes come out in column
@@ -376,12 +439,19 @@ bool softmax_bwd_lane(const void* y, const void* g, int64_t rows, int S, float o
 // ---------------------------------------------------------------- launchers
 template <int QBIT, int LPR>
 static void launch_compress(const void* a, int64_t rows, int k, void* val, uint16_t* col, void* q, void* scale,
-                            int8_t* zp, cudaStream_t st) {
-  auto kern = topk_lane_compress_kernel<QBIT, LPR>;
+                            int8_t* zp, const SoftmaxPrologue* sp, cudaStream_t st) {
   int grid, threads;
-  lane_launch_shape(kern, rows, 32 / LPR, grid, threads);
-  kern<<<grid, threads, 0, st>>>((const __nv_bfloat16*)a, rows, k, (__nv_bfloat16*)val, col,
-                                 (uint8_t*)q, (__nv_bfloat16*)scale, zp);
+  if (sp == nullptr) {
+    auto kern = topk_lane_compress_kernel<QBIT, LPR, false>;
+    lane_launch_shape(kern, rows, 32 / LPR, grid, threads);
+    kern<<<grid, threads, 0, st>>>((const __nv_bfloat16*)a, rows, k, (__nv_bfloat16*)val, col,
+                                   (uint8_t*)q, (__nv_bfloat16*)scale, zp, SoftmaxPrologue{});
+  } else {
+    auto kern = topk_lane_compress_kernel<QBIT, LPR, true>;
+    lane_launch_shape(kern, rows, 32 / LPR, grid, threads);
+    kern<<<grid, threads, 0, st>>>((const __nv_bfloat16*)a, rows, k, (__nv_bfloat16*)val, col,
+                                   (uint8_t*)q, (__nv_bfloat16*)scale, zp, *sp);
+  }
 }
 template <int QBIT, int LPR>
 static void launch_restore(const void* val, const uint16_t* col, int k, const void* q, const void* scale,
@@ -414,8 +484,8 @@ static void launch_restore(const void* val, const uint16_t* col, int k, const vo
 
 template <int QB>
 static int compress_q(const void* a, int64_t rows, int S, int k, void* val, uint16_t* col, void* q, void* scale,
-                      int8_t* zp, cudaStream_t st) {
-  HYC_LANE_DISPATCH(launch_compress, a, rows, k, val, col, q, scale, zp, st);
+                      int8_t* zp, const SoftmaxPrologue* sp, cudaStream_t st) {
+  HYC_LANE_DISPATCH(launch_compress, a, rows, k, val, col, q, scale, zp, sp, st);
   return HYC_OK;
 }
 template <int QB>
@@ -428,9 +498,28 @@ static int restore_q(const void* val, const uint16_t* col, int k, const void* q,
 int topk_lane_compress(const void* a, int64_t rows, int S, int k, void* val_out, uint16_t* col_out,
                        void* q_out, void* scale_out, int8_t* zp_out, int q_bit, cudaStream_t st) {
   if (!topk_lane_ok(S, k)) return HYC_ERR_SHAPE;
-  if (q_bit == 2) return compress_q<2>(a, rows, S, k, val_out, col_out, q_out, scale_out, zp_out, st);
-  if (q_bit == 4) return compress_q<4>(a, rows, S, k, val_out, col_out, q_out, scale_out, zp_out, st);
-  return compress_q<8>(a, rows, S, k, val_out, col_out, q_out, scale_out, zp_out, st);
+  if (q_bit == 2) return compress_q<2>(a, rows, S, k, val_out, col_out, q_out, scale_out, zp_out, nullptr, st);
+  if (q_bit == 4) return compress_q<4>(a, rows, S, k, val_out, col_out, q_out, scale_out, zp_out, nullptr, st);
+  return compress_q<8>(a, rows, S, k, val_out, col_out, q_out, scale_out, zp_out, nullptr, st);
+}
+
+// scores [rows, S] -> probabilities (written to `dense`) and their saved form, one pass.  Covered: the shapes of
+// topk_lane_ok with M a multiple of the rows a warp takes and mask rows S apart; HYC_ERR_UNSUPPORTED otherwise
+// (nothing launched: the caller runs the softmax and the compress kernels one after the other).
+int topk_lane_softmax_compress(const void* scores, float sc, const void* mask, int64_t mb, int64_t mh, int64_t mr, int heads,
+                               int M, int64_t rows, int S, int k, void* dense, void* val_out, uint16_t* col_out,
+                               void* q_out, void* scale_out, int8_t* zp_out, int q_bit, cudaStream_t st) {
+  if (!topk_lane_ok(S, k)) return HYC_ERR_UNSUPPORTED;
+  const int rpw = 32 / (S / 64);
+  if (M % rpw != 0 || (mask != nullptr && mr != S) || !aligned(scores, 32) || !aligned(dense, 32) || !aligned(q_out, 32) ||
+      (mask != nullptr && (!aligned(mask, 32) || (mb & 15) != 0 || (mh & 15) != 0)))
+    return HYC_ERR_UNSUPPORTED;
+  SoftmaxPrologue sp;
+  sp.scale = sc; sp.mask = (const __nv_bfloat16*)mask; sp.mb = mb; sp.mh = mh; sp.heads = heads; sp.M = M;
+  sp.dense = (__nv_bfloat16*)dense;
+  if (q_bit == 2) return compress_q<2>(scores, rows, S, k, val_out, col_out, q_out, scale_out, zp_out, &sp, st);
+  if (q_bit == 4) return compress_q<4>(scores, rows, S, k, val_out, col_out, q_out, scale_out, zp_out, &sp, st);
+  return compress_q<8>(scores, rows, S, k, val_out, col_out, q_out, scale_out, zp_out, &sp, st);
 }
 int topk_lane_restore(const void* val, const uint16_t* col, int k, const void* q, const void* scale,
                       const int8_t* zp, int64_t rows, int S, const void* grad_or_null, float out_scale, void* a_out,

@@ -49,7 +49,7 @@ class FusedLayerFunction(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, x, module, aw, mw, cos, sin, attention_mask, num_heads, head_dim, num_key_value_heads, *lora):
-        st = _status_tensor(x.device)
+        st = module._status_for(x.device)
         x_medium, sa = attention_forward(x, aw, module.attn_state, cos, sin, attention_mask, num_heads, head_dim,
                                          num_key_value_heads, status=st)
         y, sm = mlp_forward(x_medium, mw, module.mlp_state, status=st)
@@ -68,12 +68,13 @@ class FusedLayerFunction(torch.autograd.Function):
         gm = mlp_backward(grad_y, sm, mw, status=st, on_lora_grads=hook)
         saved_map = sa.get('a_saved')
         ga = attention_backward(gm['grad_x'], sa, aw, status=st, on_lora_grads=hook)
-        if module.check_kernel_status:
-            check_status(st, "fused layer")
-            # fixed-capacity prune buffers: more entries above the threshold than they hold would have been dropped
-            if hasattr(saved_map, "overflowed") and saved_map.overflowed():
-                raise RuntimeError("fused layer: the pruned probability map overflowed its buffers (%d entries); raise "
-                                   "AttnState.prune_capacity_margin" % saved_map.capacity)
+        # fixed-capacity prune buffers: entries beyond the capacity were dropped; the flag stays on the device
+        if hasattr(saved_map, "nnz") and hasattr(saved_map, "capacity"):
+            module._overflow.add_((saved_map.nnz > saved_map.capacity).to(torch.int32))
+        module._steps_since_check += 1
+        every = 1 if module.check_kernel_status else module.check_every
+        if every and module._steps_since_check >= every and not torch.cuda.is_current_stream_capturing():
+            module.raise_on_device_errors()
         grads = [ga['grad_aq'], ga['grad_bq'], ga['grad_ak'], ga['grad_bk'], ga['grad_av'], ga['grad_bv'],
                  ga['grad_ao'], ga['grad_bo'], gm['grad_ag'], gm['grad_bg'], gm['grad_au'], gm['grad_bu'],
                  gm['grad_ad'], gm['grad_bd']]
@@ -116,7 +117,35 @@ class FusedLlamaLayerIntraInterFullFuse(torch.nn.Module):
         self.last_saved_bytes = None
         self.keep_saved = False            # True: forward also leaves its two saved dictionaries in last_saved (inspection)
         self.last_saved = None
+        # Failures stay visible without a host synchronisation per step: the bounded-wait status word of the tensor-core
+        # kernels and the overflow flag of the fixed-capacity prune buffers live in two persistent device words that
+        # are read back (one synchronisation) every `check_every` backward passes; 0 = never, check_kernel_status = every pass
+        self.check_every = 100
+        self._status = None
+        self._overflow = None
+        self._steps_since_check = 0
         self._weights = None
+
+    def _status_for(self, device):
+        if self._status is None or self._status.device != device:
+            self._status = torch.zeros(1, dtype=torch.int32, device=device)
+            self._overflow = torch.zeros(1, dtype=torch.int32, device=device)
+        return self._status
+
+    def raise_on_device_errors(self):
+        """Read the two persistent device words (synchronises) and raise if a tensor-core kernel gave up on a bounded
+        wait or the pruned probability map did not fit its buffers since the last check."""
+        self._steps_since_check = 0
+        if self._status is None:
+            return
+        st, ov = int(self._status.item()), int(self._overflow.item())
+        self._status.zero_()
+        self._overflow.zero_()
+        if st != 0:
+            check_status(torch.tensor([st]), "fused layer")
+        if ov != 0:
+            raise RuntimeError("fused layer: the pruned probability map overflowed its buffers in %d step(s) since the last "
+                               "check (entries were dropped); raise AttnState.prune_capacity_margin" % ov)
 
     # ---- the reference's attributes
     @property
@@ -127,6 +156,7 @@ class FusedLlamaLayerIntraInterFullFuse(torch.nn.Module):
     def iteration(self, v):
         self.attn_state.iteration = v
         self.mlp_state.iteration = v
+        self.attn_state.threshold_host = None      # a re-calibration ends with another threshold
 
     @property
     def static_value(self):

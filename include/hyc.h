@@ -156,6 +156,20 @@ int hyc_softmax_prune_static(const void* a, int64_t numel, float threshold,
 int hyc_softmax_topk_compress(const void* a, int64_t rows, int S, int k,
                               void* val_out, uint16_t* col_out,
                               void* q_out, void* scale_out, int8_t* zp_out, int q_bit, void* stream);
+/* The forward side of the attention map in ONE pass: s = q k^T / sqrt(d) is already computed (library batched GEMM);
+ * this call does  a = softmax(bf16(bf16(s * scale) + mask))  (fused_llama_layer_intra_inter_full_fuse.py:152-167, the
+ * three tensor operations of the layer with their bf16 rounding points), writes the dense probabilities to a_out
+ * (the P.V product needs them; a_out may be the scores buffer) AND saves them in the top-k form of
+ * hyc_softmax_topk_compress -- the row never leaves the registers in between, so the map is read once instead of
+ * twice.  mask: additive bf16, row m of (batch b, head h) at mask + b * mask_stride_b + h * mask_stride_h +
+ * m * mask_stride_row (strides in elements, 0 = broadcast).  rows = batch * heads * M.  Returns
+ * HYC_ERR_UNSUPPORTED without launching anything for shapes outside the fused kernel (S not 64 * 2^n <= 2048, M not a
+ * multiple of 32 / (S / 64), mask_stride_row != S, buffers not 32-byte aligned): run hyc_softmax_fwd_scale_mask and
+ * hyc_softmax_topk_compress then. */
+int hyc_softmax_fwd_topk_save(const void* scores, float scale, const void* mask_or_null, int64_t mask_stride_b,
+                              int64_t mask_stride_h, int64_t mask_stride_row, int heads, int M,
+                              int64_t rows, int S, int k, void* a_out, void* val_out, uint16_t* col_out,
+                              void* q_out, void* scale_out, int8_t* zp_out, int q_bit, void* stream);
 int hyc_softmax_topk_restore(const void* val, const uint16_t* col, int k,
                              const void* q, const void* scale, const int8_t* zp,
                              int64_t rows, int S, void* a_out, int q_bit, void* stream);

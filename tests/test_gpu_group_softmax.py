@@ -286,3 +286,38 @@ def test_softmax_prune_tiled_ragged_and_negative_threshold(cf, numel, thr):
         mi, mv = m.entries()
         assert torch.equal(mi, want_idx) and torch.equal(mv, want_val)
         assert torch.equal(m.to_dense().reshape(-1), cf.decompression_softmax(sp).reshape(-1))
+
+
+@pytest.mark.parametrize("q", QS)
+@pytest.mark.parametrize("B,h,M,S,mask_kind", [(2, 4, 64, 64, "causal"), (1, 3, 128, 512, "causal"), (2, 2, 64, 1024, "batch"),
+                                               (1, 2, 32, 2048, None), (1, 2, 17, 128, "causal"), (1, 1, 8, 4096, None)])
+def test_softmax_forward_fused_with_the_topk_save(cf, q, B, h, M, S, mask_kind):
+    """scale + mask + softmax + top-k save in one kernel: the probabilities against the two-kernel path (equal up to the
+    last bf16 bit where the fp32 row sum rounds differently), and the saved map EXACTLY the stand-alone compression of
+    the probabilities the fused kernel returned (so codes, indices and values stay bit-exact against the oracle through
+    the stand-alone kernel's tests).  The last two shapes are outside the fused kernel and take the two kernels."""
+    import math
+    from hyc_lora_release_b200.operators.softmax_kernels import softmax_forward_scale_mask, softmax_forward_topk_save
+    g = torch.Generator().manual_seed(S + M + q)
+    sc = (torch.randn(B, h, M, S, generator=g) * 8).to(torch.bfloat16).to(DEV)
+    mask = None
+    if mask_kind == "causal":
+        mask = torch.full((M, S), torch.finfo(torch.bfloat16).min).triu(1).to(torch.bfloat16).reshape(1, 1, M, S).to(DEV)
+    elif mask_kind == "batch":
+        mask = (torch.randn(B, 1, M, S, generator=g) * 3).to(torch.bfloat16).to(DEV)
+    scale = 1.0 / math.sqrt(128)
+    a_ref = softmax_forward_scale_mask(sc, scale, mask)
+    a, m = softmax_forward_topk_save(sc, scale, mask, 0.05, q)
+    assert a.shape == sc.shape and a.dtype == torch.bfloat16
+    diff = (a.float() - a_ref.float()).abs()
+    assert bool((diff <= a_ref.float().abs() * 2 ** -7 + 1e-30).all()) and float((a != a_ref).float().mean()) < 0.05
+    m2 = cf.compression_softmax_topk(a, 0.05, q)
+    assert all(torch.equal(x, y) for x, y in zip(m.tensors(), m2.tensors()))
+    # in place: the scores buffer becomes the probabilities
+    buf = sc.clone()
+    a3, m3 = softmax_forward_topk_save(buf, scale, mask, 0.05, q, inplace=True)
+    assert a3.data_ptr() == buf.data_ptr() and torch.equal(a3, a)
+    assert all(torch.equal(x, y) for x, y in zip(m3.tensors(), m.tensors()))
+    # and against the oracle on the probabilities it produced
+    vals, cols, pk, s_, z_ = oracle.topk_compress(a.cpu(), 0.05, q)
+    assert torch.equal(m.val.cpu(), vals) and torch.equal(m.q.cpu(), pk) and torch.equal(m.scale.cpu(), s_)

@@ -270,3 +270,47 @@ def test_layer_module_through_autograd(heads, kv, map_mode):
     f32.default = f32.default.float()
     with pytest.raises(NotImplementedError):
         layer._bind(n1, n2, {**mods, "q": (mods["q"][0], f32, mods["q"][2])})
+
+
+def test_layer_reports_dropped_map_entries_and_recalibrates():
+    """Failures must not stay silent: a pruned map that does not fit its fixed-capacity buffers raises at the next
+    periodic check (the flag is kept on the device in between, no synchronisation per step), and setting `iteration`
+    back re-calibrates the threshold the steady state uses."""
+    from hyc_lora_release_b200.layer import FusedLlamaLayerIntraInterFullFuse
+    g = torch.Generator().manual_seed(77)
+    B, M, heads, d, kv, I, q = 1, 128, 4, 128, 4, 512, 4
+    H = heads * d
+    x, p, cos, sin, mask = layer_problem(g, B, M, H, heads, d, kv, I)
+    mods = {n: (_base(p["w" + n].t().to(DEV)), _Holder(p["a" + n].t().to(DEV)), _Holder(p["b" + n].t().to(DEV)))
+            for n in ("q", "k", "v", "o", "gate", "up", "down")}
+    layer = FusedLlamaLayerIntraInterFullFuse()
+    layer.set_hyclora_config(types.SimpleNamespace(use_hyclora=True, iteration_threshold=2, softmax_outlier_ratio=0.05,
+                                                   layernorm_outlier_ratio=0.01, q_bit=q, softmax_map_mode="prune"))
+    layer.check_every = 3
+    n1, n2 = p["norm_w1"].to(DEV), p["norm_w2"].to(DEV)
+    gy = torch.randn(B, M, H, generator=g).to(BF16).to(DEV)
+
+    def run():
+        xin = x.to(DEV).requires_grad_(True)
+        args = [xin, n1, None, cos.to(DEV), sin.to(DEV)]
+        for n in ("q", "k", "v", "o"):
+            args += list(mods[n])
+        args += [n2, None]
+        for n in ("gate", "up", "down"):
+            args += list(mods[n])
+        layer(*args, mask.to(DEV), heads, d, kv).backward(gy)
+    for _ in range(4):
+        run()                                    # 2 calibration steps, 2 steady ones: nothing to report
+    layer.raise_on_device_errors()
+    assert layer.attn_state.threshold_host is not None
+    layer.attn_state.prune_capacity_margin = 0.01      # buffers far too small for the calibrated threshold
+    with pytest.raises(RuntimeError, match="overflowed"):
+        for _ in range(3):
+            run()
+    layer.attn_state.prune_capacity_margin = 1.5
+    layer.iteration = 0                          # re-calibrate: the cached host threshold must go
+    assert layer.attn_state.threshold_host is None
+    for _ in range(3):
+        run()
+    layer.raise_on_device_errors()
+    assert layer.attn_state.threshold_host is not None
