@@ -245,78 +245,154 @@ prune_scatter_counted_kernel(const int64_t* __restrict__ idx, const __nv_bfloat1
 // (offset within the batch << 16 | bf16 value) words, reserves a span of the word list with ONE atomic add on the
 // device-side count, writes the span with consecutive lanes and records {span start, entries} in the batch's
 // directory slot.  Which span a batch gets depends on the order in which the warps arrive; inside a span the
-// entries of a lane are adjacent (the order is fixed, but not ascending).  The count keeps growing past `capacity` (the caller sees the overflow);
-// words beyond it are dropped.
+// entries of a lane are adjacent (the order is fixed, but not ascending).
+// One counter for the whole list would be the bottleneck: sixteen thousand atomic adds on ONE address take about as
+// long as reading the map.  The word list is therefore cut into kSubLists equal sub-lists with a counter each (128
+// bytes apart, behind the directory), and a batch takes its span from the sub-list its hashed index names, so every
+// sub-list receives a pseudo-random sample of the batches and fills evenly.  A span that does not fit its sub-list is
+// cut short (the directory records what was written); a last one-block kernel adds the counters up: *nnz_out = the
+// number of kept entries if everything fit, else capacity + the number of entries that were dropped.  Small maps
+// use fewer sub-lists (at least 32 batches each, so that the sample averages out), down to a single one, which
+// never drops anything that `capacity` could hold.
 constexpr int kBatchElems = 256 * kBatch;       // 2048
+constexpr int kSubLists = 64;
+constexpr int kCounterStride = 16;              // unsigned long long per counter slot (128 bytes)
+
+__host__ __device__ inline uint32_t tiled_sub_lists(int64_t numel) {
+  const int64_t nb = (numel + kBatchElems - 1) / kBatchElems;
+  const int64_t n = nb / 32;
+  return (uint32_t)(n < 1 ? 1 : (n > kSubLists ? kSubLists : n));
+}
+__host__ __device__ inline int64_t tiled_dir_entries(int64_t numel) {
+  const int64_t nb = (numel + kBatchElems - 1) / kBatchElems;
+  return (nb + 15) & ~(int64_t)15;              // the counters behind it start on a 128-byte boundary
+}
 
 template <bool NEG>
 __global__ void __launch_bounds__(kTileThreads, 4)
 prune_tiled_kernel(const __nv_bfloat16* __restrict__ a, int64_t numel, float thr, int64_t n_tiles,
                    uint32_t* __restrict__ words, uint32_t capacity, uint2* __restrict__ dir,
-                   unsigned long long* __restrict__ count) {
+                   unsigned long long* __restrict__ counters) {
+  // A warp walks batches with a fixed stride.  Per batch: masks and counts from the eight chunks in registers, ONE
+  // atomic add for the span, the entries staged in shared memory, and -- before anything waits for the atomic's
+  // answer -- the loads of the warp's NEXT batch: the round trip of the atomic and the write-out of this batch run
+  // while those loads are in flight.  (A batch with more than 1024 entries, i.e. more than the staging area holds,
+  // takes the plain sequence: group by group, next loads afterwards.)
   __shared__ uint32_t s_stage[kWarpsPerBlock][256 * kFillTrips];
   const __nv_bfloat162 t2 = __float2bfloat162_rn(thr);
   const int lane = threadIdx.x & 31;
   uint32_t* stage = s_stage[threadIdx.x >> 5];
   const int64_t n_batches = (numel + kBatchElems - 1) / kBatchElems;
-  const int64_t warp0 = (int64_t)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
-  for (int64_t tile = warp0; tile < n_tiles; tile += (int64_t)gridDim.x * kWarpsPerBlock) {
-    const int64_t t0 = tile * kTileElems + 8 * lane;
-#pragma unroll 1
-    for (int b = 0; b < kTileElems / kBatchElems; ++b) {
-      const int64_t batch = tile * (kTileElems / kBatchElems) + b;
-      if (batch >= n_batches) break;
-      uint4 u[kBatch];
+  const int64_t stride = (int64_t)gridDim.x * kWarpsPerBlock;
+  int64_t batch = (int64_t)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
+  const uint32_t n_sub = tiled_sub_lists(numel);
+  const uint32_t sub_cap = capacity / n_sub;          // words per sub-list
+  (void)n_tiles;
+  uint4 u[kBatch];
+  auto load_batch = [&](int64_t bt) {
+    const int64_t t0 = bt * kBatchElems + 8 * lane;
 #pragma unroll
-      for (int j = 0; j < kBatch; ++j) {
-        const int64_t base = t0 + 256 * (b * kBatch + j);
-        u[j] = base < numel ? load_chunk<true>(a, base, numel) : make_uint4(0u, 0u, 0u, 0u);
-      }
-      uint32_t mk[kBatch / kFillTrips];      // the keep masks of a group's four trips, one byte each
-      int cg[kBatch / kFillTrips];
+    for (int j = 0; j < kBatch; ++j) {
+      const int64_t base = t0 + 256 * j;
+      u[j] = base < numel ? load_chunk<true>(a, base, numel) : make_uint4(0u, 0u, 0u, 0u);
+    }
+  };
+  // entries of group g (four trips) into the staging area from position `pos` on, lanes in order
+  auto stage_group = [&](int g, uint32_t mkg, int pos) {
 #pragma unroll
-      for (int g = 0; g < kBatch / kFillTrips; ++g) {
-        mk[g] = 0u;
+    for (int jj = 0; jj < kFillTrips; ++jj) {
+      const int j = g * kFillTrips + jj;
+      const uint32_t w[4] = {u[j].x, u[j].y, u[j].z, u[j].w};
+      const uint32_t off = (uint32_t)(256 * j + 8 * lane);        // offset inside the batch
 #pragma unroll
-        for (int jj = 0; jj < kFillTrips; ++jj) mk[g] |= keep_mask8<NEG>(u[g * kFillTrips + jj], t2) << (8 * jj);
-        cg[g] = __popc(mk[g]);
-      }
-      // both group totals in one reduction (a group holds at most 1024 entries)
-      const unsigned packed = __reduce_add_sync(0xffffffffu, (unsigned)cg[0] | ((unsigned)cg[1] << 16));
-      const unsigned n_batch = (packed & 0xffffu) + (packed >> 16);
-      unsigned long long span = 0;
-      if (lane == 0) {
-        if (n_batch) span = atomicAdd(count, (unsigned long long)n_batch);
-        // a span that starts beyond 2^32 words cannot be addressed (and is far beyond any capacity): recorded as empty
-        dir[batch] = span <= 0xffffffffull ? make_uint2((uint32_t)span, n_batch) : make_uint2(0u, 0u);
-      }
-      if (n_batch == 0) continue;
-      unsigned long long run = __shfl_sync(0xffffffffu, span, 0);
-#pragma unroll
-      for (int g = 0; g < kBatch / kFillTrips; ++g) {
-        const int n_staged = g == 0 ? (int)(packed & 0xffffu) : (int)(packed >> 16);
-        if (n_staged == 0) continue;
-        int total;
-        int pos = warp_excl_scan(cg[g], lane, total);
-#pragma unroll
-        for (int jj = 0; jj < kFillTrips; ++jj) {
-          const int j = g * kFillTrips + jj;
-          const uint32_t w[4] = {u[j].x, u[j].y, u[j].z, u[j].w};
-          const uint32_t off = (uint32_t)(256 * j + 8 * lane);        // offset inside the batch
-#pragma unroll
-          for (int e = 0; e < 8; ++e) {
-            if (mk[g] & (1u << (8 * jj + e))) stage[pos++] = __byte_perm(w[e >> 1], off + e, (e & 1) ? 0x5432 : 0x5410);
-          }
-        }
-        __syncwarp();
-        for (int i = lane; i < n_staged; i += 32) {
-          const unsigned long long p = run + i;
-          if (p < capacity) words[p] = stage[i];
-        }
-        run += n_staged;
-        __syncwarp();
+      for (int e = 0; e < 8; ++e) {
+        if (mkg & (1u << (8 * jj + e))) stage[pos++] = __byte_perm(w[e >> 1], off + e, (e & 1) ? 0x5432 : 0x5410);
       }
     }
+  };
+  if (batch < n_batches) load_batch(batch);
+  while (batch < n_batches) {
+    uint32_t mk[kBatch / kFillTrips];      // the keep masks of a group's four trips, one byte each
+    int cg[kBatch / kFillTrips];
+#pragma unroll
+    for (int g = 0; g < kBatch / kFillTrips; ++g) {
+      mk[g] = 0u;
+#pragma unroll
+      for (int jj = 0; jj < kFillTrips; ++jj) mk[g] |= keep_mask8<NEG>(u[g * kFillTrips + jj], t2) << (8 * jj);
+      cg[g] = __popc(mk[g]);
+    }
+    // both group totals in one reduction (a group holds at most 1024 entries)
+    const unsigned packed = __reduce_add_sync(0xffffffffu, (unsigned)cg[0] | ((unsigned)cg[1] << 16));
+    const int n0 = (int)(packed & 0xffffu), n1 = (int)(packed >> 16);
+    const unsigned n_batch = (unsigned)(n0 + n1);
+    // span = {first word, words that fit}: from the sub-list the hashed batch index names
+    uint2 span = make_uint2(0u, 0u);
+    if (lane == 0) {
+      if (n_batch) {
+        const uint32_t sub = __umulhi((uint32_t)batch * 0x9E3779B1u, n_sub);
+        const unsigned long long at = atomicAdd(counters + sub * kCounterStride, (unsigned long long)n_batch);
+        const uint32_t room = at < sub_cap ? sub_cap - (uint32_t)at : 0u;
+        span = make_uint2(sub * sub_cap + (uint32_t)(at < sub_cap ? at : 0), n_batch < room ? n_batch : room);
+      }
+      dir[batch] = span;
+    }
+    const int64_t next = batch + stride;
+    if (n_batch <= 256 * kFillTrips) {
+      if (n_batch) {
+        int total;
+        const int p0 = warp_excl_scan(cg[0], lane, total);
+        stage_group(0, mk[0], p0);
+        if (n1) {
+          const int p1 = n0 + warp_excl_scan(cg[1], lane, total);
+          stage_group(1, mk[1], p1);
+        }
+      }
+      if (next < n_batches) load_batch(next);          // in flight while the atomic answers and the span is written
+      if (n_batch) {
+        __syncwarp();
+        const uint32_t run = __shfl_sync(0xffffffffu, span.x, 0), fit = __shfl_sync(0xffffffffu, span.y, 0);
+        for (unsigned i = lane; i < fit; i += 32) words[run + i] = stage[i];
+        __syncwarp();
+      }
+    } else {
+      uint32_t run = __shfl_sync(0xffffffffu, span.x, 0), fit = __shfl_sync(0xffffffffu, span.y, 0);
+#pragma unroll
+      for (int g = 0; g < kBatch / kFillTrips; ++g) {
+        const int n_staged = g == 0 ? n0 : n1;
+        if (n_staged == 0) continue;
+        int total;
+        stage_group(g, mk[g], warp_excl_scan(cg[g], lane, total));
+        __syncwarp();
+        const uint32_t n_out = (uint32_t)n_staged < fit ? (uint32_t)n_staged : fit;
+        for (uint32_t i = lane; i < n_out; i += 32) words[run + i] = stage[i];
+        run += n_out;
+        fit -= n_out;
+        __syncwarp();
+      }
+      if (next < n_batches) load_batch(next);
+    }
+    batch = next;
+  }
+}
+
+// one block: the sub-lists' counters -> *nnz_out (see above)
+__global__ void __launch_bounds__(kSubLists)
+prune_tiled_finish_kernel(const unsigned long long* __restrict__ counters, uint32_t capacity, uint32_t n_sub,
+                          int64_t* __restrict__ nnz_out) {
+  const uint32_t sub_cap = capacity / n_sub;
+  const unsigned long long c = threadIdx.x < n_sub ? counters[threadIdx.x * kCounterStride] : 0ull;
+  unsigned long long kept = c, dropped = c > sub_cap ? c - sub_cap : 0ull;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    kept += __shfl_xor_sync(0xffffffffu, kept, o);
+    dropped += __shfl_xor_sync(0xffffffffu, dropped, o);
+  }
+  __shared__ unsigned long long s_k[2], s_d[2];
+  if ((threadIdx.x & 31) == 0) { s_k[threadIdx.x >> 5] = kept; s_d[threadIdx.x >> 5] = dropped; }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned long long k = s_k[0] + s_k[1], d = s_d[0] + s_d[1];
+    *nnz_out = (int64_t)(d ? (unsigned long long)capacity + d : k);
   }
 }
 
@@ -473,7 +549,7 @@ extern "C" HYC_API int hyc_softmax_prune_restore_counted(const int64_t* idx, con
 
 extern "C" HYC_API size_t hyc_softmax_prune_tiled_directory_bytes(int64_t numel) {
   if (numel < 0) return 0;
-  return (size_t)((numel + kBatchElems - 1) / kBatchElems) * sizeof(uint2);
+  return (size_t)tiled_dir_entries(numel) * sizeof(uint2) + (size_t)kSubLists * kCounterStride * sizeof(unsigned long long);
 }
 
 extern "C" HYC_API int hyc_softmax_prune_tiled(const void* a, int64_t numel, float threshold,
@@ -482,20 +558,27 @@ extern "C" HYC_API int hyc_softmax_prune_tiled(const void* a, int64_t numel, flo
   if (!a || !nnz_out || !directory_out) return HYC_ERR_NULL;
   if (capacity > 0 && !words_out) return HYC_ERR_NULL;
   if (numel <= 0 || capacity < 0 || capacity > 0xffffffffll) return HYC_ERR_SHAPE;
-  if (!aligned(a, 16) || !aligned(nnz_out, 8) || !aligned(directory_out, 8) || !aligned(words_out, 4)) return HYC_ERR_ALIGN;
+  if (!aligned(a, 16) || !aligned(nnz_out, 8) || !aligned(directory_out, 128) || !aligned(words_out, 4)) return HYC_ERR_ALIGN;
   cudaStream_t st = (cudaStream_t)stream;
-  if (cudaMemsetAsync(nnz_out, 0, sizeof(int64_t), st) != cudaSuccess) { hyc_set_last_cuda_error((int)cudaGetLastError()); return HYC_ERR_LAUNCH; }
+  unsigned long long* counters = reinterpret_cast<unsigned long long*>(reinterpret_cast<uint2*>(directory_out) + tiled_dir_entries(numel));
+  if (cudaMemsetAsync(counters, 0, (size_t)kSubLists * kCounterStride * sizeof(unsigned long long), st) != cudaSuccess) {
+    hyc_set_last_cuda_error((int)cudaGetLastError());
+    return HYC_ERR_LAUNCH;
+  }
   const int64_t nt = n_tiles_of(numel);
   const float thr = thr_bf16(threshold);
-  // four resident blocks of eight warps per multiprocessor; larger maps wrap around
-  int64_t g = (nt + kWarpsPerBlock - 1) / kWarpsPerBlock;
+  // four resident blocks of eight warps per multiprocessor, a warp per batch; larger maps wrap around
+  const int64_t nbt = (numel + kBatchElems - 1) / kBatchElems;
+  int64_t g = (nbt + kWarpsPerBlock - 1) / kWarpsPerBlock;
   if (g > (int64_t)num_sms() * 4) g = (int64_t)num_sms() * 4;
   if (thr >= 0.f)
     prune_tiled_kernel<false><<<(int)g, kTileThreads, 0, st>>>((const __nv_bfloat16*)a, numel, thr, nt, words_out, (uint32_t)capacity,
-                                                            (uint2*)directory_out, (unsigned long long*)nnz_out);
+                                                            (uint2*)directory_out, counters);
   else
     prune_tiled_kernel<true><<<(int)g, kTileThreads, 0, st>>>((const __nv_bfloat16*)a, numel, thr, nt, words_out, (uint32_t)capacity,
-                                                           (uint2*)directory_out, (unsigned long long*)nnz_out);
+                                                           (uint2*)directory_out, counters);
+  HYC_CHECK_LAUNCH();
+  prune_tiled_finish_kernel<<<1, kSubLists, 0, st>>>(counters, (uint32_t)capacity, tiled_sub_lists(numel), nnz_out);
   HYC_CHECK_LAUNCH();
   return HYC_OK;
 }
@@ -504,7 +587,7 @@ extern "C" HYC_API int hyc_softmax_prune_tiled_restore(const uint32_t* words, in
                                                        void* a_out, int64_t numel, void* stream) {
   if (!a_out || !directory || (capacity > 0 && !words)) return HYC_ERR_NULL;
   if (numel <= 0 || capacity < 0 || capacity > 0xffffffffll) return HYC_ERR_SHAPE;
-  if (!aligned(a_out, 16) || !aligned(directory, 8)) return HYC_ERR_ALIGN;
+  if (!aligned(a_out, 16) || !aligned(directory, 128)) return HYC_ERR_ALIGN;
   const int64_t nb = (numel + kBatchElems - 1) / kBatchElems;
   int64_t g = (nb + kWarpsPerBlock - 1) / kWarpsPerBlock;
   if (g > (int64_t)num_sms() * 4) g = (int64_t)num_sms() * 4;

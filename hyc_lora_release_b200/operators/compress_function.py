@@ -325,7 +325,10 @@ class PrunedMap:
 class TiledPrunedMap:
     """The threshold-pruned map in the tiled form of ``hyc_softmax_prune_tiled``: 4-byte words (offset inside a
     2048-element batch << 16 | bf16 bits) in per-batch spans, a directory of {span start, entries} per batch and the
-    device-side count.  ``to_dense()`` rebuilds the map in one pass; nothing synchronises with the host."""
+    device-side count.  ``to_dense()`` rebuilds the map in one pass; nothing synchronises with the host.
+    ``nnz`` holds the number of kept entries when everything fit, else capacity + the number of dropped entries
+    (the word list is used as 64 equal sub-lists that fill evenly but not identically, so keep ``capacity`` a good
+    margin above the expected count: the default is 1.5 x)."""
 
     BATCH = 2048
 
@@ -358,9 +361,12 @@ class TiledPrunedMap:
     def entries(self):
         """(flattened index int64, value bf16) of the stored entries in ascending index order, decoded with torch
         operations (for inspection and tests; synchronises)."""
-        d = self.directory.view(-1, 2).to(torch.int64)
+        numel = 1
+        for n in self.shape:
+            numel *= n
+        n_batches = (numel + self.BATCH - 1) // self.BATCH          # the buffer also holds the call's counters behind these
+        d = self.directory[:2 * n_batches].view(-1, 2).to(torch.int64)
         start, cnt = d[:, 0], d[:, 1]
-        cnt = torch.minimum(cnt, (self.capacity - start).clamp(min=0))
         batch = torch.repeat_interleave(torch.arange(d.shape[0], device=d.device), cnt)
         first = torch.repeat_interleave(start, cnt)
         ofs = torch.arange(batch.numel(), device=d.device) - torch.repeat_interleave(torch.cumsum(cnt, 0) - cnt, cnt)

@@ -119,13 +119,17 @@ int hyc_softmax_prune_restore_counted(const int64_t* idx, const void* val, const
 
 /* The same threshold prune in ONE pass over the map, in a tiled form, for callers that only ever restore the map
  * (the restore of the layers is to_dense, compress_function.py:316-317; nothing reads the COO list itself): no
- * workspace, no second launch, 4 bytes per kept entry instead of 10.  The map is cut into batches of 2048
- * consecutive elements; the entries of a batch go into a span of words_out as (offset in the batch << 16 | bf16
- * bits), in no particular order inside the span, and directory_out[batch] = {first word of the span, entries} (two uint32;
- * hyc_softmax_prune_tiled_directory_bytes(numel) bytes).  Spans are handed out by one atomic add per batch on
- * *nnz_out, so their order depends on the run; the set of (index, value) pairs is that of compression_softmax
- * (compress_function.py:309-313).  nnz_out (device int64, zeroed by this call) ends up as the number of kept
- * entries, which may exceed `capacity` (<= 2^32 - 1; the excess is dropped: compare the two). */
+ * second pass over the map, 4 bytes per kept entry instead of 10.  The map is cut into batches of 2048 consecutive
+ * elements; the entries of a batch go into a span of words_out as (offset in the batch << 16 | bf16 bits), in no
+ * particular order inside the span, and directory_out[batch] = {first word of the span, entries written} (two
+ * uint32).  directory_out holds hyc_softmax_prune_tiled_directory_bytes(numel) bytes (the directory and, behind it,
+ * 8 KB of counters the call clears and uses) and must be 128-byte aligned.  words_out is used as up to 64 equal
+ * sub-lists (one per 32 batches of the map, a single one for maps below 131072 elements); a batch takes its span
+ * from the sub-list that a hash of its index names, by one atomic add on that sub-list's counter, so the order of
+ * the spans depends on the run and the sub-lists fill evenly but not identically (give `capacity` a margin); the set of (index, value) pairs is that of
+ * compression_softmax (compress_function.py:309-313).  *nnz_out (device int64) = the number of kept entries if
+ * every span fit its sub-list, else capacity + the number of dropped entries (so "nnz > capacity" means entries
+ * were dropped).  capacity <= 2^32 - 1. */
 size_t hyc_softmax_prune_tiled_directory_bytes(int64_t numel);
 int hyc_softmax_prune_tiled(const void* a, int64_t numel, float threshold,
                             uint32_t* words_out, int64_t capacity, void* directory_out,
