@@ -29,9 +29,10 @@ QBIT = 4
 NBUF = 4          # distinct input/output sets rotated between round trips (4 x 64 MiB in, > L2)
 ROUND_TRIPS = 64  # compress + decompress round trips that make one step (a step is about 4 ms of device time)
 SAMPLE_SHAPE = (1, 8, 512, 512)     # the slice of the map one step of the CPU arms works on (1/16 of the map)
-# dram__bytes_read.sum + dram__bytes_write.sum of ONE launch on this workload (bytes), taken from an ncu capture of the
-# kernels as they are built now; None when no capture of the current build exists
-NCU_TRAFFIC = {"hyc::topk_lane_compress_kernel<4,8>": None, "hyc::topk_lane_restore_kernel<4,8,false>": None}
+# dram__bytes_read.sum + dram__bytes_write.sum of ONE launch on this workload (bytes), from an ncu --set full capture of
+# the two kernels as they are built now (67.16 + 3.40 MB and 24.92 + 10.58 MB); set an entry to None when its kernel
+# changes until a new capture is taken
+NCU_TRAFFIC = {"hyc::topk_lane_compress_kernel<4,8>": 70.56e6, "hyc::topk_lane_restore_kernel<4,8,false>": 35.50e6}
 
 
 def peaks():

@@ -140,6 +140,7 @@ class LoraGradReducer:
         self._bucket_size = []
         self._works = []
         self._layers = []
+        self._local = {}
 
     def bind(self, key, name, param):
         self._params[(key, name)] = param
@@ -193,6 +194,10 @@ class LoraGradReducer:
             self._works.append((dist.all_reduce(self.flat[lo:hi], op=op, group=self.group, async_op=True), op, lo, hi))
 
     def add(self, key, grads):
+        if self.world == 1:
+            # nothing to exchange: the local gradients ARE the result; finish() hands them to .grad without a copy
+            self._local[key] = grads
+            return
         if not self._frozen:
             if key in self._first:
                 raise RuntimeError("LoraGradReducer: %r delivered twice in one step" % (key,))
@@ -210,7 +215,16 @@ class LoraGradReducer:
 
     def finish(self):
         """Wait for the exchange, write the averaged gradients into the bound parameters' ``.grad`` and return the
-        flat buffer (fp32, averaged)."""
+        flat buffer (fp32, averaged; None on a single rank, where ``.grad`` simply becomes the local gradient)."""
+        if self.world == 1:
+            if self._layers and not self._params:
+                self._bind_layers()
+            for (key, name), p in self._params.items():
+                g = self._local.get(key, {}).get(name)
+                if g is not None:
+                    p.grad = g if (g.dtype == p.dtype and g.shape == p.shape) else g.to(p.dtype).reshape(p.shape)
+            self._local = {}
+            return None
         if not self._frozen:
             if not self._first:
                 return None
