@@ -7,18 +7,27 @@
 //   GRADDOWN : grad_down tile = g * Wd (+ LoRA), then per element: unpack-dequantize the saved
 //              gate/up codes, recompute the forward, emit hadamard, grad_gate, grad_up (backward).
 //
-// Structure of a CTA (320 threads, one CTA per SM, tiles dealt round-robin):
-//   warp 0      : TMA producer; 128x64 A tile and 256x64 B tile per stage (128-byte swizzle),
-//                 4 stages of 48 KB, mbarrier full/empty pairs.
-//   warp 1      : allocates all 512 TMEM columns (two 128x256 fp32 accumulators), issues
-//                 tcgen05.mma (M128 N256 K16, bf16 -> fp32) from one lane, commits to mbarriers.
-//                 N = 256 keeps the shared-memory read rate of the MMA below the SM's limit.
-//   warps 2..9  : epilogue.  Warp w reads TMEM lanes 32*(w%4).. (tcgen05.ld 32x32b.x32) for half of
-//                 the tile's columns, so the epilogue of tile i overlaps the MMAs of tile i+1.
+// Two CTAs on neighbouring SMs (a cluster of 2) work on one 256 x 256 tile with the pair form of the MMA
+// (cta_group::2): CTA r of the pair holds rows 128 r .. 128 r + 127 of the A tile and columns 128 r .. of the
+// B tile in its shared memory, the tensor core of each SM reads both halves of B, and each CTA's tensor memory
+// receives its own 128 rows of the result.  Per 64-wide k-block an SM therefore pulls 32 KB from L2 instead of
+// the 48 KB a 128 x 256 tile of its own would need: the L2-to-SM feed is what bounds the main loop.
+//
+// Structure of a CTA (320 threads, one CTA per SM, pair tiles dealt round-robin over the pairs):
+//   warp 0      : TMA producer (both CTAs): its 128x64 A block and its 128x64 B block per stage (128-byte
+//                 swizzle), 6 stages of 32 KB.  The loads of both CTAs complete on the LEADER's (CTA 0 of the
+//                 pair) "full" barrier; each CTA waits on its own "empty" barrier.
+//   warp 1      : allocates all 512 TMEM columns (two 128x256 fp32 accumulators per CTA; both CTAs take part);
+//                 in the leader one lane issues tcgen05.mma.cta_group::2 (M256 N256 K16, bf16 -> fp32) and
+//                 commits to the "empty" / "accumulator full" barriers of BOTH CTAs (tcgen05.commit with a CTA
+//                 mask; the loads themselves are plain, no multicast).
+//   warps 2..9  : epilogue (both CTAs).  Warp w reads TMEM lanes 32*(w%4).. (tcgen05.ld 32x32b.x32) for half
+//                 of the tile's columns, so the epilogue of tile i overlaps the MMAs of tile i+1; when a warp
+//                 is done with an accumulator it arrives on the leader's "accumulator empty" barrier.
 // The B operand is either K-major ([N,K] row-major, the forward weights) or MN-major ([K,N]
 // row-major: the same weights read for the backward products, no transposed copy).
-// Every wait is bounded: when a limit is hit the kernel records a code in *status and drains.
-// No cluster launch and no multicast: each CTA fetches its own tiles.
+// Every wait is bounded: when a limit is hit the kernel records a code in *status and drains; both CTAs of a
+// pair then still meet at the cluster barrier before the tensor memory is released.
 #include "hyc_common.cuh"
 #include <cuda.h>
 
@@ -33,11 +42,21 @@ extern "C" __attribute__((visibility("default"))) void hyc_tc_debug_profile(void
 namespace hyc {
 namespace tc {
 
-constexpr int BM = 128, BN = 256, BK = 64;
-constexpr int STAGES = 4;
+constexpr int BM = 128, BN = 256, BK = 64;       // per CTA: 128 rows x 256 columns of accumulator
 constexpr int STAGE_A_BYTES = BM * BK * 2;
-constexpr int STAGE_B_BYTES = BN * BK * 2;
-constexpr int STAGE_BYTES = STAGE_A_BYTES + STAGE_B_BYTES;
+// PAIR: two CTAs share a 256 x 256 tile, each loads 128 columns of the B block (6 stages of 32 KB);
+// otherwise a CTA has a 128 x 256 tile of its own and loads the whole B block (4 stages of 48 KB)
+template <bool PAIR> struct Geo {
+  static constexpr int TILE_M = PAIR ? 2 * BM : BM;
+  static constexpr int B_COLS = PAIR ? BN / 2 : BN;
+  static constexpr int STAGE_B_BYTES = B_COLS * BK * 2;
+  static constexpr int STAGE_BYTES = STAGE_A_BYTES + STAGE_B_BYTES;
+  static constexpr int STAGES = PAIR ? 6 : 4;
+};
+constexpr int MAX_STAGES = 6;
+constexpr int PIPE_BYTES = 6 * (STAGE_A_BYTES + (BN / 2) * BK * 2);
+static_assert(PIPE_BYTES == Geo<true>::STAGES * Geo<true>::STAGE_BYTES && PIPE_BYTES == Geo<false>::STAGES * Geo<false>::STAGE_BYTES,
+              "both forms use the same amount of shared memory");
 constexpr int EPI_WARPS = 8;
 constexpr int THREADS = 64 + 32 * EPI_WARPS;
 constexpr int TMEM_COLS = 512;
@@ -47,7 +66,7 @@ constexpr int TMEM_COLS = 512;
 //   GRADDOWN per epilogue warp two [32 rows][32 columns] bf16 tiles (LoRA terms in, results out), then two bf16
 //            scale vectors of BN
 constexpr int EPI_SMEM_BYTES = 2 * BN * 16 * 4 + BN * 4;
-constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + EPI_SMEM_BYTES + 256;
+constexpr int SMEM_BYTES = 1024 + PIPE_BYTES + EPI_SMEM_BYTES + 256;
 constexpr uint32_t SPIN_LIMIT = 1u << 22;
 
 enum { EPI_STORE = 0, EPI_GATEUP = 1, EPI_GRADDOWN = 2 };
@@ -111,21 +130,60 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
   }
   return false;
 }
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(c0), "r"(c1) : "memory");
+// a tile into this CTA's shared memory; the bytes are counted on the barrier at shared::cluster address `bar`,
+// which in the pair form may belong to the other CTA of the pair (that is what .cta_group::2 permits)
+template <bool PAIR>
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1) {
+  if (PAIR)
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1) : "memory");
+  else
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// shared::cluster address of the same variable in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t map_to_cta(const void* p, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_u32(p)), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+// arrives on the barrier once the MMAs issued so far are done; pair form: on the barrier at this offset in BOTH CTAs
+template <bool PAIR>
 __device__ __forceinline__ void tc_commit(uint64_t* bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+  if (PAIR)
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(smem_u32(bar)), "h"((uint16_t)3) : "memory");
+  else
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
+template <bool PAIR>
 __device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+  if (PAIR)
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+  else
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
 }
 __device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&v)[32]) {
   asm volatile(
@@ -532,7 +590,7 @@ __device__ __forceinline__ void epi_store_block(const Params& p, int64_t row, bo
 }
 
 // ------------------------------------------------------------------ the kernel
-template <int EPI, int QBIT, bool B_MN>
+template <int EPI, int QBIT, bool B_MN, bool PAIR>
 __global__ void __launch_bounds__(THREADS, 1)
 mlp_gemm_kernel(const __grid_constant__ CUtensorMap mapA1, const __grid_constant__ CUtensorMap mapB1,
                 const __grid_constant__ CUtensorMap mapA2, const __grid_constant__ CUtensorMap mapB2,
@@ -542,34 +600,47 @@ mlp_gemm_kernel(const __grid_constant__ CUtensorMap mapA1, const __grid_constant
   // 1024-byte alignment for the 128-byte swizzle atoms
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint8_t* stage_base = smem;
-  __nv_bfloat16* epi_b = reinterpret_cast<__nv_bfloat16*>(smem + STAGES * STAGE_BYTES);
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES + EPI_SMEM_BYTES);
-  uint64_t* full = bars;                       // [STAGES]
-  uint64_t* empty = bars + STAGES;             // [STAGES]
-  uint64_t* tmem_full = bars + 2 * STAGES;     // [2]
-  uint64_t* tmem_empty = bars + 2 * STAGES + 2;  // [2]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+  constexpr int STAGES = Geo<PAIR>::STAGES, STAGE_BYTES = Geo<PAIR>::STAGE_BYTES, TILE_M = Geo<PAIR>::TILE_M;
+  constexpr int B_COLS = Geo<PAIR>::B_COLS;
+  __nv_bfloat16* epi_b = reinterpret_cast<__nv_bfloat16*>(smem + PIPE_BYTES);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + PIPE_BYTES + EPI_SMEM_BYTES);
+  uint64_t* full = bars;                           // [STAGES]
+  uint64_t* empty = bars + MAX_STAGES;             // [STAGES]
+  uint64_t* tmem_full = bars + 2 * MAX_STAGES;     // [2]
+  uint64_t* tmem_empty = bars + 2 * MAX_STAGES + 2;  // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * MAX_STAGES + 4);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int tiles_m = (p.M + BM - 1) / BM;
+  // rank 0: leader of the pair (issues the MMAs), 1: its peer; a CTA on its own is its own leader
+  const uint32_t rank = PAIR ? cluster_ctarank() : 0u;
+  const int pair = PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x, num_pairs = PAIR ? (int)(gridDim.x >> 1) : (int)gridDim.x;
+  const int tiles_m = (p.M + TILE_M - 1) / TILE_M;
   constexpr int TILE_N = (EPI == EPI_GATEUP) ? BN / 2 : BN;     // output columns per tile
   const int tiles_n = p.N / TILE_N;
   const int num_tiles = tiles_m * tiles_n;
   const int kb1 = p.K1 / BK, kb2 = (p.K1 + p.K2) / BK, kb_total = (p.K1 + p.K2 + p.K3) / BK;
 
   if (threadIdx.x == 0) {
+    // full / tmem_empty are used in the leader only: the loads of both CTAs and the epilogue warps of both CTAs
+    // arrive there; empty / tmem_full exist in both CTAs and are signalled together by the leader's commits
     for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
-    for (int b = 0; b < 2; ++b) { mbar_init(&tmem_full[b], 1); mbar_init(&tmem_empty[b], EPI_WARPS); }
+    for (int b = 0; b < 2; ++b) { mbar_init(&tmem_full[b], 1); mbar_init(&tmem_empty[b], (PAIR ? 2 : 1) * EPI_WARPS); }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    if (PAIR) {
+      asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    } else {
+      asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
   }
   tc_fence_before();
   __syncthreads();
+  if (PAIR) cluster_sync_all();      // the peer's barriers are initialised before anything is signalled there
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
@@ -580,8 +651,8 @@ mlp_gemm_kernel(const __grid_constant__ CUtensorMap mapA1, const __grid_constant
       uint32_t phase = 0;
       bool ok = true;
       int pit = 0;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++pit) {
-        const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * TILE_N;
+      for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, ++pit) {
+        const int m0 = (tile % tiles_m) * TILE_M + (int)rank * BM, n0 = (tile / tiles_m) * TILE_N;
         TC_STAMP(0, pit, 0);
         for (int kb = 0; kb < kb_total; ++kb) {
           if (!mbar_wait(&empty[stage], phase ^ 1u, abort_flag)) {
@@ -595,18 +666,25 @@ mlp_gemm_kernel(const __grid_constant__ CUtensorMap mapA1, const __grid_constant
           const int k0 = (seg == 0 ? kb : (seg == 1 ? kb - kb1 : kb - kb2)) * BK;
           const uint32_t sa = smem_u32(stage_base + stage * STAGE_BYTES);
           const uint32_t sb = sa + STAGE_A_BYTES;
-          mbar_expect_tx(&full[stage], STAGE_BYTES);
-          tma_load_2d(sa, ma, &full[stage], k0, m0);
+          // pair form: the leader's barrier counts both CTAs' bytes
+          const uint32_t fbar = PAIR ? map_to_cta(&full[stage], 0) : smem_u32(&full[stage]);
+          if (rank == 0) mbar_expect_tx(&full[stage], (PAIR ? 2 : 1) * STAGE_BYTES);
+          tma_load_2d<PAIR>(sa, ma, fbar, k0, m0);
           if (EPI == EPI_GATEUP) {
-            // 128 rows of Wg then 128 rows of Wu: one K-major 256-row B tile (two boxes of 128 rows)
-            tma_load_2d(sb, &mapB1, &full[stage], k0, n0);
-            tma_load_2d(sb + 16384, &mapB2, &full[stage], k0, n0);
+            // B columns 0..127 of the tile are 128 rows of Wg, columns 128..255 the same rows of Wu (pair form: the
+            // leader fetches the former, the peer the latter)
+            if (PAIR) {
+              tma_load_2d<PAIR>(sb, rank == 0 ? &mapB1 : &mapB2, fbar, k0, n0);
+            } else {
+              tma_load_2d<PAIR>(sb, &mapB1, fbar, k0, n0);
+              tma_load_2d<PAIR>(sb + 16384, &mapB2, fbar, k0, n0);
+            }
           } else if (B_MN) {
-            // [K, N] row-major: four boxes of 64 k-rows x 64 columns (8 KB each)
+            // [K, N] row-major: this CTA's columns as boxes of 64 k-rows x 64 columns (8 KB each)
 #pragma unroll
-            for (int j = 0; j < BN / 64; ++j) tma_load_2d(sb + j * 8192, mb, &full[stage], n0 + 64 * j, k0);
+            for (int j = 0; j < B_COLS / 64; ++j) tma_load_2d<PAIR>(sb + j * 8192, mb, fbar, n0 + (int)rank * B_COLS + 64 * j, k0);
           } else {
-            tma_load_2d(sb, mb, &full[stage], k0, n0);      // one box of 256 rows x 64 k (fewer, larger requests)
+            tma_load_2d<PAIR>(sb, mb, fbar, k0, n0 + (int)rank * B_COLS);      // one box of B_COLS rows x 64 k
           }
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
@@ -614,16 +692,16 @@ mlp_gemm_kernel(const __grid_constant__ CUtensorMap mapA1, const __grid_constant
       }
     }
   } else if (warp == 1) {
-    // ------------------------------------------------ MMA issuer
-    if (lane == 0) {
-      // instruction descriptor: fp32 accumulate, bf16 x bf16, M = 128, N = 256, B major as given
+    // ------------------------------------------------ MMA issuer (leader CTA only)
+    if (lane == 0 && rank == 0) {
+      // instruction descriptor: fp32 accumulate, bf16 x bf16, M = 256 (the pair) or 128, N = 256, B major as given
       const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((B_MN ? 1u : 0u) << 16) |
-                             ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+                             ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(TILE_M >> 4) << 24);
       int stage = 0;
       uint32_t phase = 0;
       int it = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++it) {
+      for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, ++it) {
         const int buf = it & 1;
         const uint32_t bphase = (uint32_t)(it >> 1) & 1u;
         TC_STAMP(1, it, 0);
@@ -650,12 +728,12 @@ mlp_gemm_kernel(const __grid_constant__ CUtensorMap mapA1, const __grid_constant
             // K-major: 16 elements = 32 bytes further along the swizzled row; MN-major: 16 k-rows of 128 bytes
             const uint64_t a = adesc + (uint64_t)(kk * 2);
             const uint64_t b = bdesc + (uint64_t)(B_MN ? kk * 128 : kk * 2);
-            tc_mma(d_tmem, a, b, idesc, (kb > 0 || kk > 0) ? 1u : 0u);
+            tc_mma<PAIR>(d_tmem, a, b, idesc, (kb > 0 || kk > 0) ? 1u : 0u);
           }
-          tc_commit(&empty[stage]);
+          tc_commit<PAIR>(&empty[stage]);
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
-        if (ok) tc_commit(&tmem_full[buf]);
+        if (ok) tc_commit<PAIR>(&tmem_full[buf]);
         TC_STAMP(1, it, 2);
       }
     }
@@ -675,8 +753,10 @@ mlp_gemm_kernel(const __grid_constant__ CUtensorMap mapA1, const __grid_constant
     float* sF1 = sF0 + (BN / 2) * 16;
     float* sV = sG2;                                              // ... and two float vectors at sV, sV + BN
     int it = 0;
-    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++it) {
-      const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * TILE_N;
+    const uint32_t tmem_empty_leader[2] = {PAIR ? map_to_cta(&tmem_empty[0], 0) : smem_u32(&tmem_empty[0]),
+                                           PAIR ? map_to_cta(&tmem_empty[1], 0) : smem_u32(&tmem_empty[1])};
+    for (int tile = pair; tile < num_tiles; tile += num_pairs, ++it) {
+      const int m0 = (tile % tiles_m) * TILE_M + (int)rank * BM, n0 = (tile / tiles_m) * TILE_N;
       const int buf = it & 1;
       const uint32_t bphase = (uint32_t)(it >> 1) & 1u;
       const int64_t row = (int64_t)m0 + quad * 32 + lane;
@@ -771,18 +851,21 @@ mlp_gemm_kernel(const __grid_constant__ CUtensorMap mapA1, const __grid_constant
       tc_fence_before();
       __syncwarp();
       if (et == 0) TC_STAMP(2, it, 3);
-      if (lane == 0) mbar_arrive(&tmem_empty[buf]);
+      if (lane == 0) mbar_arrive_cluster(tmem_empty_leader[buf]);
       epi_bar_sync();    // everyone is done with the staged tile before the next one overwrites it
       if (et == 0) TC_STAMP(2, it, 4);
     }
   }
 
   // ------------------------------------------------ teardown
+  // both CTAs are done with each other's barriers and tensor memory before either leaves
   tc_fence_before();
   __syncthreads();
+  if (PAIR) cluster_sync_all();
   if (warp == 1) {
     tc_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    if (PAIR) asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    else asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
   }
 }
 
@@ -817,10 +900,16 @@ static bool make_map(CUtensorMap* m, const void* ptr, int64_t rows, int64_t cols
              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// The grad_down kernel stays on single CTAs: measured 175 us single against 197 us as pairs at the Llama-2-7B
+// shapes (its epilogue runs mma.sync products on the same tensor pipe, and in a pair a stall of either SM holds
+// up both); the other three products gain 5-16 % as pairs.
+template <int EPI> struct UsePair { static constexpr bool value = EPI != EPI_GRADDOWN; };
+
 template <int EPI, int QBIT, bool B_MN>
 static int launch(const CUtensorMap& a1, const CUtensorMap& b1, const CUtensorMap& a2, const CUtensorMap& b2,
                   const CUtensorMap& a3, const CUtensorMap& b3, const Params& p, cudaStream_t st) {
-  auto kern = mlp_gemm_kernel<EPI, QBIT, B_MN>;
+  constexpr bool PAIR = UsePair<EPI>::value;
+  auto kern = mlp_gemm_kernel<EPI, QBIT, B_MN, PAIR>;
   // the attribute belongs to a (function, device) pair: set once per device (unknown device: every time)
   static bool attr[64] = {false};
   const int slot = current_device_slot();
@@ -832,16 +921,40 @@ static int launch(const CUtensorMap& a1, const CUtensorMap& b1, const CUtensorMa
     if (slot >= 0) attr[slot] = true;
   }
   constexpr int TILE_N = (EPI == EPI_GATEUP) ? BN / 2 : BN;
-  const int tiles = ((p.M + BM - 1) / BM) * (p.N / TILE_N);
-  const int grid = tiles < num_sms() ? tiles : num_sms();
-#ifdef HYC_TC_PROF
+  const int tiles = ((p.M + Geo<PAIR>::TILE_M - 1) / Geo<PAIR>::TILE_M) * (p.N / TILE_N);
+  cudaLaunchConfig_t cfg = {};
+  cfg.blockDim = dim3(THREADS);
+  cfg.dynamicSmemBytes = SMEM_BYTES;
+  cfg.stream = st;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeClusterDimension;
+  at[0].val.clusterDim.x = 2; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
+  cfg.attrs = at;
+  cfg.numAttrs = PAIR ? 1 : 0;
+  // the kernel is persistent: one CTA per SM, or one pair per two neighbouring SMs (as many as can be resident)
+  int units = num_sms();
+  if (PAIR) {
+    static int pairs_on[64] = {0};
+    int pairs = slot >= 0 ? pairs_on[slot] : 0;
+    if (pairs == 0) {
+      cfg.gridDim = dim3(2 * (unsigned)(num_sms() / 2));
+      int n = 0;
+      if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess || n < 1) { cudaGetLastError(); n = num_sms() / 2; }
+      pairs = n < num_sms() / 2 ? n : num_sms() / 2;
+      if (pairs < 1) pairs = 1;
+      if (slot >= 0) pairs_on[slot] = pairs;
+    }
+    units = pairs;
+  }
+  cfg.gridDim = dim3((unsigned)((PAIR ? 2 : 1) * (tiles < units ? tiles : units)));
   Params pp = p;
+#ifdef HYC_TC_PROF
   pp.prof = g_tc_prof;
-  kern<<<grid, THREADS, SMEM_BYTES, st>>>(a1, b1, a2, b2, a3, b3, pp);
-#else
-  kern<<<grid, THREADS, SMEM_BYTES, st>>>(a1, b1, a2, b2, a3, b3, p);
 #endif
-  HYC_CHECK_LAUNCH();
+  if (cudaLaunchKernelEx(&cfg, kern, a1, b1, a2, b2, a3, b3, pp) != cudaSuccess) {
+    hyc_set_last_cuda_error((int)cudaGetLastError());
+    return HYC_ERR_LAUNCH;
+  }
   return HYC_OK;
 }
 
@@ -877,16 +990,16 @@ extern "C" HYC_API int hyc_gemm_bf16_tcgen05(
   if ((bt0 != nullptr) != (xa0 != nullptr) || (bt1 != nullptr) != (xa1 != nullptr)) return HYC_ERR_NULL;
   CUtensorMap a1, b1, a2, b2, a3, b3;
   bool ok = make_map(&a1, A, M, K, BM);
-  ok = ok && (b_is_kn ? make_map(&b1, B, K, N, 64) : make_map(&b1, B, N, K, 256));
+  ok = ok && (b_is_kn ? make_map(&b1, B, K, N, 64) : make_map(&b1, B, N, K, 128));
   a2 = a1; b2 = b1;
   if (K2 > 0) {
     ok = ok && make_map(&a2, A2, M, K2, BM);
-    ok = ok && (b_is_kn ? make_map(&b2, B2, K2, N, 64) : make_map(&b2, B2, N, K2, 256));
+    ok = ok && (b_is_kn ? make_map(&b2, B2, K2, N, 64) : make_map(&b2, B2, N, K2, 128));
   }
   a3 = a1; b3 = b1;
   if (K3 > 0) {
     ok = ok && make_map(&a3, A3, M, K3, BM);
-    ok = ok && (b_is_kn ? make_map(&b3, B3, K3, N, 64) : make_map(&b3, B3, N, K3, 256));
+    ok = ok && (b_is_kn ? make_map(&b3, B3, K3, N, 64) : make_map(&b3, B3, N, K3, 128));
   }
   if (!ok) return HYC_ERR_UNSUPPORTED;
   Params p = {};
@@ -988,7 +1101,7 @@ extern "C" HYC_API int hyc_linear_lora_save_fwd_tcgen05(
   if (!aligned(x, 16) || !aligned(w, 16) || !aligned(y, 16) || !aligned(q_out, 16) || (xa && !aligned(xa, 16)) ||
       (main_or_null && !aligned(main_or_null, 16))) return HYC_ERR_ALIGN;
   CUtensorMap a1, b1;
-  if (!make_map(&a1, x, T, K, BM) || !make_map(&b1, w, N, K, 256)) return HYC_ERR_UNSUPPORTED;
+  if (!make_map(&a1, x, T, K, BM) || !make_map(&b1, w, N, K, 128)) return HYC_ERR_UNSUPPORTED;
   Params p = {};
   p.M = T; p.N = N; p.K1 = K; p.K2 = 0; p.K3 = 0; p.epi = EPI_STORE; p.q_bit = q_bit;
   p.l0 = make_term(xa, bt, bt_ld_col, bt_ld_r);
