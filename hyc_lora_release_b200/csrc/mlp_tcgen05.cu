@@ -32,7 +32,7 @@
 #include <cuda.h>
 
 #ifdef HYC_TC_PROF
-#define TC_STAMP(role, it, j) do { if (p.prof != nullptr && blockIdx.x == 0 && (it) < 16) p.prof[((role) * 16 + (it)) * 8 + (j)] = clock64(); } while (0)
+#define TC_STAMP(role, it, j) do { if (p.prof != nullptr && blockIdx.x < 2 && (it) < 16) p.prof[blockIdx.x * 384 + ((role) * 16 + (it)) * 8 + (j)] = clock64(); } while (0)
 static long long* g_tc_prof = nullptr;
 extern "C" __attribute__((visibility("default"))) void hyc_tc_debug_profile(void* buf) { g_tc_prof = (long long*)buf; }
 #else
@@ -903,7 +903,10 @@ static bool make_map(CUtensorMap* m, const void* ptr, int64_t rows, int64_t cols
 // The grad_down kernel stays on single CTAs: measured 175 us single against 197 us as pairs at the Llama-2-7B
 // shapes (its epilogue runs mma.sync products on the same tensor pipe, and in a pair a stall of either SM holds
 // up both); the other three products gain 5-16 % as pairs.
-template <int EPI> struct UsePair { static constexpr bool value = EPI != EPI_GRADDOWN; };
+#ifndef HYC_GD_PAIR
+#define HYC_GD_PAIR 0          // 1: build the grad_down kernel as pairs too (for measurements)
+#endif
+template <int EPI> struct UsePair { static constexpr bool value = EPI != EPI_GRADDOWN || HYC_GD_PAIR != 0; };
 
 template <int EPI, int QBIT, bool B_MN>
 static int launch(const CUtensorMap& a1, const CUtensorMap& b1, const CUtensorMap& a2, const CUtensorMap& b2,
