@@ -21,11 +21,12 @@ Weights use the nn.Linear layout ([out, in]); LoRA factors are ``lora_A.weight``
 """
 import math
 from dataclasses import dataclass, field
+from typing import Optional
 
 import torch
 
 from ._lib import require_cuda
-from .mlp import _status_tensor, gemm, linear_lora_save, lora_grad_a
+from .mlp import _status_tensor, gemm, linear_lora_save, lora_grad_a, padded_block
 from .operators import compress_function as cf
 from .operators.rmsnorm_kernels import rmsnorm_backward_packed, rmsnorm_forward, rmsnorm_forward_save
 from .operators.rope_kernels import rope_inplace
@@ -50,6 +51,13 @@ class AttnWeights:
     bv: torch.Tensor
     ao: torch.Tensor       # o lora_A.weight [r, heads*d]
     bo: torch.Tensor       # o lora_B.weight [H, r]
+    # projection biases ([out] bf16) or None.  A bias belongs to the MAIN branch (x W^T + b is what the reference
+    # saves, models/utils/compute_utils.py:21); a projection that has one runs as separate launches (GEMM, bias add,
+    # quantized save, LoRA add) instead of the one GEMM with the save in its epilogue.  Biases get no gradient.
+    bias_q: Optional[torch.Tensor] = None
+    bias_k: Optional[torch.Tensor] = None
+    bias_v: Optional[torch.Tensor] = None
+    bias_o: Optional[torch.Tensor] = None
 
     def padded(self):
         """LoRA factors zero-padded to a K of 64 so that a rank-16 product rides along a GEMM as one more K block
@@ -134,14 +142,16 @@ def _matmul_to_hidden(a4, b4):
     return out.view(B * M, n * d)
 
 
-def _project(xn2, w, a, b, q_bit, calib, sv, it, thd, status, B):
+def _project(xn2, w, a, b, q_bit, calib, sv, it, thd, status, B, bias=None):
     """One LoRA projection and the save of its main branch -> (y [T,N], q_main, scale, xa [T,r])."""
-    if not calib:
+    if not calib and bias is None:
         scale = sv['scale']
         y, qm, xa = linear_lora_save(xn2, w, a, b, scale, q_bit, status=status)
         return y, qm, scale, xa
-    # calibration iterations: the scale depends on the finished main branch
+    # calibration iterations (the scale depends on the finished main branch) and projections with a bias
     main = gemm(xn2, w, status=status)
+    if bias is not None:
+        main = main + bias.to(main.dtype)
     qm, scale = cf.compression_pack_quant_base(main.view(B, main.shape[0] // B, -1), q_bit, 'per-channel', it, thd, sv)
     xa = (xn2 @ a.t()).contiguous()
     y = main + xa @ b.t()
@@ -170,9 +180,9 @@ def attention_forward(x, w: AttnWeights, state: AttnState, cos, sin, attention_m
         x_norm, rstd, x_o, x_q, xn_q = rmsnorm_forward_save(x, w.norm_w, eps, q, x_scale, x_idx, xn_scale)
     xn2 = x_norm.reshape(T, H)
 
-    qy, q_q, q_scale, q_xa = _project(xn2, w.wq, w.aq, w.bq, q, calib, sv['q'], it, thd, st, B)
-    ky, k_q, k_scale, k_xa = _project(xn2, w.wk, w.ak, w.bk, q, calib, sv['k'], it, thd, st, B)
-    vy, v_q, v_scale, v_xa = _project(xn2, w.wv, w.av, w.bv, q, calib, sv['v'], it, thd, st, B)
+    qy, q_q, q_scale, q_xa = _project(xn2, w.wq, w.aq, w.bq, q, calib, sv['q'], it, thd, st, B, w.bias_q)
+    ky, k_q, k_scale, k_xa = _project(xn2, w.wk, w.ak, w.bk, q, calib, sv['k'], it, thd, st, B, w.bias_k)
+    vy, v_q, v_scale, v_xa = _project(xn2, w.wv, w.av, w.bv, q, calib, sv['v'], it, thd, st, B, w.bias_v)
     del x_norm, xn2
 
     rope_inplace(qy.view(B, M, num_heads, head_dim), cos, sin)
@@ -214,6 +224,8 @@ def attention_forward(x, w: AttnWeights, state: AttnState, cos, sin, attention_m
     pad = w.padded()
     o_xa64 = o2 @ pad["ao_cols"]
     x_medium = gemm(o2, w.wo, a2=o_xa64, b2=pad["bo_cols"], residual=x.reshape(T, H).to(BF16).contiguous(), status=st)
+    if w.bias_o is not None:
+        x_medium += w.bias_o.to(BF16)
     o_q, o_scale = cf.compression_pack_quant_base(o2.view(B, M, -1), q, 'per-channel', it, thd, sv['o'])
 
     if calib:
@@ -307,10 +319,10 @@ def attention_backward(grad_medium, saved, w: AttnWeights, status=None, on_lora_
     rope_inplace(grad_k.view(B, M, nkv, d), cos, sin, backward=True)
 
     # ---- q/k/v projections: LoRA gradients, then grad_x_norm as one GEMM over the three K segments
-    gmq = torch.zeros((T, 64), dtype=BF16, device=dev)       # g_q @ Bq | g_k @ Bk | g_v @ Bv side by side
-    gmq[:, :r] = grad_q @ w.bq
-    gmq[:, r:2 * r] = grad_k @ w.bk
-    gmq[:, 2 * r:3 * r] = grad_v @ w.bv
+    gmq = padded_block(w, "_gmq", T, dev)                    # g_q @ Bq | g_k @ Bk | g_v @ Bv side by side
+    torch.mm(grad_q, w.bq, out=gmq[:, :r])
+    torch.mm(grad_k, w.bk, out=gmq[:, r:2 * r])
+    torch.mm(grad_v, w.bv, out=gmq[:, 2 * r:3 * r])
     ga = lora_grad_a(saved['xn_q'].reshape(T, -1), _vec(saved['xn_scale']), gmq, 48, q)
     grad_aq, grad_ak, grad_av = ga[:r], ga[r:2 * r], ga[2 * r:3 * r]
     grad_bq = grad_q.t() @ saved['q_xa']

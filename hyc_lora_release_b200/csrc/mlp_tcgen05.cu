@@ -28,6 +28,8 @@
 // row-major: the same weights read for the backward products, no transposed copy).
 // Every wait is bounded: when a limit is hit the kernel records a code in *status and drains; both CTAs of a
 // pair then still meet at the cluster barrier before the tensor memory is released.
+// The same kernel also exists without the pairing (template argument PAIR = false: a 128 x 256 tile per CTA,
+// 4 stages of 48 KB, cta_group::1 everywhere, no cluster); the grad_down product uses that form (see UsePair).
 #include "hyc_common.cuh"
 #include <cuda.h>
 

@@ -9,7 +9,8 @@ attention mask and the head geometry.  Differences, all deliberate:
 
   * frozen weights are plain bf16 ``[out, in]`` matrices; a 4-bit ``quant_state`` is refused (the NF4
     de-quantizer of the reference is a third-party library that is not part of this build);
-  * projection biases are refused (the Llama and Mistral layers the reference drives have none);
+  * projection biases of q/k/v/o/down are added to the main branch (separate launches for such a projection);
+    gate/up biases are refused (the reference's fused layer drops them);
   * ``hyclora_config.softmax_map_mode`` (optional, default ``"prune"`` = the reference's threshold prune) may
     be ``"topk"`` for the per-row top-k + 4-bit-group form of the saved probability map.
 
@@ -86,9 +87,22 @@ def _frozen(base, name):
     if getattr(w, "quant_state", None) is not None or w.dtype != BF16:
         raise NotImplementedError("%s: frozen weights must be plain bf16 [out, in] matrices (4-bit quant_state "
                                   "weights are not supported)" % name)
-    if getattr(base, "bias", None) is not None:
-        raise NotImplementedError("%s: projection biases are not supported" % name)
     return w
+
+
+def _bias(base, name):
+    """Bias of a frozen projection or None.  The reference's fused layer never adds the gate and up biases it is
+    handed (models/llama/fused_llama_layer_intra_inter_full_fuse.py:218-226 inlines those two projections without
+    them), so a model that has them would silently compute something else there; refused here instead."""
+    b = getattr(base, "bias", None)
+    if b is None:
+        return None
+    if name in ("gate_proj", "up_proj"):
+        raise NotImplementedError("%s: a bias on the gate / up projection is not supported (the reference's fused "
+                                  "layer drops it)" % name)
+    if b.dtype != BF16:
+        raise NotImplementedError("%s: the projection bias must be bf16 (got %s)" % (name, b.dtype))
+    return b
 
 
 def _adapter(mod, name, rank_dim):
@@ -182,15 +196,18 @@ class FusedLlamaLayerIntraInterFullFuse(torch.nn.Module):
     def _bind(self, norm_w1, norm_w2, mods):
         """Weight records for the two halves, rebuilt only when a tensor was replaced."""
         tensors = [norm_w1, norm_w2]
+        biases = {}
         for name in ("q", "k", "v", "o", "gate", "up", "down"):
             base, la, lb = mods[name]
             tensors += [_frozen(base, name + "_proj"), _adapter(la, name + "_proj lora_A", 0),
                         _adapter(lb, name + "_proj lora_B", 1)]
-        key = tuple(id(t) for t in tensors)
+            biases[name] = _bias(base, name + "_proj")
+        key = tuple(id(t) for t in tensors) + tuple(id(b) for b in biases.values())
         if self._weights is None or self._weights[0] != key:
             (n1, n2, wq, aq, bq, wk, ak, bk, wv, av, bv, wo, ao, bo, wg, ag, bg, wu, au, bu, wd, ad, bd) = tensors
-            aw = AttnWeights(norm_w=n1, wq=wq, wk=wk, wv=wv, wo=wo, aq=aq, bq=bq, ak=ak, bk=bk, av=av, bv=bv, ao=ao, bo=bo)
-            mw = MLPWeights(norm_w=n2, wg=wg, wu=wu, wd=wd, ag=ag, bg=bg, au=au, bu=bu, ad=ad, bd=bd)
+            aw = AttnWeights(norm_w=n1, wq=wq, wk=wk, wv=wv, wo=wo, aq=aq, bq=bq, ak=ak, bk=bk, av=av, bv=bv, ao=ao, bo=bo,
+                             bias_q=biases["q"], bias_k=biases["k"], bias_v=biases["v"], bias_o=biases["o"])
+            mw = MLPWeights(norm_w=n2, wg=wg, wu=wu, wd=wd, ag=ag, bg=bg, au=au, bu=bu, ad=ad, bd=bd, bias_d=biases["down"])
             lora = (aq, bq, ak, bk, av, bv, ao, bo, ag, bg, au, bu, ad, bd)
             self._weights = (key, aw, mw, lora)
         return self._weights[1:]

@@ -40,6 +40,17 @@ def check_status(status, what):
         raise HycError("%s: %s" % (what, _KERNEL_STATUS.get(v, "status %d" % v)))
 
 
+def padded_block(owner, name, T, dev):
+    """A [T, 64] bf16 block of zeros kept on ``owner`` between steps (the rank-16 products of a backward pass are
+    written side by side into its first columns and ride a GEMM as one K block of 64; the other columns are never
+    written and stay zero, so the block is filled once, not once per step)."""
+    buf = getattr(owner, name, None)
+    if buf is None or buf.shape[0] != T or buf.device != dev:
+        buf = torch.zeros((T, 64), dtype=BF16, device=dev)
+        setattr(owner, name, buf)
+    return buf
+
+
 def _lora(xa, bt, ld_col, ld_r):
     if xa is None:
         return [None, None, 0, 0]
@@ -114,6 +125,7 @@ class MLPWeights:
     bu: torch.Tensor
     ad: torch.Tensor       # down lora_A.weight [r, I]
     bd: torch.Tensor       # down lora_B.weight [H, r]
+    bias_d: Optional[torch.Tensor] = None    # bias of the down projection ([H] bf16) or None; no gradient
 
     def padded(self):
         """LoRA factors zero-padded to a K of 64 so that a rank-16 product can ride along a GEMM as one more
@@ -209,6 +221,8 @@ def mlp_forward(x_medium, w: MLPWeights, state: MLPState, eps=1e-5, status=None)
     down_xa = down_xa64[:, :16]
     # down = hadamard @ Wd^T + down_xa @ Bd^T (one more K block) + residual
     x_out = gemm(had2, w.wd, a2=down_xa64, b2=pad["bd_cols"], residual=x_medium.reshape(T, H).contiguous(), status=st)
+    if w.bias_d is not None:
+        x_out += w.bias_d.to(BF16)
 
     if calib:
         it = state.iteration
@@ -251,9 +265,9 @@ def mlp_backward(grad_out, saved, w: MLPWeights, status=None, on_lora_grads=None
         ptr(had), ptr(gg), ptr(gu), q, ptr(st), stream_of(grad_out)), "hyc_mlp_graddown_bwd_tcgen05")
     grad_ad = gdm.t() @ had                        # [r, I]
 
-    gm64 = torch.zeros((T, 64), dtype=BF16, device=dev)
-    gm64[:, :16] = gg @ w.bg                       # [T, r] each, side by side in a zero-padded K block
-    gm64[:, 16:32] = gu @ w.bu
+    gm64 = padded_block(w, "_gm64", T, dev)
+    torch.mm(gg, w.bg, out=gm64[:, :16])           # [T, r] each, side by side in a zero-padded K block
+    torch.mm(gu, w.bu, out=gm64[:, 16:32])
     gm_gate, gm_up = gm64[:, :16], gm64[:, 16:32]
     # LoRA-A gradients of gate and up in one pass over the packed x_norm (de-quantized in shared memory)
     ga = lora_grad_a(saved['xn_q'].reshape(T, -1), saved['xn_scale'].to(BF16).reshape(-1).contiguous(), gm64, 32, q)

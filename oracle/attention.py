@@ -71,8 +71,10 @@ def _repeat_kv_backward(g, n_rep):
 
 def ref_attention_block_forward(x, norm_w, cos, sin, wq, wk, wv, wo, aq, bq, ak, bk, av, bv, ao, bo, mask,
                                 num_heads, head_dim, num_kv_heads, q_bit, layernorm_ratio, softmax_ratio,
-                                map_mode="prune", map_q_bit=4, static=None):
-    """:99-201.  w*: [in, out] bf16; a*: [in, r]; b*: [r, out].  -> (x_medium, saved)."""
+                                map_mode="prune", map_q_bit=4, static=None, biases=None):
+    """:99-201.  w*: [in, out] bf16; a*: [in, r]; b*: [r, out]; ``biases``: optional dict with any of "q", "k", "v",
+    "o" -> [out] bias of that projection.  -> (x_medium, saved)."""
+    biases = biases or {}
     x = x.to(BF16)
     x_norm_1, rstd = ref_rmsnorm_forward(x, norm_w, 1e-5)
     if static is None:
@@ -81,9 +83,9 @@ def ref_attention_block_forward(x, norm_w, cos, sin, wq, wk, wv, wo, aq, bq, ak,
         x_idx, x_scale = static["x_idx"], static["x_scale"]
     x_o, x_q = ref_compress_channel_base(x, x_scale, x_idx, q_bit)
 
-    q, q_main, q_xa = ref_lora_forward(wq, aq, bq, x_norm_1)
-    k, k_main, k_xa = ref_lora_forward(wk, ak, bk, x_norm_1)
-    v, v_main, v_xa = ref_lora_forward(wv, av, bv, x_norm_1)
+    q, q_main, q_xa = ref_lora_forward(wq, aq, bq, x_norm_1, biases.get("q"))
+    k, k_main, k_xa = ref_lora_forward(wk, ak, bk, x_norm_1, biases.get("k"))
+    v, v_main, v_xa = ref_lora_forward(wv, av, bv, x_norm_1, biases.get("v"))
     if static is None:
         xn_scale = ref_scale_per_channel(x_norm_1, q_bit)
         q_scale = ref_scale_per_channel(q_main, q_bit)
@@ -117,7 +119,7 @@ def ref_attention_block_forward(x, norm_w, cos, sin, wq, wk, wv, wo, aq, bq, ak,
         a_saved = ("topk",) + tuple(topk_compress(a, softmax_ratio, map_q_bit))
     o = a @ _repeat_kv(vh, n_rep)
     o = _to_hidden(o)
-    o_final, _, o_xa = ref_lora_forward(wo, ao, bo, o)
+    o_final, _, o_xa = ref_lora_forward(wo, ao, bo, o, biases.get("o"))
     o_scale = ref_scale_per_channel(o, q_bit) if static is None else static["o_scale"]
     o_q = ref_compress(o, o_scale, q_bit)
     x_medium = x + o_final
@@ -187,14 +189,16 @@ def ref_attention_block_backward(grad_medium, saved, norm_w, cos, sin, wq, wk, w
 def ref_layer_forward(x, p, cos, sin, mask, num_heads, head_dim, num_kv_heads, q_bit, layernorm_ratio,
                       softmax_ratio, map_mode="prune", map_q_bit=4, static=None):
     """The whole decoder layer (:99-252): attention half then MLP half.  ``p`` is a dict with norm_w1, norm_w2,
-    w{q,k,v,o,gate,up,down} [in, out], a* [in, r], b* [r, out].  -> (y, (saved_attention, saved_mlp))."""
+    w{q,k,v,o,gate,up,down} [in, out], a* [in, r], b* [r, out] and optionally bias_{q,k,v,o,down} [out].
+    -> (y, (saved_attention, saved_mlp))."""
     xm, sa = ref_attention_block_forward(
         x, p["norm_w1"], cos, sin, p["wq"], p["wk"], p["wv"], p["wo"], p["aq"], p["bq"], p["ak"], p["bk"],
         p["av"], p["bv"], p["ao"], p["bo"], mask, num_heads, head_dim, num_kv_heads, q_bit, layernorm_ratio,
-        softmax_ratio, map_mode, map_q_bit, None if static is None else static["attention"])
+        softmax_ratio, map_mode, map_q_bit, None if static is None else static["attention"],
+        biases={n: p["bias_" + n] for n in ("q", "k", "v", "o") if p.get("bias_" + n) is not None})
     y, sm = ref_mlp_block_forward(xm, p["norm_w2"], p["wgate"], p["wup"], p["wdown"], p["agate"], p["bgate"],
                                   p["aup"], p["bup"], p["adown"], p["bdown"], q_bit, layernorm_ratio,
-                                  None if static is None else static["mlp"])
+                                  None if static is None else static["mlp"], bias_d=p.get("bias_down"))
     return y, (sa, sm)
 
 

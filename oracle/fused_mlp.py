@@ -54,12 +54,15 @@ def ref_fused_silu_backward(xa1, b1, q1, s1, xa2, b2, q2, s2, grad_o, q_bit: int
     return o, g_gate, g_up
 
 
-def ref_lora_forward(w, a, b, x):
+def ref_lora_forward(w, a, b, x, bias=None):
     """``lora_forward`` with plain bf16 weights (models/utils/compute_utils.py:
     18-25; NF4 de-quantization is the identity here).  w [in,out] bf16 (already
-    transposed), a [in,r], b [r,out].  -> (y, x_main, x_lora_a)."""
+    transposed), a [in,r], b [r,out], bias [out] or None (part of the main
+    branch, :21).  -> (y, x_main, x_lora_a)."""
     x = x.to(BF16)
     x_main = x @ w
+    if bias is not None:
+        x_main = x_main + bias.to(BF16)
     xa = x @ a
     return x_main + xa @ b, x_main, xa
 
@@ -109,7 +112,7 @@ def ref_softmax_backward(y, g):
 
 
 def ref_mlp_block_forward(x_medium, norm_w, wg, wu, wd, ag, bg, au, bu, ad, bd,
-                          q_bit: int, outlier_ratio: float, static=None):
+                          q_bit: int, outlier_ratio: float, static=None, bias_d=None):
     """MLP half of the fused decoder layer, forward
     (models/llama/fused_llama_layer_intra_inter_full_fuse.py:203-252), with
     plain bf16 weights.  wg, wu: [H,I]; wd: [I,H] (already transposed as the
@@ -138,7 +141,7 @@ def ref_mlp_block_forward(x_medium, norm_w, wg, wu, wd, ag, bg, au, bu, ad, bd,
     gate_q, up_q, had = ref_fused_silu_forward(gate_xa, bg, gate_main, gate_scale,
                                                up_xa, bu, up_main, up_scale, q_bit)
     xn_q = ref_compress(x_norm_2, xn_scale, q_bit)
-    down, _, down_xa = ref_lora_forward(wd, ad, bd, had)
+    down, _, down_xa = ref_lora_forward(wd, ad, bd, had, bias_d)
     x_out = x_medium + down
     saved = dict(rstd=rstd, xm_o=xm_o, xm_q=xm_q, xm_scale=xm_scale, xm_idx=xm_idx,
                  xn_q=xn_q, xn_scale=xn_scale, gate_q=gate_q, gate_scale=gate_scale,

@@ -189,16 +189,19 @@ class _Holder(torch.nn.Module):
             self.default.weight.copy_(w)
 
 
-def _base(w):
-    lin = torch.nn.Linear(w.shape[1], w.shape[0], bias=False, device=DEV, dtype=BF16)
+def _base(w, bias=None):
+    lin = torch.nn.Linear(w.shape[1], w.shape[0], bias=bias is not None, device=DEV, dtype=BF16)
     with torch.no_grad():
         lin.weight.copy_(w)
+        if bias is not None:
+            lin.bias.copy_(bias)
+            lin.bias.requires_grad_(False)
     lin.weight.requires_grad_(False)
     return lin
 
 
-@pytest.mark.parametrize("heads,kv,map_mode", [(4, 4, "topk"), (4, 2, "prune")])
-def test_layer_module_through_autograd(heads, kv, map_mode):
+@pytest.mark.parametrize("heads,kv,map_mode,with_bias", [(4, 4, "topk", False), (4, 2, "prune", False), (4, 2, "prune", True)])
+def test_layer_module_through_autograd(heads, kv, map_mode, with_bias):
     from hyc_lora_release_b200.layer import FusedLlamaLayerIntraInterFullFuse, FusedMistralLayerIntraInterFullFuse
     assert FusedMistralLayerIntraInterFullFuse is FusedLlamaLayerIntraInterFullFuse
     g = torch.Generator().manual_seed(21 + kv)
@@ -207,7 +210,12 @@ def test_layer_module_through_autograd(heads, kv, map_mode):
     x, p, cos, sin, mask = layer_problem(g, B, M, H, heads, d, kv, I)
     mods = {}
     for n in ("q", "k", "v", "o", "gate", "up", "down"):
-        mods[n] = (_base(p["w" + n].t().to(DEV)), _Holder(p["a" + n].t().to(DEV)), _Holder(p["b" + n].t().to(DEV)))
+        bias = None
+        if with_bias and n not in ("gate", "up"):
+            # the bias of a projection is part of its main branch (models/utils/compute_utils.py:21)
+            bias = (0.3 * torch.randn(p["w" + n].shape[1], generator=g)).to(BF16)
+            p["bias_" + n] = bias
+        mods[n] = (_base(p["w" + n].t().to(DEV), bias), _Holder(p["a" + n].t().to(DEV)), _Holder(p["b" + n].t().to(DEV)))
     layer = FusedLlamaLayerIntraInterFullFuse()
     cfg = types.SimpleNamespace(use_hyclora=True, iteration_threshold=5, softmax_outlier_ratio=0.05,
                                 layernorm_outlier_ratio=0.01, q_bit=q, softmax_map_mode=map_mode)
@@ -258,7 +266,11 @@ def test_layer_module_through_autograd(heads, kv, map_mode):
         assert ga is not None and gb is not None, n
         assert close(ga, ref_g["grad_a" + n].t()), n
         assert close(gb, ref_g["grad_b" + n].t()), n
-    # a 4-bit quant_state or a bias is refused, not silently ignored
+    # a bias on the gate projection (which the reference's fused layer would drop) is refused, not silently ignored
+    with pytest.raises(NotImplementedError):
+        layer._bind(n1, n2, {**mods, "gate": (_base(p["wgate"].t().to(DEV), torch.zeros(I, dtype=BF16)), mods["gate"][1],
+                                              mods["gate"][2])})
+    # so is a 4-bit quant_state
     bad = _base(p["wq"].t().to(DEV))
     bad.weight.quant_state = object()
     with pytest.raises(NotImplementedError):
