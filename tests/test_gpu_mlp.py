@@ -47,6 +47,30 @@ def test_plain_gemm(mlp, M, N, K, b_is_kn):
     assert close(d, ref, rel=4e-3)
 
 
+@pytest.mark.parametrize("M,N,K", [(1, 256, 64), (129, 256, 128), (257, 512, 192), (383, 256, 64), (2304, 4096, 512),
+                                   (2500, 2048, 320)])
+@pytest.mark.parametrize("b_is_kn", [False, True])
+def test_gemm_ragged_rows_and_several_rounds_of_pairs(mlp, M, N, K, b_is_kn):
+    """Row counts that leave the second CTA of a pair with one valid row, a few, or none (the products run as pairs
+    of CTAs on 256-row tiles), and tile counts beyond one round of pairs, with a LoRA block and a residual."""
+    g = torch.Generator().manual_seed(3 * M + N + K)
+    a = _randn(g, M, K).to(DEV)
+    b = (_randn(g, K, N, scale=0.05) if b_is_kn else _randn(g, N, K, scale=0.05)).to(DEV)
+    a2 = _randn(g, M, 64).to(DEV)
+    b2 = (_randn(g, 64, N, scale=0.05) if b_is_kn else _randn(g, N, 64, scale=0.05)).to(DEV)
+    res = _randn(g, M, N).to(DEV)
+    st = torch.zeros(1, dtype=torch.int32, device=DEV)
+    from hyc_lora_release_b200._lib import lib, ptr, check, stream_of
+    big = torch.full((M + 256, N), 7.0, dtype=BF16, device=DEV)       # the rows behind the result must stay untouched
+    check(lib.hyc_gemm_bf16_tcgen05(ptr(a), ptr(b), M, N, K, 1 if b_is_kn else 0, ptr(a2), ptr(b2), 64, None, None, 0,
+                                    None, None, 0, 0, None, None, 0, 0, ptr(res), ptr(big), ptr(st), stream_of(a)), "gemm")
+    mlp.check_status(st, "gemm")
+    op = (lambda t: t.float()) if b_is_kn else (lambda t: t.float().t())
+    ref = a.float() @ op(b) + a2.float() @ op(b2) + res.float()
+    assert close(big[:M], ref, rel=6e-3)
+    assert bool((big[M:] == 7.0).all())
+
+
 def test_gemm_two_segments_lora_residual(mlp):
     g = torch.Generator().manual_seed(5)
     M, N, K, K2, R = 256, 256, 256, 384, 16
