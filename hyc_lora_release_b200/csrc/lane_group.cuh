@@ -152,6 +152,25 @@ __device__ __forceinline__ void lane_run_to_shared(const __nv_bfloat16* __restri
     *reinterpret_cast<uint4*>(dst + park_chunk(c0 + 1, owner)) = make_uint4(t[4], t[5], t[6], t[7]);
   }
 }
+// global -> shared without passing through registers (cp.async): the same placement as lane_run_to_shared.  The
+// copy is in flight while the warp does other work; lane_async_wait() + __syncwarp() before the slots are read.
+__device__ __forceinline__ void lane_run_to_shared_async(const __nv_bfloat16* __restrict__ run, int n_pieces, uint32_t* slots, int lane) {
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int p = 32 * i + lane;
+    const int owner = p >> 2, c0 = 2 * (p & 3);
+    uint32_t* dst = slots + owner * 32;
+    const bool in = p < n_pieces;
+    const __nv_bfloat16* src = run + 16 * (in ? p : 0);
+    const int nbytes = in ? 16 : 0;                 // 0: the 16 bytes are filled with zeros
+    const uint32_t d0 = (uint32_t)__cvta_generic_to_shared(dst + park_chunk(c0, owner));
+    const uint32_t d1 = (uint32_t)__cvta_generic_to_shared(dst + park_chunk(c0 + 1, owner));
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d0), "l"(src), "r"(nbytes) : "memory");
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d1), "l"(src + 8), "r"(nbytes) : "memory");
+  }
+  asm volatile("cp.async.commit_group;" ::: "memory");
+}
+__device__ __forceinline__ void lane_async_wait() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
 // shared -> global
 __device__ __forceinline__ void lane_shared_to_run(const uint32_t* slots, __nv_bfloat16* __restrict__ run, int n_pieces, int lane) {
 #pragma unroll
@@ -183,13 +202,13 @@ __device__ __forceinline__ void lane_slot_store(uint32_t* sx, int lane, const ui
 // kernel ends when the busiest warp ends: with R resident warps on the GPU the efficiency is
 // items / (ceil(items / R) * R).  The block width (5..8 warps) is picked to make that largest.
 template <typename K>
-inline void lane_launch_shape(K kern, int64_t rows, int rows_per_warp, int& grid, int& threads) {
+inline void lane_launch_shape(K kern, int64_t rows, int rows_per_warp, int& grid, int& threads, int smem_per_warp = 0) {
   const int64_t items = (rows + rows_per_warp - 1) / rows_per_warp;
   double best = -1.0;
   grid = 1; threads = 256;
   for (int w = 8; w >= 5; --w) {
     int per_sm = 0;
-    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, 32 * w, 0) != cudaSuccess || per_sm < 1) per_sm = 1;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, 32 * w, (size_t)w * smem_per_warp) != cudaSuccess || per_sm < 1) per_sm = 1;
     const int64_t resident = (int64_t)num_sms() * per_sm * w;
     int64_t blocks = (items + w - 1) / w;
     if (blocks > (int64_t)num_sms() * per_sm) blocks = (int64_t)num_sms() * per_sm;

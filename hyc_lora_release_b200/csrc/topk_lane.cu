@@ -269,7 +269,7 @@ topk_lane_compress_kernel(const __nv_bfloat16* __restrict__ a, int64_t rows, int
 // `grad`:  out = (g - sum_row(bf16(y * g))) * y  (operators/softmax_kernels.py:7-38: the product is a bf16
 // operation, the row sum and the rest fp32).  The restored map never goes to HBM.
 template <int QBIT, int LPR, bool SMBWD>
-__global__ void __launch_bounds__(256, HYC_LANE_MINB)
+__global__ void __launch_bounds__(256, SMBWD ? 3 : HYC_LANE_MINB)      // SMBWD: two tiles per warp, 3 blocks fill the SM
 topk_lane_restore_kernel(const __nv_bfloat16* __restrict__ val, const uint16_t* __restrict__ colv, int k, float inv_k,
                          const uint8_t* __restrict__ q, const __nv_bfloat16* __restrict__ scale,
                          const int8_t* __restrict__ zp, int64_t rows, const __nv_bfloat16* __restrict__ grad,
@@ -280,9 +280,12 @@ topk_lane_restore_kernel(const __nv_bfloat16* __restrict__ val, const uint16_t* 
   constexpr int PRE = 4;                 // list entries per lane fetched before the de-quantization
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
   const int lr = lane & (LPR - 1), rw = lane / LPR;
-  __shared__ __align__(16) uint32_t s_x[8][32 * 32];          // the warp's rows, 128 bytes per lane
-  uint32_t* sx = s_x[warp] + lane * 32;
-  uint16_t* sw16 = reinterpret_cast<uint16_t*>(s_x[warp]);
+  // dynamic shared memory: per warp its rows (128 bytes per lane) and, SMBWD, a second tile for the gradient rows
+  extern __shared__ __align__(16) uint32_t s_dyn[];
+  uint32_t* s_xw = s_dyn + warp * 1024;
+  uint32_t* s_gw = s_dyn + (nwarps + warp) * 1024;
+  uint32_t* sx = s_xw + lane * 32;
+  uint16_t* sw16 = reinterpret_cast<uint16_t*>(s_xw);
   const int64_t items = (rows + RPW - 1) / RPW;
   for (int64_t item = (int64_t)blockIdx.x * nwarps + warp; item < items; item += (int64_t)gridDim.x * nwarps) {
     const int64_t row0 = item * RPW, row = row0 + rw;
@@ -290,6 +293,8 @@ topk_lane_restore_kernel(const __nv_bfloat16* __restrict__ val, const uint16_t* 
     const int64_t left = rows - row0;
     const int n_rows = (int)(left < RPW ? left : RPW);
     const int n_ent = n_rows * k;
+    // the gradient rows start their way into shared memory now and arrive while the map is being rebuilt
+    if (SMBWD) lane_run_to_shared_async(grad + row0 * S, n_rows * (S / 16), s_gw, lane);
     const __nv_bfloat16* vrun = val + row0 * k;
     const uint16_t* crun = colv + row0 * k;
     uint16_t pc[PRE], pv[PRE];
@@ -335,10 +340,9 @@ topk_lane_restore_kernel(const __nv_bfloat16* __restrict__ val, const uint16_t* 
     if (SMBWD) {
       uint32_t yv[32], gv[32];
       lane_slot_load(sx, lane, yv);                       // the lane's own group of the restored row
+      lane_async_wait();
       __syncwarp();
-      lane_run_to_shared(grad + row0 * S, n_rows * (S / 16), s_x[warp], lane);
-      __syncwarp();
-      lane_slot_load(sx, lane, gv);
+      lane_slot_load(s_gw + lane * 32, lane, gv);
       float acc = 0.f;
 #pragma unroll
       for (int j = 0; j < 32; ++j) {
@@ -361,7 +365,7 @@ topk_lane_restore_kernel(const __nv_bfloat16* __restrict__ val, const uint16_t* 
       __syncwarp();
     }
     // the warp's rows leave as four fully coalesced 1 KB stores
-    lane_shared_to_run(s_x[warp], ao + row0 * S, n_rows * (S / 16), lane);
+    lane_shared_to_run(s_xw, ao + row0 * S, n_rows * (S / 16), lane);
     __syncwarp();
   }
 }
@@ -369,26 +373,28 @@ topk_lane_restore_kernel(const __nv_bfloat16* __restrict__ val, const uint16_t* 
 // ---------------------------------------------------------------- softmax backward on dense maps
 // out = (g - sum_row(bf16(y * g))) * y for rows of 64 * LPR columns, same layout and staging as above
 template <int LPR>
-__global__ void __launch_bounds__(256, HYC_LANE_MINB)
+__global__ void __launch_bounds__(256, 3)
 softmax_bwd_lane_kernel(const __nv_bfloat16* __restrict__ y, const __nv_bfloat16* __restrict__ g, int64_t rows,
                         float oscale, __nv_bfloat16* __restrict__ out) {
   constexpr int RPW = 32 / LPR;
   constexpr int S = 64 * LPR;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
-  __shared__ __align__(16) uint32_t s_x[8][32 * 32];
-  uint32_t* sx = s_x[warp] + lane * 32;
+  // dynamic shared memory: two 4 KB tiles per warp, so that both operands are on their way at once (cp.async)
+  extern __shared__ __align__(16) uint32_t s_dyn[];
+  uint32_t* s_yw = s_dyn + warp * 1024;
+  uint32_t* s_gw = s_dyn + (nwarps + warp) * 1024;
+  uint32_t* sx = s_yw + lane * 32;
   const int64_t items = (rows + RPW - 1) / RPW;
   for (int64_t item = (int64_t)blockIdx.x * nwarps + warp; item < items; item += (int64_t)gridDim.x * nwarps) {
     const int64_t row0 = item * RPW, left = rows - row0;
     const int n_pieces = (int)(left < RPW ? left : RPW) * (S / 16);
     uint32_t yv[32], gv[32];
-    lane_run_to_shared(y + row0 * S, n_pieces, s_x[warp], lane);
+    lane_run_to_shared_async(y + row0 * S, n_pieces, s_yw, lane);
+    lane_run_to_shared_async(g + row0 * S, n_pieces, s_gw, lane);
+    lane_async_wait();
     __syncwarp();
     lane_slot_load(sx, lane, yv);
-    __syncwarp();
-    lane_run_to_shared(g + row0 * S, n_pieces, s_x[warp], lane);
-    __syncwarp();
-    lane_slot_load(sx, lane, gv);
+    lane_slot_load(s_gw + lane * 32, lane, gv);
     float acc = 0.f;
 #pragma unroll
     for (int j = 0; j < 32; ++j) {
@@ -409,7 +415,7 @@ softmax_bwd_lane_kernel(const __nv_bfloat16* __restrict__ y, const __nv_bfloat16
     __syncwarp();
     lane_slot_store(sx, lane, gv);
     __syncwarp();
-    lane_shared_to_run(s_x[warp], out + row0 * S, n_pieces, lane);
+    lane_shared_to_run(s_yw, out + row0 * S, n_pieces, lane);
     __syncwarp();
   }
 }
@@ -417,9 +423,16 @@ softmax_bwd_lane_kernel(const __nv_bfloat16* __restrict__ y, const __nv_bfloat16
 template <int LPR>
 static void launch_softmax_bwd(const void* y, const void* g, int64_t rows, float oscale, void* out, cudaStream_t st) {
   auto kern = softmax_bwd_lane_kernel<LPR>;
+  static bool attr[64] = {false};      // up to 64 KB of dynamic shared memory per block: set per device
+  const int slot = current_device_slot();
+  if (slot < 0 || !attr[slot]) {
+    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 8 * 8192);
+    if (slot >= 0) attr[slot] = true;
+  }
   int grid, threads;
-  lane_launch_shape(kern, rows, 32 / LPR, grid, threads);
-  kern<<<grid, threads, 0, st>>>((const __nv_bfloat16*)y, (const __nv_bfloat16*)g, rows, oscale, (__nv_bfloat16*)out);
+  lane_launch_shape(kern, rows, 32 / LPR, grid, threads, 8192);
+  kern<<<grid, threads, (threads / 32) * 8192, st>>>((const __nv_bfloat16*)y, (const __nv_bfloat16*)g, rows, oscale,
+                                                     (__nv_bfloat16*)out);
 }
 
 // rows of 64 * 2^n <= 2048 columns, 32-byte aligned tensors; false = not covered (nothing launched)
@@ -459,13 +472,20 @@ static void launch_restore(const void* val, const uint16_t* col, int k, const vo
   int grid, threads;
   if (grad == nullptr) {
     auto kern = topk_lane_restore_kernel<QBIT, LPR, false>;
-    lane_launch_shape(kern, rows, 32 / LPR, grid, threads);
-    kern<<<grid, threads, 0, st>>>((const __nv_bfloat16*)val, col, k, k > 0 ? 1.0f / (float)k : 0.f,
+    lane_launch_shape(kern, rows, 32 / LPR, grid, threads, 4096);
+    kern<<<grid, threads, (threads / 32) * 4096, st>>>((const __nv_bfloat16*)val, col, k, k > 0 ? 1.0f / (float)k : 0.f,
                                    (const uint8_t*)q, (const __nv_bfloat16*)scale, zp, rows, nullptr, 1.f, (__nv_bfloat16*)ao);
   } else {
     auto kern = topk_lane_restore_kernel<QBIT, LPR, true>;
-    lane_launch_shape(kern, rows, 32 / LPR, grid, threads);
-    kern<<<grid, threads, 0, st>>>((const __nv_bfloat16*)val, col, k, k > 0 ? 1.0f / (float)k : 0.f,
+    // two 4 KB tiles per warp: up to 64 KB per block, above the default limit (set per device)
+    static bool attr[64] = {false};
+    const int slot = current_device_slot();
+    if (slot < 0 || !attr[slot]) {
+      cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 8 * 8192);
+      if (slot >= 0) attr[slot] = true;
+    }
+    lane_launch_shape(kern, rows, 32 / LPR, grid, threads, 8192);
+    kern<<<grid, threads, (threads / 32) * 8192, st>>>((const __nv_bfloat16*)val, col, k, k > 0 ? 1.0f / (float)k : 0.f,
                                    (const uint8_t*)q, (const __nv_bfloat16*)scale, zp, rows,
                                    (const __nv_bfloat16*)grad, oscale, (__nv_bfloat16*)ao);
   }
