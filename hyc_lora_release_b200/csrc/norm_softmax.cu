@@ -411,8 +411,11 @@ softmax_bwd_kernel(const __nv_bfloat16* __restrict__ y, const __nv_bfloat16* __r
 // reference's rounding points: t = bf16(s * scale), u = bf16(t + mask), fp32 softmax of u, bf16 result.
 // One warp per row, the row in registers (NV chunks of 32 lanes x 8 columns).  The mask is addressed as
 // mask[b * mb + head * mh + m * mr + column] for row = (b * heads + head) * M + m.
+// The exponentials are evaluated twice (once for the row sum, once for the result) instead of keeping the row as
+// fp32 values: 80 registers instead of 128, three resident blocks instead of two, half as many bytes again in flight
+// (measured at rows of 2048: 115 -> 107 us for the [1,32,2048,2048] map; no difference at rows of 512).
 template <int NV>
-__global__ void __launch_bounds__(256, NV <= 8 ? 2 : 1)
+__global__ void __launch_bounds__(256, NV <= 8 ? 3 : 1)
 softmax_fwd_kernel(const __nv_bfloat16* __restrict__ sc, float scale, const __nv_bfloat16* __restrict__ mask,
                    int64_t mb, int64_t mh, int64_t mr, int heads, int M, __nv_bfloat16* __restrict__ a,
                    int64_t rows, int S) {
@@ -460,13 +463,13 @@ softmax_fwd_kernel(const __nv_bfloat16* __restrict__ sc, float scale, const __nv
 #pragma unroll
     for (int of = 16; of > 0; of >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, of));
     const float mxl = mx * kLog2e;
-    float ef[NV][8];
     float sum = 0.f;
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
-      unpack8(raw[i], ef[i]);
+      float ef[8];
+      unpack8(raw[i], ef);
 #pragma unroll
-      for (int e = 0; e < 8; ++e) { ef[i][e] = exp2f(fmaf(ef[i][e], kLog2e, -mxl)); sum += ef[i][e]; }
+      for (int e = 0; e < 8; ++e) sum += exp2f(fmaf(ef[e], kLog2e, -mxl));
     }
 #pragma unroll
     for (int of = 16; of > 0; of >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, of);
@@ -474,9 +477,11 @@ softmax_fwd_kernel(const __nv_bfloat16* __restrict__ sc, float scale, const __nv
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
       const int v = lane + 32 * i;
+      float ef[8];
+      unpack8(raw[i], ef);
 #pragma unroll
-      for (int e = 0; e < 8; ++e) ef[i][e] *= inv;
-      if (v < nvec) st_stream_v4(a + row * S + 8 * v, pack8(ef[i]));
+      for (int e = 0; e < 8; ++e) ef[e] = exp2f(fmaf(ef[e], kLog2e, -mxl)) * inv;
+      if (v < nvec) st_stream_v4(a + row * S + 8 * v, pack8(ef));
     }
   }
 }
