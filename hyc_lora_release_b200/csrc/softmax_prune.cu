@@ -268,11 +268,32 @@ __host__ __device__ inline int64_t tiled_dir_entries(int64_t numel) {
   return (nb + 15) & ~(int64_t)15;              // the counters behind it start on a 128-byte boundary
 }
 
+// sub-list counters -> *nnz_out: kept entries, or capacity + dropped entries when a sub-list overflowed
+__device__ __forceinline__ void tiled_finish(const unsigned long long* counters, uint32_t capacity, uint32_t n_sub,
+                                             int64_t* __restrict__ nnz_out, unsigned long long* s_kd) {
+  if (threadIdx.x < 64) {
+    const uint32_t sub_cap = capacity / n_sub;
+    const unsigned long long c = threadIdx.x < n_sub ? __ldcg(counters + threadIdx.x * kCounterStride) : 0ull;
+    unsigned long long kept = c, dropped = c > sub_cap ? c - sub_cap : 0ull;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      kept += __shfl_xor_sync(0xffffffffu, kept, o);
+      dropped += __shfl_xor_sync(0xffffffffu, dropped, o);
+    }
+    if ((threadIdx.x & 31) == 0) { s_kd[threadIdx.x >> 5] = kept; s_kd[2 + (threadIdx.x >> 5)] = dropped; }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned long long k = s_kd[0] + s_kd[1], d = s_kd[2] + s_kd[3];
+    *nnz_out = (int64_t)(d ? (unsigned long long)capacity + d : k);
+  }
+}
+
 template <bool NEG>
 __global__ void __launch_bounds__(kTileThreads, 4)
 prune_tiled_kernel(const __nv_bfloat16* __restrict__ a, int64_t numel, float thr, int64_t n_tiles,
                    uint32_t* __restrict__ words, uint32_t capacity, uint2* __restrict__ dir,
-                   unsigned long long* __restrict__ counters) {
+                   unsigned long long* __restrict__ counters, int64_t* __restrict__ nnz_out) {
   // A warp walks batches with a fixed stride.  Per batch: masks and counts from the eight chunks in registers, ONE
   // atomic add for the span, the entries staged in shared memory, and -- before anything waits for the atomic's
   // answer -- the loads of the warp's NEXT batch: the round trip of the atomic and the write-out of this batch run
@@ -373,26 +394,20 @@ prune_tiled_kernel(const __nv_bfloat16* __restrict__ a, int64_t numel, float thr
     }
     batch = next;
   }
-}
-
-// one block: the sub-lists' counters -> *nnz_out (see above)
-__global__ void __launch_bounds__(kSubLists)
-prune_tiled_finish_kernel(const unsigned long long* __restrict__ counters, uint32_t capacity, uint32_t n_sub,
-                          int64_t* __restrict__ nnz_out) {
-  const uint32_t sub_cap = capacity / n_sub;
-  const unsigned long long c = threadIdx.x < n_sub ? counters[threadIdx.x * kCounterStride] : 0ull;
-  unsigned long long kept = c, dropped = c > sub_cap ? c - sub_cap : 0ull;
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) {
-    kept += __shfl_xor_sync(0xffffffffu, kept, o);
-    dropped += __shfl_xor_sync(0xffffffffu, dropped, o);
-  }
-  __shared__ unsigned long long s_k[2], s_d[2];
-  if ((threadIdx.x & 31) == 0) { s_k[threadIdx.x >> 5] = kept; s_d[threadIdx.x >> 5] = dropped; }
+  // the block that finishes last adds the counters up (no second launch): every block takes a ticket once all its
+  // atomics have returned
+  __shared__ unsigned long long s_kd[4];
+  __shared__ bool s_last;
+  __threadfence();
   __syncthreads();
   if (threadIdx.x == 0) {
-    const unsigned long long k = s_k[0] + s_k[1], d = s_d[0] + s_d[1];
-    *nnz_out = (int64_t)(d ? (unsigned long long)capacity + d : k);
+    const unsigned long long ticket = atomicAdd(counters + kSubLists * kCounterStride, 1ull);
+    s_last = ticket == (unsigned long long)gridDim.x - 1ull;
+  }
+  __syncthreads();
+  if (s_last) {
+    __threadfence();
+    tiled_finish(counters, capacity, n_sub, nnz_out, s_kd);
   }
 }
 
@@ -549,7 +564,8 @@ extern "C" HYC_API int hyc_softmax_prune_restore_counted(const int64_t* idx, con
 
 extern "C" HYC_API size_t hyc_softmax_prune_tiled_directory_bytes(int64_t numel) {
   if (numel < 0) return 0;
-  return (size_t)tiled_dir_entries(numel) * sizeof(uint2) + (size_t)kSubLists * kCounterStride * sizeof(unsigned long long);
+  // directory, the sub-lists' counters, and one more slot: the ticket of the blocks that have finished
+  return (size_t)tiled_dir_entries(numel) * sizeof(uint2) + (size_t)(kSubLists + 1) * kCounterStride * sizeof(unsigned long long);
 }
 
 extern "C" HYC_API int hyc_softmax_prune_tiled(const void* a, int64_t numel, float threshold,
@@ -561,7 +577,7 @@ extern "C" HYC_API int hyc_softmax_prune_tiled(const void* a, int64_t numel, flo
   if (!aligned(a, 16) || !aligned(nnz_out, 8) || !aligned(directory_out, 128) || !aligned(words_out, 4)) return HYC_ERR_ALIGN;
   cudaStream_t st = (cudaStream_t)stream;
   unsigned long long* counters = reinterpret_cast<unsigned long long*>(reinterpret_cast<uint2*>(directory_out) + tiled_dir_entries(numel));
-  if (cudaMemsetAsync(counters, 0, (size_t)kSubLists * kCounterStride * sizeof(unsigned long long), st) != cudaSuccess) {
+  if (cudaMemsetAsync(counters, 0, (size_t)(kSubLists + 1) * kCounterStride * sizeof(unsigned long long), st) != cudaSuccess) {
     hyc_set_last_cuda_error((int)cudaGetLastError());
     return HYC_ERR_LAUNCH;
   }
@@ -573,12 +589,10 @@ extern "C" HYC_API int hyc_softmax_prune_tiled(const void* a, int64_t numel, flo
   if (g > (int64_t)num_sms() * 4) g = (int64_t)num_sms() * 4;
   if (thr >= 0.f)
     prune_tiled_kernel<false><<<(int)g, kTileThreads, 0, st>>>((const __nv_bfloat16*)a, numel, thr, nt, words_out, (uint32_t)capacity,
-                                                            (uint2*)directory_out, counters);
+                                                            (uint2*)directory_out, counters, nnz_out);
   else
     prune_tiled_kernel<true><<<(int)g, kTileThreads, 0, st>>>((const __nv_bfloat16*)a, numel, thr, nt, words_out, (uint32_t)capacity,
-                                                           (uint2*)directory_out, counters);
-  HYC_CHECK_LAUNCH();
-  prune_tiled_finish_kernel<<<1, kSubLists, 0, st>>>(counters, (uint32_t)capacity, tiled_sub_lists(numel), nnz_out);
+                                                           (uint2*)directory_out, counters, nnz_out);
   HYC_CHECK_LAUNCH();
   return HYC_OK;
 }

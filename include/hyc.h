@@ -123,7 +123,8 @@ int hyc_softmax_prune_restore_counted(const int64_t* idx, const void* val, const
  * elements; the entries of a batch go into a span of words_out as (offset in the batch << 16 | bf16 bits), in no
  * particular order inside the span, and directory_out[batch] = {first word of the span, entries written} (two
  * uint32).  directory_out holds hyc_softmax_prune_tiled_directory_bytes(numel) bytes (the directory and, behind it,
- * 8 KB of counters the call clears and uses) and must be 128-byte aligned.  words_out is used as up to 64 equal
+ * 8 KB of counters the call clears and uses: one per sub-list and a ticket by which the block that finishes last
+ * knows to write *nnz_out, so the whole save is one memset and one kernel) and must be 128-byte aligned.  words_out is used as up to 64 equal
  * sub-lists (one per 32 batches of the map, a single one for maps below 131072 elements); a batch takes its span
  * from the sub-list that a hash of its index names, by one atomic add on that sub-list's counter, so the order of
  * the spans depends on the run and the sub-lists fill evenly but not identically (give `capacity` a margin); the set of (index, value) pairs is that of
