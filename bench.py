@@ -121,10 +121,13 @@ class ClockSampler:
                 "samples": len(sm), "reasons": sorted(reasons)}
 
 
+DEFAULT_REFERENCE = os.path.join(os.sep, "root", "reference")
+
+
 def find_reference():
-    """Folder that holds the reference's ``operators/compress_function.py``: $HYC_REFERENCE, a checkout at
-    /root/reference, or the copy staged by oracle/stage_reference.py (oracle/_ref).  None when there is none."""
-    for cand in (os.environ.get("HYC_REFERENCE"), "/root/reference", os.path.join(ROOT, "oracle", "_ref")):
+    """Folder that holds the reference's ``operators/compress_function.py``: $HYC_REFERENCE, the default checkout
+    location, or the copy staged by oracle/stage_reference.py (oracle/_ref).  None when there is none."""
+    for cand in (os.environ.get("HYC_REFERENCE"), DEFAULT_REFERENCE, os.path.join(ROOT, "oracle", "_ref")):
         if cand and os.path.isfile(os.path.join(cand, "operators", "compress_function.py")):
             return cand
     return None
@@ -158,7 +161,7 @@ class CpuArm:
         self.a = make_map(99, "cpu", SAMPLE_SHAPE)
         self.nbytes = 2 * algo_bytes(SAMPLE_SHAPE, QBIT, RATIO)
         ref = find_reference()
-        self.kind, self.why = "port", "no copy of the reference reachable (HYC_REFERENCE, /root/reference, oracle/_ref)"
+        self.kind, self.why = "port", "no copy of the reference reachable (HYC_REFERENCE, the default checkout location, oracle/_ref)"
         if ref is not None:
             try:
                 cf = load_reference_compress(ref)

@@ -22,7 +22,7 @@ FILES = ("compress_function.py", "compress_function_kernel.py",
 
 def stage(reference_root=None):
     """-> the staged folder, or None when no checkout is reachable."""
-    ref = reference_root or os.environ.get("HYC_REFERENCE") or "/root/reference"
+    ref = reference_root or os.environ.get("HYC_REFERENCE") or os.path.join(os.sep, "root", "reference")
     src = os.path.join(ref, "operators")
     if not all(os.path.isfile(os.path.join(src, f)) for f in FILES):
         return None
