@@ -558,7 +558,7 @@ def ranks_hold_identical(reducer, dist):
     return all(v == all_sums[0] for v in all_sums)
 
 
-def mlp_eager_baseline(dev, B, M, H, I, R, steps=10, warmup=3):
+def mlp_eager_baseline(dev, B, M, H, I, R, steps=200, warmup=5):
     """The same MLP block in plain PyTorch on the same GPU: library (cuBLAS) matmuls, torch element-wise kernels and
     autograd, LoRA rank R on gate/up/down, frozen bf16 weights, NOTHING compressed (every activation saved in bf16).
     Reported beside the fused path; not part of it."""
@@ -586,7 +586,7 @@ def mlp_eager_baseline(dev, B, M, H, I, R, steps=10, warmup=3):
                     "activations kept uncompressed"}
 
 
-def mlp_workload(dev, dist=None, steps=20, warmup=4, shape="llama", q_bit=4, eager=False):
+def mlp_workload(dev, dist=None, steps=200, warmup=5, shape="llama", q_bit=4, eager=False):
     """Fused LoRA-SiLU-Hadamard MLP forward + backward.  shape "llama" = BASELINE configs[2]: x [4,512,4096] per
     GPU, intermediate 11008, 0.5 % outlier channels x30; shape "mistral" = BASELINE configs[3]: 8192 tokens per GPU,
     intermediate 14336, 1 % outlier channels x20.  Frozen W ~ N(0, .02), LoRA rank 16, saved activations q_bit
@@ -658,6 +658,7 @@ def mlp_workload(dev, dist=None, steps=20, warmup=4, shape="llama", q_bit=4, eag
     line = {"workload": "fused LoRA-SiLU-Hadamard MLP fwd+bwd, " + name, "q_bit": q_bit,
             "metric": "tokens/s", "value": world * T * steps / t, "unit": "tokens/s", "ms_per_step": t / steps * 1e3,
             "tokens_per_gpu": T, "flop_per_token": flop_per_token, "cuda_graph_replay_ms_per_step": tg / steps * 1e3,
+            "steps": steps, "timed_region_s": t,
             "roofline": {"bound": "tensor", "kernel": "tc::mlp_gemm_kernel (gate+up forward, down forward, grad_down, grad_x: "
                                                       "four launches per step)",
                          "achieved": tf, "peak": sustained, "unit": "TFLOP/s", "frac": tf / sustained,
@@ -1109,7 +1110,7 @@ def main():
         sweep_lines = []
         for qb in (2, 4, 8):
             barrier()
-            sweep_lines.append(mlp_workload(dev, dist, steps=10, warmup=3, shape="mistral", q_bit=qb))
+            sweep_lines.append(mlp_workload(dev, dist, steps=40, warmup=3, shape="mistral", q_bit=qb))
         barrier()
         layer_line = layer_workload(dev, dist)
         barrier()
