@@ -26,7 +26,7 @@ from typing import Optional
 import torch
 
 from ._lib import require_cuda
-from .mlp import _status_tensor, gemm, linear_lora_save, lora_grad_a, padded_block
+from .mlp import _status_tensor, gemm, linear_lora_save, lora_a_products, lora_grad_a, padded_block
 from .operators import compress_function as cf
 from .operators.rmsnorm_kernels import rmsnorm_backward_packed, rmsnorm_forward, rmsnorm_forward_save
 from .operators.rope_kernels import rope_inplace
@@ -76,7 +76,9 @@ class AttnWeights:
             bo_cols = torch.zeros(H, 64, dtype=dt, device=dev); bo_cols[:, :r] = self.bo
             aqkv = torch.zeros(64, self.aq.shape[1], dtype=dt, device=dev)
             aqkv[:r] = self.aq; aqkv[r:2 * r] = self.ak; aqkv[2 * r:3 * r] = self.av
-            self._pad = dict(ao_rows=ao_rows, ao_cols=ao_rows.t().contiguous(), bo_cols=bo_cols, aqkv_rows=aqkv)
+            aqkv_t = torch.stack((self.aq.t(), self.ak.t(), self.av.t())).contiguous()      # [3, H, r]
+            self._pad = dict(ao_rows=ao_rows, ao_cols=ao_rows.t().contiguous(), bo_cols=bo_cols, aqkv_rows=aqkv,
+                             aqkv_t=aqkv_t)
             self._pad_key = key
         return self._pad
 
@@ -142,18 +144,20 @@ def _matmul_to_hidden(a4, b4):
     return out.view(B * M, n * d)
 
 
-def _project(xn2, w, a, b, q_bit, calib, sv, it, thd, status, B, bias=None):
-    """One LoRA projection and the save of its main branch -> (y [T,N], q_main, scale, xa [T,r])."""
+def _project(xn2, w, a, b, q_bit, calib, sv, it, thd, status, B, bias=None, xa=None):
+    """One LoRA projection and the save of its main branch -> (y [T,N], q_main, scale, xa [T,r]).  ``xa`` = x A^T when
+    the caller has it already."""
     if not calib and bias is None:
         scale = sv['scale']
-        y, qm, xa = linear_lora_save(xn2, w, a, b, scale, q_bit, status=status)
+        y, qm, xa = linear_lora_save(xn2, w, a, b, scale, q_bit, status=status, xa=xa)
         return y, qm, scale, xa
     # calibration iterations (the scale depends on the finished main branch) and projections with a bias
     main = gemm(xn2, w, status=status)
     if bias is not None:
         main = main + bias.to(main.dtype)
     qm, scale = cf.compression_pack_quant_base(main.view(B, main.shape[0] // B, -1), q_bit, 'per-channel', it, thd, sv)
-    xa = (xn2 @ a.t()).contiguous()
+    if xa is None:
+        xa = (xn2 @ a.t()).contiguous()
     y = main + xa @ b.t()
     return y, qm.reshape(main.shape[0], -1), scale, xa
 
@@ -180,9 +184,10 @@ def attention_forward(x, w: AttnWeights, state: AttnState, cos, sin, attention_m
         x_norm, rstd, x_o, x_q, xn_q = rmsnorm_forward_save(x, w.norm_w, eps, q, x_scale, x_idx, xn_scale)
     xn2 = x_norm.reshape(T, H)
 
-    qy, q_q, q_scale, q_xa = _project(xn2, w.wq, w.aq, w.bq, q, calib, sv['q'], it, thd, st, B, w.bias_q)
-    ky, k_q, k_scale, k_xa = _project(xn2, w.wk, w.ak, w.bk, q, calib, sv['k'], it, thd, st, B, w.bias_k)
-    vy, v_q, v_scale, v_xa = _project(xn2, w.wv, w.av, w.bv, q, calib, sv['v'], it, thd, st, B, w.bias_v)
+    xa3 = lora_a_products(xn2, w.padded()["aqkv_t"])         # x_norm @ Aq^T, Ak^T, Av^T in one call
+    qy, q_q, q_scale, q_xa = _project(xn2, w.wq, w.aq, w.bq, q, calib, sv['q'], it, thd, st, B, w.bias_q, xa3[0])
+    ky, k_q, k_scale, k_xa = _project(xn2, w.wk, w.ak, w.bk, q, calib, sv['k'], it, thd, st, B, w.bias_k, xa3[1])
+    vy, v_q, v_scale, v_xa = _project(xn2, w.wv, w.av, w.bv, q, calib, sv['v'], it, thd, st, B, w.bias_v, xa3[2])
     del x_norm, xn2
 
     rope_inplace(qy.view(B, M, num_heads, head_dim), cos, sin)
