@@ -66,7 +66,7 @@ class AttnWeights:
           bo_cols  [H, 64]        columns 0..15 = Bo     ([N, K] operand of the o projection's LoRA block)
           ao_rows  [64, heads*d]  rows 0..15 = Ao        ([K, N] operand of grad_o's LoRA block)
           aqkv_rows [64, H]       rows 0..15 = Aq, 16..31 = Ak, 32..47 = Av ([K, N] operand of grad_x's LoRA block)"""
-        ts = (self.aq, self.ak, self.av, self.ao, self.bo)
+        ts = (self.aq, self.ak, self.av, self.ao, self.bo, self.bq, self.bk, self.bv)
         key = tuple((t.data_ptr(), t._version) for t in ts)
         if getattr(self, "_pad_key", None) != key:
             r, D = self.ao.shape
@@ -77,8 +77,10 @@ class AttnWeights:
             aqkv = torch.zeros(64, self.aq.shape[1], dtype=dt, device=dev)
             aqkv[:r] = self.aq; aqkv[r:2 * r] = self.ak; aqkv[2 * r:3 * r] = self.av
             aqkv_t = torch.stack((self.aq.t(), self.ak.t(), self.av.t())).contiguous()      # [3, H, r]
+            same = self.bq.shape == self.bk.shape == self.bv.shape
+            bqkv = torch.stack((self.bq, self.bk, self.bv)).contiguous() if same else None   # [3, heads*d, r]
             self._pad = dict(ao_rows=ao_rows, ao_cols=ao_rows.t().contiguous(), bo_cols=bo_cols, aqkv_rows=aqkv,
-                             aqkv_t=aqkv_t)
+                             aqkv_t=aqkv_t, bqkv=bqkv)
             self._pad_key = key
         return self._pad
 
@@ -133,12 +135,13 @@ def _hidden(xh):
     return xh.transpose(1, 2).reshape(b * m, n * d)
 
 
-def _matmul_to_hidden(a4, b4):
+def _matmul_to_hidden(a4, b4, out=None):
     """[B, n, M, K] @ [B, n, K, d] -> contiguous [B*M, n*d]: every batch's product is written by the library GEMM
-    straight into the hidden layout (an [n, M, d] view with strides (d, n*d, 1)), no transposing copy."""
+    straight into the hidden layout (an [n, M, d] view with strides (d, n*d, 1)), no transposing copy.  ``out``: a
+    contiguous [B*M, n*d] tensor to write into."""
     B, n, M, _ = a4.shape
     d = b4.shape[-1]
-    out = torch.empty((B, M, n, d), dtype=a4.dtype, device=a4.device)
+    out = torch.empty((B, M, n, d), dtype=a4.dtype, device=a4.device) if out is None else out.view(B, M, n, d)
     for b in range(B):
         torch.bmm(a4[b], b4[b], out=out[b].transpose(0, 1))
     return out.view(B * M, n * d)
@@ -246,7 +249,7 @@ def attention_forward(x, w: AttnWeights, state: AttnState, cos, sin, attention_m
 
     saved = dict(rstd=rstd, x_o=x_o, x_q=x_q, x_scale=x_scale, x_idx=x_idx, xn_q=xn_q, xn_scale=xn_scale,
                  q_q=q_q, q_scale=q_scale, k_q=k_q, k_scale=k_scale, v_q=v_q, v_scale=v_scale,
-                 q_xa=q_xa, k_xa=k_xa, v_xa=v_xa, a_saved=a_saved, a_shape=a_shape, map_mode=state.map_mode,
+                 q_xa=q_xa, k_xa=k_xa, v_xa=v_xa, qkv_xa=xa3, a_saved=a_saved, a_shape=a_shape, map_mode=state.map_mode,
                  o_q=o_q.reshape(T, -1), o_scale=o_scale, o_xa=o_xa64[:, :w.ao.shape[0]], q_bit=q, shape=(B, M, H),
                  cos=cos, sin=sin, num_heads=num_heads, head_dim=head_dim, num_key_value_heads=num_key_value_heads)
     return x_medium.reshape(B, M, H), saved
@@ -293,8 +296,11 @@ def attention_backward(grad_medium, saved, w: AttnWeights, status=None, on_lora_
             cf.decompression_softmax(m).reshape(saved['a_shape'])
     v2 = _rebuild(saved['v_q'], saved['v_scale'], saved['v_xa'], w.bv, q)
     vh = _repeat_kv(_heads(v2, B, M, nkv), n_rep)
+    # without grouped key/value heads grad_q, grad_k and grad_v have one shape: kept in one buffer, their rank-16
+    # products below run as one batched library call each
+    gqkv = torch.empty((3, T, nh * d), dtype=BF16, device=dev) if n_rep == 1 else None
     if n_rep == 1:
-        grad_v = _matmul_to_hidden(a.transpose(-2, -1), grad_oh)
+        grad_v = _matmul_to_hidden(a.transpose(-2, -1), grad_oh, out=gqkv[2])
     else:
         grad_v = _hidden(_repeat_kv_backward(torch.matmul(a.transpose(-2, -1), grad_oh), n_rep))
     grad_a = torch.matmul(grad_oh, vh.transpose(-2, -1))
@@ -312,27 +318,39 @@ def attention_backward(grad_medium, saved, w: AttnWeights, status=None, on_lora_
     q2 = _rebuild(saved['q_q'], saved['q_scale'], saved['q_xa'], w.bq, q)
     rope_inplace(q2.view(B, M, nh, d), cos, sin)
     if n_rep == 1:
-        grad_k = _matmul_to_hidden(grad_s.transpose(-2, -1), _heads(q2, B, M, nh))
+        grad_k = _matmul_to_hidden(grad_s.transpose(-2, -1), _heads(q2, B, M, nh), out=gqkv[1])
     else:
         grad_k = _hidden(_repeat_kv_backward(torch.matmul(grad_s.transpose(-2, -1), _heads(q2, B, M, nh)), n_rep))
     del q2
     k2 = _rebuild(saved['k_q'], saved['k_scale'], saved['k_xa'], w.bk, q)
     rope_inplace(k2.view(B, M, nkv, d), cos, sin)
-    grad_q = _matmul_to_hidden(grad_s, _repeat_kv(_heads(k2, B, M, nkv), n_rep))
+    grad_q = _matmul_to_hidden(grad_s, _repeat_kv(_heads(k2, B, M, nkv), n_rep), out=None if gqkv is None else gqkv[0])
     del k2, grad_s
     rope_inplace(grad_q.view(B, M, nh, d), cos, sin, backward=True)
     rope_inplace(grad_k.view(B, M, nkv, d), cos, sin, backward=True)
 
     # ---- q/k/v projections: LoRA gradients, then grad_x_norm as one GEMM over the three K segments
     gmq = padded_block(w, "_gmq", T, dev)                    # g_q @ Bq | g_k @ Bk | g_v @ Bv side by side
-    torch.mm(grad_q, w.bq, out=gmq[:, :r])
-    torch.mm(grad_k, w.bk, out=gmq[:, r:2 * r])
-    torch.mm(grad_v, w.bv, out=gmq[:, 2 * r:3 * r])
+    qkv_xa = saved.get('qkv_xa')
+    if gqkv is not None and r == 16:
+        # (B200, 2048 tokens: 11.5 us against 25.6 us as three products, 9.9 us against 19.7 us for the B gradients)
+        gmq.view(T, 4, 16)[:, :3].copy_(torch.bmm(gqkv, pad["bqkv"]).transpose(0, 1))
+        if qkv_xa is None:
+            qkv_xa = torch.stack((saved['q_xa'], saved['k_xa'], saved['v_xa']))
+        grad_b3 = torch.bmm(gqkv.transpose(1, 2), qkv_xa)     # [3, heads*d, r]
+    else:
+        torch.mm(grad_q, w.bq, out=gmq[:, :r])
+        torch.mm(grad_k, w.bk, out=gmq[:, r:2 * r])
+        torch.mm(grad_v, w.bv, out=gmq[:, 2 * r:3 * r])
+        grad_b3 = None
     ga = lora_grad_a(saved['xn_q'].reshape(T, -1), _vec(saved['xn_scale']), gmq, 48, q)
     grad_aq, grad_ak, grad_av = ga[:r], ga[r:2 * r], ga[2 * r:3 * r]
-    grad_bq = grad_q.t() @ saved['q_xa']
-    grad_bk = grad_k.t() @ saved['k_xa']
-    grad_bv = grad_v.t() @ saved['v_xa']
+    if grad_b3 is not None:
+        grad_bq, grad_bk, grad_bv = grad_b3[0], grad_b3[1], grad_b3[2]
+    else:
+        grad_bq = grad_q.t() @ saved['q_xa']
+        grad_bk = grad_k.t() @ saved['k_xa']
+        grad_bv = grad_v.t() @ saved['v_xa']
     if on_lora_grads is not None:
         on_lora_grads(dict(grad_aq=grad_aq, grad_bq=grad_bq, grad_ak=grad_ak, grad_bk=grad_bk, grad_av=grad_av,
                            grad_bv=grad_bv, grad_ao=grad_ao, grad_bo=grad_bo))

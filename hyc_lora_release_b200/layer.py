@@ -31,7 +31,7 @@ def saved_nbytes(saved):
     the two passes (tensors, the top-k map handle, a sparse COO map); the shared rotary tables are not counted."""
     total = 0
     for key, v in saved.items():
-        if key in ("cos", "sin"):
+        if key in ("cos", "sin", "gu_xa", "qkv_xa"):      # shared tables; stacked views of tensors counted under their own keys
             continue
         if isinstance(v, torch.Tensor):
             if v.is_sparse:
