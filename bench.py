@@ -675,7 +675,7 @@ def mlp_workload(dev, dist=None, steps=200, warmup=5, shape="llama", q_bit=4, ea
     return line
 
 
-def layer_workload(dev, dist=None, steps=10, warmup=3, graph=True):
+def layer_workload(dev, dist=None, steps=80, warmup=3, graph=True):
     """One fused decoder layer (attention + MLP) forward + backward at the Llama-2-7B geometry of BASELINE
     configs[4]: hidden 4096, 32 heads of 128, intermediate 11008, sequence 2048, batch 1 per GPU, causal mask,
     LoRA rank 16 on q/k/v/o/gate/up/down, saved activations 4-bit with 0.5 % outlier channels, the probability
