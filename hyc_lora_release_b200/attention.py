@@ -65,7 +65,10 @@ class AttnWeights:
           ao_cols  [heads*d, 64]  columns 0..15 = Ao^T   (o -> padded LoRA activation of the o projection)
           bo_cols  [H, 64]        columns 0..15 = Bo     ([N, K] operand of the o projection's LoRA block)
           ao_rows  [64, heads*d]  rows 0..15 = Ao        ([K, N] operand of grad_o's LoRA block)
-          aqkv_rows [64, H]       rows 0..15 = Aq, 16..31 = Ak, 32..47 = Av ([K, N] operand of grad_x's LoRA block)"""
+          aqkv_rows [64, H]       rows 0..15 = Aq, 16..31 = Ak, 32..47 = Av ([K, N] operand of grad_x's LoRA block)
+        and the stacked factors of the batched rank-16 products:
+          aqkv_t   [3, H, r]        Aq^T, Ak^T, Av^T (x_norm @ all three in one call)
+          bqkv     [3, heads*d, r]  Bq, Bk, Bv (None with grouped key/value heads, whose shapes differ)"""
         ts = (self.aq, self.ak, self.av, self.ao, self.bo, self.bq, self.bk, self.bv)
         key = tuple((t.data_ptr(), t._version) for t in ts)
         if getattr(self, "_pad_key", None) != key:

@@ -141,7 +141,10 @@ class MLPWeights:
           ad_rows  [64, I]  rows 0..15 = Ad            (second operand of grad_down's LoRA part, [K, N])
           ad_cols  [I, 64]  columns 0..15 = Ad^T       (projects hadamard to the padded down LoRA activation)
           bd_cols  [H, 64]  columns 0..15 = Bd         (second operand of the down projection's LoRA part, [N, K])
-          agu_rows [64, H]  rows 0..15 = Ag, 16..31 = Au (second operand of grad_x's LoRA part, [K, N])"""
+          agu_rows [64, H]  rows 0..15 = Ag, 16..31 = Au (second operand of grad_x's LoRA part, [K, N])
+        and the stacked factors of the batched rank-16 products:
+          agu_t    [2, H, r]  Ag^T, Au^T  (x_norm @ both in one call)
+          bgu      [2, I, r]  Bg, Bu      (grad_gate @ Bg and grad_up @ Bu in one call)"""
         key = tuple(t._version for t in (self.ag, self.au, self.ad, self.bd, self.bg, self.bu))
         if getattr(self, "_pad_key", None) != key:
             r, I = self.ad.shape
