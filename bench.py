@@ -516,6 +516,9 @@ def run_profile(args):
         line = model_workload(dev, None, steps=args.steps, warmup=args.warmup, n_layers=args.layers)
         print(json.dumps(line))
         return
+    if args.profile == "attn_bwd":
+        print(json.dumps(attention_backward_workload(dev, peaks()[0])))
+        return
     if args.profile == "prune":
         print(json.dumps(prune_workload(dev, peaks()[0])))
         return
@@ -965,7 +968,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-extras", action="store_true", help="skip the secondary workloads and the CPU sample")
-    ap.add_argument("--profile", default=None, choices=["attn_topk", "channel_q4", "channel_q2", "channel_q8", "mlp", "fused", "layer", "model", "prune"],
+    ap.add_argument("--profile", default=None, choices=["attn_topk", "attn_bwd", "channel_q4", "channel_q2", "channel_q8", "mlp", "fused", "layer", "model", "prune"],
                     help="run only W+K steps of one workload and print timing (for a profiler capture)")
     ap.add_argument("--layers", type=int, default=32, help="decoder layers of --profile model")
     args = ap.parse_args()
