@@ -52,6 +52,7 @@ SIGNATURES = {
     "hyc_rope": (_i, [_p, _l, _p, _l, _p, _p, _l, _i, _l, _i, _i, _i, _i, _p]),
     "hyc_lora_grad_a_workspace_bytes": (_z, [_i, _i, _i]),
     "hyc_lora_grad_a_dequant": (_i, [_p, _p, _p, _l, _i, _i, _i, _i, _p, _p, _z, _p]),
+    "hyc_dequant_nf4": (_i, [_p, _p, _p, _p, _p, _p, _i, _f, _l, _i, _p, _p]),
     "hyc_gemm_bf16_tcgen05": (_i, [_p, _p, _i, _i, _i, _i, _p, _p, _i, _p, _p, _i,
                                    _p, _p, _l, _l, _p, _p, _l, _l, _p, _p, _p, _p]),
     "hyc_mlp_gateup_fwd_tcgen05": (_i, [_p, _p, _p, _i, _i, _i, _p, _p, _l, _l, _p, _p, _l, _l,

@@ -7,8 +7,9 @@ The module keeps the reference's interface: ``set_hyclora_config(cfg)``, the ``i
 tables, the frozen ``*_proj_base`` modules and their ``*_proj_lora_a/b`` adapter dictionaries, the additive
 attention mask and the head geometry.  Differences, all deliberate:
 
-  * frozen weights are plain bf16 ``[out, in]`` matrices; a 4-bit ``quant_state`` is refused (the NF4
-    de-quantizer of the reference is a third-party library that is not part of this build);
+  * frozen weights are plain bf16 ``[out, in]`` matrices, or 4-bit block-wise weights in the storage format of
+    bitsandbytes (packed codes with a ``quant_state``), de-quantized to bf16 for each pass by a kernel of this
+    package (``nf4.py``; the library itself is not part of this build, parity with it is unpinned);
   * projection biases of q/k/v/o/down are added to the main branch (separate launches for such a projection);
     gate/up biases are refused (the reference's fused layer drops them);
   * ``hyclora_config.softmax_map_mode`` (optional, default ``"prune"`` = the reference's threshold prune) may
@@ -22,6 +23,7 @@ host has to read back.
 import torch
 
 from .attention import AttnState, AttnWeights, attention_backward, attention_forward
+from . import nf4
 from .mlp import MLPState, MLPWeights, _status_tensor, check_status, mlp_backward, mlp_forward
 
 BF16 = torch.bfloat16
@@ -51,9 +53,17 @@ class FusedLayerFunction(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, module, aw, mw, cos, sin, attention_mask, num_heads, head_dim, num_key_value_heads, *lora):
         st = module._status_for(x.device)
-        x_medium, sa = attention_forward(x, aw, module.attn_state, cos, sin, attention_mask, num_heads, head_dim,
+        # 4-bit frozen weights become bf16 for the duration of the half that uses them, as in the reference
+        # (BF.dequantize_nf4 before every frozen matmul); records without such weights pass through unchanged
+        aw_now = nf4.materialize(aw)
+        x_medium, sa = attention_forward(x, aw_now, module.attn_state, cos, sin, attention_mask, num_heads, head_dim,
                                          num_key_value_heads, status=st)
-        y, sm = mlp_forward(x_medium, mw, module.mlp_state, status=st)
+        nf4.release(aw, aw_now)
+        del aw_now
+        mw_now = nf4.materialize(mw)
+        y, sm = mlp_forward(x_medium, mw_now, module.mlp_state, status=st)
+        nf4.release(mw, mw_now)
+        del mw_now
         if module.track_saved_bytes:
             module.last_saved_bytes = saved_nbytes(sa) + saved_nbytes(sm)
         if module.keep_saved:
@@ -66,9 +76,15 @@ class FusedLayerFunction(torch.autograd.Function):
         sa, sm, aw, mw, st, module, x_dtype = ctx.hyc
         ctx.hyc = None
         hook = module.on_lora_grads
-        gm = mlp_backward(grad_y, sm, mw, status=st, on_lora_grads=hook)
+        mw_now = nf4.materialize(mw)
+        gm = mlp_backward(grad_y, sm, mw_now, status=st, on_lora_grads=hook)
+        nf4.release(mw, mw_now)
+        del mw_now
         saved_map = sa.get('a_saved')
-        ga = attention_backward(gm['grad_x'], sa, aw, status=st, on_lora_grads=hook)
+        aw_now = nf4.materialize(aw)
+        ga = attention_backward(gm['grad_x'], sa, aw_now, status=st, on_lora_grads=hook)
+        nf4.release(aw, aw_now)
+        del aw_now
         # fixed-capacity prune buffers: entries beyond the capacity were dropped; the flag stays on the device
         if hasattr(saved_map, "nnz") and hasattr(saved_map, "capacity"):
             module._overflow.add_((saved_map.nnz > saved_map.capacity).to(torch.int32))
@@ -83,10 +99,17 @@ class FusedLayerFunction(torch.autograd.Function):
 
 
 def _frozen(base, name):
+    """The frozen weight of a projection: a plain bf16 [out, in] matrix, or a 4-bit block-wise weight (packed codes
+    with a ``quant_state``, bitsandbytes' storage format) wrapped for de-quantization pass by pass."""
     w = base.weight
-    if getattr(w, "quant_state", None) is not None or w.dtype != BF16:
-        raise NotImplementedError("%s: frozen weights must be plain bf16 [out, in] matrices (4-bit quant_state "
-                                  "weights are not supported)" % name)
+    if nf4.is_quantized(w):
+        qw = nf4.QuantizedWeight(w)
+        if len(qw.shape) != 2:
+            raise NotImplementedError("%s: the quant state of a projection weight must describe a matrix" % name)
+        return qw
+    if w.dtype != BF16:
+        raise NotImplementedError("%s: frozen weights must be bf16 [out, in] matrices or 4-bit block-wise weights with "
+                                  "a quant_state (got %s)" % (name, w.dtype))
     return w
 
 
@@ -196,13 +219,16 @@ class FusedLlamaLayerIntraInterFullFuse(torch.nn.Module):
     def _bind(self, norm_w1, norm_w2, mods):
         """Weight records for the two halves, rebuilt only when a tensor was replaced."""
         tensors = [norm_w1, norm_w2]
+        idents = [id(norm_w1), id(norm_w2)]
         biases = {}
         for name in ("q", "k", "v", "o", "gate", "up", "down"):
             base, la, lb = mods[name]
             tensors += [_frozen(base, name + "_proj"), _adapter(la, name + "_proj lora_A", 0),
                         _adapter(lb, name + "_proj lora_B", 1)]
+            # (a 4-bit weight is wrapped anew on every call: the parameter it wraps is what identifies it)
+            idents += [id(base.weight), id(tensors[-2]), id(tensors[-1])]
             biases[name] = _bias(base, name + "_proj")
-        key = tuple(id(t) for t in tensors) + tuple(id(b) for b in biases.values())
+        key = tuple(idents) + tuple(id(b) for b in biases.values())
         if self._weights is None or self._weights[0] != key:
             (n1, n2, wq, aq, bq, wk, ak, bk, wv, av, bv, wo, ao, bo, wg, ag, bg, wu, au, bu, wd, ad, bd) = tensors
             aw = AttnWeights(norm_w=n1, wq=wq, wk=wk, wv=wv, wo=wo, aq=aq, bq=bq, ak=ak, bk=bk, av=av, bv=bv, ao=ao, bo=bo,

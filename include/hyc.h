@@ -261,6 +261,19 @@ int hyc_softmax_fwd_scale_mask(const void* scores, float scale, const void* mask
  * the bf16 result once more (o = bf16(o * out_scale)). */
 int hyc_softmax_bwd(const void* y, const void* g, void* o, int64_t rows, int S, float out_scale, void* stream);
 
+/* ---- frozen weights stored as 4-bit block-wise codes -------------------------------------------
+ * De-quantizer for weights in the storage format of bitsandbytes 0.43.2 (requirements.txt:3), which the reference
+ * calls as BF.dequantize_nf4(w, quant_state) before every frozen matmul (models/utils/compute_utils.py:19, 29;
+ * models/llama/fused_llama_layer_intra_inter_full_fuse.py:218-219, 359, 367, 379).  The library itself is not part
+ * of this build; its published format is restated: two codes per byte, high nibble first; value = code16[code] *
+ * absmax[element / blocksize] in fp32, rounded to bf16; with "double quantization" absmax_f32 is NULL and absmax =
+ * code256[absmax_q[block]] * absmax2[block / blocksize2] + offset.  packed: numel/2 bytes (16-byte aligned);
+ * code16: 16 floats (the table of the quant state: NF4 or FP4); out: numel bf16.  Parity unpinned (no copy of the
+ * library to compare with). */
+int hyc_dequant_nf4(const void* packed, const float* code16, const float* absmax_f32,
+                    const uint8_t* absmax_q, const float* code256, const float* absmax2,
+                    int blocksize2, float offset, int64_t numel, int blocksize, void* out, void* stream);
+
 /* ---- tcgen05 / TMEM GEMMs of the LoRA MLP (activation compression in the epilogue) ------------
  * bf16 operands, fp32 accumulation in tensor memory, operands staged by TMA.  `status` is a
  * caller-provided device int, zero before the call; a non-zero value afterwards means a bounded

@@ -270,7 +270,7 @@ def test_layer_module_through_autograd(heads, kv, map_mode, with_bias):
     with pytest.raises(NotImplementedError):
         layer._bind(n1, n2, {**mods, "gate": (_base(p["wgate"].t().to(DEV), torch.zeros(I, dtype=BF16)), mods["gate"][1],
                                               mods["gate"][2])})
-    # so is a 4-bit quant_state
+    # so is a quant state that is not a 4-bit block-wise one (those are covered in test_nf4.py)
     bad = _base(p["wq"].t().to(DEV))
     bad.weight.quant_state = object()
     with pytest.raises(NotImplementedError):
