@@ -103,7 +103,10 @@ def _frozen(base, name):
     with a ``quant_state``, bitsandbytes' storage format) wrapped for de-quantization pass by pass."""
     w = base.weight
     if nf4.is_quantized(w):
-        qw = nf4.QuantizedWeight(w)
+        qw = getattr(w, "_hyc_quantized", None)        # wrapped once per parameter (the tables move to the device once)
+        if qw is None or qw.quant_state is not w.quant_state:
+            qw = nf4.QuantizedWeight(w)
+            w._hyc_quantized = qw
         if len(qw.shape) != 2:
             raise NotImplementedError("%s: the quant state of a projection weight must describe a matrix" % name)
         return qw

@@ -32,60 +32,62 @@ def is_quantized(weight):
 
 def dequantize_nf4(weight, quant_state=None):
     """-> bf16 tensor of shape ``quant_state.shape`` (the reference's ``BF.dequantize_nf4(w, quant_state)``)."""
-    qs = quant_state if quant_state is not None else weight.quant_state
-    packed = weight.data if isinstance(weight, torch.nn.Parameter) else weight
-    require_cuda(packed)
-    if packed.dtype != torch.uint8:
-        raise TypeError("a 4-bit weight is a uint8 tensor of packed codes (got %s)" % packed.dtype)
-    shape = tuple(qs.shape)
-    numel = 1
-    for d in shape:
-        numel *= int(d)
-    if packed.numel() * 2 < numel:
-        raise ValueError("%d packed bytes cannot hold %d 4-bit codes" % (packed.numel(), numel))
-    out_dtype = getattr(qs, "dtype", BF16)
-    if out_dtype != BF16:
-        raise NotImplementedError("4-bit weights de-quantize to bf16 here (quant state says %s)" % out_dtype)
-    dev = packed.device
-    code = qs.code.to(device=dev, dtype=torch.float32).contiguous()
-    if code.numel() != 16:
-        raise NotImplementedError("the code table of a 4-bit weight has 16 entries (got %d)" % code.numel())
-    packed = packed.contiguous()
-    out = torch.empty(shape, dtype=BF16, device=dev)
-    blocksize = int(qs.blocksize)
-    if getattr(qs, "nested", False):
-        s2 = qs.state2
-        absmax_q = qs.absmax.to(dev).contiguous()
-        if absmax_q.dtype != torch.uint8:
-            raise TypeError("a nested quant state keeps its block maxima as uint8 codes")
-        code2 = s2.code.to(device=dev, dtype=torch.float32).contiguous()
-        absmax2 = s2.absmax.to(device=dev, dtype=torch.float32).contiguous()
-        offset = float(qs.offset)
-        check(lib.hyc_dequant_nf4(ptr(packed), ptr(code), None, ptr(absmax_q), ptr(code2), ptr(absmax2), int(s2.blocksize),
-                                  offset, numel, blocksize, ptr(out), stream_of(packed)), "hyc_dequant_nf4")
-    else:
-        absmax = qs.absmax.to(device=dev, dtype=torch.float32).contiguous()
-        check(lib.hyc_dequant_nf4(ptr(packed), ptr(code), ptr(absmax), None, None, None, 1, 0.0, numel, blocksize,
-                                  ptr(out), stream_of(packed)), "hyc_dequant_nf4")
-    return out
+    return QuantizedWeight(weight, quant_state).dequantize()
 
 
 class QuantizedWeight:
-    """A frozen 4-bit weight as the fused layer holds it between steps: the packed codes and their quant state.
-    ``dequantize()`` builds the bf16 matrix for the duration of one pass, as the reference does."""
+    """A frozen 4-bit weight as the fused layer holds it between steps: the packed codes and the tables of their quant
+    state, moved to the weight's device once.  ``dequantize()`` builds the bf16 matrix for the duration of one pass,
+    as the reference does."""
 
-    def __init__(self, weight):
-        self.packed = weight.data if isinstance(weight, torch.nn.Parameter) else weight
-        self.quant_state = weight.quant_state
-        missing = [a for a in ("shape", "code", "blocksize", "absmax") if not hasattr(self.quant_state, a)]
+    def __init__(self, weight, quant_state=None):
+        qs = quant_state if quant_state is not None else weight.quant_state
+        missing = [a for a in ("shape", "code", "blocksize", "absmax") if not hasattr(qs, a)]
         if missing:
             raise NotImplementedError("unrecognised quant state (no %s): 4-bit block-wise weights in the storage format "
                                       "of bitsandbytes are what this layer reads" % ", ".join(missing))
-        self.shape = tuple(self.quant_state.shape)
-        self.device = self.packed.device
+        packed = weight.data if isinstance(weight, torch.nn.Parameter) else weight
+        require_cuda(packed)
+        if packed.dtype != torch.uint8:
+            raise TypeError("a 4-bit weight is a uint8 tensor of packed codes (got %s)" % packed.dtype)
+        self.quant_state = qs
+        self.packed = packed.contiguous()
+        self.shape = tuple(int(d) for d in qs.shape)
+        self.device = dev = packed.device
+        self.numel = 1
+        for d in self.shape:
+            self.numel *= d
+        if self.packed.numel() * 2 < self.numel:
+            raise ValueError("%d packed bytes cannot hold %d 4-bit codes" % (self.packed.numel(), self.numel))
+        if getattr(qs, "dtype", BF16) != BF16:
+            raise NotImplementedError("4-bit weights de-quantize to bf16 here (quant state says %s)" % qs.dtype)
+        self.code = qs.code.to(device=dev, dtype=torch.float32).contiguous()
+        if self.code.numel() != 16:
+            raise NotImplementedError("the code table of a 4-bit weight has 16 entries (got %d)" % self.code.numel())
+        self.blocksize = int(qs.blocksize)
+        self.nested = bool(getattr(qs, "nested", False))
+        if self.nested:
+            s2 = qs.state2
+            self.absmax = qs.absmax.to(dev).contiguous()
+            if self.absmax.dtype != torch.uint8:
+                raise TypeError("a nested quant state keeps its block maxima as uint8 codes")
+            self.code2 = s2.code.to(device=dev, dtype=torch.float32).contiguous()
+            self.absmax2 = s2.absmax.to(device=dev, dtype=torch.float32).contiguous()
+            self.blocksize2 = int(s2.blocksize)
+            self.offset = float(qs.offset)
+        else:
+            self.absmax = qs.absmax.to(device=dev, dtype=torch.float32).contiguous()
 
     def dequantize(self):
-        return dequantize_nf4(self.packed, self.quant_state)
+        out = torch.empty(self.shape, dtype=BF16, device=self.device)
+        if self.nested:
+            check(lib.hyc_dequant_nf4(ptr(self.packed), ptr(self.code), None, ptr(self.absmax), ptr(self.code2),
+                                      ptr(self.absmax2), self.blocksize2, self.offset, self.numel, self.blocksize,
+                                      ptr(out), stream_of(self.packed)), "hyc_dequant_nf4")
+        else:
+            check(lib.hyc_dequant_nf4(ptr(self.packed), ptr(self.code), ptr(self.absmax), None, None, None, 1, 0.0,
+                                      self.numel, self.blocksize, ptr(out), stream_of(self.packed)), "hyc_dequant_nf4")
+        return out
 
 
 _CACHE_ATTRS = ("_pad", "_pad_key", "_gm64", "_gmq")      # what AttnWeights / MLPWeights keep between steps

@@ -267,7 +267,7 @@ int hyc_softmax_bwd(const void* y, const void* g, void* o, int64_t rows, int S, 
  * models/llama/fused_llama_layer_intra_inter_full_fuse.py:218-219, 359, 367, 379).  The library itself is not part
  * of this build; its published format is restated: two codes per byte, high nibble first; value = code16[code] *
  * absmax[element / blocksize] in fp32, rounded to bf16; with "double quantization" absmax_f32 is NULL and absmax =
- * code256[absmax_q[block]] * absmax2[block / blocksize2] + offset.  packed: numel/2 bytes (16-byte aligned);
+ * code256[absmax_q[block]] * absmax2[block / blocksize2] + offset.  packed: numel/2 bytes (4-byte aligned);
  * code16: 16 floats (the table of the quant state: NF4 or FP4); out: numel bf16.  Parity unpinned (no copy of the
  * library to compare with). */
 int hyc_dequant_nf4(const void* packed, const float* code16, const float* absmax_f32,
