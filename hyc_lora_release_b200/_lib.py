@@ -112,9 +112,15 @@ def ptr(t):
     return ctypes.c_void_p(t.data_ptr())
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)     # the handle without building a Stream object
+
+
 def stream_of(t):
     """torch's current stream on the device of ``t``; also notes that device for the call that follows."""
-    _pending.device = t.device.index
+    idx = t.device.index
+    _pending.device = idx
+    if _raw_stream is not None:
+        return ctypes.c_void_p(_raw_stream(idx))
     return ctypes.c_void_p(torch.cuda.current_stream(t.device).cuda_stream)
 
 
